@@ -1,0 +1,114 @@
+"""Stage-2 block-sparse attention oracle (fp32 dense-with-mask, CPU).  Test infrastructure only.
+
+Follows tests/utils.py:224-260 (convert_topk_to_base_blockmask), :1027-1085
+(prepare_mixed_mask), :1133-1195 (attention_blocksparse_ref, upcast=True) for the forward and
+uses autograd of the same expression for dQ/dK/dV; the visibility rule is the device rule of
+csrc/flash_attn/src/mask.h:181-203 (bottom-right aligned causal mask) combined with the
+per-token block mask of flash_blockmask.h:26-31.  Decode follows tests/test_kvcache_simple.py:5-15
+and csrc/flash_attn/flash_api.cpp:1628 (a single query token is never causally masked).
+"""
+import math
+import torch
+
+
+def expand_topk_mask(topk_idx: torch.Tensor, k_blocks: int) -> torch.Tensor:
+    """int32 (Hk, T, k) block lists (-1 = unused) -> bool (Hk, T, k_blocks)."""
+    hk, t, k = topk_idx.shape
+    m = torch.zeros(hk, t, k_blocks + 1, dtype=torch.bool)
+    idx = topk_idx.long()
+    idx = torch.where((idx < 0) | (idx >= k_blocks), torch.tensor(k_blocks), idx)
+    m.scatter_(2, idx, True)
+    return m[..., :k_blocks]
+
+
+def _seq_attention(q, k, v, blk_mask, causal, scale, block_size):
+    """q: (Lq, Hq, d) fp32, k/v: (Lk, Hk, d) fp32, blk_mask: bool (Hk, Lq, nblk) or None.
+    Returns out (Lq, Hq, d) fp32 and lse (Hq, Lq) fp32 (+inf for rows that see no key)."""
+    lq, hq, d = q.shape
+    lk, hk, _ = k.shape
+    g = hq // hk
+    s = torch.einsum("thd,shd->hts", q, k.repeat_interleave(g, dim=1)) * scale   # (Hq, Lq, Lk)
+    vis = torch.ones(hk, lq, lk, dtype=torch.bool)
+    if blk_mask is not None:
+        vis = blk_mask.repeat_interleave(block_size, dim=2)[..., :lk]
+        if vis.shape[-1] < lk:                       # mask narrower than the keys: rest unselected
+            vis = torch.nn.functional.pad(vis, (0, lk - vis.shape[-1]))
+    if causal:
+        i = torch.arange(lq)[:, None]
+        j = torch.arange(lk)[None, :]
+        vis = vis & (j <= i + lk - lq)[None]
+    vis = vis.repeat_interleave(g, dim=0)
+    s = s.masked_fill(~vis, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.masked_fill(lse == float("-inf"), 0.0)[..., None])
+    p = torch.where(vis, p, torch.zeros((), dtype=p.dtype))
+    out = torch.einsum("hts,shd->thd", p, v.repeat_interleave(g, dim=1))
+    lse = torch.where(lse == float("-inf"), torch.tensor(float("inf")), lse)
+    return out, lse
+
+
+def sparse_attention_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, topk_idx, causal=True,
+                         softmax_scale=None, block_size: int = 64):
+    """Varlen block-sparse attention.  q: (T, Hq, d); k, v: (Tk, Hk, d); topk_idx: int32
+    (Hk, T, k) with block indices local to each sequence's keys (rows indexed by the global
+    token), or None for dense attention.  Returns fp32 out (T, Hq, d) and lse (Hk, T*g) whose
+    row index is token*g + head-in-group (csrc/flash_attn/flash_api.cpp:665)."""
+    t, hq, d = q.shape
+    hk = k.shape[1]
+    g = hq // hk
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    cu_q = [int(x) for x in cu_seqlens_q]
+    cu_k = [int(x) for x in cu_seqlens_k]
+    outs, lses = [], []
+    for b in range(len(cu_q) - 1):
+        q0, q1, k0, k1 = cu_q[b], cu_q[b + 1], cu_k[b], cu_k[b + 1]
+        lk = k1 - k0
+        bm = None
+        if topk_idx is not None:
+            bm = expand_topk_mask(topk_idx[:, q0:q1], (lk + block_size - 1) // block_size)
+        o, l = _seq_attention(q[q0:q1].float(), k[k0:k1].float(), v[k0:k1].float(),
+                              bm, causal, scale, block_size)
+        outs.append(o)
+        lses.append(l)
+    out = torch.cat(outs, 0)
+    lse = torch.cat(lses, 1)                                     # (Hq, T)
+    lse = lse.view(hk, g, t).permute(0, 2, 1).reshape(hk, t * g)
+    return out, lse
+
+
+def sparse_attention_fwd_bwd(q, k, v, dout, cu_seqlens_q, cu_seqlens_k, topk_idx, causal=True,
+                             softmax_scale=None, block_size: int = 64):
+    """Forward plus dQ, dK, dV by autograd on the fp32 expression."""
+    qf = q.detach().float().requires_grad_(True)
+    kf = k.detach().float().requires_grad_(True)
+    vf = v.detach().float().requires_grad_(True)
+    out, lse = sparse_attention_fwd(qf, kf, vf, cu_seqlens_q, cu_seqlens_k, topk_idx, causal,
+                                    softmax_scale, block_size)
+    dq, dk, dv = torch.autograd.grad(out, (qf, kf, vf), dout.float())
+    return out.detach(), lse.detach(), dq, dk, dv
+
+
+def kvcache_decode(q, k_cache, v_cache, cache_seqlens, topk_idx=None, k_new=None, v_new=None,
+                   softmax_scale=None, block_size: int = 64):
+    """q: (B, 1, Hq, d); caches (B, S, Hk, d) updated in place at cache_seqlens[b] when k_new /
+    v_new (B, 1, Hk, d) are given; topk_idx (B, Hk, 1, k) or None.  Returns fp32 out
+    (B, 1, Hq, d) and lse (B, Hq, 1)."""
+    b, sq, hq, d = q.shape
+    assert sq == 1
+    hk = k_cache.shape[2]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    outs, lses = [], []
+    for i in range(b):
+        n = int(cache_seqlens[i])
+        if k_new is not None:
+            k_cache[i, n:n + 1] = k_new[i]
+            v_cache[i, n:n + 1] = v_new[i]
+            n += 1
+        bm = None
+        if topk_idx is not None:
+            bm = expand_topk_mask(topk_idx[i], (n + block_size - 1) // block_size)
+        o, l = _seq_attention(q[i].float(), k_cache[i, :n].float(), v_cache[i, :n].float(),
+                              bm, False, scale, block_size)
+        outs.append(o)
+        lses.append(l)
+    return torch.stack(outs, 0), torch.stack(lses, 0)
