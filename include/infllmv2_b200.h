@@ -1,0 +1,164 @@
+/*
+ * infllmv2_b200 -- C ABI of the B200 (sm_100a) kernels for InfLLM-V2 two-stage sparse attention.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes only; every pointer is DEVICE memory of the current CUDA device
+ *     unless stated otherwise; the caller allocates every output and every workspace;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised;
+ *   - return value: 0 on success, a negative IFV2_ERR_* for a rejected argument (nothing was
+ *     launched), or a positive cudaError_t reported by the launch;
+ *   - ifv2_last_error() returns a thread-local, human-readable message for the last non-zero
+ *     return on the calling thread.
+ *
+ * Each declaration names the interface of the reference (OpenBMB/infllmv2_cuda_impl) that it
+ * replaces, by file:line inside that project.
+ */
+#ifndef INFLLMV2_B200_H_
+#define INFLLMV2_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IFV2_OK                 0
+#define IFV2_ERR_INVALID_ARG   -1   /* null pointer, negative size, bad flag             */
+#define IFV2_ERR_UNSUPPORTED   -2   /* feature the reference compiles out / d != 128 ... */
+#define IFV2_ERR_TOO_LARGE     -3   /* size beyond a documented limit                    */
+#define IFV2_ERR_DRIVER        -4   /* a driver entry point (tensor-map encode) failed   */
+#define IFV2_ERR_DEVICE_STATUS -5   /* a kernel reported a bounded wait that ran out     */
+
+const char* ifv2_last_error(void);
+/* Library version, for loaders that want to check what they bound. */
+int ifv2_version(void);
+
+/* ---------------------------------------------------------------- bitmask kernels ---------- */
+
+/* Rows of block indices -> rows of 64-bit words (bit idx%64 of word idx/64; indices outside
+ * [0, 64*words) are skipped).  Writes every output word.
+ * Replaces C.topk_to_uint64: csrc/entry.cu:79-97, kernel csrc/topk_to_uint64.cuh:10-76. */
+int ifv2_topk_to_uint64(const int32_t* topk_idx, int64_t* out_words, int64_t rows, int k,
+                        int k_blocks, int words, void* stream);
+
+/* Bool rows (1 byte per element) -> 64-bit words, element 64w+b = bit b of word w, tail bits 0.
+ * Replaces C.blockmask_to_uint64: csrc/entry.cu:61-77, kernel csrc/blockmask_to_uint64.cuh:10-74. */
+int ifv2_blockmask_to_uint64(const uint8_t* mask, int64_t* out_words, int64_t rows,
+                             int64_t last_dim, int64_t words, void* stream);
+
+/* Inverse of the above, restricted to the first last_dim bits of each row.
+ * Replaces C.uint64_to_bool: csrc/entry.cu:99-115, kernel csrc/uint64_to_bool.cuh:10-66. */
+int ifv2_uint64_to_bool(const int64_t* in_words, uint8_t* out_mask, int64_t rows,
+                        int64_t last_dim, int64_t words, void* stream);
+
+/* Row mask (heads, tokens, ceil(k_blocks/64)) -> column mask (heads, k_blocks, ceil(tokens/64)):
+ * out[h, blk, t/64] bit t%64 = in[h, t, blk/64] bit blk%64.  One kernel in place of the
+ * reference's unpack -> transpose(1,2).contiguous() -> synchronize -> pack sequence,
+ * infllm_v2/infllmv2_sparse_attention.py:343-350. */
+int ifv2_transpose_blockmask(const int64_t* fwd_words, int64_t* bwd_words, int heads,
+                             int64_t tokens, int k_blocks, void* stream);
+
+/* ---------------------------------------------------------------- selection kernels -------- */
+
+/* 1-D max-pool of stage-1 scores to block scores with +inf on the init and causal-local blocks.
+ * in: (heads, q_len, k_len) with `in_row_stride` elements between rows (>= k_len);
+ * out: (heads, q_len, out_len) contiguous.  dtype: is_bf16 ? bf16 : fp16.
+ * Replaces C.max_pooling_1d: csrc/entry.cu:117-152, kernel csrc/max_pooling_1d.cuh:106-160. */
+int ifv2_max_pooling_1d(const void* in, void* out, int is_bf16, int heads, int q_len, int k_len,
+                        int64_t in_row_stride, int out_len, int cache_len, int kernel_size,
+                        int stride, int padding, int block_size, int local_blocks,
+                        int init_blocks, void* stream);
+
+/* Packed-sequence variant: rows are global query tokens, the key length and cache length are
+ * per sequence.  total_q is taken from the caller (no device->host read).
+ * Replaces C.max_pooling_1d_varlen: csrc/entry.cu:154-195, kernel csrc/max_pooling_1d.cuh:11-103. */
+int ifv2_max_pooling_1d_varlen(const void* in, void* out, const int32_t* cu_seqlens_q,
+                               const int32_t* cu_seqlens_k, const int32_t* cache_lens,
+                               int is_bf16, int batch, int heads, int64_t total_q,
+                               int max_seqlen_k, int64_t in_row_stride, int out_len,
+                               int kernel_size, int stride, int padding, int block_size,
+                               int local_blocks, int init_blocks, void* stream);
+
+/* Per-row top-k of block scores: the k entries first in (value descending, index ascending)
+ * order, written ascending as int32 with -1 in the unused tail; indices greater than the
+ * row's own query block ((local token + cache_len) / block_size) become -1.
+ * score: (heads, total_q, n_blocks), `row_stride` elements between rows.
+ * cu_seqlens_q / cache_lens may be null (single sequence, scalar cache_len).
+ * The reference has no public op for this step (README.md:40-42); the ordering is that of its
+ * bitonic top-k, csrc/topk.cuh:6-42.  n_blocks <= 8192. */
+int ifv2_topk_select(const void* score, int32_t* out_idx, int is_bf16, int heads, int64_t total_q,
+                     int n_blocks, int64_t row_stride, int k, const int32_t* cu_seqlens_q,
+                     const int32_t* cache_lens, int batch, int cache_len, int block_size,
+                     void* stream);
+
+/* ---------------------------------------------------------------- stage 1 ------------------ */
+
+/* Stage-1 scorer: out[h, t, j] = sum over the 16 query heads of KV head h of
+ * softmax_j(scale * q[t, 16h+g] . kc[j, h]) over the compressed keys visible to token t.
+ * q: (total_q, heads_q, 128) bf16, kc: (total_c, heads_k, 128) bf16, both dense row-major.
+ * out: (heads_k, total_q, out_row_stride) bf16; columns [0, max_seqlen_k) of every row are
+ * written (0 where invisible).  status: int32[4] device words, word 0 != 0 after the launch
+ * means a bounded wait ran out.
+ * Replaces C.varlen_fwd_stage1: csrc/entry.cu:209-214 -> mha_varlen_fwd_stage1,
+ * csrc/flash_attn/flash_api.cpp:784-1049 (+ the GQA transpose, slice and NaN scrub of
+ * infllm_v2/infllmv2_sparse_attention.py:554-589). */
+int ifv2_stage1_scores(const void* q, const void* kc, void* out, const int32_t* cu_seqlens_q,
+                       const int32_t* cu_seqlens_k, int batch, int64_t total_q, int64_t total_c,
+                       int heads_q, int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                       int64_t out_row_stride, float softmax_scale, int causal,
+                       int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------- stage 2 ------------------ */
+
+/* Block-sparse varlen attention forward.  q/out: (total_q, heads_q, 128) bf16; k, v:
+ * (total_k, heads_k, 128) bf16; fwd_mask: (heads_k, total_q, mask_words) 64-bit words from
+ * ifv2_topk_to_uint64, or null for dense attention; lse: (heads_k, total_q*16) fp32 with row
+ * token*16 + head-in-group.  Rows that see no key get out = 0 and lse = +inf.
+ * Replaces C.varlen_fwd: csrc/entry.cu:209-214 -> mha_varlen_fwd,
+ * csrc/flash_attn/flash_api.cpp:519-782 (+ the GQA transposes of
+ * infllm_v2/infllmv2_sparse_attention.py:81-90, 123-130). */
+int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                         const int64_t* fwd_mask, int mask_words, const int32_t* cu_seqlens_q,
+                         const int32_t* cu_seqlens_k, int batch, int64_t total_q, int64_t total_k,
+                         int heads_q, int heads_k, int head_dim, int max_seqlen_q,
+                         int max_seqlen_k, float softmax_scale, int causal, int32_t* status,
+                         void* stream);
+
+/* Bytes of scratch ifv2_sparse_attn_bwd needs (fp32 dQ accumulator + D rows). */
+int64_t ifv2_sparse_attn_bwd_workspace_bytes(int64_t total_q, int heads_q, int head_dim);
+
+/* Backward of the above: dq (total_q, heads_q, 128), dk/dv (total_k, heads_k, 128) bf16.
+ * bwd_mask: (heads_k, ceil(max_seqlen_k/64), ceil(total_q/64)) words from
+ * ifv2_transpose_blockmask, or null for dense.  workspace: caller-allocated scratch of at
+ * least ifv2_sparse_attn_bwd_workspace_bytes bytes (contents on entry are ignored).
+ * Replaces C.varlen_bwd: csrc/entry.cu:209-214 -> mha_varlen_bwd,
+ * csrc/flash_attn/flash_api.cpp:1278-1547. */
+int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
+                         const void* out, const float* lse, void* dq, void* dk, void* dv,
+                         const int64_t* bwd_mask, int64_t bwd_mask_words,
+                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                         int64_t total_q, int64_t total_k, int heads_q, int heads_k,
+                         int head_dim, int max_seqlen_q, int max_seqlen_k, float softmax_scale,
+                         int causal, void* workspace, int64_t workspace_bytes, int32_t* status,
+                         void* stream);
+
+/* Bytes of scratch ifv2_decode needs for its split partials. */
+int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_dim, int max_blocks);
+
+/* Sparse decode over a KV cache: one query token per sequence.
+ * q/out: (batch, heads_q, 128) bf16; k_cache, v_cache: (batch_cache, cache_capacity, heads_k,
+ * 128) bf16 with `cache_batch_stride` elements between sequences; k_new/v_new (batch, heads_k,
+ * 128) or null are first written in place at position cache_seqlens[b]; mask: (batch, heads_k,
+ * mask_words) words or null; lse: (batch, heads_q) fp32 or null.
+ * Replaces C.fwd_kvcache: csrc/entry.cu:209-214 -> mha_fwd_kvcache,
+ * csrc/flash_attn/flash_api.cpp:1549-1843. */
+int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                void* out, float* lse, const int64_t* mask, int mask_words,
+                const int32_t* cache_seqlens, int batch, int heads_q, int heads_k, int head_dim,
+                int64_t cache_capacity, int64_t cache_batch_stride, float softmax_scale,
+                void* workspace, int64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFLLMV2_B200_H_ */

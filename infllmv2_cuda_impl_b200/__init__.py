@@ -1,0 +1,15 @@
+"""B200-native (sm_100a) InfLLM-V2 two-stage sparse attention behind the reference's `infllm_v2`
+Python API.  Every operator runs hand-written CUDA through the C ABI of
+include/infllmv2_b200.h; there is no CPU or library fallback."""
+__version__ = "0.1.0"
+
+from .ops import (blockmask_to_uint64, topk_to_uint64, uint64_to_bool, max_pooling_1d,
+                  max_pooling_1d_varlen, infllmv2_topk, transpose_blockmask)
+from .attention import (infllmv2_attn_varlen_func, infllmv2_attn_stage1,
+                        infllmv2_attn_with_kvcache, check_device_status)
+
+__all__ = [
+    "blockmask_to_uint64", "topk_to_uint64", "uint64_to_bool", "max_pooling_1d",
+    "max_pooling_1d_varlen", "infllmv2_attn_varlen_func", "infllmv2_attn_stage1",
+    "infllmv2_attn_with_kvcache", "infllmv2_topk", "transpose_blockmask", "check_device_status",
+]

@@ -1,0 +1,329 @@
+"""Stage-1 scorer, stage-2 block-sparse attention (forward + backward) and KV-cache decode with the
+reference's Python signatures (infllm_v2/infllmv2_sparse_attention.py:388-406, 483-501, 609-630).
+
+The bodies differ from the reference on purpose: the kernels read q / write out in the caller's
+(token, head, d) layout, so none of the GQA reshape-transpose-contiguous copies remain, the
+backward mask comes from one bit-transpose kernel, and nothing synchronises the device.
+Features the reference's build compiles out (dropout, softcap, ALiBi, sliding window, fp16,
+head_dim != 128, GQA group != 16) raise on the host, as its TORCH_CHECKs do.
+"""
+import math
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+from .ops import topk_to_uint64, transpose_blockmask
+
+BLOCK_N = 64      # tokens per KV block (the reference's N_BLOCK_DIM)
+GROUP = 16        # query heads per KV head (the reference's m_block_dim)
+HEAD_DIM = 128
+
+_status = {}
+
+
+def _status_words(device) -> torch.Tensor:
+    """Per-device int32[4] that kernels write when one of their bounded waits runs out."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel launched through this module gave up on a wait.
+    Not called on the hot path; tests, the smoke entry and the benchmark call it."""
+    devices = list(_status) if device is None else [torch.device(device).index or 0]
+    for idx in devices:
+        if idx in _status:
+            torch.cuda.synchronize(idx)
+            code = int(_status[idx][0].item())
+            if code != 0:
+                _status[idx].zero_()
+                raise _lib.Ifv2Error(f"a kernel on cuda:{idx} abandoned a bounded wait (site {code})")
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def maybe_contiguous(x):
+    return x.contiguous() if x is not None and x.stride(-1) != 1 else x
+
+
+def round_multiple(x, m):
+    return (x + m - 1) // m * m
+
+
+def _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table, what):
+    if not q.is_cuda:
+        raise RuntimeError(f"{what}: tensors must be on a CUDA device; this library has no CPU path")
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16:
+        raise RuntimeError(f"{what}: only bf16 is supported (as in the reference build)")
+    if dropout_p != 0.0:
+        raise RuntimeError(f"{what}: dropout is not supported (compiled out in the reference)")
+    if softcap != 0.0:
+        raise RuntimeError(f"{what}: softcap is not supported (compiled out in the reference)")
+    if alibi_slopes is not None:
+        raise RuntimeError(f"{what}: ALiBi is not supported (compiled out in the reference)")
+    if tuple(window_size) != (-1, -1):
+        raise RuntimeError(f"{what}: sliding-window attention is not supported (compiled out in the reference)")
+    if block_table is not None:
+        raise NotImplementedError(f"{what}: paged KV (block_table) is not supported")
+    if q.shape[-1] != HEAD_DIM or k.shape[-1] != HEAD_DIM:
+        raise RuntimeError(f"{what}: head_dim must be {HEAD_DIM}")
+    if q.shape[-2] != GROUP * k.shape[-2]:
+        raise RuntimeError(f"{what}: the number of query heads must be {GROUP} x the number of KV heads")
+
+
+def _dense(x):
+    """(T, H, d) with unit stride in d and H, i.e. rows of H*d contiguous elements."""
+    return x if x.is_contiguous() else x.contiguous()
+
+
+# ------------------------------------------------------------------------------------ stage 1 --
+
+def infllmv2_attn_stage1(
+    q, k, v, cu_seqlens_q, cu_seqlens_k, cu_seqlens_v, max_seqlen_q, max_seqlen_k,
+    dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0,
+    alibi_slopes=None, deterministic=False, return_attn_probs=True, block_table=None,
+):
+    """Stage-1 scores: for every KV head, softmax(q . k_compressed) summed over its 16 query heads.
+
+    q: (total_q, nheads, 128) bf16; k: (total_c, nheads_k, 128) bf16 compressed keys;
+    v / cu_seqlens_v: the keys the log-sum-exp is taken over -- must be the same tensor as k
+    (the coarse-LSE mode with a differently compressed v is not built).
+    Returns (nheads_k, total_q, max_seqlen_k) bf16; entries a token cannot see are 0.
+    The returned tensor is a column slice of a buffer whose rows are padded to a multiple of
+    128 elements, like the reference's (infllm_v2/infllmv2_sparse_attention.py:587).
+    """
+    _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table,
+                  "infllmv2_attn_stage1")
+    if v is not None and (v.shape != k.shape):
+        raise NotImplementedError(
+            "infllmv2_attn_stage1: a separately compressed `v` (coarse-LSE mode) is not supported; "
+            "pass the compressed keys as both k and v")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    q, k = _dense(maybe_contiguous(q)), _dense(maybe_contiguous(k))
+    total_q, nheads, _ = q.shape
+    nheads_k = k.shape[1]
+    batch = cu_seqlens_q.numel() - 1
+    assert cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32
+    row_stride = max(round_multiple(max_seqlen_k, 128), 128)
+    buf = torch.empty(nheads_k, total_q, row_stride, dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("ifv2_stage1_scores", q.data_ptr(), k.data_ptr(), buf.data_ptr(),
+                  cu_seqlens_q.contiguous().data_ptr(), cu_seqlens_k.contiguous().data_ptr(), batch,
+                  total_q, k.shape[0], nheads, nheads_k, q.shape[-1], max_seqlen_q, max_seqlen_k,
+                  row_stride, float(softmax_scale), int(bool(causal)),
+                  _status_words(q.device).data_ptr(), _stream(q.device))
+    return buf[:, :, :max_seqlen_k]
+
+
+# ------------------------------------------------------------------------------------ stage 2 --
+
+def _fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
+         fwd_mask):
+    total_q, nheads, d = q.shape
+    nheads_k = k.shape[1]
+    batch = cu_seqlens_q.numel() - 1
+    out = torch.empty_like(q)
+    lse = torch.empty(nheads_k, total_q * GROUP, dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("ifv2_sparse_attn_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                  lse.data_ptr(), fwd_mask.data_ptr() if fwd_mask is not None else None,
+                  fwd_mask.shape[-1] if fwd_mask is not None else 0,
+                  cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), batch, total_q, k.shape[0],
+                  nheads, nheads_k, d, max_seqlen_q, max_seqlen_k, float(softmax_scale),
+                  int(bool(causal)), _status_words(q.device).data_ptr(), _stream(q.device))
+    return out, lse
+
+
+def _bwd(dout, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+         softmax_scale, causal, bwd_mask):
+    total_q, nheads, d = q.shape
+    nheads_k = k.shape[1]
+    batch = cu_seqlens_q.numel() - 1
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    lib = _lib.load()
+    ws_bytes = int(lib.ifv2_sparse_attn_bwd_workspace_bytes(total_q, nheads, d))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("ifv2_sparse_attn_bwd", dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                  out.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                  bwd_mask.data_ptr() if bwd_mask is not None else None,
+                  bwd_mask.shape[-1] if bwd_mask is not None else 0,
+                  cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), batch, total_q, k.shape[0],
+                  nheads, nheads_k, d, max_seqlen_q, max_seqlen_k, float(softmax_scale),
+                  int(bool(causal)), ws.data_ptr(), ws_bytes, _status_words(q.device).data_ptr(),
+                  _stream(q.device))
+    return dq, dk, dv
+
+
+@torch.library.custom_op("infllmv2_attn::_infllmv2_attn_varlen_forward", mutates_args=(),
+                         device_types="cuda")
+def _infllmv2_attn_varlen_forward(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, softmax_scale: float,
+    causal: bool, topk_idx: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (out, softmax_lse (nheads_k, total_q*16), fwd_blockmask int64 or an empty tensor)."""
+    q, k, v = [_dense(maybe_contiguous(x)) for x in (q, k, v)]
+    if topk_idx is not None:
+        assert topk_idx.dtype == torch.int32
+        fwd_mask, _ = topk_to_uint64(topk_idx, max_seqlen_k, BLOCK_N)
+    else:
+        fwd_mask = None
+    out, lse = _fwd(q, k, v, cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous(), max_seqlen_q,
+                    max_seqlen_k, softmax_scale, causal, fwd_mask)
+    if fwd_mask is None:
+        fwd_mask = torch.empty(0, dtype=torch.int64, device=q.device)
+    return out, lse, fwd_mask
+
+
+@_infllmv2_attn_varlen_forward.register_fake
+def _(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
+      topk_idx=None):
+    words = ((max_seqlen_k + BLOCK_N - 1) // BLOCK_N + 63) // 64
+    mask = (q.new_empty((k.shape[1], q.shape[0], words), dtype=torch.int64)
+            if topk_idx is not None else q.new_empty((0,), dtype=torch.int64))
+    return (torch.empty_like(q),
+            q.new_empty((k.shape[1], q.shape[0] * GROUP), dtype=torch.float32), mask)
+
+
+@torch.library.custom_op("infllmv2_attn::_infllmv2_attn_varlen_backward", mutates_args=(),
+                         device_types="cuda")
+def _infllmv2_attn_varlen_backward(
+    dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+    softmax_lse: torch.Tensor, cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int, max_seqlen_k: int, softmax_scale: float, causal: bool,
+    fwd_blockmask: torch.Tensor,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    dout = _dense(maybe_contiguous(dout))
+    bwd_mask = None
+    if fwd_blockmask.numel() > 0:
+        k_blocks = (max_seqlen_k + BLOCK_N - 1) // BLOCK_N
+        bwd_mask = transpose_blockmask(fwd_blockmask, k_blocks)
+    return _bwd(dout, q, k, v, out, softmax_lse, cu_seqlens_q.contiguous(),
+                cu_seqlens_k.contiguous(), max_seqlen_q, max_seqlen_k, softmax_scale, causal,
+                bwd_mask)
+
+
+@_infllmv2_attn_varlen_backward.register_fake
+def _(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+      softmax_scale, causal, fwd_blockmask):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+class Infllmv2AttnVarlenFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p,
+                softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic,
+                return_softmax, block_table, topk_idx):
+        _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table,
+                      "infllmv2_attn_varlen_func")
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** (-0.5)
+        out, lse, fwd_mask = _infllmv2_attn_varlen_forward(
+            q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
+            topk_idx)
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, fwd_mask)
+        ctx.max_seqlen_q, ctx.max_seqlen_k = max_seqlen_q, max_seqlen_k
+        ctx.softmax_scale, ctx.causal = softmax_scale, causal
+        return out if not return_softmax else (out, lse, None)
+
+    @staticmethod
+    def backward(ctx, dout, *args):
+        q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, fwd_mask = ctx.saved_tensors
+        dq, dk, dv = _infllmv2_attn_varlen_backward(
+            dout, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, ctx.max_seqlen_q,
+            ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal, fwd_mask)
+        return (dq, dk, dv) + (None,) * 14
+
+
+def infllmv2_attn_varlen_func(
+    q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p=0.0,
+    softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0, alibi_slopes=None,
+    deterministic=False, return_attn_probs=False, block_table=None, topk_idx=None,
+):
+    """Block-sparse varlen attention (stage 2), differentiable.
+
+    q: (total_q, nheads, 128); k, v: (total_k, nheads_k, 128), bf16, nheads = 16 * nheads_k.
+    cu_seqlens_q / cu_seqlens_k: (batch + 1,) int32.  topk_idx: int32 (nheads_k, total_q, topk)
+    block indices local to each sequence's keys (64-token blocks, -1 = unused); None = dense
+    attention.  causal=True aligns the diagonal to the bottom right when seqlen_q != seqlen_k.
+    Rows that see no key return 0.  Returns out (total_q, nheads, 128), or
+    (out, softmax_lse (nheads_k, total_q * 16), None) with return_attn_probs=True.
+    """
+    return Infllmv2AttnVarlenFunc.apply(
+        q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale,
+        causal, window_size, softcap, alibi_slopes, deterministic, return_attn_probs, block_table,
+        topk_idx)
+
+
+# ------------------------------------------------------------------------------------ decode --
+
+def infllmv2_attn_with_kvcache(
+    q, k_cache, v_cache, k=None, v=None, rotary_cos=None, rotary_sin=None,
+    cache_seqlens: Optional[Union[int, torch.Tensor]] = None,
+    cache_batch_idx: Optional[torch.Tensor] = None, cache_leftpad: Optional[torch.Tensor] = None,
+    block_table: Optional[torch.Tensor] = None, softmax_scale=None, causal=False,
+    window_size=(-1, -1), softcap=0.0, rotary_interleaved=True, alibi_slopes=None, num_splits=0,
+    return_softmax_lse=False, topk_idx=None,
+):
+    """Sparse decode step over a KV cache (one new query token per sequence).
+
+    q: (batch, 1, nheads, 128); k_cache, v_cache: (batch, seqlen_cache, nheads_k, 128);
+    k, v: optional (batch, 1, nheads_k, 128), written in place at cache_seqlens first;
+    cache_seqlens: int or (batch,) int32; topk_idx: int32 (batch, nheads_k, 1, topk) blocks of
+    the cache to attend (None = the whole cache).  A single query token is never causally
+    masked (csrc/flash_attn/flash_api.cpp:1628).  Returns out (batch, 1, nheads, 128)
+    [, softmax_lse (batch, nheads, 1)].
+    """
+    assert k_cache.stride(-1) == 1, "k_cache must have contiguous last dimension"
+    assert v_cache.stride(-1) == 1, "v_cache must have contiguous last dimension"
+    _check_common(q, k_cache, 0.0, window_size, softcap, alibi_slopes, block_table,
+                  "infllmv2_attn_with_kvcache")
+    if rotary_cos is not None or rotary_sin is not None:
+        raise NotImplementedError("infllmv2_attn_with_kvcache: rotary-on-append is not supported")
+    if cache_batch_idx is not None or cache_leftpad is not None:
+        raise NotImplementedError("infllmv2_attn_with_kvcache: cache_batch_idx / cache_leftpad are not supported")
+    if q.shape[1] != 1:
+        raise NotImplementedError("infllmv2_attn_with_kvcache: only one query token per sequence is supported")
+    q, k, v = [maybe_contiguous(x) for x in (q, k, v)]
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    batch, _, nheads, d = q.shape
+    cap, nheads_k = k_cache.shape[1], k_cache.shape[2]
+    if cache_seqlens is None:
+        cache_seqlens = cap
+    if isinstance(cache_seqlens, int):
+        cache_seqlens = torch.full((batch,), cache_seqlens, dtype=torch.int32, device=q.device)
+    cache_seqlens = cache_seqlens.contiguous()
+    assert cache_seqlens.dtype == torch.int32
+    for c in (k_cache, v_cache):
+        if c.stride(2) != d or c.stride(1) != nheads_k * d:
+            raise RuntimeError("infllmv2_attn_with_kvcache: caches must be dense in (seqlen, heads, d)")
+    mask = None
+    if topk_idx is not None:
+        assert topk_idx.dtype == torch.int32
+        mask, _ = topk_to_uint64(topk_idx, cap, BLOCK_N)
+    q2 = q.reshape(batch, nheads, d).contiguous()
+    out = torch.empty_like(q2)
+    lse = torch.empty(batch, nheads, dtype=torch.float32, device=q.device)
+    lib = _lib.load()
+    max_blocks = (cap + BLOCK_N - 1) // BLOCK_N
+    ws_bytes = int(lib.ifv2_decode_workspace_bytes(batch, nheads, d, max_blocks))
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("ifv2_decode", q2.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                  k.contiguous().data_ptr() if k is not None else None,
+                  v.contiguous().data_ptr() if v is not None else None, out.data_ptr(),
+                  lse.data_ptr(), mask.data_ptr() if mask is not None else None,
+                  mask.shape[-1] if mask is not None else 0, cache_seqlens.data_ptr(), batch,
+                  nheads, nheads_k, d, cap, k_cache.stride(0), float(softmax_scale), ws.data_ptr(),
+                  ws_bytes, _stream(q.device))
+    out = out.view(batch, 1, nheads, d)
+    return (out, lse.view(batch, nheads, 1)) if return_softmax_lse else out

@@ -1,0 +1,420 @@
+// Stage-2 forward: block-sparse varlen flash attention on tcgen05 tensor cores.
+//
+// One CTA owns a 128-row query tile = 8 consecutive tokens x the 16 query heads of one KV head
+// (in the caller's (token, head, d) layout those 16 heads are contiguous, so one 3-D TMA box
+// {64 d, 16 heads, 8 tokens} fetches the tile with no host-side transpose).  The CTA walks the
+// UNION of its 8 tokens' block-mask rows from the highest block down; a token that did not
+// select a block sees -inf for it.  Per 64-key block:
+//     S(128x64)  = Q . K^T      tcgen05.mma, operands in swizzled smem, accumulator in TMEM
+//     P = exp2(S*c - m*c)       4 softmax warps, one TMEM lane (= row) per thread; P is written
+//                               back over S in TMEM as packed bf16
+//     O(128x128) += P . V       tcgen05.mma with the A operand read from TMEM
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-5 = softmax /
+// epilogue.  K and V each have a 2-deep ring; S/P is double-buffered in TMEM so Q.K^T of the
+// next block overlaps the softmax of the current one.  TMEM: 2 x 64 (S/P) + 128 (O) = 256
+// columns, shared memory 96 KB, so two CTAs share an SM and fill each other's bubbles.
+// The running max is only raised when it grows by more than 2^8 (the accumulator then needs a
+// rescale); P stays bounded by 256 and the final 1/l normalisation makes the result exact.
+#include "tc05.cuh"
+
+namespace ifv2 {
+namespace {
+
+using namespace tc;
+
+constexpr int kTokPerTile = 8;
+constexpr int kThreads = 192;
+constexpr int kMaxMaskWords = 128;            // 8192 key blocks = 524288 keys per sequence
+constexpr uint32_t kQHalfBytes = 128 * 128;   // 128 rows x 64 bf16
+constexpr uint32_t kKVHalfBytes = 64 * 128;   // 64 keys x 64 bf16
+constexpr uint32_t kTmemCols = 256;
+constexpr float kRescaleThreshold = 8.0f;     // log2 units
+
+struct FwdParams {
+  __nv_bfloat16* out;
+  float* lse;
+  const unsigned long long* mask;
+  int mask_words;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int64_t total_q;
+  int heads_q, heads_k;
+  float scale, scale_log2;
+  int causal;
+  int32_t* status;
+};
+
+struct Smem {
+  uint8_t q[2][kQHalfBytes];          // [d half]
+  uint8_t k[2][2][kKVHalfBytes];      // [stage][d half]
+  uint8_t v[2][2][kKVHalfBytes];      // [stage][d half]
+  unsigned long long umask[kMaxMaskWords];
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done;
+  uint32_t tmem_base;
+  int n_blocks;
+  int abort_flag;
+};
+
+// Highest-to-lowest walk over the set bits of the tile's union mask.
+struct BlockWalk {
+  const unsigned long long* words;
+  int w;
+  unsigned long long cur;
+  __device__ BlockWalk(const unsigned long long* u, int nwords) : words(u), w(nwords), cur(0) {}
+  __device__ int next() {
+    while (cur == 0ull) {
+      if (w == 0) return -1;
+      cur = words[--w];
+    }
+    const int b = 63 - __clzll(cur);
+    cur &= ~(1ull << b);
+    return w * 64 + b;
+  }
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
+                       const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                      ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.y, h = blockIdx.z;
+  const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
+  const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTokPerTile;   // long tiles first
+  if (tok0 >= lq) return;
+  // an earlier CTA gave up on a wait: the launch is already failed, do not pile up more waits
+  if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
+  const int ntok = min(kTokPerTile, lq - tok0);
+  const int shift = lk - lq;                        // bottom-right aligned causal diagonal
+  const int nblk_k = (lk + kBlockN - 1) / kBlockN;
+  const int words = (p.mask != nullptr) ? p.mask_words : min(kMaxMaskWords, (nblk_k + 63) / 64);
+
+  // ---- union of the tile's mask rows, trimmed to the blocks any of its tokens can see
+  {
+    int last_blk = nblk_k - 1;
+    if (p.causal) last_blk = min(last_blk, (tok0 + ntok - 1 + shift) >= 0
+                                               ? (tok0 + ntok - 1 + shift) / kBlockN : -1);
+    for (int w = threadIdx.x; w < words; w += kThreads) {
+      unsigned long long u = 0ull;
+      if (p.mask != nullptr) {
+        const unsigned long long* row =
+            p.mask + ((int64_t)h * p.total_q + q0 + tok0) * p.mask_words + w;
+        for (int t = 0; t < ntok; ++t) u |= __ldg(row + (int64_t)t * p.mask_words);
+      } else {
+        u = ~0ull;
+      }
+      const int first = w * 64;
+      if (last_blk < first) u = 0ull;
+      else if (last_blk - first < 63) u &= (2ull << (last_blk - first)) - 1ull;
+      sm.umask[w] = u;
+    }
+  }
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sm.k_full[s], 1);
+      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.v_full[s], 1);
+      mbar_init(&sm.v_empty[s], 1);
+      mbar_init(&sm.s_full[s], 1);
+      mbar_init(&sm.p_ready[s], 128);
+    }
+    mbar_init(&sm.o_done, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int w = 0; w < words; ++w) n += __popcll(sm.umask[w]);
+    sm.n_blocks = n;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const int n_blocks = sm.n_blocks;
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_o = tmem + 128;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (warp == 0) {
+    // ================================================================ TMA producer
+    if (lane == 0 && n_blocks > 0) {
+      mbar_expect_tx(&sm.q_full, 2 * kQHalfBytes);
+      tma_load_3d(sm.q[0], &map_q, &sm.q_full, 0, h * kGroup, q0 + tok0);
+      tma_load_3d(sm.q[1], &map_q, &sm.q_full, 64, h * kGroup, q0 + tok0);
+      BlockWalk walk(sm.umask, words);
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < n_blocks && ok; ++i) {
+        const int blk = walk.next();
+        const int s = i & 1, key = k0 + blk * kBlockN;
+        const uint32_t par = (uint32_t)((i >> 1) & 1);
+        if (i >= 2) ok = mbar_wait(&sm.k_empty[s], par ^ 1u, abort_flag, p.status, 11);
+        if (!ok) break;
+        mbar_expect_tx(&sm.k_full[s], 2 * kKVHalfBytes);
+        tma_load_3d(sm.k[s][0], &map_k, &sm.k_full[s], 0, h, key);
+        tma_load_3d(sm.k[s][1], &map_k, &sm.k_full[s], 64, h, key);
+        if (i >= 2) ok = mbar_wait(&sm.v_empty[s], par ^ 1u, abort_flag, p.status, 12);
+        if (!ok) { issued = i + 1; break; }
+        mbar_expect_tx(&sm.v_full[s], 2 * kKVHalfBytes);
+        tma_load_3d(sm.v[s][0], &map_v, &sm.v_full[s], 0, h, key);
+        tma_load_3d(sm.v[s][1], &map_v, &sm.v_full[s], 64, h, key);
+        issued = i + 1;
+      }
+      if (*abort_flag) {   // let the copies already in flight land before the CTA retires
+        mbar_wait_drain(&sm.q_full, 0);
+        for (int j = max(0, issued - 2); j < issued; ++j) {
+          mbar_wait_drain(&sm.k_full[j & 1], (uint32_t)((j >> 1) & 1));
+          mbar_wait_drain(&sm.v_full[j & 1], (uint32_t)((j >> 1) & 1));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer
+    if (lane == 0 && n_blocks > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, true);
+      const uint32_t q_addr = smem_u32(sm.q[0]);
+      bool ok = mbar_wait(&sm.q_full, 0, abort_flag, p.status, 21);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(&sm.k_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 22))
+          return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sm.k[s][0]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t qoff = (kk >> 2) * kQHalfBytes + (kk & 3) * 32;
+          const uint32_t koff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
+          umma_ss(tmem + s * 64, umma_desc_sw128(q_addr + qoff, 16, 1024),
+                  umma_desc_sw128(k_addr + koff, 16, 1024), idesc_qk, kk > 0);
+        }
+        umma_commit(&sm.k_empty[s]);
+        umma_commit(&sm.s_full[s]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int i = 0; i < n_blocks && ok; ++i) {
+        const int s = i & 1;
+        const uint32_t par = (uint32_t)((i >> 1) & 1);
+        if (i + 1 < n_blocks) ok = issue_qk(i + 1);
+        if (!ok) break;
+        ok = mbar_wait(&sm.p_ready[s], par, abort_flag, p.status, 23) &&
+             mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 24);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sm.v[s][0]);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem_o, tmem + s * 64 + kk * 8,
+                  umma_desc_sw128(v_addr + kk * 2048, kKVHalfBytes, 1024), idesc_pv,
+                  (i > 0) || (kk > 0));
+        umma_commit(&sm.v_empty[s]);
+        umma_commit(&sm.o_done);
+      }
+    }
+  } else {
+    // ================================================================ softmax + epilogue
+    const int quad = warp & 3;                       // TMEM lane quadrant this warp may access
+    const int r = quad * 32 + lane;                  // row of the tile = TMEM lane
+    const int tl = r >> 4, g = r & 15;
+    const int tok = tok0 + tl;                       // local token index
+    const bool valid = tl < ntok;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const unsigned long long* mrow =
+        (p.mask != nullptr && valid)
+            ? p.mask + ((int64_t)h * p.total_q + q0 + tok) * p.mask_words : nullptr;
+    const int row_limit = valid ? min(lk, p.causal ? tok + shift + 1 : lk) : 0;   // visible keys
+
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    BlockWalk walk(sm.umask, words);
+    for (int i = 0; i < n_blocks; ++i) {
+      const int blk = walk.next();
+      const int s = i & 1;
+      const uint32_t par = (uint32_t)((i >> 1) & 1);
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[s], par, abort_flag, p.status, 31));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t raw[2][32];
+      tmem_ld32(tmem + lane_off + s * 64, raw[0]);
+      tmem_ld32(tmem + lane_off + s * 64 + 32, raw[1]);
+      tmem_wait_ld();
+
+      bool selected = valid;
+      if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
+      const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
+
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float x = __uint_as_float(raw[c >> 5][c & 31]);
+        x = (c < lim) ? x : -INFINITY;
+        raw[c >> 5][c & 31] = __float_as_uint(x);
+        mx = fmaxf(mx, x);
+      }
+      // raise the reference max only when it moves by more than the threshold
+      float f = 1.f;
+      if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > kRescaleThreshold)) {
+        if (m_ref != -INFINITY) f = exp2f((m_ref - mx) * p.scale_log2);
+        m_ref = mx;
+        l *= f;
+      }
+      if (i > 0 && __any_sync(0xFFFFFFFFu, f != 1.f)) {
+        ok = __all_sync(0xFFFFFFFFu,
+                        mbar_wait(&sm.o_done, (uint32_t)((i - 1) & 1), abort_flag, p.status, 32));
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tmem_o + lane_off + c, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
+          tmem_st32(tmem_o + lane_off + c, o);
+        }
+        tmem_wait_st();
+      }
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
+      uint32_t packed[32];
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = exp2f(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.scale_log2, neg_m));
+        const float p1 =
+            exp2f(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.scale_log2, neg_m));
+        sum += p0 + p1;
+        packed[c >> 1] = pack_bf16(p0, p1);
+      }
+      l += sum;
+      tmem_st32(tmem + lane_off + s * 64, packed);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.p_ready[s]);
+    }
+
+    // ---- epilogue: O / l -> bf16, lse
+    if (ok && n_blocks > 0) {
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag,
+                                             p.status, 33));
+      tc_fence_after();
+    }
+    if (ok) {
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow =
+          p.out + ((int64_t)(q0 + tok) * p.heads_q + h * kGroup + g) * kHeadDim;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t o[32];
+        if (n_blocks > 0) {
+          tmem_ld32(tmem_o + lane_off + c, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v4;
+            v4.x = pack_bf16(__uint_as_float(o[8 * j + 0]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
+            v4.y = pack_bf16(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
+            v4.z = pack_bf16(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
+            v4.w = pack_bf16(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
+            dst[j] = v4;
+          }
+        }
+      }
+      if (valid)
+        p.lse[(int64_t)h * p.total_q * kGroup + (int64_t)(q0 + tok) * kGroup + g] =
+            (l > 0.f) ? m_ref * p.scale + logf(l) : INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+}  // namespace ifv2
+
+using namespace ifv2;
+
+extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out,
+                                    float* lse, const int64_t* fwd_mask, int mask_words,
+                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                    int batch, int64_t total_q, int64_t total_k, int heads_q,
+                                    int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                    float softmax_scale, int causal, int32_t* status,
+                                    void* stream) {
+  IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED,
+               "sparse_attn_fwd: head_dim %d not supported (only 128, as in the reference build)",
+               head_dim);
+  IFV2_REQUIRE(heads_k >= 1 && heads_q == heads_k * kGroup, IFV2_ERR_UNSUPPORTED,
+               "sparse_attn_fwd: heads_q (%d) must be 16 x heads_k (%d)", heads_q, heads_k);
+  IFV2_REQUIRE(batch >= 1 && total_q >= 0 && total_k >= 0 && max_seqlen_q >= 0 && max_seqlen_k >= 0,
+               IFV2_ERR_INVALID_ARG, "sparse_attn_fwd: negative size or batch < 1");
+  if (total_q == 0 || max_seqlen_q == 0) return IFV2_OK;
+  IFV2_REQUIRE(q && k && v && out && lse && cu_seqlens_q && cu_seqlens_k && status,
+               IFV2_ERR_INVALID_ARG, "sparse_attn_fwd: null pointer");
+  IFV2_REQUIRE(total_q <= INT32_MAX && total_k <= INT32_MAX, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_fwd: more than 2^31-1 tokens");
+  const int k_blocks = (max_seqlen_k + kBlockN - 1) / kBlockN;
+  IFV2_REQUIRE((k_blocks + 63) / 64 <= kMaxMaskWords, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_fwd: max_seqlen_k %d exceeds %d keys", max_seqlen_k,
+               kMaxMaskWords * 64 * kBlockN);
+  IFV2_REQUIRE(fwd_mask == nullptr || (mask_words >= 1 && mask_words <= kMaxMaskWords),
+               IFV2_ERR_INVALID_ARG, "sparse_attn_fwd: mask_words %d out of range [1, %d]",
+               mask_words, kMaxMaskWords);
+  IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_fwd: batch or heads_k > 65535");
+
+  CUtensorMap map_q, map_k, map_v;
+  int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, total_q, kHeadDim * 2,
+                                   (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerTile);
+  if (rc) return rc;
+  rc = make_tensor_map_bf16_3d(&map_k, k, kHeadDim, heads_k, total_k > 0 ? total_k : 1,
+                               kHeadDim * 2, (uint64_t)heads_k * kHeadDim * 2, 64, 1, kBlockN);
+  if (rc) return rc;
+  rc = make_tensor_map_bf16_3d(&map_v, v, kHeadDim, heads_k, total_k > 0 ? total_k : 1,
+                               kHeadDim * 2, (uint64_t)heads_k * kHeadDim * 2, 64, 1, kBlockN);
+  if (rc) return rc;
+
+  FwdParams p;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.mask = reinterpret_cast<const unsigned long long*>(fwd_mask);
+  p.mask_words = mask_words;
+  p.cu_q = cu_seqlens_q;
+  p.cu_k = cu_seqlens_k;
+  p.total_q = total_q;
+  p.heads_q = heads_q;
+  p.heads_k = heads_k;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.causal = causal ? 1 : 0;
+  p.status = status;
+
+  const size_t smem = sizeof(Smem) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(sparse_attn_fwd_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return set_error((int)e, "sparse_attn_fwd: %s", cudaGetErrorString(e));
+  dim3 grid((max_seqlen_q + kTokPerTile - 1) / kTokPerTile, batch, heads_k);
+  sparse_attn_fwd_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
+  return check_launch("sparse_attn_fwd");
+}

@@ -1,0 +1,153 @@
+// Single-tile checks of the tcgen05 building blocks the attention kernels rely on: TMA tiles
+// with 128-byte swizzle feeding K-major and MN-major shared-memory operands, an A operand held
+// in TMEM, and TMEM load/store.  Each mode computes one small product that the test-suite
+// compares with a plain matmul, so a wrong descriptor shows up here and not inside a pipeline.
+#include "tc05.cuh"
+
+namespace ifv2 {
+namespace {
+
+using namespace tc;
+
+struct SelfTestParams {
+  const __nv_bfloat16* a;   // mode 2: A read with plain loads (128 x 64)
+  float* d;                 // (128, n) fp32
+  int mode;
+  int32_t* status;
+};
+
+// mode 0: D(128x64)  = A(128x128, K-major) * B(64x128, K-major)^T      [the Q.K^T shape]
+// mode 1: D(128x128) = A(128x64,  K-major) * Bt(64x128, MN-major)      [the P.V shape, P in smem]
+// mode 2: D(128x128) = A(128x64 in TMEM)   * Bt(64x128, MN-major)      [the P.V shape, P in TMEM]
+__global__ void __launch_bounds__(128)
+umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b, const SelfTestParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  uint8_t* sA = smem;              // up to 32 KB
+  uint8_t* sB = smem + 32768;      // up to 16 KB
+  __shared__ uint64_t bar_load, bar_mma;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar_load, 1);
+    mbar_init(&bar_mma, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+  const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
+  const int n = (p.mode == 0) ? 64 : 128;
+
+  if (p.mode == 2) {   // every thread stores its A row into TMEM as packed bf16 pairs
+    uint32_t regs[32];
+    const uint32_t* row = reinterpret_cast<const uint32_t*>(p.a + (size_t)threadIdx.x * 64);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) regs[j] = row[j];
+    tmem_st32(tmem_a + ((uint32_t)(warp * 32) << 16), regs);
+    tmem_wait_st();
+    tc_fence_before();
+  }
+  __syncthreads();
+
+  if (warp == 0 && elect_one()) {
+    tc_fence_after();
+    if (p.mode == 0) {
+      mbar_expect_tx(&bar_load, 2 * 16384 + 2 * 8192);
+      tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);
+      tma_load_3d(sA + 16384, &map_a, &bar_load, 64, 0, 0);
+      tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);
+      tma_load_3d(sB + 8192, &map_b, &bar_load, 64, 0, 0);
+    } else if (p.mode == 1) {
+      mbar_expect_tx(&bar_load, 16384 + 2 * 8192);
+      tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);
+      tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);
+      tma_load_3d(sB + 8192, &map_b, &bar_load, 64, 0, 0);
+    } else {
+      mbar_expect_tx(&bar_load, 2 * 8192);
+      tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);
+      tma_load_3d(sB + 8192, &map_b, &bar_load, 64, 0, 0);
+    }
+    if (mbar_wait(&bar_load, 0, &abort_flag, p.status, 1)) {
+      tc_fence_after();
+      if (p.mode == 0) {
+        const uint32_t idesc = umma_idesc_bf16(128, 64, false);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + off, 16, 1024),
+                  umma_desc_sw128(smem_u32(sB) + offb, 16, 1024), idesc, kk > 0);
+        }
+      } else {
+        const uint32_t idesc = umma_idesc_bf16(128, 128, true);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t bdesc = umma_desc_sw128(smem_u32(sB) + kk * 2048, 8192, 1024);
+          if (p.mode == 1)
+            umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + kk * 32, 16, 1024), bdesc, idesc, kk > 0);
+          else
+            umma_ts(tmem_d, tmem_a + kk * 8, bdesc, idesc, kk > 0);
+        }
+      }
+      umma_commit(&bar_mma);
+    }
+  }
+  __syncwarp();
+  const bool ok = mbar_wait(&bar_mma, 0, &abort_flag, p.status, 2);
+  tc_fence_after();
+  if (ok) {
+    for (int c = 0; c < n; c += 32) {
+      uint32_t regs[32];
+      tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + c, regs);
+      tmem_wait_ld();
+      float* out = p.d + (size_t)threadIdx.x * n + c;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) out[j] = __uint_as_float(regs[j]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace
+}  // namespace ifv2
+
+using namespace ifv2;
+
+// Test hook (declared here, not part of the public header): runs one tile product.
+//   mode 0: a (128,128), b (64,128)  -> d (128,64);  modes 1, 2: a (128,64), b (64,128) -> d (128,128)
+extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float* d, int32_t* status,
+                                  void* stream) {
+  IFV2_REQUIRE(mode >= 0 && mode <= 2, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0, 1 or 2");
+  IFV2_REQUIRE(a && b && d && status, IFV2_ERR_INVALID_ARG, "selftest: null pointer");
+  CUtensorMap map_a, map_b;
+  int rc;
+  if (mode == 0) {
+    rc = make_tensor_map_bf16_3d(&map_a, a, 128, 128, 1, 256, 256 * 128, 64, 128, 1);
+    if (rc) return rc;
+    rc = make_tensor_map_bf16_3d(&map_b, b, 128, 64, 1, 256, 256 * 64, 64, 64, 1);
+  } else {
+    rc = make_tensor_map_bf16_3d(&map_a, a, 64, 128, 1, 128, 128 * 128, 64, 128, 1);
+    if (rc) return rc;
+    rc = make_tensor_map_bf16_3d(&map_b, b, 128, 64, 1, 256, 256 * 64, 64, 64, 1);
+  }
+  if (rc) return rc;
+  static const cudaError_t attr = cudaFuncSetAttribute(
+      umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 50 * 1024);
+  (void)attr;
+  SelfTestParams p{static_cast<const __nv_bfloat16*>(a), d, mode, status};
+  umma_selftest_kernel<<<1, 128, 50 * 1024, (cudaStream_t)stream>>>(map_a, map_b, p);
+  return check_launch("umma_selftest");
+}

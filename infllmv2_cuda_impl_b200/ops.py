@@ -1,0 +1,211 @@
+"""Selection and bitmask operators with the reference's Python signatures.
+
+Same names, argument order, defaults and return values as infllm_v2/{topk_to_uint64,
+blockmask_to_uint64, uint64_to_bool, max_pooling_1d}.py of the reference; every call goes to
+the CUDA library through the C ABI on the current stream.  `infllmv2_topk` and
+`transpose_blockmask` are additions (the reference leaves top-k to its caller and builds the
+backward mask through a bool round trip).
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (got {t.device}); this library has no CPU path")
+
+
+def topk_to_uint64(topk_idx: torch.Tensor, max_seqlen_k: int, block_size: int,
+                   memory_buffer: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, int]:
+    """Top-k block indices -> packed int64 bitmask rows.
+
+    topk_idx: int32 [num_heads, total_seqlen, k] or [batch, num_heads, seqlen, k]; -1 = unused.
+    Returns (int64 tensor with the last dim replaced by ceil(k_blocks/64), k_blocks).
+    Mirrors infllm_v2/topk_to_uint64.py:5-72.
+    """
+    assert topk_idx.dtype == torch.int32
+    _require_cuda(topk_idx, "topk_idx")
+    if topk_idx.dim() not in (3, 4):
+        raise ValueError("topk_idx must be 3-D or 4-D")
+    k_blocks = (max_seqlen_k + block_size - 1) // block_size
+    words = (k_blocks + 63) // 64
+    topk_idx = topk_idx.contiguous()
+    out_shape = tuple(topk_idx.shape[:-1]) + (words,)
+    rows = topk_idx.numel() // max(topk_idx.shape[-1], 1) if topk_idx.shape[-1] else \
+        int(torch.Size(topk_idx.shape[:-1]).numel())
+    if (memory_buffer is not None and memory_buffer.dtype == torch.int64
+            and tuple(memory_buffer.shape) == out_shape and memory_buffer.is_contiguous()
+            and memory_buffer.device == topk_idx.device):
+        result = memory_buffer
+    else:
+        result = torch.empty(out_shape, dtype=torch.int64, device=topk_idx.device)
+    with torch.cuda.device(topk_idx.device):
+        _lib.call("ifv2_topk_to_uint64", topk_idx.data_ptr(), result.data_ptr(), rows,
+                  topk_idx.shape[-1], k_blocks, words, _stream(topk_idx.device))
+    return result, k_blocks
+
+
+def blockmask_to_uint64(blockmask: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """Bool mask [..., n] -> (int64 [..., ceil(n/64)], n).  Mirrors infllm_v2/blockmask_to_uint64.py:5-42."""
+    _require_cuda(blockmask, "blockmask")
+    if blockmask.dtype != torch.bool:
+        raise TypeError("blockmask must be a bool tensor")
+    blockmask = blockmask.contiguous()
+    last = blockmask.shape[-1]
+    words = (last + 63) // 64
+    rows = int(torch.Size(blockmask.shape[:-1]).numel())
+    result = torch.empty(tuple(blockmask.shape[:-1]) + (words,), dtype=torch.int64,
+                         device=blockmask.device)
+    with torch.cuda.device(blockmask.device):
+        _lib.call("ifv2_blockmask_to_uint64", blockmask.data_ptr(), result.data_ptr(), rows, last,
+                  words, _stream(blockmask.device))
+    return result, last
+
+
+def uint64_to_bool(uint64_array: torch.Tensor, last_dim_size: int) -> torch.Tensor:
+    """Packed int64 rows -> bool [..., last_dim_size].  Mirrors infllm_v2/uint64_to_bool.py:5-38."""
+    _require_cuda(uint64_array, "uint64_array")
+    if uint64_array.dtype != torch.int64:
+        raise TypeError("uint64_array must be an int64 tensor")
+    uint64_array = uint64_array.contiguous()
+    words = uint64_array.shape[-1]
+    rows = int(torch.Size(uint64_array.shape[:-1]).numel())
+    result = torch.empty(tuple(uint64_array.shape[:-1]) + (last_dim_size,), dtype=torch.bool,
+                         device=uint64_array.device)
+    with torch.cuda.device(uint64_array.device):
+        _lib.call("ifv2_uint64_to_bool", uint64_array.data_ptr(), result.data_ptr(), rows,
+                  last_dim_size, words, _stream(uint64_array.device))
+    return result
+
+
+def transpose_blockmask(fwd_mask: torch.Tensor, k_blocks: int) -> torch.Tensor:
+    """Row mask (Hk, T, ceil(k_blocks/64)) -> column mask (Hk, k_blocks, ceil(T/64)) in one kernel:
+    out[h, blk, t//64] bit t%64 = in[h, t, blk//64] bit blk%64.  Equals the reference's
+    uint64_to_bool -> transpose(1, 2) -> blockmask_to_uint64 sequence
+    (infllm_v2/infllmv2_sparse_attention.py:343-350) without the bool tensors or the sync."""
+    _require_cuda(fwd_mask, "fwd_mask")
+    if fwd_mask.dtype != torch.int64 or fwd_mask.dim() != 3:
+        raise TypeError("fwd_mask must be a 3-D int64 tensor")
+    fwd_mask = fwd_mask.contiguous()
+    hk, t, words = fwd_mask.shape
+    if words != (k_blocks + 63) // 64:
+        raise ValueError(f"fwd_mask has {words} words per row, k_blocks={k_blocks} needs {(k_blocks + 63) // 64}")
+    out = torch.empty(hk, k_blocks, (t + 63) // 64, dtype=torch.int64, device=fwd_mask.device)
+    with torch.cuda.device(fwd_mask.device):
+        _lib.call("ifv2_transpose_blockmask", fwd_mask.data_ptr(), out.data_ptr(), hk, t, k_blocks,
+                  _stream(fwd_mask.device))
+    return out
+
+
+def _row_view(x: torch.Tensor):
+    """Accept (H, R, C) tensors whose rows are contiguous and evenly strided (e.g. a column
+    slice of a padded buffer) without copying; anything else is made contiguous.
+    Returns (tensor, elements between consecutive rows)."""
+    h, r, c = x.shape
+    if x.numel() and x.stride(2) == 1 and x.stride(1) >= c and x.stride(0) == x.stride(1) * r:
+        return x, x.stride(1)
+    return x.contiguous(), c
+
+
+def max_pooling_1d(input: torch.Tensor, cache_len: int, local_blocks: int, init_blocks: int,
+                   block_size: int = 64, stride: int = 16) -> torch.Tensor:
+    """input: (num_heads, q_len, k_len) bf16/fp16 stage-1 scores -> (num_heads, q_len,
+    ceil((q_len + cache_len) / block_size)).  Mirrors infllm_v2/max_pooling_1d.py:4-46."""
+    assert input.dtype == torch.float16 or input.dtype == torch.bfloat16
+    _require_cuda(input, "input")
+    if input.dim() != 3:
+        raise ValueError(f"Expected 3D input, got {input.dim()}D")
+    input, row_stride = _row_view(input)
+    pool_stride = block_size // stride
+    kernel_size, padding = pool_stride + 1, 1
+    num_heads, q_len, k_len = input.shape
+    out_len = (q_len + cache_len + block_size - 1) // block_size
+    output = torch.empty(num_heads, q_len, out_len, device=input.device, dtype=input.dtype)
+    with torch.cuda.device(input.device):
+        _lib.call("ifv2_max_pooling_1d", input.data_ptr(), output.data_ptr(),
+                  int(input.dtype == torch.bfloat16), num_heads, q_len, k_len, row_stride, out_len,
+                  cache_len, kernel_size, pool_stride, padding, block_size, local_blocks,
+                  init_blocks, _stream(input.device))
+    return output
+
+
+def max_pooling_1d_varlen(input: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                          cu_seqlens_k: torch.Tensor, cache_lens: torch.Tensor,
+                          max_seqlen_q: int, max_seqlen_k: int, local_blocks: int,
+                          init_blocks: int, block_size: int = 64, stride: int = 16,
+                          max_cache_len: Optional[int] = None) -> torch.Tensor:
+    """Packed-sequence max-pool.  input: (num_heads, total_q, max_k).  Mirrors
+    infllm_v2/max_pooling_1d.py:49-138.  `max_cache_len` (an addition) lets the caller pass
+    max(cache_lens) and so avoid the device->host read the output shape otherwise needs."""
+    assert input.dtype == torch.float16 or input.dtype == torch.bfloat16
+    assert cu_seqlens_q.dtype == torch.int32
+    assert cu_seqlens_k.dtype == torch.int32
+    assert cache_lens.dtype == torch.int32
+    assert input.dim() == 3, f"Expected 3D input, got {input.dim()}D"
+    _require_cuda(input, "input")
+    input, row_stride = _row_view(input)
+    cu_seqlens_q, cu_seqlens_k = cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous()
+    cache_lens = cache_lens.contiguous()
+    pool_stride = block_size // stride
+    kernel_size, padding = pool_stride + 1, 1
+    batch_size = cu_seqlens_q.shape[0] - 1
+    num_heads, total_q, max_k = input.shape
+    assert max_k == max_seqlen_k, f"max_k mismatch: {max_k} vs {max_seqlen_k}"
+    assert cache_lens.shape[0] == batch_size, \
+        f"cache_lens batch size mismatch: {cache_lens.shape[0]} vs {batch_size}"
+    if max_cache_len is None:
+        max_cache_len = int(cache_lens.max().item())
+    out_len = (max_seqlen_q + max_cache_len + block_size - 1) // block_size
+    output = torch.empty(num_heads, total_q, out_len, device=input.device, dtype=input.dtype)
+    with torch.cuda.device(input.device):
+        _lib.call("ifv2_max_pooling_1d_varlen", input.data_ptr(), output.data_ptr(),
+                  cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), cache_lens.data_ptr(),
+                  int(input.dtype == torch.bfloat16), batch_size, num_heads, total_q, max_seqlen_k,
+                  row_stride, out_len, kernel_size, pool_stride, padding, block_size, local_blocks,
+                  init_blocks, _stream(input.device))
+    return output
+
+
+def infllmv2_topk(block_score: torch.Tensor, k: int, cache_len: int = 0,
+                  cu_seqlens_q: Optional[torch.Tensor] = None,
+                  cache_lens: Optional[torch.Tensor] = None, block_size: int = 64) -> torch.Tensor:
+    """Per-query top-k of block scores (Hk, T, n_blocks) -> int32 (Hk, T, k).
+
+    Picks the k entries first in (value descending, index ascending) order -- the ordering of
+    the reference's bitonic top-k, csrc/topk.cuh:17 -- and returns their indices ascending, -1
+    in the unused tail.  Indices greater than the query's own block
+    ((local token + cache_len) // block_size) are replaced by -1.  With cu_seqlens_q the token
+    index is local to its sequence and cache_lens (optional) gives a per-sequence cache length.
+    """
+    assert block_score.dtype == torch.float16 or block_score.dtype == torch.bfloat16
+    _require_cuda(block_score, "block_score")
+    if block_score.dim() != 3:
+        raise ValueError("block_score must be (num_heads, total_q, n_blocks)")
+    block_score, row_stride = _row_view(block_score)
+    hk, t, n = block_score.shape
+    out = torch.empty(hk, t, k, dtype=torch.int32, device=block_score.device)
+    batch = 1
+    cu_ptr = cl_ptr = None
+    if cu_seqlens_q is not None:
+        assert cu_seqlens_q.dtype == torch.int32
+        cu_seqlens_q = cu_seqlens_q.contiguous()
+        batch = cu_seqlens_q.shape[0] - 1
+        cu_ptr = cu_seqlens_q.data_ptr()
+        if cache_lens is not None:
+            assert cache_lens.dtype == torch.int32 and cache_lens.shape[0] == batch
+            cache_lens = cache_lens.contiguous()
+            cl_ptr = cache_lens.data_ptr()
+    elif cache_lens is not None:
+        raise ValueError("cache_lens needs cu_seqlens_q")
+    with torch.cuda.device(block_score.device):
+        _lib.call("ifv2_topk_select", block_score.data_ptr(), out.data_ptr(),
+                  int(block_score.dtype == torch.bfloat16), hk, t, n, row_stride, k, cu_ptr, cl_ptr,
+                  batch, cache_len, block_size, _stream(block_score.device))
+    return out

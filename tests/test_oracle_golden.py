@@ -1,0 +1,132 @@
+"""CPU: the oracle restatements against the committed golden vectors (made by running the
+reference's own Python oracles, tests/golden/make_golden.py)."""
+import os
+
+import numpy as np
+import torch
+
+import oracle
+from oracle.pooling import max_pooling_1d_literal
+from inputs import det_array, det_perm_rows
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def test_bitmask_golden(golden_dir):
+    g = _load(golden_dir, "bitmask.npz")
+    for key in [k for k in g.files if k.endswith("_idx")]:
+        base = key[:-4]
+        got, kb = oracle.topk_to_uint64(g[key], int(g[base + "_maxk"]), 64)
+        assert np.array_equal(got, g[base + "_out"]), key
+    for key in [k for k in g.files if k.endswith("_mask")]:
+        base = key[:-5]
+        got, n = oracle.blockmask_to_uint64(g[key])
+        assert np.array_equal(got, g[base + "_out"]), key
+        assert np.array_equal(oracle.uint64_to_bool(got, n), g[key]), key
+
+
+def test_transpose_matches_roundtrip():
+    rng = np.random.default_rng(3)
+    for hk, t, kb in ((2, 130, 70), (1, 64, 64), (3, 1, 129)):
+        m = rng.random((hk, t, kb)) < 0.3
+        fwd, _ = oracle.blockmask_to_uint64(m)
+        bwd = oracle.transpose_blockmask(fwd, kb)
+        assert bwd.shape == (hk, kb, (t + 63) // 64)
+        assert np.array_equal(oracle.uint64_to_bool(bwd, t), np.swapaxes(m, 1, 2))
+
+
+def test_stage1_golden(golden_dir):
+    g = _load(golden_dir, "stage1.npz")
+    for key in [k for k in g.files if k.endswith("_shape")]:
+        base = key[:-6]
+        lq, lc, seed = (int(x) for x in g[key])
+        q = torch.from_numpy(det_array((lq, 32, 128), seed))
+        k = torch.from_numpy(det_array((lc, 2, 128), seed + 1000))
+        got = oracle.stage1_scores(q, k, [0, lq], [0, lc], lc, bool(g[base + "_causal"]))
+        assert np.abs(got.numpy() - g[base + "_out"]).max() < 2e-6, base
+
+
+def test_stage1_varlen_equals_per_sequence():
+    q = torch.from_numpy(det_array((96 + 40, 32, 128), 7))
+    k = torch.from_numpy(det_array((5 + 1, 2, 128), 8))
+    both = oracle.stage1_scores(q, k, [0, 96, 136], [0, 5, 6], 5, True)
+    a = oracle.stage1_scores(q[:96], k[:5], [0, 96], [0, 5], 5, True)
+    b = oracle.stage1_scores(q[96:], k[5:], [0, 40], [0, 1], 5, True)
+    assert torch.equal(both[:, :96], a) and torch.equal(both[:, 96:], b)
+
+
+def test_stage2_and_decode_golden(golden_dir):
+    g = _load(golden_dir, "stage2.npz")
+    step = int(g["out_row_step"])
+    hq, hk, d = 32, 2, 128
+    for name in ("a", "b", "c"):
+        seed, k_sel = (int(x) for x in g[f"s2_{name}_seed"])
+        cu_q, cu_k = g[f"s2_{name}_cuq"], g[f"s2_{name}_cuk"]
+        sk = int(np.diff(cu_k).max())
+        q = torch.from_numpy(det_array((int(cu_q[-1]), hq, d), seed, 0.25))
+        k = torch.from_numpy(det_array((int(cu_k[-1]), hk, d), seed + 1000, 0.25))
+        v = torch.from_numpy(det_array((int(cu_k[-1]), hk, d), seed + 2000))
+        idx = torch.from_numpy(det_perm_rows(hk * int(cu_q[-1]), (sk + 63) // 64, k_sel, seed + 3000)
+                               ).view(hk, -1, k_sel)
+        for causal in (0, 1):
+            key = f"s2_{name}_{causal}_out"
+            if key not in g.files:
+                continue
+            got, _ = oracle.sparse_attention_fwd(q, k, v, cu_q, cu_k, idx, causal=bool(causal))
+            # the reference turns rows without a visible key into NaN -> 0 as well
+            lens = np.diff(cu_q)
+            per_seq = torch.cat([got[cu_q[b]:cu_q[b + 1]][:] for b in range(len(lens))], 0)
+            # golden rows were subsampled per sequence-concatenated tensor
+            assert np.abs(per_seq[::step].numpy() - g[key]).max() < 5e-6, key
+    bsz, hq, hk, d, cache = (int(x) for x in g["dec_shape"])
+    q = torch.from_numpy(det_array((bsz, hq, 1, d), 301, 0.25))
+    kc = torch.from_numpy(det_array((bsz, hk, cache + 1, d), 302, 0.25))
+    vc = torch.from_numpy(det_array((bsz, hk, cache + 1, d), 303))
+    idx = torch.from_numpy(det_perm_rows(bsz * hk, (cache + 1 + 63) // 64, 3, 304)).view(bsz, hk, 1, 3)
+    got, _ = oracle.kvcache_decode(q.transpose(1, 2), kc.transpose(1, 2).contiguous(),
+                                   vc.transpose(1, 2).contiguous(),
+                                   torch.full((bsz,), cache + 1, dtype=torch.int32), idx)
+    assert np.abs(got.numpy() - g["dec_out"]).max() < 5e-6
+
+
+def test_pool_topk_golden(golden_dir):
+    g = _load(golden_dir, "pool_topk.npz")
+    for name in ("a", "b", "c", "d"):
+        x = torch.from_numpy(g[f"pool_{name}_x"]).to(torch.bfloat16)
+        cache, local, init = (int(v) for v in g[f"pool_{name}_args"])
+        y = oracle.max_pooling_1d(x, cache, local, init).float().numpy()
+        assert np.array_equal(y, g[f"pool_{name}_y"]), name
+    y = torch.from_numpy(g["topk_y"])
+    assert np.array_equal(oracle.topk_select(y, 5, torch.tensor([7, 7, 7])).numpy(), g["topk_exp_all"])
+    assert np.array_equal(oracle.topk_select(y, 5, torch.from_numpy(g["topk_bq_cut"])).numpy(),
+                          g["topk_exp_cut"])
+
+
+def test_pool_varlen_equals_fixed():
+    rng = np.random.default_rng(5)
+    x = torch.from_numpy(rng.random((2, 150, 9)).astype(np.float32)).to(torch.bfloat16)
+    cu_q, cu_k, cl = [0, 100, 150], [0, 9, 15], [0, 64]
+    y = oracle.max_pooling_1d_varlen(x, cu_q, cu_k, cl, 100, 9, 2, 1)
+    a = oracle.max_pooling_1d(x[:, :100], 0, 2, 1)
+    b = oracle.max_pooling_1d(x[:, 100:, :6], 64, 2, 1)
+    assert torch.equal(y[:, :100, :a.shape[2]], a)
+    assert torch.equal(y[:, 100:, :b.shape[2]], b)
+
+
+def test_backward_oracle_matches_finite_difference():
+    torch.manual_seed(0)
+    q = torch.randn(20, 16, 8, dtype=torch.float64) * 0.5
+    k = torch.randn(70, 1, 8, dtype=torch.float64) * 0.5
+    v = torch.randn(70, 1, 8, dtype=torch.float64)
+    idx = torch.tensor([[[0, 1]] * 20], dtype=torch.int32)
+    do = torch.randn(20, 16, 8, dtype=torch.float64)
+
+    def f(q_, k_, v_):
+        from oracle.attention import _seq_attention
+        bm = oracle.expand_topk_mask(idx, 2)
+        return _seq_attention(q_, k_, v_, bm, True, 0.3, 64)[0]
+
+    assert torch.autograd.gradcheck(f, (q.requires_grad_(), k.requires_grad_(), v.requires_grad_()),
+                                    eps=1e-6, atol=1e-5)

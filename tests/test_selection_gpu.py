@@ -1,0 +1,105 @@
+"""GPU: max-pool and top-k kernels, bit-exact against the oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import infllm_v2
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _scores(shape, seed, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    return torch.rand(shape, generator=g).to(dtype)
+
+
+def test_pool_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "pool_topk.npz"))
+    for name in ("a", "b", "c", "d"):
+        x = torch.from_numpy(g[f"pool_{name}_x"]).to(torch.bfloat16)
+        cache, local, init = (int(v) for v in g[f"pool_{name}_args"])
+        y = infllm_v2.max_pooling_1d(x.to(DEV), cache, local, init)
+        assert np.array_equal(y.float().cpu().numpy(), g[f"pool_{name}_y"]), name
+
+
+@pytest.mark.parametrize("hk,ql,kl,cache,local,init,dtype", [
+    (2, 256, 15, 0, 2, 1, torch.bfloat16), (2, 1000, 61, 0, 32, 1, torch.bfloat16),
+    (1, 333, 255, 4096, 2, 1, torch.float16), (2, 64, 2047, 32704, 32, 1, torch.bfloat16),
+    (1, 70, 3, 0, 0, 0, torch.bfloat16), (3, 129, 8, 1, 1, 2, torch.bfloat16),
+])
+def test_pool_random(hk, ql, kl, cache, local, init, dtype):
+    x = _scores((hk, ql, kl), ql + kl, dtype)
+    exp = oracle.max_pooling_1d(x, cache, local, init)
+    got = infllm_v2.max_pooling_1d(x.to(DEV), cache, local, init)
+    assert got.dtype == dtype and torch.equal(got.cpu(), exp)
+
+
+def test_pool_strided_view_fast_path():
+    # a column slice of a padded buffer (what stage 1 returns) takes the vector path, no copy
+    buf = _scores((2, 300, 128), 11)
+    x = buf[:, :, :61]
+    exp = oracle.max_pooling_1d(x.contiguous(), 0, 2, 1)
+    got = infllm_v2.max_pooling_1d(buf.to(DEV)[:, :, :61], 0, 2, 1)
+    assert torch.equal(got.cpu(), exp)
+
+
+def test_pool_varlen():
+    lens_q, lens_c, cl = [100, 37, 200], [5, 1, 11], [0, 64, 130]
+    x = _scores((2, sum(lens_q), 11), 3)
+    cu_q = torch.tensor(np.concatenate([[0], np.cumsum(lens_q)]), dtype=torch.int32)
+    cu_k = torch.tensor(np.concatenate([[0], np.cumsum(lens_c)]), dtype=torch.int32)
+    cache = torch.tensor(cl, dtype=torch.int32)
+    exp = oracle.max_pooling_1d_varlen(x, cu_q, cu_k, cache, 200, 11, 2, 1)
+    got = infllm_v2.max_pooling_1d_varlen(x.to(DEV), cu_q.to(DEV), cu_k.to(DEV), cache.to(DEV),
+                                          200, 11, 2, 1)
+    assert torch.equal(got.cpu(), exp)
+
+
+def test_topk_kats(golden_dir):
+    g = np.load(os.path.join(golden_dir, "pool_topk.npz"))
+    y = torch.from_numpy(g["topk_y"]).to(torch.bfloat16).to(DEV)          # (1, 3, 8)
+    # rows are tokens 0..2; pick cache_len so that every index stays visible
+    got = infllm_v2.infllmv2_topk(y, 5, cache_len=7 * 64)
+    assert np.array_equal(got.cpu().numpy(), g["topk_exp_all"])
+
+
+@pytest.mark.parametrize("hk,t,n,k,dtype", [
+    (2, 300, 512, 64, torch.bfloat16), (2, 130, 2048, 64, torch.bfloat16), (1, 70, 40, 64, torch.bfloat16),
+    (2, 100, 384, 16, torch.float16), (1, 64, 2049, 64, torch.bfloat16), (1, 33, 4100, 64, torch.bfloat16),
+    (2, 200, 100, 1, torch.bfloat16), (1, 50, 257, 64, torch.bfloat16),
+])
+def test_topk_random_with_ties(hk, t, n, k, dtype):
+    g = torch.Generator().manual_seed(n + k)
+    # few distinct values -> many ties, plus forced +inf entries and -inf tails
+    y = (torch.randint(0, 12, (hk, t, n), generator=g).float() / 8).to(dtype)
+    y[:, :, 0] = float("inf")
+    y[:, : t // 2, n // 2:] = float("-inf")
+    y[:, 1::3, 3:9] = float("inf")
+    q_block = (torch.arange(t) + 64 * (n - 1)) // 64          # nothing is in the future
+    exp = oracle.topk_select(y, k, q_block)
+    got = infllm_v2.infllmv2_topk(y.to(DEV), k, cache_len=64 * (n - 1))
+    assert got.dtype == torch.int32 and torch.equal(got.cpu(), exp)
+
+
+def test_topk_future_blocks_and_varlen():
+    lens = [130, 64, 200]
+    t = sum(lens)
+    y = _scores((2, t, 8), 9)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    cl = torch.tensor([0, 128, 64], dtype=torch.int32)
+    qb = torch.cat([(torch.arange(l) + int(c)) // 64 for l, c in zip(lens, cl)])
+    exp = oracle.topk_select(y, 4, qb)
+    got = infllm_v2.infllmv2_topk(y.to(DEV), 4, cu_seqlens_q=cu.to(DEV), cache_lens=cl.to(DEV))
+    assert torch.equal(got.cpu(), exp)
+    # pool -> topk composition on the forced-block pattern: block 0 and the local blocks always win
+    x = _scores((2, 640, 39), 10)
+    pooled = infllm_v2.max_pooling_1d(x.to(DEV), 0, 2, 1)
+    sel = infllm_v2.infllmv2_topk(pooled, 6).cpu()
+    for tok in (0, 63, 64, 300, 639):
+        bq = tok // 64
+        forced = {0} | {b for b in range(max(bq - 2, 0), bq + 1)}
+        assert forced <= set(sel[0, tok].tolist()) and sel[0, tok].max() <= bq

@@ -1,0 +1,69 @@
+"""GPU: stage-1 scorer against the fp32 oracle and the golden vectors.
+Tolerance: max-abs <= 2e-2 on scores that sum to 16 per row (bf16 output)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import infllm_v2
+from helpers import det_tensor, cu
+from inputs import det_array
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+MAX_ABS = 2e-2
+
+
+def _run(q, kc, cu_q, cu_k, max_q, max_k, causal):
+    s = infllm_v2.infllmv2_attn_stage1(q.to(DEV), kc.to(DEV), kc.to(DEV), cu_q.to(DEV), cu_k.to(DEV),
+                                       cu_k.to(DEV), max_q, max_k, causal=causal)
+    infllm_v2.check_device_status()
+    assert s.dtype == torch.bfloat16 and s.shape == (kc.shape[1], q.shape[0], max_k)
+    return s.float().cpu()
+
+
+def test_stage1_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "stage1.npz"))
+    for key in [k for k in g.files if k.endswith("_shape")]:
+        base = key[:-6]
+        lq, lc, seed = (int(x) for x in g[key])
+        q = torch.from_numpy(det_array((lq, 32, 128), seed)).to(torch.bfloat16)
+        k = torch.from_numpy(det_array((lc, 2, 128), seed + 1000)).to(torch.bfloat16)
+        got = _run(q, k, cu([lq]), cu([lc]), lq, lc, bool(g[base + "_causal"]))
+        err = np.abs(got.numpy() - g[base + "_out"]).max()
+        assert err <= MAX_ABS, (base, err)
+        assert not np.isnan(got.numpy()).any()
+
+
+@pytest.mark.parametrize("lens_q,causal", [([4096], True), ([700, 33, 1500], True), ([513], False),
+                                           ([40], True), ([4096 + 64], True)])
+def test_stage1_vs_oracle(lens_q, causal):
+    hq, hk, d = 32, 2, 128
+    seed = sum(lens_q)
+    q = det_tensor((sum(lens_q), hq, d), seed, 0.5)
+    k = det_tensor((sum(lens_q), hk, d), seed + 1, 0.5)
+    kc, cu_c = oracle.compress_keys(k, cu(lens_q))
+    max_k = int(np.diff(cu_c).max())
+    if max_k == 0:
+        pytest.skip("no compressed key")
+    cu_c_t = torch.tensor(cu_c, dtype=torch.int32)
+    got = _run(q, kc, cu(lens_q), cu_c_t, max(lens_q), max_k, causal)
+    ref = oracle.stage1_scores(q, kc, cu(lens_q), cu_c_t, max_k, causal)
+    err = (got - ref).abs().max().item()
+    assert err <= MAX_ABS, err
+    rows = ref.sum(-1)
+    assert ((got.sum(-1) - rows).abs() < 0.25).all()          # visible rows sum to 16, others to 0
+
+
+def test_stage1_query_chunk_bottom_right_alignment():
+    # a query chunk shorter than the span of the keys (context-parallel prefix scoring)
+    hq, hk, d = 32, 2, 128
+    full = 1024
+    q = det_tensor((full, hq, d), 31, 0.5)
+    k = det_tensor((full, hk, d), 32, 0.5)
+    kc, cu_c = oracle.compress_keys(k, cu([full]))
+    whole = _run(q, kc, cu([full]), torch.tensor(cu_c, dtype=torch.int32), full, cu_c[-1], True)
+    tail = _run(q[512:], kc, cu([512]), torch.tensor(cu_c, dtype=torch.int32), 512, cu_c[-1], True)
+    assert (whole[:, 512:] - tail).abs().max() <= 1e-2
