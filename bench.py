@@ -1,0 +1,401 @@
+#!/usr/bin/env python
+"""Benchmark of the InfLLM-V2 sparse-attention prefill path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--seqlen L]
+
+One "step" is one pass of the hot path over one synthetic 131072-token sequence (128 query heads,
+8 KV heads, head_dim 128, bf16): stage-1 scores against the compressed keys -> 64-token max-pool
+-> top-64 blocks (1 init + 32 local forced) -> uint64 block mask -> stage-2 block-sparse attention
+forward.  Rank 0 prints ONE JSON line; metric = prefill tokens/s.
+
+  * `value`   : inputs already resident in HBM, CUDA-event timed, max over ranks.
+  * `e2e`     : the same step through the public Python API starting from pinned HOST buffers,
+                host->device copies of q/k/v/compressed-k and the device->host copy of the
+                output inside the timed region.
+  * `roofline`: the dominant kernel's algorithmic FLOP/s (CUDA events around that kernel inside
+                the timed steps) against the measured bf16 peak of this pool.
+  * `cpu_baseline`: the pure-PyTorch CPU oracle timed on a bounded sample of the same sequence.
+
+With N > 1 GPUs the KV heads are sharded across ranks (8/N per GPU, no collective: every kernel's
+grid has an independent KV-head axis), so the total work is fixed ("strong" scaling).
+`--impl reference` times the CPU oracle (the reference's pure-PyTorch path) instead.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+SEQLEN, HQ, HK, D = 131072, 128, 8, 128
+TOPK, INIT_BLOCKS, LOCAL_BLOCKS, BLOCK = 64, 1, 32, 64
+KERNEL, STRIDE = 32, 16
+METRIC = "sparse-attn prefill tokens/s at 128k"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p.get(k, FALLBACK_PEAKS[k])) for k in FALLBACK_PEAKS}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        os.unlink(self.path)
+        if sm:
+            sm.sort()
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(smax), reasons=sorted(reasons))
+        return out
+
+
+# ------------------------------------------------------------------------------ workload ------
+
+def make_inputs(seqlen, hk_local, device, seed):
+    """q, k, v ~ N(0,1)/sqrt(128) in bf16 for `hk_local` KV heads (16 query heads each), plus the
+    compressed keys (mean over windows of 32 tokens, stride 16)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    s = 1.0 / math.sqrt(D)
+    q = (torch.randn(seqlen, hk_local * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    k = (torch.randn(seqlen, hk_local, D, device=device, generator=g) * s).to(torch.bfloat16)
+    v = (torch.randn(seqlen, hk_local, D, device=device, generator=g) * s).to(torch.bfloat16)
+    kc = k.float().unfold(0, KERNEL, STRIDE).mean(-1).to(torch.bfloat16).contiguous()
+    return q, k, v, kc
+
+
+def visible_compressed(seqlen, n_comp):
+    """Sum over tokens of the number of visible compressed keys (stage-1 algorithmic pairs)."""
+    i = torch.arange(seqlen, dtype=torch.int64)
+    off = n_comp - (seqlen - 15) // 16
+    return int(((i + 1) // 16 - 1 + off).clamp(0, n_comp).sum())
+
+
+def attended_pairs(topk_idx, seqlen):
+    """Sum over (KV head, token, selected block) of the keys of that block the token may see."""
+    hk = topk_idx.shape[0]
+    total = 0
+    i = torch.arange(seqlen, device=topk_idx.device, dtype=torch.int64).view(1, -1, 1)
+    for h in range(hk):
+        blk = topk_idx[h:h + 1].long()
+        vis = (i + 1 - blk * BLOCK).clamp(0, BLOCK)
+        vis = torch.where(blk >= 0, vis, torch.zeros_like(vis))
+        total += int(vis.sum())
+    return total
+
+
+def run_ours(args, rank, world, device):
+    import infllm_v2
+    seqlen = args.seqlen
+    assert HK % world == 0, "the KV heads (8) must divide over the GPUs"
+    hk_local = HK // world
+    q, k, v, kc = make_inputs(seqlen, hk_local, device, seed=rank)
+    n_comp = kc.shape[0]
+    cu_q = torch.tensor([0, seqlen], dtype=torch.int32, device=device)
+    cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=device)
+    names = ["stage1_scores", "max_pooling_1d", "topk_select", "topk_to_uint64", "sparse_attn_fwd"]
+
+    def step(events=None):
+        def mark(j):
+            if events is not None:
+                events[j].record()
+        mark(0)
+        score = infllm_v2.infllmv2_attn_stage1(q, kc, kc, cu_q, cu_c, cu_c, seqlen, n_comp, causal=True)
+        mark(1)
+        pooled = infllm_v2.max_pooling_1d(score, 0, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
+        del score
+        mark(2)
+        idx = infllm_v2.infllmv2_topk(pooled, TOPK)
+        del pooled
+        mark(3)
+        # the mask is built inside infllmv2_attn_varlen_func (as in the reference); marks 3->4
+        # therefore cover topk_to_uint64 + sparse_attn_fwd together, split below by a direct call
+        out = infllm_v2.infllmv2_attn_varlen_func(q, k, v, cu_q, cu_q, seqlen, seqlen, causal=True,
+                                                  topk_idx=idx)
+        mark(4)
+        return out, idx
+
+    for _ in range(args.warmup):
+        step()
+    infllm_v2.check_device_status()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        t0.record()
+        for s in range(args.steps):
+            out, idx = step(ev[s])
+        t1.record()
+        torch.cuda.synchronize()
+    infllm_v2.check_device_status()
+    total_ms = t0.elapsed_time(t1)
+    if world > 1:
+        t = torch.tensor([total_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    per_kernel = [sum(ev[s][j].elapsed_time(ev[s][j + 1]) for s in range(args.steps)) / args.steps
+                  for j in range(4)]
+
+    # split topk_to_uint64 from the stage-2 kernel (both are inside infllmv2_attn_varlen_func)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(3):
+        infllm_v2.topk_to_uint64(idx, seqlen, BLOCK)
+    b.record()
+    torch.cuda.synchronize()
+    pack_ms = a.elapsed_time(b) / 3
+    kernel_ms = dict(zip(names, per_kernel[:3] + [pack_ms, max(per_kernel[3] - pack_ms, 1e-6)]))
+
+    # ---- algorithmic work of this rank's shard
+    pk, pk_kind = peaks()
+    v_pairs = visible_compressed(seqlen, n_comp)
+    flops_s1 = 2.0 * D * (hk_local * 16) * v_pairs
+    pairs = attended_pairs(idx, seqlen)                     # over this rank's KV heads
+    flops_s2 = 4.0 * D * 16 * pairs
+    n_blk = (seqlen + BLOCK - 1) // BLOCK
+    row_stride = max((n_comp + 127) // 128 * 128, 128)
+    bytes_pool = hk_local * seqlen * (n_comp * 2 + n_blk * 2)
+    bytes_topk = hk_local * seqlen * (n_blk * 2 + TOPK * 4)
+    bytes_pack = hk_local * seqlen * (TOPK * 4 + ((n_blk + 63) // 64) * 8)
+    roof = {
+        "stage1_scores": ("tensor", flops_s1 / (kernel_ms["stage1_scores"] * 1e-3) / 1e12,
+                          pk["bf16_tflops_sustained"], "TFLOP/s"),
+        "sparse_attn_fwd": ("tensor", flops_s2 / (kernel_ms["sparse_attn_fwd"] * 1e-3) / 1e12,
+                            pk["bf16_tflops_sustained"], "TFLOP/s"),
+        "max_pooling_1d": ("hbm", bytes_pool / (kernel_ms["max_pooling_1d"] * 1e-3) / 1e9,
+                           pk["hbm_gbs"], "GB/s"),
+        "topk_select": ("hbm", bytes_topk / (kernel_ms["topk_select"] * 1e-3) / 1e9, pk["hbm_gbs"],
+                        "GB/s"),
+        "topk_to_uint64": ("hbm", bytes_pack / (kernel_ms["topk_to_uint64"] * 1e-3) / 1e9,
+                           pk["hbm_gbs"], "GB/s"),
+    }
+    dominant = max(kernel_ms, key=kernel_ms.get)
+    bound, ach, peak, unit = roof[dominant]
+    roofline = {"kernel": dominant, "bound": bound, "achieved": round(ach, 2), "peak": peak,
+                "unit": unit, "frac": round(ach / peak, 4), "traffic": None, "peak_source": pk_kind,
+                "ms_per_launch": round(kernel_ms[dominant], 3)}
+    kernels = {n: {"ms": round(kernel_ms[n], 3), "bound": roof[n][0], "achieved": round(roof[n][1], 2),
+                   "unit": roof[n][3], "frac": round(roof[n][1] / roof[n][2], 4)} for n in names}
+
+    # ---- end to end from pinned host memory through the public API
+    e2e = run_e2e(args, step, q, k, v, kc, seqlen, world, device)
+
+    result = {
+        "metric": METRIC, "value": round(seqlen / (ms_per_step * 1e-3), 1), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"prefill {seqlen} tokens, 128q/8kv heads, d128: stage1 + max-pool + "
+                               f"top-64 (1 init + 32 local) + uint64 mask + stage-2 fwd",
+                   "seq_len": seqlen, "global_batch": 1, "kv_heads_per_gpu": hk_local,
+                   "parallelism": f"kv-head shards x{world}" if world > 1 else "single GPU",
+                   "l2": "inputs (q alone is %.1f GB per GPU) exceed the 126 MB L2" % (q.numel() * 2 / 1e9)},
+        "clocks": clocks.summary(),
+        "e2e": e2e,
+        "gpu_launches": 5 * args.steps,
+        "roofline": roofline,
+        "kernels": kernels,
+        "flops_per_step": {"stage1_algorithmic": flops_s1 * world, "stage2_fwd_algorithmic": flops_s2 * world},
+    }
+    return result
+
+
+def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
+    """Same step, but every step starts from pinned host buffers and ends with the output on the
+    host.  The device tensors the step closure captured are overwritten in place."""
+    host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v, kc)]
+    for h, t in zip(host, (q, k, v, kc)):
+        h.copy_(t)
+    out_host = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    torch.cuda.synchronize()
+    steps = max(1, min(args.steps, 3))
+
+    def one():
+        for h, t in zip(host, (q, k, v, kc)):
+            t.copy_(h, non_blocking=True)
+        out, _ = step()
+        out_host.copy_(out, non_blocking=True)
+
+    one()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        one()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    h2d = sum(h.numel() * h.element_size() for h in host)
+    d2h = out_host.numel() * out_host.element_size()
+    return {"value": round(seqlen / (ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 3),
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+
+# ------------------------------------------------------------------------------ CPU oracle ----
+
+def cpu_sample(seqlen, sample_tokens, threads):
+    """The reference's pure-PyTorch path (fp32, dense attention under the block mask) for the LAST
+    `sample_tokens` query tokens of one `seqlen`-token sequence, all 128 query heads.  Returns
+    seconds.  Keys are scored as a prefix (bottom-right alignment), so the work per token equals
+    that of the full job's most expensive tokens."""
+    import oracle
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    s = 1.0 / math.sqrt(D)
+    k = (torch.randn(seqlen, HK, D, generator=g) * s).to(torch.bfloat16)
+    v = (torch.randn(seqlen, HK, D, generator=g) * s).to(torch.bfloat16)
+    q = (torch.randn(sample_tokens, HQ, D, generator=g) * s).to(torch.bfloat16)
+    cu_k = [0, seqlen]
+    kc, cu_c = oracle.compress_keys(k, cu_k, KERNEL, STRIDE)       # input preparation, not timed
+    n_comp = cu_c[-1]
+    t0 = time.perf_counter()
+    score = oracle.stage1_scores(q, kc, [0, sample_tokens], cu_c, n_comp, True).to(torch.bfloat16)
+    pooled = oracle.max_pooling_1d(score, seqlen - sample_tokens, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
+    qb = (torch.arange(sample_tokens) + seqlen - sample_tokens) // BLOCK
+    idx = oracle.topk_select(pooled, TOPK, qb)
+    _mask = oracle.topk_to_uint64(idx.numpy(), seqlen, BLOCK)
+    out, _ = oracle.sparse_attention_fwd(q, k, v, [0, sample_tokens], cu_k, idx, causal=True)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    threads = os.cpu_count() or 1
+    sample = args.cpu_tokens
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(args.seqlen, sample, threads)
+    times = [cpu_sample(args.seqlen, sample, threads) for _ in range(args.steps)]
+    sec = sum(times) / len(times)
+    val = sample / sec
+    desc = (f"last {sample} query tokens of one {args.seqlen}-token sequence, 128q/8kv heads, fp32 "
+            f"pure-PyTorch path (stage1 + pool + top-64 + mask + dense-with-mask attention)")
+    return {
+        "impl": "reference", "metric": METRIC, "value": round(val, 2), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"prefill {args.seqlen} tokens, 128q/8kv heads, d128 (CPU sample)",
+                   "seq_len": args.seqlen, "global_batch": 1},
+        "cpu_baseline": {"value": round(val, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": desc},
+        "e2e": {"value": round(val, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seqlen", type=int, default=SEQLEN)
+    ap.add_argument("--cpu-tokens", type=int, default=16,
+                    help="query tokens in the CPU sample (cpu_baseline / --impl reference)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        res = run_reference(args, rank, world)
+        if res is not None:
+            print(json.dumps(res), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path "
+                         "(use --impl reference for the CPU oracle)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    res = run_ours(args, rank, world, device)
+    if rank == 0:
+        if not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            sec = cpu_sample(args.seqlen, args.cpu_tokens, threads)
+            res["cpu_baseline"] = {
+                "value": round(args.cpu_tokens / sec, 2), "unit": "tokens/s", "cores": threads,
+                "kind": "port",
+                "sample": f"last {args.cpu_tokens} query tokens of the {args.seqlen}-token sequence, all "
+                          f"128 query heads, fp32 pure-PyTorch oracle, {sec:.1f} s"}
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -49,7 +49,9 @@ struct Smem {
   uint8_t k[2][2][kKVHalfBytes];      // [stage][d half]
   uint8_t v[2][2][kKVHalfBytes];      // [stage][d half]
   unsigned long long umask[kMaxMaskWords];
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done;
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2];
+  uint64_t o_done;    // one arrival per P.V product: phase i completes with block i
+  uint64_t o_final;   // one arrival after the last P.V product (an unambiguous wait for the epilogue)
   uint32_t tmem_base;
   int n_blocks;
   int abort_flag;
@@ -124,6 +126,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.p_ready[s], 128);
     }
     mbar_init(&sm.o_done, 1);
+    mbar_init(&sm.o_final, 1);
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -223,6 +226,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                   (i > 0) || (kk > 0));
         umma_commit(&sm.v_empty[s]);
         umma_commit(&sm.o_done);
+        if (i + 1 == n_blocks) umma_commit(&sm.o_final);
       }
     }
   } else {
@@ -308,8 +312,9 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 
     // ---- epilogue: O / l -> bf16, lse
     if (ok && n_blocks > 0) {
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag,
-                                             p.status, 33));
+      // (o_done cannot be used here: two products may still be in flight, and a parity wait
+      //  cannot tell "two phases behind" from "done")
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.o_final, 0, abort_flag, p.status, 33));
       tc_fence_after();
     }
     if (ok) {

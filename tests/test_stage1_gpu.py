@@ -1,5 +1,7 @@
 """GPU: stage-1 scorer against the fp32 oracle and the golden vectors.
-Tolerance: max-abs <= 2e-2 on scores that sum to 16 per row (bf16 output)."""
+Tolerance: |got - ref| <= 2e-2, or within 2^-7 relative where a score is large (the output is
+bf16 and a row's 16 units of probability can sit on a handful of keys: one bf16 step at 8..16
+is 2^-4, already above 2e-2)."""
 import os
 
 import numpy as np
@@ -13,7 +15,14 @@ from inputs import det_array
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-MAX_ABS = 2e-2
+MAX_ABS, REL = 2e-2, 2.0 ** -7
+
+
+def _within(got, ref):
+    got, ref = torch.as_tensor(got).float(), torch.as_tensor(ref).float()
+    diff = (got - ref).abs()
+    ok = (diff <= MAX_ABS) | (diff <= REL * ref.abs())
+    return bool(ok.all()), diff.max().item()
 
 
 def _run(q, kc, cu_q, cu_k, max_q, max_k, causal):
@@ -32,8 +41,8 @@ def test_stage1_golden(golden_dir):
         q = torch.from_numpy(det_array((lq, 32, 128), seed)).to(torch.bfloat16)
         k = torch.from_numpy(det_array((lc, 2, 128), seed + 1000)).to(torch.bfloat16)
         got = _run(q, k, cu([lq]), cu([lc]), lq, lc, bool(g[base + "_causal"]))
-        err = np.abs(got.numpy() - g[base + "_out"]).max()
-        assert err <= MAX_ABS, (base, err)
+        ok, err = _within(got, g[base + "_out"])
+        assert ok, (base, err)
         assert not np.isnan(got.numpy()).any()
 
 
@@ -51,8 +60,8 @@ def test_stage1_vs_oracle(lens_q, causal):
     cu_c_t = torch.tensor(cu_c, dtype=torch.int32)
     got = _run(q, kc, cu(lens_q), cu_c_t, max(lens_q), max_k, causal)
     ref = oracle.stage1_scores(q, kc, cu(lens_q), cu_c_t, max_k, causal)
-    err = (got - ref).abs().max().item()
-    assert err <= MAX_ABS, err
+    ok, err = _within(got, ref)
+    assert ok, err
     rows = ref.sum(-1)
     assert ((got.sum(-1) - rows).abs() < 0.25).all()          # visible rows sum to 16, others to 0
 
