@@ -124,23 +124,27 @@ int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out,
                          int max_seqlen_k, float softmax_scale, int causal, int32_t* status,
                          void* stream);
 
-/* Bytes of scratch ifv2_sparse_attn_bwd needs (fp32 dQ accumulator + D rows). */
+/* Bytes of scratch ifv2_sparse_attn_bwd needs (D = rowsum(dO * O), one fp32 per query row). */
 int64_t ifv2_sparse_attn_bwd_workspace_bytes(int64_t total_q, int heads_q, int head_dim);
 
-/* Backward of the above: dq (total_q, heads_q, 128), dk/dv (total_k, heads_k, 128) bf16.
- * bwd_mask: (heads_k, ceil(max_seqlen_k/64), ceil(total_q/64)) words from
- * ifv2_transpose_blockmask, or null for dense.  workspace: caller-allocated scratch of at
- * least ifv2_sparse_attn_bwd_workspace_bytes bytes (contents on entry are ignored).
+/* Backward of the above: dq (total_q, heads_q, 128), dk/dv (total_k, heads_k, 128) bf16; every
+ * element of dq, dk and dv is written.  Needs BOTH mask layouts or neither (dense):
+ * fwd_mask (heads_k, total_q, fwd_mask_words) as given to the forward, and bwd_mask
+ * (heads_k, ceil(max_seqlen_k/64), bwd_mask_words = ceil(total_q/64)) from
+ * ifv2_transpose_blockmask.  workspace: caller-allocated, 16-byte aligned scratch of at least
+ * ifv2_sparse_attn_bwd_workspace_bytes bytes (contents on entry are ignored).  Deterministic:
+ * no atomics are used.
  * Replaces C.varlen_bwd: csrc/entry.cu:209-214 -> mha_varlen_bwd,
- * csrc/flash_attn/flash_api.cpp:1278-1547. */
+ * csrc/flash_attn/flash_api.cpp:1278-1547 (+ the transposes, the Python loop and the
+ * synchronisations of infllm_v2/infllmv2_sparse_attention.py:174-263, 343-350). */
 int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
                          const void* out, const float* lse, void* dq, void* dk, void* dv,
-                         const int64_t* bwd_mask, int64_t bwd_mask_words,
-                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
-                         int64_t total_q, int64_t total_k, int heads_q, int heads_k,
-                         int head_dim, int max_seqlen_q, int max_seqlen_k, float softmax_scale,
-                         int causal, void* workspace, int64_t workspace_bytes, int32_t* status,
-                         void* stream);
+                         const int64_t* fwd_mask, int fwd_mask_words, const int64_t* bwd_mask,
+                         int64_t bwd_mask_words, const int32_t* cu_seqlens_q,
+                         const int32_t* cu_seqlens_k, int batch, int64_t total_q, int64_t total_k,
+                         int heads_q, int heads_k, int head_dim, int max_seqlen_q,
+                         int max_seqlen_k, float softmax_scale, int causal, void* workspace,
+                         int64_t workspace_bytes, int32_t* status, void* stream);
 
 /* Bytes of scratch ifv2_decode needs for its split partials. */
 int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_dim, int max_blocks);

@@ -36,7 +36,7 @@ SIGNATURES = {
     "ifv2_sparse_attn_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int,
                              c_int, c_int, c_float, c_int, c_void_p, c_void_p],
-    "ifv2_sparse_attn_bwd": [c_void_p] * 9 + [c_void_p, c_int64, c_void_p, c_void_p, c_int,
+    "ifv2_sparse_attn_bwd": [c_void_p] * 9 + [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int,
                                               c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                                               c_float, c_int, c_void_p, c_int64, c_void_p,
                                               c_void_p],

@@ -142,7 +142,7 @@ def _fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softma
 
 
 def _bwd(dout, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-         softmax_scale, causal, bwd_mask):
+         softmax_scale, causal, fwd_mask, bwd_mask):
     total_q, nheads, d = q.shape
     nheads_k = k.shape[1]
     batch = cu_seqlens_q.numel() - 1
@@ -153,6 +153,8 @@ def _bwd(dout, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_
     with torch.cuda.device(q.device):
         _lib.call("ifv2_sparse_attn_bwd", dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                   out.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                  fwd_mask.data_ptr() if fwd_mask is not None else None,
+                  fwd_mask.shape[-1] if fwd_mask is not None else 0,
                   bwd_mask.data_ptr() if bwd_mask is not None else None,
                   bwd_mask.shape[-1] if bwd_mask is not None else 0,
                   cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), batch, total_q, k.shape[0],
@@ -202,13 +204,14 @@ def _infllmv2_attn_varlen_backward(
     fwd_blockmask: torch.Tensor,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     dout = _dense(maybe_contiguous(dout))
-    bwd_mask = None
+    fwd_mask = bwd_mask = None
     if fwd_blockmask.numel() > 0:
         k_blocks = (max_seqlen_k + BLOCK_N - 1) // BLOCK_N
+        fwd_mask = fwd_blockmask
         bwd_mask = transpose_blockmask(fwd_blockmask, k_blocks)
     return _bwd(dout, q, k, v, out, softmax_lse, cu_seqlens_q.contiguous(),
                 cu_seqlens_k.contiguous(), max_seqlen_q, max_seqlen_k, softmax_scale, causal,
-                bwd_mask)
+                fwd_mask, bwd_mask)
 
 
 @_infllmv2_attn_varlen_backward.register_fake

@@ -2,15 +2,6 @@
 #include "common.cuh"
 using namespace ifv2;
 
-extern "C" int64_t ifv2_sparse_attn_bwd_workspace_bytes(int64_t total_q, int heads_q, int head_dim) {
-  return total_q * heads_q * (int64_t)(head_dim + 1) * 4;
-}
-extern "C" int ifv2_sparse_attn_bwd(const void*, const void*, const void*, const void*, const void*,
-                                    const float*, void*, void*, void*, const int64_t*, int64_t,
-                                    const int32_t*, const int32_t*, int, int64_t, int64_t, int, int,
-                                    int, int, int, float, int, void*, int64_t, int32_t*, void*) {
-  return set_error(IFV2_ERR_UNSUPPORTED, "sparse_attn_bwd: not built yet");
-}
 extern "C" int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_dim, int max_blocks) {
   return (int64_t)batch * heads_q * max_blocks * (head_dim + 2) * 4;
 }

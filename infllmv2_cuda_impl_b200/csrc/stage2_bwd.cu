@@ -1,0 +1,778 @@
+// Stage-2 backward on tcgen05 tensor cores, without atomics and without an fp32 dQ accumulator
+// in HBM.  Three launches:
+//   1. dot_do_o      D[row] = sum_c dO[row,c] * O[row,c]                       (HBM-bound)
+//   2. dq kernel     one CTA per 128-row query tile (8 tokens x 16 heads), walking the union of
+//                    its tokens' selected blocks exactly like the forward:
+//                      S = Q.K^T, dP = dO.V^T, dS = exp2(S*c - lse) * (dP - D), dQ += dS.K
+//                    dQ stays in TMEM for the whole walk and is written once, as bf16.
+//   3. dkv kernel    one CTA per (64-key block, sequence, KV head), walking the token octets
+//                    that selected the block (from the transposed bitmask):
+//                      S, dP as above, P and dS go to swizzled shared memory, then
+//                      dV^T += dO^T.P, dK^T += Q^T.dS with both operands MN-major.
+//                    dK / dV of a block are written once; the sum over the 16 query heads of
+//                    the group is implicit because those heads are rows of the same tile.
+// Recomputing S and dP in both kernels costs 7 tile products instead of 5, but removes the
+// scatter of 16x128 fp32 tiles per (token, block) pair that bounds an atomics-based design.
+#include "tc05.cuh"
+
+namespace ifv2 {
+namespace {
+
+using namespace tc;
+
+constexpr int kTokPerTile = 8;
+constexpr int kThreads = 192;
+constexpr int kMaxMaskWords = 128;
+constexpr uint32_t kTileHalfBytes = 128 * 128;   // 128 rows x 64 bf16
+constexpr uint32_t kKVHalfBytes = 64 * 128;      // 64 keys x 64 bf16
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdParams {
+  const float* lse;           // (heads_k, total_q * 16)
+  float* dvec;                // (heads_k, total_q * 16)   D = rowsum(dO * O)
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  const unsigned long long* fwd_mask;   // (heads_k, total_q, fwd_words) or null
+  int fwd_words;
+  const unsigned long long* bwd_mask;   // (heads_k, k_blocks, bwd_words) or null
+  int64_t bwd_words;
+  int k_blocks;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int64_t total_q;
+  int heads_q, heads_k;
+  float scale, scale_log2;
+  int causal;
+  int32_t* status;
+};
+
+// ------------------------------------------------------------------ 1. D = rowsum(dO * O) ----
+__global__ void __launch_bounds__(256)
+dot_do_o_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                float* __restrict__ dvec, int64_t total_q, int heads_q) {
+  const int lane = threadIdx.x & 31, sub = lane >> 4, l16 = lane & 15;
+  const int64_t rows = total_q * heads_q;
+  const int64_t warp0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * 256) >> 5;
+  for (int64_t r2 = warp0; r2 * 2 < rows; r2 += nwarps) {
+    const int64_t row = r2 * 2 + sub;
+    float acc = 0.f;
+    if (row < rows) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(dout + row * kHeadDim) + l16);
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(out + row * kHeadDim) + l16);
+      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(pa[j]), y = __bfloat1622float2(pb[j]);
+        acc = fmaf(x.x, y.x, acc);
+        acc = fmaf(x.y, y.y, acc);
+      }
+    }
+#pragma unroll
+    for (int d = 8; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, d);
+    if (l16 == 0 && row < rows) {
+      const int64_t tok = row / heads_q;
+      const int hq = (int)(row - tok * heads_q);
+      dvec[(int64_t)(hq / kGroup) * total_q * kGroup + tok * kGroup + (hq % kGroup)] = acc;
+    }
+  }
+}
+
+// Highest-to-lowest walk over the set bits of a tile's union mask.
+struct BlockWalk {
+  const unsigned long long* words;
+  int w;
+  unsigned long long cur;
+  __device__ BlockWalk(const unsigned long long* u, int nwords) : words(u), w(nwords), cur(0) {}
+  __device__ int next() {
+    while (cur == 0ull) {
+      if (w == 0) return -1;
+      cur = words[--w];
+    }
+    const int b = 63 - __clzll(cur);
+    cur &= ~(1ull << b);
+    return w * 64 + b;
+  }
+};
+
+// ------------------------------------------------------------------ 2. dQ kernel -------------
+struct DqSmem {
+  uint8_t q[2][kTileHalfBytes];
+  uint8_t dout[2][kTileHalfBytes];
+  uint8_t k[3][2][kKVHalfBytes];      // [stage][d half]; K lives until dS.K of its block is done,
+  uint8_t v[2][2][kKVHalfBytes];      // so it needs one more stage than V to be prefetched in time
+  unsigned long long umask[kMaxMaskWords];
+  uint64_t qdo_full, k_full[3], k_empty[3], v_full[2], v_empty[2], sdp_full[2], ds_ready[2];
+  uint64_t dq_final;
+  uint32_t tmem_base;
+  int n_blocks;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
+                          const __grid_constant__ CUtensorMap map_do,
+                          const __grid_constant__ CUtensorMap map_k,
+                          const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  DqSmem& sm = *reinterpret_cast<DqSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                          ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.y, h = blockIdx.z;
+  const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
+  const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTokPerTile;
+  if (tok0 >= lq) return;
+  if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
+  const int ntok = min(kTokPerTile, lq - tok0);
+  const int shift = lk - lq;
+  const int nblk_k = (lk + kBlockN - 1) / kBlockN;
+  const int words =
+      (p.fwd_mask != nullptr) ? p.fwd_words : min(kMaxMaskWords, (nblk_k + 63) / 64);
+  {
+    int last_blk = nblk_k - 1;
+    if (p.causal) last_blk = min(last_blk, (tok0 + ntok - 1 + shift) >= 0
+                                               ? (tok0 + ntok - 1 + shift) / kBlockN : -1);
+    for (int w = threadIdx.x; w < words; w += kThreads) {
+      unsigned long long u = 0ull;
+      if (p.fwd_mask != nullptr) {
+        const unsigned long long* row =
+            p.fwd_mask + ((int64_t)h * p.total_q + q0 + tok0) * p.fwd_words + w;
+        for (int t = 0; t < ntok; ++t) u |= __ldg(row + (int64_t)t * p.fwd_words);
+      } else {
+        u = ~0ull;
+      }
+      const int first = w * 64;
+      if (last_blk < first) u = 0ull;
+      else if (last_blk - first < 63) u &= (2ull << (last_blk - first)) - 1ull;
+      sm.umask[w] = u;
+    }
+  }
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.qdo_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&sm.k_full[s], 1);
+      mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sm.v_full[s], 1);
+      mbar_init(&sm.v_empty[s], 1);
+      mbar_init(&sm.sdp_full[s], 1);
+      mbar_init(&sm.ds_ready[s], 128);
+    }
+    mbar_init(&sm.dq_final, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int w = 0; w < words; ++w) n += __popcll(sm.umask[w]);
+    sm.n_blocks = n;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const int n_blocks = sm.n_blocks;
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_dq = tmem + 256;             // [0,128) buffer 0: S | dP, [128,256) buffer 1
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0 && n_blocks > 0) {
+      mbar_expect_tx(&sm.qdo_full, 4 * kTileHalfBytes);
+      tma_load_3d(sm.q[0], &map_q, &sm.qdo_full, 0, h * kGroup, q0 + tok0);
+      tma_load_3d(sm.q[1], &map_q, &sm.qdo_full, 64, h * kGroup, q0 + tok0);
+      tma_load_3d(sm.dout[0], &map_do, &sm.qdo_full, 0, h * kGroup, q0 + tok0);
+      tma_load_3d(sm.dout[1], &map_do, &sm.qdo_full, 64, h * kGroup, q0 + tok0);
+      BlockWalk walk(sm.umask, words);
+      int issued = 0;
+      for (int i = 0; i < n_blocks; ++i) {
+        const int blk = walk.next();
+        const int s = i & 1, sk = i % 3, key = k0 + blk * kBlockN;
+        const uint32_t par = (uint32_t)((i >> 1) & 1), park = (uint32_t)((i / 3) & 1);
+        if (i >= 3 && !mbar_wait(&sm.k_empty[sk], park ^ 1u, abort_flag, p.status, 71)) break;
+        mbar_expect_tx(&sm.k_full[sk], 2 * kKVHalfBytes);
+        tma_load_3d(sm.k[sk][0], &map_k, &sm.k_full[sk], 0, h, key);
+        tma_load_3d(sm.k[sk][1], &map_k, &sm.k_full[sk], 64, h, key);
+        if (i >= 2 && !mbar_wait(&sm.v_empty[s], par ^ 1u, abort_flag, p.status, 72)) {
+          issued = i + 1;
+          break;
+        }
+        mbar_expect_tx(&sm.v_full[s], 2 * kKVHalfBytes);
+        tma_load_3d(sm.v[s][0], &map_v, &sm.v_full[s], 0, h, key);
+        tma_load_3d(sm.v[s][1], &map_v, &sm.v_full[s], 64, h, key);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait_drain(&sm.qdo_full, 0);
+        for (int j = max(0, issued - 2); j < issued; ++j) {
+          mbar_wait_drain(&sm.k_full[j % 3], (uint32_t)((j / 3) & 1));
+          mbar_wait_drain(&sm.v_full[j & 1], (uint32_t)((j >> 1) & 1));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_blocks > 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, true);
+      const uint32_t q_addr = smem_u32(sm.q[0]), do_addr = smem_u32(sm.dout[0]);
+      bool ok = mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 73);
+      auto issue_sdp = [&](int j) -> bool {
+        const int s = j & 1, sk = j % 3;
+        const uint32_t par = (uint32_t)((j >> 1) & 1);
+        if (!mbar_wait(&sm.k_full[sk], (uint32_t)((j / 3) & 1), abort_flag, p.status, 74)) return false;
+        if (!mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sm.k[sk][0]), v_addr = smem_u32(sm.v[s][0]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
+          umma_ss(tmem + s * 128, umma_desc_sw128(q_addr + aoff, 16, 1024),
+                  umma_desc_sw128(k_addr + boff, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
+          umma_ss(tmem + s * 128 + 64, umma_desc_sw128(do_addr + aoff, 16, 1024),
+                  umma_desc_sw128(v_addr + boff, 16, 1024), idesc_s, kk > 0);
+        }
+        umma_commit(&sm.v_empty[s]);
+        umma_commit(&sm.sdp_full[s]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int i = 0; i < n_blocks && ok; ++i) {
+        const int s = i & 1;
+        if (i + 1 < n_blocks) ok = issue_sdp(i + 1);
+        if (!ok) break;
+        ok = mbar_wait(&sm.ds_ready[s], (uint32_t)((i >> 1) & 1), abort_flag, p.status, 76);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sm.k[i % 3][0]);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem_dq, tmem + s * 128 + kk * 8,
+                  umma_desc_sw128(k_addr + kk * 2048, kKVHalfBytes, 1024), idesc_dq,
+                  (i > 0) || (kk > 0));
+        umma_commit(&sm.k_empty[i % 3]);
+        if (i + 1 == n_blocks) umma_commit(&sm.dq_final);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int tl = r >> 4, g = r & 15;
+    const int tok = tok0 + tl;
+    const bool valid = tl < ntok;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const unsigned long long* mrow =
+        (p.fwd_mask != nullptr && valid)
+            ? p.fwd_mask + ((int64_t)h * p.total_q + q0 + tok) * p.fwd_words : nullptr;
+    const int row_limit = valid ? min(lk, p.causal ? tok + shift + 1 : lk) : 0;
+    const int64_t stat_idx = (int64_t)h * p.total_q * kGroup + (int64_t)(q0 + tok) * kGroup + g;
+    const float neg_lse = valid ? -p.lse[stat_idx] * kLog2e : -INFINITY;   // +inf lse -> P = 0
+    const float dsum = valid ? p.dvec[stat_idx] : 0.f;
+    bool ok = true;
+    BlockWalk walk(sm.umask, words);
+    for (int i = 0; i < n_blocks; ++i) {
+      const int blk = walk.next();
+      const int s = i & 1;
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.sdp_full[s], (uint32_t)((i >> 1) & 1),
+                                             abort_flag, p.status, 77));
+      if (!ok) break;
+      tc_fence_after();
+      bool selected = valid;
+      if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
+      const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
+      uint32_t packed[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32], dpv[32];
+        tmem_ld32(tmem + lane_off + s * 128 + half * 32, sv);
+        tmem_ld32(tmem + lane_off + s * 128 + 64 + half * 32, dpv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float pr = exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, neg_lse));
+            const float d = pr * (__uint_as_float(dpv[c + e]) - dsum);
+            ds[e] = (half * 32 + c + e < lim) ? d : 0.f;
+          }
+          packed[half * 16 + (c >> 1)] = pack_bf16(ds[0], ds[1]);
+        }
+      }
+      tmem_st32(tmem + lane_off + s * 128, packed);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.ds_ready[s]);
+    }
+    if (ok && n_blocks > 0) {
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dq_final, 0, abort_flag, p.status, 78));
+      tc_fence_after();
+    }
+    if (ok) {
+      __nv_bfloat16* orow = p.dq + ((int64_t)(q0 + tok) * p.heads_q + h * kGroup + g) * kHeadDim;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t o[32];
+        if (n_blocks > 0) {
+          tmem_ld32(tmem_dq + lane_off + c, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v4;
+            v4.x = pack_bf16(__uint_as_float(o[8 * j + 0]) * p.scale, __uint_as_float(o[8 * j + 1]) * p.scale);
+            v4.y = pack_bf16(__uint_as_float(o[8 * j + 2]) * p.scale, __uint_as_float(o[8 * j + 3]) * p.scale);
+            v4.z = pack_bf16(__uint_as_float(o[8 * j + 4]) * p.scale, __uint_as_float(o[8 * j + 5]) * p.scale);
+            v4.w = pack_bf16(__uint_as_float(o[8 * j + 6]) * p.scale, __uint_as_float(o[8 * j + 7]) * p.scale);
+            dst[j] = v4;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------ 3. dK / dV kernel --------
+struct DkvSmem {
+  uint8_t k[2][kKVHalfBytes];          // resident K block, [d half]
+  uint8_t v[2][kKVHalfBytes];
+  uint8_t q[2][2][kTileHalfBytes];     // [stage][d half]
+  uint8_t dout[2][2][kTileHalfBytes];
+  uint8_t pmat[kTileHalfBytes];        // P  (128 rows x 64 keys bf16, 128-byte swizzle)
+  uint8_t dsmat[kTileHalfBytes];       // dS
+  uint64_t kv_full, qdo_full[2], qdo_empty[2], sdp_full[2], sdp_empty[2], pds_ready, pds_empty;
+  uint64_t acc_final;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Walk over the token octets [8m, 8m+8) of a sequence in which at least one token selected the
+// key block (bits of the transposed mask row, indexed by GLOBAL token), lowest octet first.
+struct OctetWalk {
+  const unsigned long long* row;   // null = dense
+  int64_t words;
+  int q0, lq, m, m_end;
+  __device__ OctetWalk(const unsigned long long* r, int64_t w, int q0_, int lq_, int m_lo)
+      : row(r), words(w), q0(q0_), lq(lq_), m(m_lo), m_end((lq_ + 7) / 8) {}
+  __device__ uint32_t bits_at(int mm) const {      // selection bits of the octet's 8 tokens
+    const int ntok = min(8, lq - 8 * mm);
+    const uint32_t vmask = (1u << ntok) - 1u;
+    if (row == nullptr) return vmask;
+    const int64_t t = (int64_t)q0 + 8 * mm;
+    const int64_t w = t >> 6;
+    const int sh = (int)(t & 63);
+    unsigned long long lo = __ldg(row + w) >> sh;
+    if (sh > 56 && w + 1 < words) lo |= __ldg(row + w + 1) << (64 - sh);
+    return (uint32_t)lo & vmask;
+  }
+  // returns the octet index and its bits, or -1 when exhausted
+  __device__ int next(uint32_t& bits) {
+    while (m < m_end) {
+      if (row != nullptr) {
+        const int64_t t = (int64_t)q0 + 8 * m;
+        if ((t & 63) == 0 && m + 8 <= m_end && __ldg(row + (t >> 6)) == 0ull) {   // empty word
+          m += 8;
+          continue;
+        }
+      }
+      bits = bits_at(m);
+      const int cur = m++;
+      if (bits) return cur;
+    }
+    return -1;
+  }
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
+                           const __grid_constant__ CUtensorMap map_do,
+                           const __grid_constant__ CUtensorMap map_k,
+                           const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  DkvSmem& sm = *reinterpret_cast<DkvSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                            ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x, b = blockIdx.y, h = blockIdx.z;   // block 0 (selected by all) first
+  const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
+  if (n * kBlockN >= lk) return;
+  if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
+  const int shift = lk - lq;
+  const int nkeys = min(kBlockN, lk - n * kBlockN);
+  // first token that can see key 64n (causal), as an octet index
+  const int m_lo = p.causal ? max(0, n * kBlockN - shift) / kTokPerTile : 0;
+  const unsigned long long* mask_row =
+      (p.bwd_mask != nullptr && n < p.k_blocks)
+          ? p.bwd_mask + ((int64_t)h * p.k_blocks + n) * p.bwd_words : nullptr;
+  const bool never_selected = (p.bwd_mask != nullptr && n >= p.k_blocks);
+
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sm.qdo_full[s], 1);
+      mbar_init(&sm.qdo_empty[s], 1);
+      mbar_init(&sm.sdp_full[s], 1);
+      mbar_init(&sm.sdp_empty[s], 128);
+    }
+    mbar_init(&sm.pds_ready, 128);
+    mbar_init(&sm.pds_empty, 1);
+    mbar_init(&sm.acc_final, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_dv = tmem + 256, tmem_dk = tmem + 320;   // [128 d lanes x 64 key columns]
+  volatile int* abort_flag = &sm.abort_flag;
+
+  // every role walks the same octet list; the count is not known up front, so the walk itself
+  // tells each role when to stop and the MMA role signals acc_final after its last step
+  if (warp == 0) {
+    if (lane == 0 && !never_selected) {
+      mbar_expect_tx(&sm.kv_full, 4 * kKVHalfBytes);
+      tma_load_3d(sm.k[0], &map_k, &sm.kv_full, 0, h, k0 + n * kBlockN);
+      tma_load_3d(sm.k[1], &map_k, &sm.kv_full, 64, h, k0 + n * kBlockN);
+      tma_load_3d(sm.v[0], &map_v, &sm.kv_full, 0, h, k0 + n * kBlockN);
+      tma_load_3d(sm.v[1], &map_v, &sm.kv_full, 64, h, k0 + n * kBlockN);
+      OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
+      uint32_t bits;
+      int issued = 0;
+      for (int i = 0;; ++i) {
+        const int m = walk.next(bits);
+        if (m < 0) break;
+        const int s = i & 1;
+        if (i >= 2 && !mbar_wait(&sm.qdo_empty[s], (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag,
+                                 p.status, 81))
+          break;
+        mbar_expect_tx(&sm.qdo_full[s], 4 * kTileHalfBytes);
+        const int tok = q0 + m * kTokPerTile;
+        tma_load_3d(sm.q[s][0], &map_q, &sm.qdo_full[s], 0, h * kGroup, tok);
+        tma_load_3d(sm.q[s][1], &map_q, &sm.qdo_full[s], 64, h * kGroup, tok);
+        tma_load_3d(sm.dout[s][0], &map_do, &sm.qdo_full[s], 0, h * kGroup, tok);
+        tma_load_3d(sm.dout[s][1], &map_do, &sm.qdo_full[s], 64, h * kGroup, tok);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait_drain(&sm.kv_full, 0);
+        for (int j = max(0, issued - 2); j < issued; ++j)
+          mbar_wait_drain(&sm.qdo_full[j & 1], (uint32_t)((j >> 1) & 1));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && !never_selected) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);             // K-major x K-major
+      constexpr uint32_t idesc_t = umma_idesc_bf16(128, 64, true, true);        // MN-major x MN-major
+      const uint32_t k_addr = smem_u32(sm.k[0]), v_addr = smem_u32(sm.v[0]);
+      const uint32_t p_addr = smem_u32(sm.pmat), ds_addr = smem_u32(sm.dsmat);
+      OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
+      uint32_t bits;
+      bool ok = mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 82);
+      int have = ok ? walk.next(bits) : -1;      // octet of step 0
+      auto issue_sdp = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t par = (uint32_t)((j >> 1) & 1);
+        if (!mbar_wait(&sm.qdo_full[s], par, abort_flag, p.status, 83)) return false;
+        if (j >= 2 && !mbar_wait(&sm.sdp_empty[s], par ^ 1u, abort_flag, p.status, 84)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sm.q[s][0]), do_addr = smem_u32(sm.dout[s][0]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
+          umma_ss(tmem + s * 128, umma_desc_sw128(q_addr + aoff, 16, 1024),
+                  umma_desc_sw128(k_addr + boff, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
+          umma_ss(tmem + s * 128 + 64, umma_desc_sw128(do_addr + aoff, 16, 1024),
+                  umma_desc_sw128(v_addr + boff, 16, 1024), idesc_s, kk > 0);
+        }
+        umma_commit(&sm.sdp_full[s]);
+        return true;
+      };
+      int i = 0;
+      if (have >= 0) ok = issue_sdp(0);
+      while (ok && have >= 0) {
+        const int s = i & 1;
+        const int next = walk.next(bits);
+        if (next >= 0) ok = issue_sdp(i + 1);
+        if (!ok) break;
+        ok = mbar_wait(&sm.pds_ready, (uint32_t)(i & 1), abort_flag, p.status, 85);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sm.q[s][0]), do_addr = smem_u32(sm.dout[s][0]);
+        // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tmem_dv, umma_desc_sw128(do_addr + kk * 2048, kTileHalfBytes, 1024),
+                  umma_desc_sw128(p_addr + kk * 2048, 16, 1024), idesc_t, (i > 0) || (kk > 0));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tmem_dk, umma_desc_sw128(q_addr + kk * 2048, kTileHalfBytes, 1024),
+                  umma_desc_sw128(ds_addr + kk * 2048, 16, 1024), idesc_t, (i > 0) || (kk > 0));
+        umma_commit(&sm.qdo_empty[s]);
+        umma_commit(&sm.pds_empty);
+        if (next < 0) umma_commit(&sm.acc_final);
+        have = next;
+        ++i;
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int tl = r >> 4, g = r & 15;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
+    uint32_t bits;
+    bool ok = true;
+    int steps = 0;
+    if (!never_selected) {
+      for (int i = 0;; ++i) {
+        const int m = walk.next(bits);
+        if (m < 0) break;
+        steps = i + 1;
+        const int s = i & 1;
+        const int tok = m * kTokPerTile + tl;                     // local token of this row
+        const bool selected = (bits >> tl) & 1u;
+        const int64_t stat_idx = (int64_t)h * p.total_q * kGroup + (int64_t)(q0 + tok) * kGroup + g;
+        const float neg_lse = selected ? -__ldg(p.lse + stat_idx) * kLog2e : -INFINITY;
+        const float dsum = selected ? __ldg(p.dvec + stat_idx) : 0.f;
+        // keys of this block the row may see
+        const int row_limit = selected ? min(lk, p.causal ? tok + shift + 1 : lk) : 0;
+        const int lim = min(max(row_limit - n * kBlockN, 0), kBlockN);
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.sdp_full[s], (uint32_t)((i >> 1) & 1),
+                                               abort_flag, p.status, 86));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t pp[32], dd[32];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t sv[32], dpv[32];
+          tmem_ld32(tmem + lane_off + s * 128 + half * 32, sv);
+          tmem_ld32(tmem + lane_off + s * 128 + 64 + half * 32, dpv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float pr[2], ds[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const bool vis = half * 32 + c + e < lim;
+              const float x = exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, neg_lse));
+              pr[e] = vis ? x : 0.f;
+              ds[e] = vis ? x * (__uint_as_float(dpv[c + e]) - dsum) : 0.f;
+            }
+            pp[half * 16 + (c >> 1)] = pack_bf16(pr[0], pr[1]);
+            dd[half * 16 + (c >> 1)] = pack_bf16(ds[0], ds[1]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&sm.sdp_empty[s]);                  // S / dP of this buffer may be overwritten
+        // P and dS of the previous step must have been consumed before the tiles are rewritten
+        if (i >= 1) {
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_empty, (uint32_t)((i - 1) & 1),
+                                                 abort_flag, p.status, 87));
+          if (!ok) break;
+        }
+        // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk (c ^ (r & 7))
+        uint8_t* prow = sm.pmat + r * 128;
+        uint8_t* drow = sm.dsmat + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int pc = (c ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(prow + pc) =
+              make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+          *reinterpret_cast<uint4*>(drow + pc) =
+              make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&sm.pds_ready);
+      }
+    }
+    if (ok && steps > 0) {
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.acc_final, 0, abort_flag, p.status, 88));
+      tc_fence_after();
+    }
+    if (ok) {
+      // this thread owns feature d = r of dV^T / dK^T; 64 key columns each
+      const int d = r;
+      __nv_bfloat16* dv_base = p.dv + ((int64_t)(k0 + n * kBlockN) * p.heads_k + h) * kHeadDim + d;
+      __nv_bfloat16* dk_base = p.dk + ((int64_t)(k0 + n * kBlockN) * p.heads_k + h) * kHeadDim + d;
+      const int64_t key_stride = (int64_t)p.heads_k * kHeadDim;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t a[32], bb[32];
+        if (steps > 0) {
+          tmem_ld32(tmem_dv + lane_off + c0, a);
+          tmem_ld32(tmem_dk + lane_off + c0, bb);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { a[j] = 0u; bb[j] = 0u; }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (c0 + j < nkeys) {
+            dv_base[(int64_t)(c0 + j) * key_stride] = __float2bfloat16_rn(__uint_as_float(a[j]));
+            dk_base[(int64_t)(c0 + j) * key_stride] =
+                __float2bfloat16_rn(__uint_as_float(bb[j]) * p.scale);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+}  // namespace ifv2
+
+using namespace ifv2;
+
+extern "C" int64_t ifv2_sparse_attn_bwd_workspace_bytes(int64_t total_q, int heads_q, int head_dim) {
+  (void)head_dim;
+  return total_q * heads_q * 4 + 256;       // D = rowsum(dO * O), one fp32 per (token, query head)
+}
+
+extern "C" int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
+                                    const void* out, const float* lse, void* dq, void* dk, void* dv,
+                                    const int64_t* fwd_mask, int fwd_mask_words,
+                                    const int64_t* bwd_mask, int64_t bwd_mask_words,
+                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                    int batch, int64_t total_q, int64_t total_k, int heads_q,
+                                    int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                    float softmax_scale, int causal, void* workspace,
+                                    int64_t workspace_bytes, int32_t* status, void* stream) {
+  IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED,
+               "sparse_attn_bwd: head_dim %d not supported (only 128)", head_dim);
+  IFV2_REQUIRE(heads_k >= 1 && heads_q == heads_k * kGroup, IFV2_ERR_UNSUPPORTED,
+               "sparse_attn_bwd: heads_q (%d) must be 16 x heads_k (%d)", heads_q, heads_k);
+  IFV2_REQUIRE(batch >= 1 && total_q >= 0 && total_k >= 0 && max_seqlen_q >= 0 && max_seqlen_k >= 0,
+               IFV2_ERR_INVALID_ARG, "sparse_attn_bwd: negative size or batch < 1");
+  if (total_q == 0 && total_k == 0) return IFV2_OK;
+  IFV2_REQUIRE(dout && q && k && v && out && lse && dq && dk && dv && cu_seqlens_q && cu_seqlens_k &&
+                   status && workspace,
+               IFV2_ERR_INVALID_ARG, "sparse_attn_bwd: null pointer");
+  IFV2_REQUIRE((fwd_mask == nullptr) == (bwd_mask == nullptr), IFV2_ERR_INVALID_ARG,
+               "sparse_attn_bwd: pass both the row mask and the column mask, or neither");
+  IFV2_REQUIRE(workspace_bytes >= ifv2_sparse_attn_bwd_workspace_bytes(total_q, heads_q, head_dim),
+               IFV2_ERR_INVALID_ARG, "sparse_attn_bwd: workspace too small");
+  IFV2_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, IFV2_ERR_INVALID_ARG,
+               "sparse_attn_bwd: workspace must be 16-byte aligned");
+  IFV2_REQUIRE(total_q <= INT32_MAX && total_k <= INT32_MAX, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_bwd: more than 2^31-1 tokens");
+  const int k_blocks = (max_seqlen_k + kBlockN - 1) / kBlockN;
+  IFV2_REQUIRE((k_blocks + 63) / 64 <= kMaxMaskWords, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_bwd: max_seqlen_k %d exceeds %d keys", max_seqlen_k,
+               kMaxMaskWords * 64 * kBlockN);
+  if (fwd_mask != nullptr) {
+    IFV2_REQUIRE(fwd_mask_words == (k_blocks + 63) / 64, IFV2_ERR_INVALID_ARG,
+                 "sparse_attn_bwd: row mask must have ceil(ceil(max_seqlen_k/64)/64) = %d words",
+                 (k_blocks + 63) / 64);
+    IFV2_REQUIRE(bwd_mask_words == (total_q + 63) / 64, IFV2_ERR_INVALID_ARG,
+                 "sparse_attn_bwd: column mask must have ceil(total_q/64) = %lld words",
+                 (long long)((total_q + 63) / 64));
+  }
+  IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_bwd: batch or heads_k > 65535");
+  cudaStream_t st = (cudaStream_t)stream;
+
+  BwdParams p;
+  p.lse = lse;
+  p.dvec = static_cast<float*>(workspace);
+  p.dq = static_cast<__nv_bfloat16*>(dq);
+  p.dk = static_cast<__nv_bfloat16*>(dk);
+  p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.fwd_mask = reinterpret_cast<const unsigned long long*>(fwd_mask);
+  p.fwd_words = fwd_mask_words;
+  p.bwd_mask = reinterpret_cast<const unsigned long long*>(bwd_mask);
+  p.bwd_words = bwd_mask_words;
+  p.k_blocks = k_blocks;
+  p.cu_q = cu_seqlens_q;
+  p.cu_k = cu_seqlens_k;
+  p.total_q = total_q;
+  p.heads_q = heads_q;
+  p.heads_k = heads_k;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * kLog2e;
+  p.causal = causal ? 1 : 0;
+  p.status = status;
+
+  if (total_q > 0) {
+    const int64_t rows = total_q * heads_q;
+    int64_t blocks = ceil_div64(rows, 16);
+    if (blocks > (int64_t)kNumSMs * 16) blocks = (int64_t)kNumSMs * 16;
+    dot_do_o_kernel<<<(int)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dout),
+                                                 static_cast<const __nv_bfloat16*>(out), p.dvec,
+                                                 total_q, heads_q);
+    int rc = check_launch("dot_do_o");
+    if (rc) return rc;
+  }
+
+  CUtensorMap map_q, map_do, map_k, map_v;
+  const uint64_t tq = total_q > 0 ? total_q : 1, tk = total_k > 0 ? total_k : 1;
+  int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, tq, kHeadDim * 2,
+                                   (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerTile);
+  if (rc) return rc;
+  rc = make_tensor_map_bf16_3d(&map_do, dout, kHeadDim, heads_q, tq, kHeadDim * 2,
+                               (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerTile);
+  if (rc) return rc;
+  rc = make_tensor_map_bf16_3d(&map_k, k, kHeadDim, heads_k, tk, kHeadDim * 2,
+                               (uint64_t)heads_k * kHeadDim * 2, 64, 1, kBlockN);
+  if (rc) return rc;
+  rc = make_tensor_map_bf16_3d(&map_v, v, kHeadDim, heads_k, tk, kHeadDim * 2,
+                               (uint64_t)heads_k * kHeadDim * 2, 64, 1, kBlockN);
+  if (rc) return rc;
+
+  if (total_q > 0 && max_seqlen_q > 0) {
+    const size_t smem = sizeof(DqSmem) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(sparse_attn_bwd_dq_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return set_error((int)e, "sparse_attn_bwd: %s", cudaGetErrorString(e));
+    dim3 grid((max_seqlen_q + kTokPerTile - 1) / kTokPerTile, batch, heads_k);
+    sparse_attn_bwd_dq_kernel<<<grid, kThreads, smem, st>>>(map_q, map_do, map_k, map_v, p);
+    rc = check_launch("sparse_attn_bwd_dq");
+    if (rc) return rc;
+  }
+  if (total_k > 0 && max_seqlen_k > 0) {
+    const size_t smem = sizeof(DkvSmem) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(sparse_attn_bwd_dkv_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return set_error((int)e, "sparse_attn_bwd: %s", cudaGetErrorString(e));
+    dim3 grid(k_blocks, batch, heads_k);
+    sparse_attn_bwd_dkv_kernel<<<grid, kThreads, smem, st>>>(map_q, map_do, map_k, map_v, p);
+    rc = check_launch("sparse_attn_bwd_dkv");
+    if (rc) return rc;
+  }
+  return IFV2_OK;
+}

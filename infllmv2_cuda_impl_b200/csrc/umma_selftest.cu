@@ -19,6 +19,7 @@ struct SelfTestParams {
 // mode 0: D(128x64)  = A(128x128, K-major) * B(64x128, K-major)^T      [the Q.K^T shape]
 // mode 1: D(128x128) = A(128x64,  K-major) * Bt(64x128, MN-major)      [the P.V shape, P in smem]
 // mode 2: D(128x128) = A(128x64 in TMEM)   * Bt(64x128, MN-major)      [the P.V shape, P in TMEM]
+// mode 3: D(128x64)  = At(128x128, MN-major)^T * Bt(128x64, MN-major)  [the dO^T.P shape of the backward]
 __global__ void __launch_bounds__(128)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const SelfTestParams p) {
@@ -47,7 +48,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
-  const int n = (p.mode == 0) ? 64 : 128;
+  const int n = (p.mode == 0 || p.mode == 3) ? 64 : 128;
 
   if (p.mode == 2) {   // every thread stores its A row into TMEM as packed bf16 pairs
     uint32_t regs[32];
@@ -68,6 +69,11 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
       tma_load_3d(sA + 16384, &map_a, &bar_load, 64, 0, 0);
       tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);
       tma_load_3d(sB + 8192, &map_b, &bar_load, 64, 0, 0);
+    } else if (p.mode == 3) {
+      mbar_expect_tx(&bar_load, 2 * 16384 + 16384);
+      tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);            // At rows 0..127, M columns 0..63
+      tma_load_3d(sA + 16384, &map_a, &bar_load, 64, 0, 0);   //                  M columns 64..127
+      tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);            // Bt rows 0..127, N columns 0..63
     } else if (p.mode == 1) {
       mbar_expect_tx(&bar_load, 16384 + 2 * 8192);
       tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);
@@ -89,6 +95,12 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
           umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + off, 16, 1024),
                   umma_desc_sw128(smem_u32(sB) + offb, 16, 1024), idesc, kk > 0);
         }
+      } else if (p.mode == 3) {
+        const uint32_t idesc = umma_idesc_bf16(128, 64, true, true);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + kk * 2048, 16384, 1024),
+                  umma_desc_sw128(smem_u32(sB) + kk * 2048, 16, 1024), idesc, kk > 0);
       } else {
         const uint32_t idesc = umma_idesc_bf16(128, 128, true);
 #pragma unroll
@@ -128,9 +140,10 @@ using namespace ifv2;
 
 // Test hook (declared here, not part of the public header): runs one tile product.
 //   mode 0: a (128,128), b (64,128)  -> d (128,64);  modes 1, 2: a (128,64), b (64,128) -> d (128,128)
+//   mode 3: a (128,128) = At, b (128,64) = Bt -> d = At^T . Bt (128,64)
 extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float* d, int32_t* status,
                                   void* stream) {
-  IFV2_REQUIRE(mode >= 0 && mode <= 2, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0, 1 or 2");
+  IFV2_REQUIRE(mode >= 0 && mode <= 3, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0..3");
   IFV2_REQUIRE(a && b && d && status, IFV2_ERR_INVALID_ARG, "selftest: null pointer");
   CUtensorMap map_a, map_b;
   int rc;
@@ -138,15 +151,19 @@ extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float*
     rc = make_tensor_map_bf16_3d(&map_a, a, 128, 128, 1, 256, 256 * 128, 64, 128, 1);
     if (rc) return rc;
     rc = make_tensor_map_bf16_3d(&map_b, b, 128, 64, 1, 256, 256 * 64, 64, 64, 1);
+  } else if (mode == 3) {
+    rc = make_tensor_map_bf16_3d(&map_a, a, 128, 128, 1, 256, 256 * 128, 64, 128, 1);
+    if (rc) return rc;
+    rc = make_tensor_map_bf16_3d(&map_b, b, 64, 128, 1, 128, 128 * 128, 64, 128, 1);
   } else {
     rc = make_tensor_map_bf16_3d(&map_a, a, 64, 128, 1, 128, 128 * 128, 64, 128, 1);
     if (rc) return rc;
     rc = make_tensor_map_bf16_3d(&map_b, b, 128, 64, 1, 256, 256 * 64, 64, 64, 1);
   }
   if (rc) return rc;
-  static const cudaError_t attr = cudaFuncSetAttribute(
-      umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 50 * 1024);
-  (void)attr;
+  cudaError_t attr = cudaFuncSetAttribute(umma_selftest_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 50 * 1024);
+  if (attr != cudaSuccess) return set_error((int)attr, "selftest: %s", cudaGetErrorString(attr));
   SelfTestParams p{static_cast<const __nv_bfloat16*>(a), d, mode, status};
   umma_selftest_kernel<<<1, 128, 50 * 1024, (cudaStream_t)stream>>>(map_a, map_b, p);
   return check_launch("umma_selftest");
