@@ -146,6 +146,27 @@ int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void* k, const v
                          int max_seqlen_k, float softmax_scale, int causal, void* workspace,
                          int64_t workspace_bytes, int32_t* status, void* stream);
 
+/* Backward without any allocation, for hosts that bind this C ABI directly and cannot hand over
+ * a workspace: a serving engine that reserved all of HBM for its own pools at start-up has no
+ * memory left for cudaMalloc at request time, and cudaMalloc/cudaFree also serialise the whole
+ * device, which a latency-bound decode or training loop cannot afford.  Same arguments and
+ * results as ifv2_sparse_attn_bwd minus (workspace, workspace_bytes): the scratch (one fp32 per
+ * query row) is a 16 MiB array built into the library and resident on every GPU that loads it.
+ * Limit: total_q * heads_q <= 4194304 rows; larger calls return IFV2_ERR_TOO_LARGE.
+ * The first call on each device looks the array's device address up (with that device
+ * current); make that first call before any stream capture begins.  All calls on a device share
+ * the array: two calls whose kernels overlap on the GPU (different streams) race on it.  Nothing
+ * in it needs clearing between calls.  No cudaMalloc, cudaFree or allocating library routine
+ * is called.  This entry point has no counterpart in the reference. */
+int ifv2_sparse_attn_bwd_noalloc(const void* dout, const void* q, const void* k, const void* v,
+                                 const void* out, const float* lse, void* dq, void* dk, void* dv,
+                                 const int64_t* fwd_mask, int fwd_mask_words,
+                                 const int64_t* bwd_mask, int64_t bwd_mask_words,
+                                 const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                 int batch, int64_t total_q, int64_t total_k, int heads_q,
+                                 int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                 float softmax_scale, int causal, int32_t* status, void* stream);
+
 /* Bytes of scratch ifv2_decode needs for its split partials. */
 int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_dim, int max_blocks);
 

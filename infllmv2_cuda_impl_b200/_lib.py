@@ -40,6 +40,10 @@ SIGNATURES = {
                                               c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                                               c_float, c_int, c_void_p, c_int64, c_void_p,
                                               c_void_p],
+    "ifv2_sparse_attn_bwd_noalloc": [c_void_p] * 9 + [c_void_p, c_int, c_void_p, c_int64, c_void_p,
+                                                      c_void_p, c_int, c_int64, c_int64, c_int,
+                                                      c_int, c_int, c_int, c_int, c_float, c_int,
+                                                      c_void_p, c_void_p],
     "ifv2_decode": [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int64,
                                      c_int64, c_float, c_void_p, c_int64, c_void_p],
 }

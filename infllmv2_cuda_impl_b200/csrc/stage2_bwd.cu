@@ -776,3 +776,60 @@ extern "C" int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void*
   }
   return IFV2_OK;
 }
+
+// ------------------------------------------------------------------ allocation-free variant --
+// Scratch for ifv2_sparse_attn_bwd_noalloc: the D = rowsum(dO * O) rows, one fp32 per
+// (token, query head), for up to kNoAllocMaxRows rows.  Every process that loads the library
+// holds these 16 MiB on each GPU it touches, until it exits.
+#include <mutex>
+
+static constexpr long long kNoAllocMaxRows = 4ll << 20;
+static __device__ __align__(256) unsigned char g_bwd_noalloc_scratch[kNoAllocMaxRows * 4 + 256];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+}  // namespace
+
+extern "C" int ifv2_sparse_attn_bwd_noalloc(
+    const void* dout, const void* q, const void* k, const void* v, const void* out,
+    const float* lse, void* dq, void* dk, void* dv, const int64_t* fwd_mask, int fwd_mask_words,
+    const int64_t* bwd_mask, int64_t bwd_mask_words, const int32_t* cu_seqlens_q,
+    const int32_t* cu_seqlens_k, int batch, int64_t total_q, int64_t total_k, int heads_q,
+    int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k, float softmax_scale, int causal,
+    int32_t* status, void* stream) {
+  IFV2_REQUIRE(total_q >= 0 && heads_q >= 0, IFV2_ERR_INVALID_ARG,
+               "sparse_attn_bwd_noalloc: negative size");
+  IFV2_REQUIRE(total_q * (int64_t)heads_q <= kNoAllocMaxRows, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_bwd_noalloc: total_q x heads_q = %lld query rows exceed the built-in "
+               "scratch of %lld rows; use ifv2_sparse_attn_bwd with a caller workspace",
+               (long long)(total_q * (int64_t)heads_q), kNoAllocMaxRows);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess)
+    return set_error((int)e, "sparse_attn_bwd_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  IFV2_REQUIRE(dev >= 0 && dev < kMaxDevices, IFV2_ERR_TOO_LARGE,
+               "sparse_attn_bwd_noalloc: device ordinal %d not supported", dev);
+  void* scratch = nullptr;
+  {
+    // Set-up, once per device, with that device current: in host code the array's name is only a
+    // stand-in, the address a kernel can use comes from the runtime.
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_bwd_noalloc_scratch);
+      if (e != cudaSuccess || ptr == nullptr)
+        return set_error(e != cudaSuccess ? (int)e : IFV2_ERR_DRIVER,
+                         "sparse_attn_bwd_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      g_noalloc_ptr[dev] = ptr;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  // Nothing in the scratch has to start at zero: the first kernel of the backward overwrites
+  // every D row that the later kernels read.
+  return ifv2_sparse_attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, fwd_mask, fwd_mask_words, bwd_mask,
+                              bwd_mask_words, cu_seqlens_q, cu_seqlens_k, batch, total_q, total_k,
+                              heads_q, heads_k, head_dim, max_seqlen_q, max_seqlen_k, softmax_scale,
+                              causal, scratch, (int64_t)sizeof(g_bwd_noalloc_scratch), status, stream);
+}
