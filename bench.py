@@ -296,6 +296,144 @@ def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
 
+
+# ------------------------------------------------------------------------------ other configs --
+
+def _time_ms(fn, reps=5, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def config3_topk(lens, hk, topk, seed):
+    """Block lists of BASELINE config 3: per 64-token query block and KV head, block 0, the 32
+    causal-local blocks and uniformly random earlier blocks up to `topk`, ascending, -1 tail."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    per_head = []
+    for h in range(hk):
+        rows = []
+        for lq in lens:
+            for bq in range((lq + BLOCK - 1) // BLOCK):
+                forced = set([0]) | set(range(max(0, bq - 31), bq + 1))
+                rest = [b for b in range(bq + 1) if b not in forced]
+                extra = rng.choice(rest, size=min(len(rest), topk - len(forced)), replace=False) if rest and len(forced) < topk else []
+                sel = np.sort(np.array(sorted(forced) + list(extra), dtype=np.int32))[:topk]
+                row = np.full(topk, -1, np.int32)
+                row[:len(sel)] = sel
+                n_tok = min(BLOCK, lq - bq * BLOCK)
+                rows.append(np.repeat(row[None], n_tok, 0))
+        per_head.append(np.concatenate(rows))
+    return torch.from_numpy(np.stack(per_head))
+
+
+def extra_configs(device, pk):
+    """Secondary numbers on one GPU: config 2 (selection micro-benchmark), config 3 (varlen
+    training forward + backward) and config 5 (decode).  Each kernel against its own roofline."""
+    import infllm_v2
+    from infllmv2_cuda_impl_b200 import attention
+    out = {}
+    s = 1.0 / math.sqrt(D)
+    g = torch.Generator(device=device).manual_seed(0)
+
+    # ---- config 2: 32768 tokens, 32q/2kv
+    L, hk = 32768, 2
+    q = (torch.randn(L, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    k = (torch.randn(L, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    kc = k.float().unfold(0, KERNEL, STRIDE).mean(-1).to(torch.bfloat16).contiguous()
+    n_comp, n_blk = kc.shape[0], L // BLOCK
+    cu_q = torch.tensor([0, L], dtype=torch.int32, device=device)
+    cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=device)
+    score = infllm_v2.infllmv2_attn_stage1(q, kc, kc, cu_q, cu_c, cu_c, L, n_comp, causal=True)
+    pooled = infllm_v2.max_pooling_1d(score, 0, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
+    idx = infllm_v2.infllmv2_topk(pooled, TOPK)
+    t_s1 = _time_ms(lambda: infllm_v2.infllmv2_attn_stage1(q, kc, kc, cu_q, cu_c, cu_c, L, n_comp, causal=True))
+    t_pool = _time_ms(lambda: infllm_v2.max_pooling_1d(score, 0, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE))
+    t_topk = _time_ms(lambda: infllm_v2.infllmv2_topk(pooled, TOPK))
+    t_pack = _time_ms(lambda: infllm_v2.topk_to_uint64(idx, L, BLOCK))
+    fl = 2.0 * D * hk * 16 * visible_compressed(L, n_comp)
+    b_pool = hk * L * (n_comp + n_blk) * 2
+    b_topk = hk * L * (n_blk * 2 + TOPK * 4)
+    b_pack = hk * L * (TOPK * 4 + ((n_blk + 63) // 64) * 8)
+    out["config2_selection_32k"] = {
+        "stage1_ms": round(t_s1, 4), "stage1_tflops": round(fl / t_s1 / 1e9, 1),
+        "stage1_frac": round(fl / t_s1 / 1e9 / pk["bf16_tflops"], 4),
+        "pool_ms": round(t_pool, 4), "pool_gbs": round(b_pool / t_pool / 1e6, 1),
+        "pool_frac": round(b_pool / t_pool / 1e6 / pk["hbm_gbs"], 4),
+        "topk_ms": round(t_topk, 4), "topk_gbs": round(b_topk / t_topk / 1e6, 1),
+        "topk_frac": round(b_topk / t_topk / 1e6 / pk["hbm_gbs"], 4),
+        "pack_ms": round(t_pack, 4), "pack_gbs": round(b_pack / t_pack / 1e6, 1),
+        "pack_frac": round(b_pack / t_pack / 1e6 / pk["hbm_gbs"], 4),
+        "note": "32 MB working sets fit the 126 MB L2: GB/s here are L2-assisted"}
+    del q, k, kc, score, pooled, idx
+
+    # ---- config 3: varlen fwd + bwd, 4 packed sequences, 65536 tokens, 32q/2kv
+    lens, hk = [8192, 16384, 24576, 16384], 2
+    T = sum(lens)
+    q = (torch.randn(T, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    k = (torch.randn(T, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    v = (torch.randn(T, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    do = torch.randn(T, hk * 16, D, device=device, generator=g).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=device)
+    idx = config3_topk(lens, hk, TOPK, seed=1).to(device)
+    max_l = max(lens)
+    scale = D ** -0.5
+    o, lse, mask = attention._infllmv2_attn_varlen_forward(q, k, v, cu, cu, max_l, max_l, scale, True, idx)
+    t_fwd = _time_ms(lambda: attention._infllmv2_attn_varlen_forward(q, k, v, cu, cu, max_l, max_l, scale, True, idx))
+    t_bwd = _time_ms(lambda: attention._infllmv2_attn_varlen_backward(do, q, k, v, o, lse, cu, cu, max_l, max_l,
+                                                                      scale, True, mask))
+    attention.check_device_status()
+    i_local = torch.cat([torch.arange(l, device=device) for l in lens]).view(1, -1, 1)
+    pairs = 0
+    for h in range(hk):
+        blk = idx[h:h + 1].long()
+        vis = (i_local + 1 - blk * BLOCK).clamp(0, BLOCK)
+        pairs += int(torch.where(blk >= 0, vis, torch.zeros_like(vis)).sum())
+    f_fwd, f_bwd = 4.0 * D * 16 * pairs, 10.0 * D * 16 * pairs
+    out["config3_varlen_fwd_bwd_64k"] = {
+        "fwd_ms": round(t_fwd, 3), "bwd_ms": round(t_bwd, 3),
+        "fwd_tflops": round(f_fwd / t_fwd / 1e9, 1), "bwd_tflops": round(f_bwd / t_bwd / 1e9, 1),
+        "fwd_bwd_tflops": round((f_fwd + f_bwd) / (t_fwd + t_bwd) / 1e9, 1),
+        "fwd_bwd_frac": round((f_fwd + f_bwd) / (t_fwd + t_bwd) / 1e9 / pk["bf16_tflops_sustained"], 4),
+        "algorithmic_flops": f_fwd + f_bwd, "tokens_per_s_fwd_bwd": round(T / ((t_fwd + t_bwd) * 1e-3), 1),
+        "note": "bwd includes the mask transpose, the dO.O pre-pass and both gradient kernels"}
+    del q, k, v, do, o, lse, mask, idx
+
+    # ---- config 5: decode, batch 64, cache 32768..131072, 32q/2kv, top-64 blocks
+    B, hk, cap = 64, 2, 131072 + 64
+    lens_t = torch.randint(32768, 131072 + 1, (B,), generator=torch.Generator().manual_seed(0)).to(torch.int32)
+    kcache = (torch.randn(B, cap, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    vcache = (torch.randn(B, cap, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    q = (torch.randn(B, 1, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    import numpy as np
+    rng = np.random.default_rng(0)
+    rows = np.full((B, hk, 1, TOPK), -1, np.int32)
+    for b in range(B):
+        nblk = (int(lens_t[b]) + BLOCK - 1) // BLOCK
+        for h in range(hk):
+            forced = [0] + list(range(nblk - 33, nblk))
+            rest = rng.choice(np.arange(1, nblk - 33), size=TOPK - len(forced), replace=False)
+            rows[b, h, 0] = np.sort(np.array(forced + list(rest), dtype=np.int32))
+    idx = torch.from_numpy(rows).to(device)
+    lens_d = lens_t.to(device)
+    t_dec = _time_ms(lambda: infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d,
+                                                                  topk_idx=idx), reps=10)
+    bytes_dec = B * hk * TOPK * BLOCK * D * 2 * 2 + 2 * B * hk * 16 * D * 2
+    out["config5_decode_b64"] = {
+        "ms": round(t_dec, 4), "gbs": round(bytes_dec / t_dec / 1e6, 1),
+        "frac": round(bytes_dec / t_dec / 1e6 / pk["hbm_gbs"], 4),
+        "tokens_per_s": round(B / (t_dec * 1e-3), 1),
+        "note": "stage-2 sparse decode step incl. the uint64 mask build; 268 MB of selected K/V per step"}
+    return out
+
+
 # ------------------------------------------------------------------------------ CPU oracle ----
 
 def cpu_sample(seqlen, sample_tokens, threads):
@@ -360,6 +498,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16,
                     help="query tokens in the CPU sample (cpu_baseline / --impl reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the secondary configs (selection micro-benchmark, varlen fwd+bwd, decode)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -383,6 +523,12 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     res = run_ours(args, rank, world, device)
     if rank == 0:
+        if world == 1 and not args.no_extras and args.seqlen == SEQLEN:
+            torch.cuda.empty_cache()
+            try:
+                res["other_configs"] = extra_configs(device, peaks()[0])
+            except Exception as e:                         # the headline line must still be printed
+                res["other_configs"] = {"error": repr(e)[:300]}
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             sec = cpu_sample(args.seqlen, args.cpu_tokens, threads)

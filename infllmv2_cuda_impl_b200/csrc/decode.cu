@@ -1,0 +1,433 @@
+// Sparse decode over a KV cache: one new query token per sequence, 16 query heads per KV head.
+//
+// With a single token the query tile is 16 rows, far too small for a tcgen05 tile, and the work
+// is HBM-bound: every selected 64-key block is read once (K and V, 32 KB) and used by 16 rows.
+// So this kernel is built around bandwidth: the selected blocks of one (sequence, KV head) are
+// split over kSplits CTAs, each warp streams whole blocks into swizzled shared memory with
+// cp.async (K and V of the next block are prefetched as soon as the current product has
+// consumed its tile), the 16 x 64 products run on mma.sync m16n8k16 (exactly one M tile), and
+// the per-split (max, sum, O) partials are merged by a small second kernel.
+//
+// Launches: [append new K/V in place] -> split kernel -> combine kernel.
+#include "common.cuh"
+
+namespace ifv2 {
+namespace {
+
+constexpr int kSplits = 16;
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kPartialFloats = kHeadDim + 4;            // O row, running max (log2 units), sum, pad (16-byte rows)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct DecodeParams {
+  const __nv_bfloat16* q;         // (batch, heads_q, 128)
+  const __nv_bfloat16* k_cache;   // (batch, capacity, heads_k, 128), batch stride given
+  const __nv_bfloat16* v_cache;
+  const unsigned long long* mask; // (batch, heads_k, mask_words) or null
+  int mask_words;
+  const int32_t* cache_seqlens;
+  int new_tokens;                 // 1 when k_new / v_new were appended, else 0
+  int heads_q, heads_k;
+  int64_t batch_stride;           // elements between sequences in the caches
+  float scale_log2;
+  float* partial;                 // (batch, heads_k, kSplits, 16, kPartialFloats)
+  __nv_bfloat16* out;             // (batch, heads_q, 128)
+  float* lse;                     // (batch, heads_q) or null
+};
+
+__global__ void decode_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                                     const __nv_bfloat16* k_new, const __nv_bfloat16* v_new,
+                                     const int32_t* cache_seqlens, int heads_k, int64_t capacity,
+                                     int64_t batch_stride) {
+  const int b = blockIdx.x;
+  const int64_t pos = cache_seqlens[b];
+  if (pos < 0 || pos >= capacity) return;           // no room: the host documents this as an error
+  const int n = heads_k * kHeadDim / 8;             // 16-byte vectors per token
+  const uint4* ks = reinterpret_cast<const uint4*>(k_new + (int64_t)b * heads_k * kHeadDim);
+  const uint4* vs = reinterpret_cast<const uint4*>(v_new + (int64_t)b * heads_k * kHeadDim);
+  uint4* kd = reinterpret_cast<uint4*>(k_cache + b * batch_stride + pos * heads_k * kHeadDim);
+  uint4* vd = reinterpret_cast<uint4*>(v_cache + b * batch_stride + pos * heads_k * kHeadDim);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    kd[i] = ks[i];
+    vd[i] = vs[i];
+  }
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A 64-key x 128-d bf16 tile in shared memory: row = key (256 B), 16-byte chunk c of row r is
+// stored at chunk (c ^ (r & 7)) so that ldmatrix reads of 8 consecutive rows hit 8 bank groups.
+__device__ __forceinline__ uint8_t* tile_addr(uint8_t* tile, int row, int chunk) {
+  return tile + row * 256 + ((chunk ^ (row & 7)) << 4);
+}
+
+// one warp copies keys [key0, key0 + 64) of one KV head; rows past `len` are not fetched
+__device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* base, int64_t row_stride,
+                                          int key0, int len, int lane) {
+#pragma unroll 4
+  for (int i = lane; i < 64 * 16; i += 32) {
+    const int row = i >> 4, chunk = i & 15;
+    if (key0 + row < len)
+      cp_async16(tile_addr(tile, row, chunk), base + (int64_t)(key0 + row) * row_stride + chunk * 8);
+  }
+}
+
+// index of the j-th (0-based) block of the selection, scanning the mask words upward
+struct BlockList {
+  const unsigned long long* words;   // null = every block below nblk
+  int nwords, nblk;
+  __device__ unsigned long long word(int w) const {
+    unsigned long long x = __ldg(words + w);
+    const int first = w * 64;
+    if (nblk - first < 64) x &= (nblk > first) ? ((1ull << (nblk - first)) - 1ull) : 0ull;
+    return x;
+  }
+  __device__ int count() const {
+    if (words == nullptr) return nblk;
+    int n = 0;
+    for (int w = 0; w < nwords; ++w) n += __popcll(word(w));
+    return n;
+  }
+  __device__ int nth(int j) const {
+    if (words == nullptr) return j;
+    for (int w = 0; w < nwords; ++w) {
+      unsigned long long x = word(w);
+      const int c = __popcll(x);
+      if (j < c) {
+        for (int i = 0; i < j; ++i) x &= x - 1;      // drop the j lowest set bits
+        return w * 64 + __ffsll((long long)x) - 1;
+      }
+      j -= c;
+    }
+    return -1;
+  }
+};
+
+__global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* k_tile = smem + warp * 32768;
+  uint8_t* v_tile = k_tile + 16384;
+
+  const int len = p.cache_seqlens[b] + p.new_tokens;
+  BlockList list{p.mask ? p.mask + ((int64_t)b * p.heads_k + h) * p.mask_words : nullptr, p.mask_words,
+                 (len + kBlockN - 1) / kBlockN};
+  const int n = list.count();
+  const int per_split = (n + kSplits - 1) / kSplits;
+  const int j_begin = split * per_split, j_end = min(n, j_begin + per_split);
+
+  const __nv_bfloat16* kbase = p.k_cache + b * p.batch_stride + (int64_t)h * kHeadDim;
+  const __nv_bfloat16* vbase = p.v_cache + b * p.batch_stride + (int64_t)h * kHeadDim;
+  const int64_t row_stride = (int64_t)p.heads_k * kHeadDim;
+
+  // Q fragments of the 16 heads (rows g and g + 8), all 8 k-steps
+  uint32_t qf[8][4];
+  {
+    const __nv_bfloat16* q0 = p.q + ((int64_t)b * p.heads_q + h * kGroup + g) * kHeadDim;
+    const __nv_bfloat16* q1 = q0 + 8 * kHeadDim;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qf[ks][0] = *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t);
+      qf[ks][1] = *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t);
+      qf[ks][2] = *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t);
+      qf[ks][3] = *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t);
+    }
+  }
+
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;    // rows g and g + 8 (log2 units)
+
+  int j = j_begin + warp;
+  int blk = (j < j_end) ? list.nth(j) : -1;
+  if (blk >= 0) {
+    load_tile(k_tile, kbase, row_stride, blk * kBlockN, len, lane);
+    cp_async_commit();
+    load_tile(v_tile, vbase, row_stride, blk * kBlockN, len, lane);
+    cp_async_commit();
+  }
+  while (blk >= 0) {
+    const int jn = j + kWarps;
+    const int blk_next = (jn < j_end) ? list.nth(jn) : -1;
+    const int key0 = blk * kBlockN;
+    cp_async_wait<1>();                 // K of this block has landed (V may still be in flight)
+    __syncwarp();
+
+    // ---- S = Q . K^T   (16 x 64)
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {        // two k-steps (32 d) per ldmatrix.x4
+        uint32_t bf[4];
+        ldmatrix_x4(bf, tile_addr(k_tile, nt * 8 + (lane & 7), kp * 4 + (lane >> 3)));
+        mma_bf16(s[nt], qf[2 * kp], bf[0], bf[1]);
+        mma_bf16(s[nt], qf[2 * kp + 1], bf[2], bf[3]);
+      }
+    }
+    __syncwarp();
+    if (blk_next >= 0) load_tile(k_tile, kbase, row_stride, blk_next * kBlockN, len, lane);
+    cp_async_commit();
+
+    // ---- online softmax (rows g and g + 8; a row's 64 scores live in the 4 lanes of a quad)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const bool vis = key0 + nt * 8 + 2 * t + e < len;
+        s[nt][e] = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
+        s[nt][2 + e] = vis ? s[nt][2 + e] * p.scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, s[nt][e]);
+        mx1 = fmaxf(mx1, s[nt][2 + e]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float f0 = (mn0 == -INFINITY) ? 1.f : exp2f(m0 - mn0);
+    const float f1 = (mn1 == -INFINITY) ? 1.f : exp2f(m1 - mn1);
+    const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
+    m0 = mn0;
+    m1 = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+    uint32_t pf[4][4];                        // P as A fragments for the 4 k-steps of P . V
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float p00 = exp2f(s[nt][0] - sub0), p01 = exp2f(s[nt][1] - sub0);
+      const float p10 = exp2f(s[nt][2] - sub1), p11 = exp2f(s[nt][3] - sub1);
+      sum0 += p00 + p01;
+      sum1 += p10 + p11;
+      pf[nt >> 1][(nt & 1) * 2 + 0] = pack2(p00, p01);
+      pf[nt >> 1][(nt & 1) * 2 + 1] = pack2(p10, p11);
+    }
+    l0 = l0 * f0 + sum0;                      // per-lane partial sums; reduced over the quad at the end
+    l1 = l1 * f1 + sum1;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      o[i][0] *= f0;
+      o[i][1] *= f0;
+      o[i][2] *= f1;
+      o[i][3] *= f1;
+    }
+
+    // ---- O += P . V   (16 x 128), V rows past `len` were never fetched: their P is 0, but the
+    //      stale shared-memory bytes could be NaN, so those rows are zeroed first
+    cp_async_wait<1>();                       // V of this block has landed
+    __syncwarp();
+    if (key0 + kBlockN > len) {
+      for (int i = lane; i < 64 * 16; i += 32) {
+        const int row = i >> 4;
+        if (key0 + row >= len)
+          *reinterpret_cast<uint4*>(tile_addr(v_tile, row, i & 15)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {        // two 8-wide d tiles per ldmatrix.x4.trans
+        uint32_t bf[4];
+        ldmatrix_x4_trans(bf, tile_addr(v_tile, kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                        np * 2 + (lane >> 4)));
+        mma_bf16(o[2 * np], pf[kk], bf[0], bf[1]);
+        mma_bf16(o[2 * np + 1], pf[kk], bf[2], bf[3]);
+      }
+    }
+    __syncwarp();
+    if (blk_next >= 0) load_tile(v_tile, vbase, row_stride, blk_next * kBlockN, len, lane);
+    cp_async_commit();
+    j = jn;
+    blk = blk_next;
+  }
+  cp_async_wait<0>();
+  l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
+  l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+  l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1);
+  l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+
+  // ---- merge the 4 warps of the CTA through shared memory (reusing the tile space)
+  __syncthreads();
+  float* stage = reinterpret_cast<float*>(smem);             // [warp][16 rows][kPartialFloats]
+  {
+    float* w0 = stage + ((size_t)warp * 16 + g) * kPartialFloats;
+    float* w1 = w0 + 8 * kPartialFloats;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      w0[i * 8 + 2 * t] = o[i][0];
+      w0[i * 8 + 2 * t + 1] = o[i][1];
+      w1[i * 8 + 2 * t] = o[i][2];
+      w1[i * 8 + 2 * t + 1] = o[i][3];
+    }
+    if (t == 0) {
+      w0[kHeadDim] = m0;
+      w0[kHeadDim + 1] = l0;
+      w1[kHeadDim] = m1;
+      w1[kHeadDim + 1] = l1;
+    }
+  }
+  __syncthreads();
+  float* dst = p.partial + ((((int64_t)b * p.heads_k + h) * kSplits + split) * 16) * kPartialFloats;
+  for (int i = threadIdx.x; i < 16 * kPartialFloats; i += kThreads) {
+    const int row = i / kPartialFloats, c = i - row * kPartialFloats;
+    float mw[kWarps], mmax = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      mw[w] = stage[((size_t)w * 16 + row) * kPartialFloats + kHeadDim];
+      mmax = fmaxf(mmax, mw[w]);
+    }
+    float acc = 0.f;
+    if (c == kHeadDim) {
+      acc = mmax;
+    } else if (c < kHeadDim + 2) {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float f = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - mmax);
+        acc += f * stage[((size_t)w * 16 + row) * kPartialFloats + c];    // O columns and the sum
+      }
+    }
+    dst[i] = acc;
+  }
+}
+
+// one CTA per (sequence, KV head): merge the kSplits partials, normalise, write bf16 + lse
+__global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams p) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int row = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+  const float* src = p.partial + (((int64_t)b * p.heads_k + h) * kSplits * 16 + row) * kPartialFloats;
+  float ms[kSplits], mmax = -INFINITY;
+#pragma unroll
+  for (int s = 0; s < kSplits; ++s) {
+    ms[s] = src[(size_t)s * 16 * kPartialFloats + kHeadDim];
+    mmax = fmaxf(mmax, ms[s]);
+  }
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, lsum = 0.f;
+#pragma unroll
+  for (int s = 0; s < kSplits; ++s) {
+    const float f = (ms[s] == -INFINITY) ? 0.f : exp2f(ms[s] - mmax);
+    const float* ps = src + (size_t)s * 16 * kPartialFloats;
+    lsum += f * ps[kHeadDim + 1];
+    const float4 a = *reinterpret_cast<const float4*>(ps + c0);
+    const float4 bq = *reinterpret_cast<const float4*>(ps + c0 + 4);
+    acc[0] += f * a.x; acc[1] += f * a.y; acc[2] += f * a.z; acc[3] += f * a.w;
+    acc[4] += f * bq.x; acc[5] += f * bq.y; acc[6] += f * bq.z; acc[7] += f * bq.w;
+  }
+  const float inv = (lsum > 0.f) ? 1.f / lsum : 0.f;
+  const int64_t qrow = (int64_t)b * p.heads_q + h * kGroup + row;
+  uint4 v4;
+  v4.x = pack2(acc[0] * inv, acc[1] * inv);
+  v4.y = pack2(acc[2] * inv, acc[3] * inv);
+  v4.z = pack2(acc[4] * inv, acc[5] * inv);
+  v4.w = pack2(acc[6] * inv, acc[7] * inv);
+  *reinterpret_cast<uint4*>(p.out + qrow * kHeadDim + c0) = v4;
+  if (p.lse != nullptr && (threadIdx.x & 15) == 0)
+    p.lse[qrow] = (lsum > 0.f) ? (mmax + log2f(lsum)) * kLn2 : INFINITY;
+}
+
+}  // namespace
+}  // namespace ifv2
+
+using namespace ifv2;
+
+extern "C" int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_dim, int max_blocks) {
+  (void)max_blocks;
+  if (batch < 0 || heads_q < 0 || head_dim != kHeadDim) return 0;
+  return (int64_t)batch * heads_q * kSplits * kPartialFloats * 4 + 256;
+}
+
+extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new,
+                           const void* v_new, void* out, float* lse, const int64_t* mask,
+                           int mask_words, const int32_t* cache_seqlens, int batch, int heads_q,
+                           int heads_k, int head_dim, int64_t cache_capacity,
+                           int64_t cache_batch_stride, float softmax_scale, void* workspace,
+                           int64_t workspace_bytes, void* stream) {
+  IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED, "decode: head_dim %d not supported (only 128)",
+               head_dim);
+  IFV2_REQUIRE(heads_k >= 1 && heads_q == heads_k * kGroup, IFV2_ERR_UNSUPPORTED,
+               "decode: heads_q (%d) must be 16 x heads_k (%d)", heads_q, heads_k);
+  IFV2_REQUIRE(batch >= 0 && cache_capacity >= 1, IFV2_ERR_INVALID_ARG, "decode: bad batch or capacity");
+  if (batch == 0) return IFV2_OK;
+  IFV2_REQUIRE(q && k_cache && v_cache && out && cache_seqlens && workspace, IFV2_ERR_INVALID_ARG,
+               "decode: null pointer");
+  IFV2_REQUIRE((k_new == nullptr) == (v_new == nullptr), IFV2_ERR_INVALID_ARG,
+               "decode: pass both k_new and v_new, or neither");
+  IFV2_REQUIRE(cache_batch_stride >= cache_capacity * heads_k * kHeadDim, IFV2_ERR_INVALID_ARG,
+               "decode: cache_batch_stride smaller than one sequence");
+  IFV2_REQUIRE(mask == nullptr || mask_words >= 1, IFV2_ERR_INVALID_ARG, "decode: mask_words < 1");
+  IFV2_REQUIRE(workspace_bytes >= ifv2_decode_workspace_bytes(batch, heads_q, head_dim, 0),
+               IFV2_ERR_INVALID_ARG, "decode: workspace too small");
+  IFV2_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, IFV2_ERR_INVALID_ARG,
+               "decode: workspace must be 16-byte aligned");
+  IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE, "decode: batch or heads_k > 65535");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (k_new != nullptr) {
+    decode_append_kernel<<<batch, 128, 0, st>>>(
+        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
+        static_cast<const __nv_bfloat16*>(k_new), static_cast<const __nv_bfloat16*>(v_new),
+        cache_seqlens, heads_k, cache_capacity, cache_batch_stride);
+    int rc = check_launch("decode_append");
+    if (rc) return rc;
+  }
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.mask = reinterpret_cast<const unsigned long long*>(mask);
+  p.mask_words = mask_words;
+  p.cache_seqlens = cache_seqlens;
+  p.new_tokens = k_new != nullptr ? 1 : 0;
+  p.heads_q = heads_q;
+  p.heads_k = heads_k;
+  p.batch_stride = cache_batch_stride;
+  p.scale_log2 = softmax_scale * kLog2e;
+  p.partial = static_cast<float*>(workspace);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  const size_t smem = (size_t)kWarps * 32768;
+  cudaError_t e = cudaFuncSetAttribute(decode_split_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return set_error((int)e, "decode: %s", cudaGetErrorString(e));
+  decode_split_kernel<<<dim3(kSplits, heads_k, batch), kThreads, smem, st>>>(p);
+  int rc = check_launch("decode_split");
+  if (rc) return rc;
+  decode_combine_kernel<<<dim3(heads_k, batch), 256, 0, st>>>(p);
+  return check_launch("decode_combine");
+}

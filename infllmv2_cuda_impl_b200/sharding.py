@@ -1,0 +1,135 @@
+"""Partitioning of the sparse-attention path over the GPUs of one box (one process per GPU).
+
+The path shards along three independent axes, none of which needs cross-shard arithmetic:
+
+* KV-head groups (tensor parallel): every kernel's grid has an independent KV-head axis and the
+  masks / top-k lists are per KV head -> `head_shard`; no collective at all.
+* sequences of a batch (decode, packed training batches) -> `batch_shard`; no collective.
+* query-sequence chunks for long prefill when there are fewer KV heads than GPUs: rank r owns
+  the zig-zag chunks {r, 2R-1-r} of the sequence (balanced causal work) and needs the keys
+  BEFORE each chunk's end -> one exchange step, an all-gather of the compressed keys and of K/V
+  into local HBM (NCCL over NVLink; payloads are MBs).  Each chunk is then an ordinary call with
+  seqlen_q < seqlen_k: the stage-1 and stage-2 kernels align the causal diagonal bottom-right
+  and the pool / top-k kernels take the chunk start as `cache_len`.
+
+The reference has no distributed code; the chunk layout follows the contract visible in its
+tests (tests/test_stage1_cp_load.py:43-47: head, tail = cp_rank + 1, 2*cp - cp_rank).
+Kernels only ever read local memory; nothing here uses peer pointers or multicast.
+"""
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def head_shard(num_kv_heads: int, world: int, rank: int) -> slice:
+    """KV heads owned by `rank` (query heads are 16x that slice)."""
+    if num_kv_heads % world != 0:
+        raise ValueError(f"{num_kv_heads} KV heads do not divide over {world} ranks")
+    per = num_kv_heads // world
+    return slice(rank * per, (rank + 1) * per)
+
+
+def batch_shard(batch: int, world: int, rank: int) -> range:
+    """Sequences owned by `rank` (contiguous, sizes differ by at most one)."""
+    base, rem = divmod(batch, world)
+    start = rank * base + min(rank, rem)
+    return range(start, start + base + (1 if rank < rem else 0))
+
+
+@dataclass(frozen=True)
+class Chunk:
+    index: int      # position of the chunk in the sequence, 0 .. 2*world-1
+    start: int      # first token
+    end: int        # one past the last token
+
+
+def zigzag_chunks(seqlen: int, world: int, rank: int, align: int = 64) -> List[Chunk]:
+    """The two chunks of a `seqlen`-token sequence owned by `rank`: chunk r and chunk 2R-1-r of
+    2R equal chunks (chunk length a multiple of `align`, so chunks start on KV-block borders)."""
+    n = 2 * world
+    if seqlen % (n * align) != 0:
+        raise ValueError(f"seqlen {seqlen} must be a multiple of {n * align} for {world} ranks")
+    clen = seqlen // n
+    return [Chunk(i, i * clen, (i + 1) * clen) for i in (rank, n - 1 - rank)]
+
+
+def gather_sequence(local: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """All-gather per-rank zig-zag shards (2 chunks concatenated along dim 0, equal sizes on all
+    ranks) and put the chunks back in sequence order."""
+    if world == 1:
+        return local
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local.contiguous(), group=group)
+    half = local.shape[0] // 2
+    chunks: List[Optional[torch.Tensor]] = [None] * (2 * world)
+    for r, p in enumerate(parts):
+        chunks[r] = p[:half]
+        chunks[2 * world - 1 - r] = p[half:]
+    return torch.cat(chunks, dim=0)
+
+
+def compressed_range(chunk: Chunk, stride: int = 16) -> Tuple[int, int]:
+    """Compressed-key slots [lo, hi) that a rank contributes for a chunk: key j (tokens
+    [16j, 16j+32)) belongs to the chunk that holds its first token."""
+    return chunk.start // stride, chunk.end // stride
+
+
+@dataclass
+class PrefillOps:
+    """The five operators of the prefill path; defaults are the CUDA ones."""
+    stage1: Callable
+    max_pool: Callable
+    topk: Callable
+    attn: Callable
+
+    @staticmethod
+    def cuda() -> "PrefillOps":
+        from . import attention, ops
+        return PrefillOps(attention.infllmv2_attn_stage1, ops.max_pooling_1d, ops.infllmv2_topk,
+                          attention.infllmv2_attn_varlen_func)
+
+
+def prefill_chunk(q_chunk: torch.Tensor, kc: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                  chunk: Chunk, topk: int, init_blocks: int, local_blocks: int,
+                  ops: Optional[PrefillOps] = None, block_size: int = 64, kernel: int = 32,
+                  stride: int = 16) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Full two-stage pipeline for the query tokens [chunk.start, chunk.end) of one sequence
+    against the keys before chunk.end.  kc, k, v hold (at least) the sequence prefix up to
+    chunk.end.  Returns (out_chunk, topk_idx_chunk)."""
+    ops = ops or PrefillOps.cuda()
+    dev = q_chunk.device
+    lq, lk = chunk.end - chunk.start, chunk.end
+    n_comp = (lk - kernel) // stride + 1 if lk >= kernel else 0
+    cu_q = torch.tensor([0, lq], dtype=torch.int32, device=dev)
+    cu_k = torch.tensor([0, lk], dtype=torch.int32, device=dev)
+    cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=dev)
+    kc_p = kc[:n_comp]
+    score = ops.stage1(q_chunk, kc_p, kc_p, cu_q, cu_c, cu_c, lq, n_comp, causal=True)
+    pooled = ops.max_pool(score, chunk.start, local_blocks, init_blocks, block_size, stride)
+    idx = ops.topk(pooled, topk, chunk.start)
+    out = ops.attn(q_chunk, k[:lk], v[:lk], cu_q, cu_k, lq, lk, causal=True, topk_idx=idx)
+    return out, idx
+
+
+def sharded_prefill(q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
+                    kc_local: torch.Tensor, seqlen: int, world: int, rank: int, topk: int,
+                    init_blocks: int, local_blocks: int, ops: Optional[PrefillOps] = None,
+                    group=None, stride: int = 16) -> torch.Tensor:
+    """Query-chunk-parallel prefill of ONE sequence.  Every rank passes the rows of its two
+    zig-zag chunks (concatenated): q_local (2*clen, Hq, d), k_local / v_local (2*clen, Hk, d) and
+    kc_local (2*clen/stride, Hk, d) -- the compressed keys whose first token lies in the chunk;
+    the slot of the sequence's last, incomplete window is padding.  Returns the attention output
+    for the local rows, in the same order."""
+    chunks = zigzag_chunks(seqlen, world, rank)
+    k = gather_sequence(k_local, world, group)
+    v = gather_sequence(v_local, world, group)
+    kc = gather_sequence(kc_local, world, group)
+    clen = chunks[0].end - chunks[0].start
+    outs = []
+    for i, ch in enumerate(chunks):
+        out, _ = prefill_chunk(q_local[i * clen:(i + 1) * clen], kc, k, v, ch, topk, init_blocks,
+                               local_blocks, ops, stride=stride)
+        outs.append(out)
+    return torch.cat(outs, dim=0)
