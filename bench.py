@@ -334,17 +334,27 @@ def config3_topk(lens, hk, topk, seed):
     return torch.from_numpy(np.stack(per_head))
 
 
-def extra_configs(device, pk):
+def extra_configs(device, pk, only=None, small=False):
     """Secondary numbers on one GPU: config 2 (selection micro-benchmark), config 3 (varlen
-    training forward + backward) and config 5 (decode).  Each kernel against its own roofline."""
+    training forward + backward) and config 5 (decode).  Each kernel against its own roofline.
+    `only` picks one of them; `small` shrinks it (for profiler captures)."""
+    out = {}
+    if only in (None, "selection"):
+        out.update(config2_selection(device, pk, small))
+    if only in (None, "train"):
+        out.update(config3_train(device, pk, small))
+    if only in (None, "decode"):
+        out.update(config5_decode(device, pk, small))
+    return out
+
+
+def config2_selection(device, pk, small=False):
     import infllm_v2
-    from infllmv2_cuda_impl_b200 import attention
     out = {}
     s = 1.0 / math.sqrt(D)
     g = torch.Generator(device=device).manual_seed(0)
-
     # ---- config 2: 32768 tokens, 32q/2kv
-    L, hk = 32768, 2
+    L, hk = (8192 if small else 32768), 2
     q = (torch.randn(L, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
     k = (torch.randn(L, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
     kc = k.float().unfold(0, KERNEL, STRIDE).mean(-1).to(torch.bfloat16).contiguous()
@@ -372,10 +382,17 @@ def extra_configs(device, pk):
         "pack_ms": round(t_pack, 4), "pack_gbs": round(b_pack / t_pack / 1e6, 1),
         "pack_frac": round(b_pack / t_pack / 1e6 / pk["hbm_gbs"], 4),
         "note": "32 MB working sets fit the 126 MB L2: GB/s here are L2-assisted"}
-    del q, k, kc, score, pooled, idx
+    return out
 
+
+def config3_train(device, pk, small=False):
+    import infllm_v2
+    from infllmv2_cuda_impl_b200 import attention
+    out = {}
+    s = 1.0 / math.sqrt(D)
+    g = torch.Generator(device=device).manual_seed(0)
     # ---- config 3: varlen fwd + bwd, 4 packed sequences, 65536 tokens, 32q/2kv
-    lens, hk = [8192, 16384, 24576, 16384], 2
+    lens, hk = ([2048, 4096, 6144, 4096] if small else [8192, 16384, 24576, 16384]), 2
     T = sum(lens)
     q = (torch.randn(T, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
     k = (torch.randn(T, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
@@ -404,11 +421,19 @@ def extra_configs(device, pk):
         "fwd_bwd_frac": round((f_fwd + f_bwd) / (t_fwd + t_bwd) / 1e9 / pk["bf16_tflops_sustained"], 4),
         "algorithmic_flops": f_fwd + f_bwd, "tokens_per_s_fwd_bwd": round(T / ((t_fwd + t_bwd) * 1e-3), 1),
         "note": "bwd includes the mask transpose, the dO.O pre-pass and both gradient kernels"}
-    del q, k, v, do, o, lse, mask, idx
+    return out
 
+
+def config5_decode(device, pk, small=False):
+    import infllm_v2
+    out = {}
+    s = 1.0 / math.sqrt(D)
+    g = torch.Generator(device=device).manual_seed(0)
     # ---- config 5: decode, batch 64, cache 32768..131072, 32q/2kv, top-64 blocks
-    B, hk, cap = 64, 2, 131072 + 64
-    lens_t = torch.randint(32768, 131072 + 1, (B,), generator=torch.Generator().manual_seed(0)).to(torch.int32)
+    B, hk = 64, 2
+    lo, hi = (8192, 16384) if small else (32768, 131072)
+    cap = hi + 64
+    lens_t = torch.randint(lo, hi + 1, (B,), generator=torch.Generator().manual_seed(0)).to(torch.int32)
     kcache = (torch.randn(B, cap, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
     vcache = (torch.randn(B, cap, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
     q = (torch.randn(B, 1, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
@@ -498,6 +523,9 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16,
                     help="query tokens in the CPU sample (cpu_baseline / --impl reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, choices=["selection", "train", "decode"],
+                    help="run just one secondary config and print its numbers (profiling aid)")
+    ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the secondary configs (selection micro-benchmark, varlen fwd+bwd, decode)")
     args = ap.parse_args()
@@ -521,6 +549,9 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+    if args.only is not None:
+        print(json.dumps(extra_configs(device, peaks()[0], args.only, args.small)), flush=True)
+        return
     res = run_ours(args, rank, world, device)
     if rank == 0:
         if world == 1 and not args.no_extras and args.seqlen == SEQLEN:
