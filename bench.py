@@ -149,26 +149,35 @@ def run_ours(args, rank, world, device):
     n_comp = kc.shape[0]
     cu_q = torch.tensor([0, seqlen], dtype=torch.int32, device=device)
     cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=device)
-    names = ["stage1_scores", "max_pooling_1d", "topk_select", "topk_to_uint64", "sparse_attn_fwd"]
+    fused = not args.unfused
+    names = (["stage1_block_scores", "topk_select", "topk_to_uint64", "sparse_attn_fwd"] if fused else
+             ["stage1_scores", "max_pooling_1d", "topk_select", "topk_to_uint64", "sparse_attn_fwd"])
+    n_marks = len(names)                 # marks 0 .. n_marks-1; the last interval is mask + stage 2
 
     def step(events=None):
         def mark(j):
             if events is not None:
                 events[j].record()
         mark(0)
-        score = infllm_v2.infllmv2_attn_stage1(q, kc, kc, cu_q, cu_c, cu_c, seqlen, n_comp, causal=True)
-        mark(1)
-        pooled = infllm_v2.max_pooling_1d(score, 0, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
-        del score
-        mark(2)
+        if fused:
+            # stage 1 and the max-pool in one kernel: the 17 GB score tensor never reaches HBM
+            pooled = infllm_v2.infllmv2_stage1_block_scores(q, kc, cu_q, cu_c, seqlen, n_comp,
+                                                            LOCAL_BLOCKS, INIT_BLOCKS, causal=True)
+            mark(1)
+        else:
+            score = infllm_v2.infllmv2_attn_stage1(q, kc, kc, cu_q, cu_c, cu_c, seqlen, n_comp, causal=True)
+            mark(1)
+            pooled = infllm_v2.max_pooling_1d(score, 0, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
+            del score
+            mark(2)
         idx = infllm_v2.infllmv2_topk(pooled, TOPK)
         del pooled
-        mark(3)
-        # the mask is built inside infllmv2_attn_varlen_func (as in the reference); marks 3->4
-        # therefore cover topk_to_uint64 + sparse_attn_fwd together, split below by a direct call
+        mark(n_marks - 2)
+        # the mask is built inside infllmv2_attn_varlen_func (as in the reference); the last
+        # interval therefore covers topk_to_uint64 + sparse_attn_fwd, split below by a direct call
         out = infllm_v2.infllmv2_attn_varlen_func(q, k, v, cu_q, cu_q, seqlen, seqlen, causal=True,
                                                   topk_idx=idx)
-        mark(4)
+        mark(n_marks - 1)
         return out, idx
 
     for _ in range(args.warmup):
@@ -177,7 +186,7 @@ def run_ours(args, rank, world, device):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n_marks)] for _ in range(args.steps)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(torch.cuda.current_device()) as clocks:
         t0.record()
@@ -193,7 +202,7 @@ def run_ours(args, rank, world, device):
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
     per_kernel = [sum(ev[s][j].elapsed_time(ev[s][j + 1]) for s in range(args.steps)) / args.steps
-                  for j in range(4)]
+                  for j in range(n_marks - 1)]
 
     # split topk_to_uint64 from the stage-2 kernel (both are inside infllmv2_attn_varlen_func)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -203,7 +212,7 @@ def run_ours(args, rank, world, device):
     b.record()
     torch.cuda.synchronize()
     pack_ms = a.elapsed_time(b) / 3
-    kernel_ms = dict(zip(names, per_kernel[:3] + [pack_ms, max(per_kernel[3] - pack_ms, 1e-6)]))
+    kernel_ms = dict(zip(names, per_kernel[:-1] + [pack_ms, max(per_kernel[-1] - pack_ms, 1e-6)]))
 
     # ---- algorithmic work of this rank's shard
     pk, pk_kind = peaks()
@@ -216,18 +225,18 @@ def run_ours(args, rank, world, device):
     bytes_pool = hk_local * seqlen * (n_comp * 2 + n_blk * 2)
     bytes_topk = hk_local * seqlen * (n_blk * 2 + TOPK * 4)
     bytes_pack = hk_local * seqlen * (TOPK * 4 + ((n_blk + 63) // 64) * 8)
+    tens, hbm = pk["bf16_tflops_sustained"], pk["hbm_gbs"]
     roof = {
-        "stage1_scores": ("tensor", flops_s1 / (kernel_ms["stage1_scores"] * 1e-3) / 1e12,
-                          pk["bf16_tflops_sustained"], "TFLOP/s"),
-        "sparse_attn_fwd": ("tensor", flops_s2 / (kernel_ms["sparse_attn_fwd"] * 1e-3) / 1e12,
-                            pk["bf16_tflops_sustained"], "TFLOP/s"),
-        "max_pooling_1d": ("hbm", bytes_pool / (kernel_ms["max_pooling_1d"] * 1e-3) / 1e9,
-                           pk["hbm_gbs"], "GB/s"),
-        "topk_select": ("hbm", bytes_topk / (kernel_ms["topk_select"] * 1e-3) / 1e9, pk["hbm_gbs"],
-                        "GB/s"),
-        "topk_to_uint64": ("hbm", bytes_pack / (kernel_ms["topk_to_uint64"] * 1e-3) / 1e9,
-                           pk["hbm_gbs"], "GB/s"),
+        "sparse_attn_fwd": ("tensor", flops_s2 / (kernel_ms["sparse_attn_fwd"] * 1e-3) / 1e12, tens, "TFLOP/s"),
+        "topk_select": ("hbm", bytes_topk / (kernel_ms["topk_select"] * 1e-3) / 1e9, hbm, "GB/s"),
+        "topk_to_uint64": ("hbm", bytes_pack / (kernel_ms["topk_to_uint64"] * 1e-3) / 1e9, hbm, "GB/s"),
     }
+    if fused:
+        roof["stage1_block_scores"] = ("tensor", flops_s1 / (kernel_ms["stage1_block_scores"] * 1e-3) / 1e12,
+                                       tens, "TFLOP/s")
+    else:
+        roof["stage1_scores"] = ("tensor", flops_s1 / (kernel_ms["stage1_scores"] * 1e-3) / 1e12, tens, "TFLOP/s")
+        roof["max_pooling_1d"] = ("hbm", bytes_pool / (kernel_ms["max_pooling_1d"] * 1e-3) / 1e9, hbm, "GB/s")
     dominant = max(kernel_ms, key=kernel_ms.get)
     bound, ach, peak, unit = roof[dominant]
     roofline = {"kernel": dominant, "bound": bound, "achieved": round(ach, 2), "peak": peak,
@@ -245,13 +254,14 @@ def run_ours(args, rank, world, device):
         "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"prefill {seqlen} tokens, 128q/8kv heads, d128: stage1 + max-pool + "
-                               f"top-64 (1 init + 32 local) + uint64 mask + stage-2 fwd",
+                               f"top-64 (1 init + 32 local) + uint64 mask + stage-2 fwd"
+                               + ("" if fused else " [stage 1 and pool as separate kernels]"),
                    "seq_len": seqlen, "global_batch": 1, "kv_heads_per_gpu": hk_local,
                    "parallelism": f"kv-head shards x{world}" if world > 1 else "single GPU",
                    "l2": "inputs (q alone is %.1f GB per GPU) exceed the 126 MB L2" % (q.numel() * 2 / 1e9)},
         "clocks": clocks.summary(),
         "e2e": e2e,
-        "gpu_launches": 5 * args.steps,
+        "gpu_launches": len(names) * args.steps,
         "roofline": roofline,
         "kernels": kernels,
         "flops_per_step": {"stage1_algorithmic": flops_s1 * world, "stage2_fwd_algorithmic": flops_s2 * world},
@@ -523,6 +533,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16,
                     help="query tokens in the CPU sample (cpu_baseline / --impl reference)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--unfused", action="store_true",
+                    help="run stage 1 and the max-pool as two kernels (the reference's op sequence)")
     ap.add_argument("--only", default=None, choices=["selection", "train", "decode"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")

@@ -108,6 +108,24 @@ int ifv2_stage1_scores(const void* q, const void* kc, void* out, const int32_t* 
                        int64_t out_row_stride, float softmax_scale, int causal,
                        int32_t* status, void* stream);
 
+/* Stage-1 scorer with the 64-token max-pool fused in: writes block scores
+ * (heads_k, total_q, n_blocks) bf16 that are bit-identical to ifv2_max_pooling_1d[_varlen]
+ * (kernel 5, stride 4, padding 1, block 64) applied to the output of ifv2_stage1_scores, without
+ * the score tensor ever reaching HBM.  scores_or_null: optional (heads_k, total_q,
+ * scores_row_stride) score output as in ifv2_stage1_scores.  cache_lens: per-sequence cache
+ * length (may be null -> scalar cache_len); n_blocks = ceil((max_seqlen_q + max cache) / 64).
+ * Fuses mha_varlen_fwd_stage1 (csrc/flash_attn/flash_api.cpp:784-1049) with
+ * max_pooling_1d_varlen_kernel (csrc/max_pooling_1d.cuh:11-103); the reference runs them as two
+ * launches with a (heads_k, total_q, max_seqlen_k) tensor in between. */
+int ifv2_stage1_block_scores(const void* q, const void* kc, void* scores_or_null,
+                             void* block_scores, const int32_t* cu_seqlens_q,
+                             const int32_t* cu_seqlens_k, const int32_t* cache_lens, int batch,
+                             int64_t total_q, int64_t total_c, int heads_q, int heads_k,
+                             int head_dim, int max_seqlen_q, int max_seqlen_k,
+                             int64_t scores_row_stride, int n_blocks, int cache_len,
+                             int local_blocks, int init_blocks, float softmax_scale, int causal,
+                             int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------- stage 2 ------------------ */
 
 /* Block-sparse varlen attention forward.  q/out: (total_q, heads_q, 128) bf16; k, v:

@@ -122,6 +122,51 @@ def infllmv2_attn_stage1(
     return buf[:, :, :max_seqlen_k]
 
 
+def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                 local_blocks, init_blocks, cache_len=0, cache_lens=None,
+                                 max_cache_len=None, softmax_scale=None, causal=True,
+                                 block_size=64, stride=16, return_scores=False):
+    """Stage 1 and the 64-token max-pool in one kernel (an addition to the reference API).
+
+    Returns block scores (nheads_k, total_q, ceil((max_seqlen_q + cache) / 64)) bf16 equal, bit
+    for bit, to `max_pooling_1d[_varlen](infllmv2_attn_stage1(...), ...)`; the
+    (nheads_k, total_q, max_seqlen_k) score tensor is only materialised with return_scores=True
+    (then the result is (block_scores, scores)).  cache_lens: optional per-sequence int32 tensor
+    (pass max_cache_len to avoid a device->host read); otherwise the scalar cache_len applies.
+    """
+    _check_common(q, k, 0.0, (-1, -1), 0.0, None, None, "infllmv2_stage1_block_scores")
+    if block_size != BLOCK_N or stride != 16:
+        raise NotImplementedError("infllmv2_stage1_block_scores: only block_size 64 / stride 16")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    q, k = _dense(maybe_contiguous(q)), _dense(maybe_contiguous(k))
+    total_q, nheads, _ = q.shape
+    nheads_k = k.shape[1]
+    batch = cu_seqlens_q.numel() - 1
+    if cache_lens is not None:
+        assert cache_lens.dtype == torch.int32 and cache_lens.numel() == batch
+        if max_cache_len is None:
+            max_cache_len = int(cache_lens.max().item())
+        cache_lens = cache_lens.contiguous()
+    else:
+        max_cache_len = cache_len
+    n_blocks = (max_seqlen_q + max_cache_len + BLOCK_N - 1) // BLOCK_N
+    pooled = torch.empty(nheads_k, total_q, n_blocks, dtype=torch.bfloat16, device=q.device)
+    buf, row_stride = None, 0
+    if return_scores:
+        row_stride = max(round_multiple(max_seqlen_k, 128), 128)
+        buf = torch.empty(nheads_k, total_q, row_stride, dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("ifv2_stage1_block_scores", q.data_ptr(), k.data_ptr(),
+                  buf.data_ptr() if buf is not None else None, pooled.data_ptr(),
+                  cu_seqlens_q.contiguous().data_ptr(), cu_seqlens_k.contiguous().data_ptr(),
+                  cache_lens.data_ptr() if cache_lens is not None else None, batch, total_q,
+                  k.shape[0], nheads, nheads_k, q.shape[-1], max_seqlen_q, max_seqlen_k, row_stride,
+                  n_blocks, int(cache_len), int(local_blocks), int(init_blocks), float(softmax_scale),
+                  int(bool(causal)), _status_words(q.device).data_ptr(), _stream(q.device))
+    return (pooled, buf[:, :, :max_seqlen_k]) if return_scores else pooled
+
+
 # ------------------------------------------------------------------------------------ stage 2 --
 
 def _fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,

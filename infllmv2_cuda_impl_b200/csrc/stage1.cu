@@ -1,16 +1,26 @@
-// Stage-1 scorer: group-summed softmax probabilities of the queries against the compressed keys.
+// Stage-1 scorer: group-summed softmax probabilities of the queries against the compressed keys,
+// optionally max-pooled to 64-token block scores in the same kernel.
 //
 // One CTA owns 8 consecutive tokens x the 16 query heads of one KV head (128 rows, fetched by one
 // 3-D TMA box from the caller's (token, head, d) layout) and streams 128-key tiles of the
 // compressed keys twice:
 //   pass 1:  S   = Q . Kc^T   (rows = query rows in TMEM lanes)   -> running max m and sum l per row
-//   pass 2:  S^T = Kc . Q^T   (rows = keys in TMEM lanes)         -> p = exp2(s*c - m*c) / l,
-//            and because the 16 heads of a token are now 16 adjacent COLUMNS of one thread's
-//            row, the GQA group sum is an in-register sum: no shuffles, no shared memory.
+//   pass 2:  S^T = Kc . Q^T   (rows = keys in TMEM lanes)         -> p = exp2(c*s - c*m - log2 l);
+//            because the 16 heads of a token are now 16 adjacent COLUMNS of one thread's row,
+//            the GQA group sum is an in-register sum: no shuffles, no shared memory.
 // Both products use the same two swizzled shared-memory tiles with the operand roles swapped.
-// The bf16 result row (Hk, token, key) is written straight from registers; columns past the
-// last visible key are zero-filled, so the output needs no pre-zeroing, no slice and no NaN
-// scrub.  Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = softmax.
+// In pass 2 the per-row constant -(c*m + log2 l)/c rides along inside the tensor-core product as
+// one extra 16-wide K step (a tile of ones against a tile holding the constant split into three
+// bf16 terms), so the softmax warps do one multiply and one ex2 per score and nothing else.
+// The bf16 result row (Hk, token, key) is written straight from registers, columns past the last
+// visible key are zero-filled (no pre-zeroing, slice or NaN scrub).  With pooling enabled each
+// tile's 128 x 8 scores also go through a small shared-memory window and leave as 32 x 8 block
+// scores (5-wide / stride-4 max, +inf on the init and causal-local blocks), bit-identical to
+// running the max-pool kernel on the score tensor.
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = softmax: two groups of four
+// warps; both groups cover all 128 TMEM lanes and each takes half of every tile's 128 columns
+// (pass 1: 64 of the keys, merged once at the end; pass 2: 4 of the 8 tokens), which doubles the
+// number of warps the MUFU-bound exponential loops can be issued from.
 #include "tc05.cuh"
 
 namespace ifv2 {
@@ -19,20 +29,25 @@ namespace {
 using namespace tc;
 
 constexpr int kTokPerTile = 8;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 256;
 constexpr int kKeysPerTile = 128;
 constexpr uint32_t kHalfBytes = 128 * 128;    // 128 rows x 64 bf16
 constexpr uint32_t kTmemCols = 256;
+constexpr int kPoolSlots = 136;               // 1 halo + 128 keys, padded
 
 struct Stage1Params {
-  __nv_bfloat16* out;
+  __nv_bfloat16* out;             // scores, may be null when only block scores are wanted
+  __nv_bfloat16* pooled;          // block scores, may be null
   const int32_t* cu_q;
   const int32_t* cu_k;
+  const int32_t* cache_lens;      // per sequence, may be null
   int64_t total_q;
   int heads_q, heads_k;
   int max_seqlen_k;
   int64_t out_row_stride;
-  float scale_log2;
+  int pooled_len, cache_len, local_blocks, init_blocks;
+  float scale_log2, inv_scale_log2;
   int causal;
   int32_t* status;
 };
@@ -40,8 +55,12 @@ struct Stage1Params {
 struct Smem {
   uint8_t q[2][kHalfBytes];          // [d half]
   uint8_t kc[2][2][kHalfBytes];      // [stage][d half]
-  float2 stat[128];                  // per query row: {-m * scale_log2, 1 / l}
-  uint64_t q_full, kc_full[2], kc_empty[2], acc_full[2], acc_empty[2];
+  uint8_t ones[4096];                // 128 x 16 bf16, no swizzle: columns 0..2 = 1
+  uint8_t rowc[4096];                // 128 x 16 bf16, no swizzle: columns 0..2 = row constant (3 terms)
+  __nv_bfloat16 pool[3][kTokPerTile][kPoolSlots];   // scores of the last three key tiles (pooling is
+  __nv_bfloat16 carry[4][kTokPerTile];              // deferred by one tile), and each tile's last key
+  float2 stat[128];                  // pass-1 (max, sum) of the second column half, per row
+  uint64_t q_full, kc_full[2], kc_empty[2], acc_full[2], acc_empty[2], rowc_ready, pool_full[3];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -55,6 +74,11 @@ __device__ __forceinline__ int visible_limit(int i, int lq, int lc, int causal) 
   return min(lc, max(0, (i + 1) / 16 - 1 + off));
 }
 
+__device__ __forceinline__ float bf16_round(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+template <bool kPooled>
 __global__ void __launch_bounds__(kThreads, 2)
 stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kc,
               const Stage1Params p) {
@@ -81,8 +105,10 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_init(&sm.kc_full[s], 1);
       mbar_init(&sm.kc_empty[s], 1);
       mbar_init(&sm.acc_full[s], 1);
-      mbar_init(&sm.acc_empty[s], 128);
+      mbar_init(&sm.acc_empty[s], 8);       // one arrival per softmax warp
     }
+    mbar_init(&sm.rowc_ready, 4);
+    for (int s = 0; s < 3; ++s) mbar_init(&sm.pool_full[s], 8);
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_kc);
@@ -91,6 +117,18 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     tmem_alloc(&sm.tmem_base, kTmemCols);
     tmem_relinquish();
   }
+  // the tile of ones (columns 0..2) and the zero part of the row-constant tile
+  for (int i = threadIdx.x; i < 4096 / 4; i += kThreads) {
+    reinterpret_cast<uint32_t*>(sm.ones)[i] = 0u;
+    reinterpret_cast<uint32_t*>(sm.rowc)[i] = 0u;
+  }
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const __nv_bfloat16 one = __float2bfloat16_rn(1.f);
+    for (int c = 0; c < 3; ++c)
+      *reinterpret_cast<__nv_bfloat16*>(sm.ones + umma_noswz16_off(threadIdx.x, c)) = one;
+  }
+  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -125,16 +163,19 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     if (lane == 0 && n_steps > 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128, false);
       const uint32_t q_addr = smem_u32(sm.q[0]);
+      const uint64_t d_ones = umma_desc_noswz16(smem_u32(sm.ones));
+      const uint64_t d_rowc = umma_desc_noswz16(smem_u32(sm.rowc));
       bool ok = mbar_wait(&sm.q_full, 0, abort_flag, p.status, 51);
       for (int t = 0; t < n_steps && ok; ++t) {
         const int s = t & 1;
         const uint32_t par = (uint32_t)((t >> 1) & 1);
+        const bool pass2 = t >= n_tiles;
         ok = mbar_wait(&sm.kc_full[s], par, abort_flag, p.status, 52);
         if (ok && t >= 2) ok = mbar_wait(&sm.acc_empty[s], par ^ 1u, abort_flag, p.status, 53);
+        if (ok && t == n_tiles) ok = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
         if (!ok) break;
         tc_fence_after();
         const uint32_t kc_addr = smem_u32(sm.kc[s][0]);
-        const bool pass2 = t >= n_tiles;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
@@ -142,6 +183,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           const uint64_t dk = umma_desc_sw128(kc_addr + off, 16, 1024);
           umma_ss(tmem + s * 128, pass2 ? dk : dq, pass2 ? dq : dk, idesc, kk > 0);
         }
+        if (pass2) umma_ss(tmem + s * 128, d_ones, d_rowc, idesc, true);   // + row constant
         umma_commit(&sm.kc_empty[s]);
         umma_commit(&sm.acc_full[s]);
       }
@@ -149,9 +191,10 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   } else {
     // ================================================================ softmax warps
     const int quad = warp & 3;
+    const int grp = (warp - 2) >> 2;                 // which half of the columns this warp takes
     const int r = quad * 32 + lane;                  // TMEM lane: pass 1 = query row, pass 2 = key
-    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const int st = threadIdx.x - 64;                 // 0..127 among the softmax threads
+    const uint32_t lane_off = ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * 64);
+    const int st = threadIdx.x - 64;                 // 0..255 among the softmax threads
     bool ok = true;
 
     // ---------------- pass 1: running max / sum of this thread's query row
@@ -165,84 +208,172 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                                abort_flag, p.status, 61));
         if (!ok) break;
         tc_fence_after();
-        const int lim = min(max(lim_row - t * kKeysPerTile, 0), kKeysPerTile);
-#pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 64) {
-          uint32_t raw[2][32];
-          tmem_ld32(tmem + lane_off + s * 128 + c0, raw[0]);
-          tmem_ld32(tmem + lane_off + s * 128 + c0 + 32, raw[1]);
-          tmem_wait_ld();
-          float mx = -INFINITY;
+        // visible columns among this group's 64
+        const int lim = min(max(lim_row - t * kKeysPerTile - grp * 64, 0), 64);
+        const bool full = __all_sync(0xFFFFFFFFu, lim == 64);
+        uint32_t buf[2][32];
+        tmem_ld32(tmem + lane_off + s * 128, buf[0]);
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            float x = __uint_as_float(raw[c >> 5][c & 31]);
-            x = (c0 + c < lim) ? x : -INFINITY;
-            raw[c >> 5][c & 31] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
+        for (int ch = 0; ch < 2; ++ch) {
+          tmem_wait_ld_dep(buf[ch & 1]);
+          if (ch < 1) tmem_ld32(tmem + lane_off + s * 128 + (ch + 1) * 32, buf[(ch + 1) & 1]);
+          uint32_t (&x)[32] = buf[ch & 1];
+          if (!full) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (ch * 32 + c >= lim) x[c] = 0xFF800000u;                 // -inf
           }
-          if (mx > -INFINITY) {
-            const float m_new = fmaxf(m, mx);
-            const float neg = -m_new * p.scale_log2;
-            float sum = 0.f;
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 64; ++c)
-              sum += exp2f(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.scale_log2, neg));
-            l = l * exp2f((m - m_new) * p.scale_log2) + sum;     // m = -inf -> factor 0, l was 0
+          for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(x[c]));
+          const float cm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+          const float m_new = fmaxf(m, cm);
+          if (m_new > -INFINITY) {
+            const float neg = -m_new * p.scale_log2;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              sum[c & 3] += exp2f(fmaf(__uint_as_float(x[c]), p.scale_log2, neg));
+            const float f = (m > -INFINITY) ? exp2f(fmaf(m, p.scale_log2, neg)) : 0.f;
+            l = l * f + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
             m = m_new;
           }
         }
         tc_fence_before();
-        mbar_arrive(&sm.acc_empty[s]);
+        mbar_arrive_warp(&sm.acc_empty[s]);
       }
-      sm.stat[r] = (l > 0.f) ? make_float2(-m * p.scale_log2, 1.f / l) : make_float2(0.f, 0.f);
+      // merge the two column halves of every row, then publish the row constant for pass 2, in
+      // units of the raw score: -(m + log2(l) / c), as three bf16 terms
+      if (grp == 1) sm.stat[r] = make_float2(m, l);
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (grp == 0) {
+        const float2 o = sm.stat[r];
+        const float mm = fmaxf(m, o.x);
+        if (mm > -INFINITY)
+          l = l * ((m > -INFINITY) ? exp2f((m - mm) * p.scale_log2) : 0.f) +
+              o.y * ((o.x > -INFINITY) ? exp2f((o.x - mm) * p.scale_log2) : 0.f);
+        m = mm;
+        const float rc = (l > 0.f) ? -(m + log2f(l) * p.inv_scale_log2) : -30000.f;
+        const float t0 = bf16_round(rc), t1 = bf16_round(rc - t0), t2 = bf16_round(rc - t0 - t1);
+        *reinterpret_cast<__nv_bfloat16*>(sm.rowc + umma_noswz16_off(r, 0)) = __float2bfloat16_rn(t0);
+        *reinterpret_cast<__nv_bfloat16*>(sm.rowc + umma_noswz16_off(r, 1)) = __float2bfloat16_rn(t1);
+        *reinterpret_cast<__nv_bfloat16*>(sm.rowc + umma_noswz16_off(r, 2)) = __float2bfloat16_rn(t2);
+        fence_proxy_async_smem();
+        mbar_arrive_warp(&sm.rowc_ready);
+      }
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");    // the four softmax warps only
 
     // ---------------- pass 2: this thread's key against all 128 query rows
-    if (ok) {
-      int lim_tok[kTokPerTile];
+    constexpr int kTokPerThread = kTokPerTile / 2;           // tokens grp*4 .. grp*4+3
+    int lim_tok[kTokPerThread];
+    const int cache_len = p.cache_lens ? p.cache_lens[b] : p.cache_len;
 #pragma unroll
-      for (int t8 = 0; t8 < kTokPerTile; ++t8)
-        lim_tok[t8] = (t8 < ntok) ? visible_limit(tok0 + t8, lq, lc, p.causal) : 0;
-      __nv_bfloat16* out_base =
-          p.out + ((int64_t)h * p.total_q + q0 + tok0) * p.out_row_stride;
+    for (int j = 0; j < kTokPerThread; ++j)
+      lim_tok[j] = (grp * 4 + j < ntok) ? visible_limit(tok0 + grp * 4 + j, lq, lc, p.causal) : 0;
+    __nv_bfloat16* out_base =
+        p.out ? p.out + ((int64_t)h * p.total_q + q0 + tok0) * p.out_row_stride : nullptr;
+    __nv_bfloat16* pool_base =
+        kPooled ? p.pooled + ((int64_t)h * p.total_q + q0 + tok0) * p.pooled_len : nullptr;
+    const __nv_bfloat16 ninf_b = __float2bfloat16_rn(-INFINITY);
+
+    // Max-pool of one finished key tile: 32 blocks x 8 tokens, two per thread.  It runs one tile
+    // late, after the next tile's exponentials, so that no warp waits for the others here.
+    auto pool_tile = [&](int tile) -> bool {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pool_full[tile % 3], (uint32_t)((tile / 3) & 1),
+                                             abort_flag, p.status, 63)))
+        return false;
+      {
+        const int t8 = st >> 5, bl = st & 31;
+        const int blk = tile * 32 + bl;
+        const __nv_bfloat16* w = &sm.pool[tile % 3][t8][4 * bl];          // slots 4bl .. 4bl+4
+        float mxv = fmaxf(fmaxf(__bfloat162float(w[1]), __bfloat162float(w[2])),
+                          fmaxf(__bfloat162float(w[3]), __bfloat162float(w[4])));
+        float first = -INFINITY;                                          // key 4*blk - 1
+        if (bl > 0) first = __bfloat162float(w[0]);
+        else if (tile > 0) first = __bfloat162float(sm.carry[(tile - 1) & 3][t8]);
+        mxv = fmaxf(mxv, first);
+        const int bq = (tok0 + t8 + cache_len) / kBlockN;
+        if (blk < p.init_blocks || (bq >= blk && bq <= blk + p.local_blocks)) mxv = INFINITY;
+        if (t8 < ntok && blk < p.pooled_len)
+          pool_base[(int64_t)t8 * p.pooled_len + blk] = __float2bfloat16_rn(mxv);
+      }
+      return true;
+    };
+
+    if (ok) {
       for (int t = n_tiles; t < n_steps; ++t) {
-        const int s = t & 1;
+        const int s = t & 1, tile = t - n_tiles;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.acc_full[s], (uint32_t)((t >> 1) & 1),
                                                abort_flag, p.status, 62));
         if (!ok) break;
         tc_fence_after();
-        const int key = (t - n_tiles) * kKeysPerTile + r;
+        const int key = tile * kKeysPerTile + r;
+        float val[kTokPerThread];
+        uint32_t buf[2][32];
+        tmem_ld32(tmem + lane_off + s * 128, buf[0]);
 #pragma unroll
-        for (int c0 = 0; c0 < 128; c0 += 32) {          // 32 columns = 2 tokens x 16 heads
-          uint32_t raw[32];
-          tmem_ld32(tmem + lane_off + s * 128 + c0, raw);
-          tmem_wait_ld();
+        for (int ch = 0; ch < 2; ++ch) {                  // 32 columns = 2 tokens x 16 heads
+          tmem_wait_ld_dep(buf[ch & 1]);
+          if (ch < 1) tmem_ld32(tmem + lane_off + s * 128 + (ch + 1) * 32, buf[(ch + 1) & 1]);
+          const uint32_t (&x)[32] = buf[ch & 1];
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            const int t8 = (c0 >> 4) + half;
-            float acc = 0.f;
+            float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {
-              const float2 st2 = sm.stat[c0 + half * 16 + g];
-              acc += exp2f(fmaf(__uint_as_float(raw[half * 16 + g]), p.scale_log2, st2.x)) * st2.y;
+            for (int g = 0; g < 16; g += 2) {
+              a0 += exp2f(__uint_as_float(x[half * 16 + g]) * p.scale_log2);
+              a1 += exp2f(__uint_as_float(x[half * 16 + g + 1]) * p.scale_log2);
             }
-            if (t8 < ntok && key < p.max_seqlen_k)
-              out_base[(int64_t)t8 * p.out_row_stride + key] =
-                  __float2bfloat16_rn(key < lim_tok[t8] ? acc : 0.f);
+            val[ch * 2 + half] = a0 + a1;
           }
         }
+        if (kPooled && tile > 0) {
+          ok = pool_tile(tile - 1);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int j = 0; j < kTokPerThread; ++j) {
+          const int t8 = grp * 4 + j;
+          // existing but invisible keys score 0; keys past the sequence do not exist (-inf in the pool)
+          const __nv_bfloat16 vb = __float2bfloat16_rn((key < lim_tok[j]) ? val[j] : 0.f);
+          if (out_base != nullptr && t8 < ntok && key < p.max_seqlen_k)
+            out_base[(int64_t)t8 * p.out_row_stride + key] = vb;
+          if (kPooled) {
+            const __nv_bfloat16 pv = (key < lc) ? vb : ninf_b;
+            sm.pool[tile % 3][t8][1 + r] = pv;
+            if (r == 127) sm.carry[tile & 3][t8] = pv;
+          }
+        }
+        if (kPooled) mbar_arrive_warp(&sm.pool_full[tile % 3]);
+        // (after the deferred pooling reads: this arrival is what lets a later tile reuse them)
         tc_fence_before();
-        mbar_arrive(&sm.acc_empty[s]);
+        mbar_arrive_warp(&sm.acc_empty[s]);
       }
+      if (ok && kPooled && n_tiles > 0) ok = pool_tile(n_tiles - 1);
       // columns past the last tile are zero (rows are 16-byte aligned: stride % 8 == 0)
       const int first = n_tiles * kKeysPerTile;
-      if (ok && first < p.max_seqlen_k) {
+      if (ok && out_base != nullptr && first < p.max_seqlen_k) {
         const int vec_per_row = (p.max_seqlen_k - first + 7) / 8;   // may spill into row padding
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
         for (int t8 = 0; t8 < ntok; ++t8) {
           uint4* dst = reinterpret_cast<uint4*>(out_base + (int64_t)t8 * p.out_row_stride + first);
-          for (int i = st; i < vec_per_row; i += 128) dst[i] = z;
+          for (int i = st; i < vec_per_row; i += kSoftmaxThreads) dst[i] = z;
+        }
+      }
+      // block scores past the last tile: their keys are invisible (0) or do not exist (-inf);
+      // the first such block still sees the last key of the last tile
+      if (ok && kPooled) {
+        const int first_blk = n_tiles * 32;
+        for (int t8 = 0; t8 < ntok; ++t8) {
+          const int bq = (tok0 + t8 + cache_len) / kBlockN;
+          for (int blk = first_blk + st; blk < p.pooled_len; blk += kSoftmaxThreads) {
+            float v = (4 * blk < lc) ? 0.f : -INFINITY;                   // keys 4blk .. 4blk+3
+            if (blk > 0 && 4 * blk - 1 < lc)                              // key 4blk - 1
+              v = fmaxf(v, (blk == first_blk && n_tiles > 0)
+                               ? __bfloat162float(sm.carry[(n_tiles - 1) & 3][t8]) : 0.f);
+            if (blk < p.init_blocks || (bq >= blk && bq <= blk + p.local_blocks)) v = INFINITY;
+            pool_base[(int64_t)t8 * p.pooled_len + blk] = __float2bfloat16_rn(v);
+          }
         }
       }
     }
@@ -253,37 +384,39 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
-}  // namespace
-}  // namespace ifv2
-
-using namespace ifv2;
-
-extern "C" int ifv2_stage1_scores(const void* q, const void* kc, void* out,
-                                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                  int batch, int64_t total_q, int64_t total_c, int heads_q,
-                                  int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
-                                  int64_t out_row_stride, float softmax_scale, int causal,
-                                  int32_t* status, void* stream) {
+int launch_stage1(const void* q, const void* kc, void* out, void* pooled,
+                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                  const int32_t* cache_lens, int batch, int64_t total_q, int64_t total_c,
+                  int heads_q, int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                  int64_t out_row_stride, int pooled_len, int cache_len, int local_blocks,
+                  int init_blocks, float softmax_scale, int causal, int32_t* status, void* stream,
+                  const char* what) {
   IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED,
-               "stage1_scores: head_dim %d not supported (only 128, as in the reference build)",
-               head_dim);
+               "%s: head_dim %d not supported (only 128, as in the reference build)", what, head_dim);
   IFV2_REQUIRE(heads_k >= 1 && heads_q == heads_k * kGroup, IFV2_ERR_UNSUPPORTED,
-               "stage1_scores: heads_q (%d) must be 16 x heads_k (%d)", heads_q, heads_k);
+               "%s: heads_q (%d) must be 16 x heads_k (%d)", what, heads_q, heads_k);
   IFV2_REQUIRE(batch >= 1 && total_q >= 0 && total_c >= 0 && max_seqlen_q >= 0 && max_seqlen_k >= 0,
-               IFV2_ERR_INVALID_ARG, "stage1_scores: negative size or batch < 1");
-  if (total_q == 0 || max_seqlen_q == 0 || max_seqlen_k == 0) return IFV2_OK;
-  IFV2_REQUIRE(q && out && cu_seqlens_q && cu_seqlens_k && status && (kc || total_c == 0),
-               IFV2_ERR_INVALID_ARG, "stage1_scores: null pointer");
-  IFV2_REQUIRE(out_row_stride >= ((max_seqlen_k + 7) / 8) * 8 && out_row_stride % 8 == 0,
-               IFV2_ERR_INVALID_ARG,
-               "stage1_scores: out_row_stride (%lld) must be a multiple of 8 and >= max_seqlen_k "
-               "rounded up to 8", (long long)out_row_stride);
-  IFV2_REQUIRE(reinterpret_cast<uintptr_t>(out) % 16 == 0, IFV2_ERR_INVALID_ARG,
-               "stage1_scores: out must be 16-byte aligned");
+               IFV2_ERR_INVALID_ARG, "%s: negative size or batch < 1", what);
+  if (total_q == 0 || max_seqlen_q == 0) return IFV2_OK;
+  if (max_seqlen_k == 0 && pooled == nullptr) return IFV2_OK;
+  IFV2_REQUIRE(softmax_scale > 0.f, IFV2_ERR_INVALID_ARG, "%s: softmax_scale must be > 0", what);
+  IFV2_REQUIRE(q && cu_seqlens_q && cu_seqlens_k && status && (kc || total_c == 0) && (out || pooled),
+               IFV2_ERR_INVALID_ARG, "%s: null pointer", what);
+  if (out != nullptr) {
+    IFV2_REQUIRE(out_row_stride >= ((max_seqlen_k + 7) / 8) * 8 && out_row_stride % 8 == 0,
+                 IFV2_ERR_INVALID_ARG,
+                 "%s: out_row_stride (%lld) must be a multiple of 8 and >= max_seqlen_k rounded up to 8",
+                 what, (long long)out_row_stride);
+    IFV2_REQUIRE(reinterpret_cast<uintptr_t>(out) % 16 == 0, IFV2_ERR_INVALID_ARG,
+                 "%s: out must be 16-byte aligned", what);
+  }
+  IFV2_REQUIRE(pooled == nullptr ||
+                   (pooled_len >= 1 && cache_len >= 0 && local_blocks >= 0 && init_blocks >= 0),
+               IFV2_ERR_INVALID_ARG, "%s: bad pooling arguments", what);
   IFV2_REQUIRE(total_q <= INT32_MAX && total_c <= INT32_MAX, IFV2_ERR_TOO_LARGE,
-               "stage1_scores: more than 2^31-1 rows");
-  IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE,
-               "stage1_scores: batch or heads_k > 65535");
+               "%s: more than 2^31-1 rows", what);
+  IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE, "%s: batch or heads_k > 65535",
+               what);
 
   CUtensorMap map_q, map_kc;
   int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, total_q, kHeadDim * 2,
@@ -297,22 +430,73 @@ extern "C" int ifv2_stage1_scores(const void* q, const void* kc, void* out,
 
   Stage1Params p;
   p.out = static_cast<__nv_bfloat16*>(out);
+  p.pooled = static_cast<__nv_bfloat16*>(pooled);
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
+  p.cache_lens = cache_lens;
   p.total_q = total_q;
   p.heads_q = heads_q;
   p.heads_k = heads_k;
   p.max_seqlen_k = max_seqlen_k;
   p.out_row_stride = out_row_stride;
+  p.pooled_len = pooled_len;
+  p.cache_len = cache_len;
+  p.local_blocks = local_blocks;
+  p.init_blocks = init_blocks;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.inv_scale_log2 = 1.f / p.scale_log2;
   p.causal = causal ? 1 : 0;
   p.status = status;
 
   const size_t smem = sizeof(Smem) + 1024;
-  cudaError_t e =
-      cudaFuncSetAttribute(stage1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return set_error((int)e, "stage1_scores: %s", cudaGetErrorString(e));
   dim3 grid((max_seqlen_q + kTokPerTile - 1) / kTokPerTile, batch, heads_k);
-  stage1_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_kc, p);
-  return check_launch("stage1_scores");
+  cudaError_t e;
+  if (pooled != nullptr) {
+    e = cudaFuncSetAttribute(stage1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    if (e != cudaSuccess) return set_error((int)e, "%s: %s", what, cudaGetErrorString(e));
+    stage1_kernel<true><<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_kc, p);
+  } else {
+    e = cudaFuncSetAttribute(stage1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    if (e != cudaSuccess) return set_error((int)e, "%s: %s", what, cudaGetErrorString(e));
+    stage1_kernel<false><<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_kc, p);
+  }
+  return check_launch(what);
+}
+
+}  // namespace
+}  // namespace ifv2
+
+using namespace ifv2;
+
+extern "C" int ifv2_stage1_scores(const void* q, const void* kc, void* out,
+                                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                  int batch, int64_t total_q, int64_t total_c, int heads_q,
+                                  int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                  int64_t out_row_stride, float softmax_scale, int causal,
+                                  int32_t* status, void* stream) {
+  IFV2_REQUIRE(out != nullptr || total_q == 0 || max_seqlen_k == 0 || max_seqlen_q == 0,
+               IFV2_ERR_INVALID_ARG, "stage1_scores: null pointer");
+  return launch_stage1(q, kc, out, nullptr, cu_seqlens_q, cu_seqlens_k, nullptr, batch, total_q,
+                       total_c, heads_q, heads_k, head_dim, max_seqlen_q, max_seqlen_k,
+                       out_row_stride, 0, 0, 0, 0, softmax_scale, causal, status, stream,
+                       "stage1_scores");
+}
+
+extern "C" int ifv2_stage1_block_scores(const void* q, const void* kc, void* scores_or_null,
+                                        void* block_scores, const int32_t* cu_seqlens_q,
+                                        const int32_t* cu_seqlens_k, const int32_t* cache_lens,
+                                        int batch, int64_t total_q, int64_t total_c, int heads_q,
+                                        int heads_k, int head_dim, int max_seqlen_q,
+                                        int max_seqlen_k, int64_t scores_row_stride, int n_blocks,
+                                        int cache_len, int local_blocks, int init_blocks,
+                                        float softmax_scale, int causal, int32_t* status,
+                                        void* stream) {
+  IFV2_REQUIRE(block_scores != nullptr || total_q == 0 || max_seqlen_q == 0, IFV2_ERR_INVALID_ARG,
+               "stage1_block_scores: null block_scores");
+  return launch_stage1(q, kc, scores_or_null, block_scores, cu_seqlens_q, cu_seqlens_k, cache_lens,
+                       batch, total_q, total_c, heads_q, heads_k, head_dim, max_seqlen_q,
+                       max_seqlen_k, scores_row_stride, n_blocks, cache_len, local_blocks,
+                       init_blocks, softmax_scale, causal, status, stream, "stage1_block_scores");
 }

@@ -161,7 +161,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
       mbar_init(&sm.sdp_full[s], 1);
-      mbar_init(&sm.ds_ready[s], 128);
+      mbar_init(&sm.ds_ready[s], 4);         // one arrival per softmax warp
     }
     mbar_init(&sm.dq_final, 1);
     fence_barrier_init();
@@ -315,7 +315,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       tmem_st32(tmem + lane_off + s * 128, packed);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.ds_ready[s]);
+      mbar_arrive_warp(&sm.ds_ready[s]);
     }
     if (ok && n_blocks > 0) {
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dq_final, 0, abort_flag, p.status, 78));
@@ -434,9 +434,9 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.qdo_full[s], 1);
       mbar_init(&sm.qdo_empty[s], 1);
       mbar_init(&sm.sdp_full[s], 1);
-      mbar_init(&sm.sdp_empty[s], 128);
+      mbar_init(&sm.sdp_empty[s], 4);
     }
-    mbar_init(&sm.pds_ready, 128);
+    mbar_init(&sm.pds_ready, 4);
     mbar_init(&sm.pds_empty, 1);
     mbar_init(&sm.acc_final, 1);
     fence_barrier_init();
@@ -595,7 +595,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
         tc_fence_before();
-        mbar_arrive(&sm.sdp_empty[s]);                  // S / dP of this buffer may be overwritten
+        mbar_arrive_warp(&sm.sdp_empty[s]);                  // S / dP of this buffer may be overwritten
         // P and dS of the previous step must have been consumed before the tiles are rewritten
         if (i >= 1) {
           ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_empty, (uint32_t)((i - 1) & 1),
@@ -614,7 +614,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
               make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
         }
         fence_proxy_async_smem();
-        mbar_arrive(&sm.pds_ready);
+        mbar_arrive_warp(&sm.pds_ready);
       }
     }
     if (ok && steps > 0) {

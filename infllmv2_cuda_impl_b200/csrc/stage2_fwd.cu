@@ -123,7 +123,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
       mbar_init(&sm.s_full[s], 1);
-      mbar_init(&sm.p_ready[s], 128);
+      mbar_init(&sm.p_ready[s], 4);          // one arrival per softmax warp
     }
     mbar_init(&sm.o_done, 1);
     mbar_init(&sm.o_final, 1);
@@ -249,26 +249,33 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       const int blk = walk.next();
       const int s = i & 1;
       const uint32_t par = (uint32_t)((i >> 1) & 1);
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[s], par, abort_flag, p.status, 31));
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t raw[2][32];
-      tmem_ld32(tmem + lane_off + s * 64, raw[0]);
-      tmem_ld32(tmem + lane_off + s * 64 + 32, raw[1]);
-      tmem_wait_ld();
-
       bool selected = valid;
       if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
       const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
+      // only the diagonal / ragged block needs per-element masking; a row that did not select
+      // the block is handled by the row-level terms below
+      const bool partial = __any_sync(0xFFFFFFFFu, lim > 0 && lim < kBlockN);
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[s], par, abort_flag, p.status, 31));
+      if (!ok) break;
+      tc_fence_after();
 
-      float mx = -INFINITY;
+      uint32_t raw[2][32];
+      tmem_ld32(tmem + lane_off + s * 64, raw[0]);
+      tmem_wait_ld_dep(raw[0]);
+      tmem_ld32(tmem + lane_off + s * 64 + 32, raw[1]);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float x = __uint_as_float(raw[c >> 5][c & 31]);
-        x = (c < lim) ? x : -INFINITY;
-        raw[c >> 5][c & 31] = __float_as_uint(x);
-        mx = fmaxf(mx, x);
+      for (int half = 0; half < 2; ++half) {
+        if (half == 1) tmem_wait_ld_dep(raw[1]);
+        if (partial) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (half * 32 + c >= lim) raw[half][c] = 0xFF800000u;          // -inf
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(raw[half][c]));
       }
+      const float mx = (lim > 0) ? fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) : -INFINITY;
       // raise the reference max only when it moves by more than the threshold
       float f = 1.f;
       if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > kRescaleThreshold)) {
@@ -292,22 +299,24 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         tmem_wait_st();
       }
-      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
+      // rows that take nothing from this block get an exponent of -inf (P = 0) for every column
+      const float neg_m = (lim == 0) ? -INFINITY : -m_ref * p.scale_log2;
       uint32_t packed[32];
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
         const float p0 = exp2f(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.scale_log2, neg_m));
         const float p1 =
             exp2f(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.scale_log2, neg_m));
-        sum += p0 + p1;
+        sum4[(c >> 1) & 3] += p0 + p1;
         packed[c >> 1] = pack_bf16(p0, p1);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l += sum;
       tmem_st32(tmem + lane_off + s * 64, packed);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.p_ready[s]);
+      mbar_arrive_warp(&sm.p_ready[s]);
     }
 
     // ---- epilogue: O / l -> bf16, lse

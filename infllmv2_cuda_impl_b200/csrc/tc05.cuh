@@ -30,6 +30,13 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for the whole warp: every lane must already have made its own data visible (its
+// tcgen05.wait / fence, or fence.proxy.async for shared-memory operand tiles); __syncwarp orders
+// those before the single arrive, which keeps 31 shared-memory atomics per warp off the barrier.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
@@ -159,6 +166,20 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+// tcgen05.wait::ld that also names the destination registers of the load it completes, so that
+// no use of those registers can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_wait_ld_dep(uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+        "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+        "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]),
+        "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
+        "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
+
 // ------------------------------------------------------------------ UMMA ---------------------
 // Shared-memory matrix descriptor, 128-byte swizzle (tiles 1024-byte aligned, base_offset 0).
 //   bits [0,14)  start address >> 4        bits [16,30) leading-dim byte offset >> 4
@@ -174,6 +195,21 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
   d |= 2ull << 61;
+  return d;
+}
+
+// A (rows x 16) bf16 K-major operand WITHOUT swizzle, written by threads: 8 x 8 core matrices of
+// 128 contiguous bytes (row r of a core matrix at r*16 B); the two K halves of a row group are
+// 128 B apart (leading offset), consecutive 8-row groups 256 B apart (stride offset).
+__device__ __forceinline__ uint32_t umma_noswz16_off(int row, int col) {
+  return (uint32_t)((row >> 3) * 256 + (col >> 3) * 128 + (row & 7) * 16 + (col & 7) * 2);
+}
+__device__ __forceinline__ uint64_t umma_desc_noswz16(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)(128u >> 4) << 16;
+  d |= (uint64_t)(256u >> 4) << 32;
+  d |= 1ull << 46;                        // layout type 0 = no swizzle
   return d;
 }
 

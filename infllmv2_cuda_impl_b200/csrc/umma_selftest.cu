@@ -10,7 +10,8 @@ namespace {
 using namespace tc;
 
 struct SelfTestParams {
-  const __nv_bfloat16* a;   // mode 2: A read with plain loads (128 x 64)
+  const __nv_bfloat16* a;   // modes 2, 4: A read with plain loads
+  const __nv_bfloat16* b;   // mode 4: B read with plain loads
   float* d;                 // (128, n) fp32
   int mode;
   int32_t* status;
@@ -20,6 +21,8 @@ struct SelfTestParams {
 // mode 1: D(128x128) = A(128x64,  K-major) * Bt(64x128, MN-major)      [the P.V shape, P in smem]
 // mode 2: D(128x128) = A(128x64 in TMEM)   * Bt(64x128, MN-major)      [the P.V shape, P in TMEM]
 // mode 3: D(128x64)  = At(128x128, MN-major)^T * Bt(128x64, MN-major)  [the dO^T.P shape of the backward]
+// mode 4: D(128x64)  = A(128x16) * B(64x16)^T, both K-major WITHOUT swizzle, written by threads
+//                                                                        [the row-constant K step of stage 1]
 __global__ void __launch_bounds__(128)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const SelfTestParams p) {
@@ -48,7 +51,14 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
-  const int n = (p.mode == 0 || p.mode == 3) ? 64 : 128;
+  const int n = (p.mode == 0 || p.mode == 3 || p.mode == 4) ? 64 : 128;
+  if (p.mode == 4) {
+    for (int i = threadIdx.x; i < 128 * 16; i += 128)
+      *reinterpret_cast<__nv_bfloat16*>(sA + umma_noswz16_off(i >> 4, i & 15)) = p.a[i];
+    for (int i = threadIdx.x; i < 64 * 16; i += 128)
+      *reinterpret_cast<__nv_bfloat16*>(sB + umma_noswz16_off(i >> 4, i & 15)) = p.b[i];
+    fence_proxy_async_smem();
+  }
 
   if (p.mode == 2) {   // every thread stores its A row into TMEM as packed bf16 pairs
     uint32_t regs[32];
@@ -63,7 +73,9 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp == 0 && elect_one()) {
     tc_fence_after();
-    if (p.mode == 0) {
+    if (p.mode == 4) {
+      mbar_arrive(&bar_load);                                 // nothing to fetch
+    } else if (p.mode == 0) {
       mbar_expect_tx(&bar_load, 2 * 16384 + 2 * 8192);
       tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);
       tma_load_3d(sA + 16384, &map_a, &bar_load, 64, 0, 0);
@@ -86,7 +98,10 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     if (mbar_wait(&bar_load, 0, &abort_flag, p.status, 1)) {
       tc_fence_after();
-      if (p.mode == 0) {
+      if (p.mode == 4) {
+        umma_ss(tmem_d, umma_desc_noswz16(smem_u32(sA)), umma_desc_noswz16(smem_u32(sB)),
+                umma_idesc_bf16(128, 64, false), false);
+      } else if (p.mode == 0) {
         const uint32_t idesc = umma_idesc_bf16(128, 64, false);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -141,9 +156,10 @@ using namespace ifv2;
 // Test hook (declared here, not part of the public header): runs one tile product.
 //   mode 0: a (128,128), b (64,128)  -> d (128,64);  modes 1, 2: a (128,64), b (64,128) -> d (128,128)
 //   mode 3: a (128,128) = At, b (128,64) = Bt -> d = At^T . Bt (128,64)
+//   mode 4: a (128,16), b (64,16) -> d = a . b^T (128,64)
 extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float* d, int32_t* status,
                                   void* stream) {
-  IFV2_REQUIRE(mode >= 0 && mode <= 3, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0..3");
+  IFV2_REQUIRE(mode >= 0 && mode <= 4, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0..4");
   IFV2_REQUIRE(a && b && d && status, IFV2_ERR_INVALID_ARG, "selftest: null pointer");
   CUtensorMap map_a, map_b;
   int rc;
@@ -151,6 +167,10 @@ extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float*
     rc = make_tensor_map_bf16_3d(&map_a, a, 128, 128, 1, 256, 256 * 128, 64, 128, 1);
     if (rc) return rc;
     rc = make_tensor_map_bf16_3d(&map_b, b, 128, 64, 1, 256, 256 * 64, 64, 64, 1);
+  } else if (mode == 4) {       // operands are written by threads; the maps are not used
+    rc = make_tensor_map_bf16_3d(&map_a, d, 64, 128, 1, 128, 128 * 128, 64, 128, 1);
+    if (rc) return rc;
+    rc = make_tensor_map_bf16_3d(&map_b, d, 64, 128, 1, 128, 128 * 128, 64, 128, 1);
   } else if (mode == 3) {
     rc = make_tensor_map_bf16_3d(&map_a, a, 128, 128, 1, 256, 256 * 128, 64, 128, 1);
     if (rc) return rc;
@@ -164,7 +184,8 @@ extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float*
   cudaError_t attr = cudaFuncSetAttribute(umma_selftest_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 50 * 1024);
   if (attr != cudaSuccess) return set_error((int)attr, "selftest: %s", cudaGetErrorString(attr));
-  SelfTestParams p{static_cast<const __nv_bfloat16*>(a), d, mode, status};
+  SelfTestParams p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, mode,
+                   status};
   umma_selftest_kernel<<<1, 128, 50 * 1024, (cudaStream_t)stream>>>(map_a, map_b, p);
   return check_launch("umma_selftest");
 }

@@ -76,3 +76,48 @@ def test_stage1_query_chunk_bottom_right_alignment():
     whole = _run(q, kc, cu([full]), torch.tensor(cu_c, dtype=torch.int32), full, cu_c[-1], True)
     tail = _run(q[512:], kc, cu([512]), torch.tensor(cu_c, dtype=torch.int32), 512, cu_c[-1], True)
     assert (whole[:, 512:] - tail).abs().max() <= 1e-2
+
+
+@pytest.mark.parametrize("lens_q,cache,local,init", [([4096], 0, 2, 1), ([700, 33, 1500], 0, 32, 1),
+                                                     ([513], 0, 1, 0), ([40], 0, 2, 1),
+                                                     ([2048 + 64], 0, 32, 1)])
+def test_fused_block_scores_equal_pool_of_scores(lens_q, cache, local, init):
+    """The fused stage-1 + max-pool kernel against the two separate kernels: bit-exact."""
+    hq, hk, d = 32, 2, 128
+    seed = sum(lens_q) + 5
+    q = det_tensor((sum(lens_q), hq, d), seed, 0.5).to(DEV)
+    k = det_tensor((sum(lens_q), hk, d), seed + 1, 0.5)
+    kc, cu_c = oracle.compress_keys(k, cu(lens_q))
+    max_k = int(np.diff(cu_c).max())
+    cu_q, cu_ct = cu(lens_q).to(DEV), torch.tensor(cu_c, dtype=torch.int32, device=DEV)
+    kc = kc.to(DEV)
+    pooled, scores = infllm_v2.infllmv2_stage1_block_scores(
+        q, kc, cu_q, cu_ct, max(lens_q), max_k, local, init, cache_len=cache, return_scores=True)
+    infllm_v2.check_device_status()
+    plain = infllm_v2.infllmv2_attn_stage1(q, kc, kc, cu_q, cu_ct, cu_ct, max(lens_q), max_k, causal=True)
+    assert torch.equal(scores, plain)
+    if len(lens_q) == 1:
+        ref = infllm_v2.max_pooling_1d(plain, cache, local, init)
+    else:
+        ref = infllm_v2.max_pooling_1d_varlen(plain, cu_q, cu_ct, torch.zeros(len(lens_q), dtype=torch.int32, device=DEV),
+                                              max(lens_q), max_k, local, init)
+    assert pooled.shape == ref.shape
+    assert torch.equal(pooled, ref)
+    only = infllm_v2.infllmv2_stage1_block_scores(q, kc, cu_q, cu_ct, max(lens_q), max_k, local, init,
+                                                  cache_len=cache)
+    assert torch.equal(only, ref)
+
+
+def test_fused_block_scores_query_chunk_with_cache_len():
+    hq, hk, d, full = 32, 2, 128, 2048
+    q = det_tensor((full, hq, d), 41, 0.5).to(DEV)
+    k = det_tensor((full, hk, d), 42, 0.5)
+    kc, cu_c = oracle.compress_keys(k, cu([full]))
+    kc = kc.to(DEV)
+    cu_ct = torch.tensor(cu_c, dtype=torch.int32, device=DEV)
+    start = 1024
+    got = infllm_v2.infllmv2_stage1_block_scores(q[start:], kc, cu([full - start]).to(DEV), cu_ct, full - start,
+                                                 cu_c[-1], 2, 1, cache_len=start)
+    plain = infllm_v2.infllmv2_attn_stage1(q[start:], kc, kc, cu([full - start]).to(DEV), cu_ct, cu_ct,
+                                           full - start, cu_c[-1], causal=True)
+    assert torch.equal(got, infllm_v2.max_pooling_1d(plain, start, 2, 1))

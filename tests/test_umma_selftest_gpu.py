@@ -8,12 +8,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4])
 def test_umma_tile(lib, mode):
     g = torch.Generator().manual_seed(mode)
     if mode == 0:
         a = torch.randn(128, 128, generator=g).to(torch.bfloat16)
         b = torch.randn(64, 128, generator=g).to(torch.bfloat16)
+        ref = a.float() @ b.float().t()
+    elif mode == 4:
+        a = torch.randn(128, 16, generator=g).to(torch.bfloat16)
+        b = torch.randn(64, 16, generator=g).to(torch.bfloat16)
         ref = a.float() @ b.float().t()
     elif mode == 3:
         a = torch.randn(128, 128, generator=g).to(torch.bfloat16)      # At: (K rows, M)
