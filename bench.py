@@ -461,10 +461,27 @@ def config5_decode(device, pk, small=False):
     t_dec = _time_ms(lambda: infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d,
                                                                   topk_idx=idx), reps=10)
     bytes_dec = B * hk * TOPK * BLOCK * D * 2 * 2 + 2 * B * hk * 16 * D * 2
+    # the step is four short launches: replayed from a CUDA graph the host launch cost disappears
+    t_graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d, topk_idx=idx)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d, topk_idx=idx)
+        t_graph = _time_ms(graph.replay, reps=20)
+    except Exception as e:                                  # keep the eager number
+        out["config5_graph_error"] = repr(e)[:200]
+    best = min(t_dec, t_graph) if t_graph else t_dec
     out["config5_decode_b64"] = {
-        "ms": round(t_dec, 4), "gbs": round(bytes_dec / t_dec / 1e6, 1),
-        "frac": round(bytes_dec / t_dec / 1e6 / pk["hbm_gbs"], 4),
-        "tokens_per_s": round(B / (t_dec * 1e-3), 1),
+        "ms": round(best, 4), "ms_eager": round(t_dec, 4),
+        "ms_cuda_graph": round(t_graph, 4) if t_graph else None,
+        "gbs": round(bytes_dec / best / 1e6, 1),
+        "frac": round(bytes_dec / best / 1e6 / pk["hbm_gbs"], 4),
+        "tokens_per_s": round(B / (best * 1e-3), 1),
         "note": "stage-2 sparse decode step incl. the uint64 mask build; 268 MB of selected K/V per step"}
     return out
 

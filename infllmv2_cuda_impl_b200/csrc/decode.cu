@@ -3,9 +3,10 @@
 // With a single token the query tile is 16 rows, far too small for a tcgen05 tile, and the work
 // is HBM-bound: every selected 64-key block is read once (K and V, 32 KB) and used by 16 rows.
 // So this kernel is built around bandwidth: the selected blocks of one (sequence, KV head) are
-// split over kSplits CTAs, each warp streams whole blocks into swizzled shared memory with
-// cp.async (K and V of the next block are prefetched as soon as the current product has
-// consumed its tile), the 16 x 64 products run on mma.sync m16n8k16 (exactly one M tile), and
+// split over several CTAs, each warp streams its blocks as 32-key units into swizzled shared
+// memory with cp.async (K and V of the next unit are prefetched as soon as the current product
+// has consumed its tile; 64 KB per CTA, two CTAs per SM), the 16 x 32 products run on mma.sync
+// m16n8k16 (exactly one M tile), and
 // the per-split (max, sum, O) partials are merged by a small second kernel.
 //
 // Launches: [append new K/V in place] -> split kernel -> combine kernel.
@@ -14,8 +15,10 @@
 namespace ifv2 {
 namespace {
 
-constexpr int kSplits = 16;
+constexpr int kMaxSplits = 16;                          // CTAs per (sequence, KV head), chosen per launch
 constexpr int kWarps = 4;
+constexpr int kUnit = 32;                               // keys per shared-memory tile
+constexpr int kWarpSmem = 2 * kUnit * 256;              // one K tile + one V tile per warp
 constexpr int kThreads = kWarps * 32;
 constexpr int kPartialFloats = kHeadDim + 4;            // O row, running max (log2 units), sum, pad (16-byte rows)
 constexpr float kLog2e = 1.4426950408889634f;
@@ -32,7 +35,8 @@ struct DecodeParams {
   int heads_q, heads_k;
   int64_t batch_stride;           // elements between sequences in the caches
   float scale_log2;
-  float* partial;                 // (batch, heads_k, kSplits, 16, kPartialFloats)
+  int splits;                     // CTAs sharing one (sequence, KV head), 1 .. kMaxSplits
+  float* partial;                 // (batch, heads_k, splits, 16, kPartialFloats)
   __nv_bfloat16* out;             // (batch, heads_q, 128)
   float* lse;                     // (batch, heads_q) or null
 };
@@ -86,17 +90,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// A 64-key x 128-d bf16 tile in shared memory: row = key (256 B), 16-byte chunk c of row r is
+// A (kUnit keys) x 128-d bf16 tile in shared memory: row = key (256 B), 16-byte chunk c of row r is
 // stored at chunk (c ^ (r & 7)) so that ldmatrix reads of 8 consecutive rows hit 8 bank groups.
 __device__ __forceinline__ uint8_t* tile_addr(uint8_t* tile, int row, int chunk) {
   return tile + row * 256 + ((chunk ^ (row & 7)) << 4);
 }
 
-// one warp copies keys [key0, key0 + 64) of one KV head; rows past `len` are not fetched
+// one warp copies keys [key0, key0 + kUnit) of one KV head; rows past `len` are not fetched
 __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* base, int64_t row_stride,
                                           int key0, int len, int lane) {
 #pragma unroll 4
-  for (int i = lane; i < 64 * 16; i += 32) {
+  for (int i = lane; i < kUnit * 16; i += 32) {
     const int row = i >> 4, chunk = i & 15;
     if (key0 + row < len)
       cp_async16(tile_addr(tile, row, chunk), base + (int64_t)(key0 + row) * row_stride + chunk * 8);
@@ -134,19 +138,19 @@ struct BlockList {
   }
 };
 
-__global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  uint8_t* k_tile = smem + warp * 32768;
-  uint8_t* v_tile = k_tile + 16384;
+  uint8_t* k_tile = smem + warp * kWarpSmem;
+  uint8_t* v_tile = k_tile + kUnit * 256;
 
   const int len = p.cache_seqlens[b] + p.new_tokens;
   BlockList list{p.mask ? p.mask + ((int64_t)b * p.heads_k + h) * p.mask_words : nullptr, p.mask_words,
                  (len + kBlockN - 1) / kBlockN};
   const int n = list.count();
-  const int per_split = (n + kSplits - 1) / kSplits;
+  const int per_split = (n + p.splits - 1) / p.splits;
   const int j_begin = split * per_split, j_end = min(n, j_begin + per_split);
 
   const __nv_bfloat16* kbase = p.k_cache + b * p.batch_stride + (int64_t)h * kHeadDim;
@@ -172,27 +176,41 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
   for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;    // rows g and g + 8 (log2 units)
 
-  int j = j_begin + warp;
+  // The warp streams its blocks as 32-key units (two per block), so that the K tile of the next
+  // unit is already in flight while this unit's softmax and P.V run.
+  int j = j_begin + warp, half = 0;
   int blk = (j < j_end) ? list.nth(j) : -1;
+  int key0 = blk * kBlockN;
+  auto advance = [&](int& jj, int& hh, int& bb) -> int {          // next unit; returns its first key or -1
+    if (hh == 0 && bb * kBlockN + kUnit < len) {
+      hh = 1;
+      return bb * kBlockN + kUnit;
+    }
+    jj += kWarps;
+    hh = 0;
+    bb = (jj < j_end) ? list.nth(jj) : -1;
+    return bb >= 0 ? bb * kBlockN : -1;
+  };
   if (blk >= 0) {
-    load_tile(k_tile, kbase, row_stride, blk * kBlockN, len, lane);
+    load_tile(k_tile, kbase, row_stride, key0, len, lane);
     cp_async_commit();
-    load_tile(v_tile, vbase, row_stride, blk * kBlockN, len, lane);
+    load_tile(v_tile, vbase, row_stride, key0, len, lane);
     cp_async_commit();
+  } else {
+    key0 = -1;
   }
-  while (blk >= 0) {
-    const int jn = j + kWarps;
-    const int blk_next = (jn < j_end) ? list.nth(jn) : -1;
-    const int key0 = blk * kBlockN;
-    cp_async_wait<1>();                 // K of this block has landed (V may still be in flight)
+  while (key0 >= 0) {
+    int jn = j, hn = half, bn = blk;
+    const int key_next = advance(jn, hn, bn);
+    cp_async_wait<1>();                 // K of this unit has landed (V may still be in flight)
     __syncwarp();
 
-    // ---- S = Q . K^T   (16 x 64)
-    float s[8][4];
+    // ---- S = Q . K^T   (16 x 32)
+    float s[kUnit / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    for (int nt = 0; nt < kUnit / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < kUnit / 8; ++nt) {
 #pragma unroll
       for (int kp = 0; kp < 4; ++kp) {        // two k-steps (32 d) per ldmatrix.x4
         uint32_t bf[4];
@@ -202,13 +220,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
       }
     }
     __syncwarp();
-    if (blk_next >= 0) load_tile(k_tile, kbase, row_stride, blk_next * kBlockN, len, lane);
+    if (key_next >= 0) load_tile(k_tile, kbase, row_stride, key_next, len, lane);
     cp_async_commit();
 
-    // ---- online softmax (rows g and g + 8; a row's 64 scores live in the 4 lanes of a quad)
+    // ---- online softmax (rows g and g + 8; a row's scores live in the 4 lanes of a quad)
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < kUnit / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const bool vis = key0 + nt * 8 + 2 * t + e < len;
@@ -229,9 +247,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
     m0 = mn0;
     m1 = mn1;
     float sum0 = 0.f, sum1 = 0.f;
-    uint32_t pf[4][4];                        // P as A fragments for the 4 k-steps of P . V
+    uint32_t pf[kUnit / 16][4];               // P as A fragments for the k-steps of P . V
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < kUnit / 8; ++nt) {
       const float p00 = exp2f(s[nt][0] - sub0), p01 = exp2f(s[nt][1] - sub0);
       const float p10 = exp2f(s[nt][2] - sub1), p11 = exp2f(s[nt][3] - sub1);
       sum0 += p00 + p01;
@@ -241,20 +259,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
     }
     l0 = l0 * f0 + sum0;                      // per-lane partial sums; reduced over the quad at the end
     l1 = l1 * f1 + sum1;
+    if (__any_sync(0xFFFFFFFFu, f0 != 1.f || f1 != 1.f)) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      o[i][0] *= f0;
-      o[i][1] *= f0;
-      o[i][2] *= f1;
-      o[i][3] *= f1;
+      for (int i = 0; i < 16; ++i) {
+        o[i][0] *= f0;
+        o[i][1] *= f0;
+        o[i][2] *= f1;
+        o[i][3] *= f1;
+      }
     }
 
     // ---- O += P . V   (16 x 128), V rows past `len` were never fetched: their P is 0, but the
     //      stale shared-memory bytes could be NaN, so those rows are zeroed first
-    cp_async_wait<1>();                       // V of this block has landed
+    cp_async_wait<1>();                       // V of this unit has landed
     __syncwarp();
-    if (key0 + kBlockN > len) {
-      for (int i = lane; i < 64 * 16; i += 32) {
+    if (key0 + kUnit > len) {
+      for (int i = lane; i < kUnit * 16; i += 32) {
         const int row = i >> 4;
         if (key0 + row >= len)
           *reinterpret_cast<uint4*>(tile_addr(v_tile, row, i & 15)) = make_uint4(0u, 0u, 0u, 0u);
@@ -262,7 +282,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
       __syncwarp();
     }
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
+    for (int kk = 0; kk < kUnit / 16; ++kk) {
 #pragma unroll
       for (int np = 0; np < 8; ++np) {        // two 8-wide d tiles per ldmatrix.x4.trans
         uint32_t bf[4];
@@ -273,10 +293,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
       }
     }
     __syncwarp();
-    if (blk_next >= 0) load_tile(v_tile, vbase, row_stride, blk_next * kBlockN, len, lane);
+    if (key_next >= 0) load_tile(v_tile, vbase, row_stride, key_next, len, lane);
     cp_async_commit();
     j = jn;
-    blk = blk_next;
+    half = hn;
+    blk = bn;
+    key0 = key_next;
   }
   cp_async_wait<0>();
   l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
@@ -305,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
     }
   }
   __syncthreads();
-  float* dst = p.partial + ((((int64_t)b * p.heads_k + h) * kSplits + split) * 16) * kPartialFloats;
+  float* dst = p.partial + ((((int64_t)b * p.heads_k + h) * p.splits + split) * 16) * kPartialFloats;
   for (int i = threadIdx.x; i < 16 * kPartialFloats; i += kThreads) {
     const int row = i / kPartialFloats, c = i - row * kPartialFloats;
     float mw[kWarps], mmax = -INFINITY;
@@ -328,20 +350,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeP
   }
 }
 
-// one CTA per (sequence, KV head): merge the kSplits partials, normalise, write bf16 + lse
+// one CTA per (sequence, KV head): merge the per-split partials, normalise, write bf16 + lse
 __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams p) {
   const int h = blockIdx.x, b = blockIdx.y;
   const int row = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
-  const float* src = p.partial + (((int64_t)b * p.heads_k + h) * kSplits * 16 + row) * kPartialFloats;
-  float ms[kSplits], mmax = -INFINITY;
+  const float* src = p.partial + (((int64_t)b * p.heads_k + h) * p.splits * 16 + row) * kPartialFloats;
+  float ms[kMaxSplits], mmax = -INFINITY;
 #pragma unroll
-  for (int s = 0; s < kSplits; ++s) {
-    ms[s] = src[(size_t)s * 16 * kPartialFloats + kHeadDim];
+  for (int s = 0; s < kMaxSplits; ++s) {
+    ms[s] = (s < p.splits) ? src[(size_t)s * 16 * kPartialFloats + kHeadDim] : -INFINITY;
     mmax = fmaxf(mmax, ms[s]);
   }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, lsum = 0.f;
 #pragma unroll
-  for (int s = 0; s < kSplits; ++s) {
+  for (int s = 0; s < kMaxSplits; ++s) {
+    if (s >= p.splits) break;
     const float f = (ms[s] == -INFINITY) ? 0.f : exp2f(ms[s] - mmax);
     const float* ps = src + (size_t)s * 16 * kPartialFloats;
     lsum += f * ps[kHeadDim + 1];
@@ -370,7 +393,7 @@ using namespace ifv2;
 extern "C" int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_dim, int max_blocks) {
   (void)max_blocks;
   if (batch < 0 || heads_q < 0 || head_dim != kHeadDim) return 0;
-  return (int64_t)batch * heads_q * kSplits * kPartialFloats * 4 + 256;
+  return (int64_t)batch * heads_q * kMaxSplits * kPartialFloats * 4 + 256;
 }
 
 extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new,
@@ -418,14 +441,20 @@ extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const vo
   p.heads_k = heads_k;
   p.batch_stride = cache_batch_stride;
   p.scale_log2 = softmax_scale * kLog2e;
+  // about four waves of two CTAs per SM over the whole launch
+  // (a power of two, so that top-k lists of 32 / 64 blocks divide evenly over CTAs and warps)
+  int splits = 1;
+  while (splits < kMaxSplits && (int64_t)2 * splits * batch * heads_k <= 8 * kNumSMs) splits *= 2;
+  p.splits = splits;
   p.partial = static_cast<float*>(workspace);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.lse = lse;
-  const size_t smem = (size_t)kWarps * 32768;
+  const size_t smem = (size_t)kWarps * kWarpSmem > (size_t)kWarps * 16 * kPartialFloats * 4
+                          ? (size_t)kWarps * kWarpSmem : (size_t)kWarps * 16 * kPartialFloats * 4;
   cudaError_t e = cudaFuncSetAttribute(decode_split_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error((int)e, "decode: %s", cudaGetErrorString(e));
-  decode_split_kernel<<<dim3(kSplits, heads_k, batch), kThreads, smem, st>>>(p);
+  decode_split_kernel<<<dim3(p.splits, heads_k, batch), kThreads, smem, st>>>(p);
   int rc = check_launch("decode_split");
   if (rc) return rc;
   decode_combine_kernel<<<dim3(heads_k, batch), 256, 0, st>>>(p);
