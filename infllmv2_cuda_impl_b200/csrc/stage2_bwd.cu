@@ -21,7 +21,9 @@ namespace {
 using namespace tc;
 
 constexpr int kTokPerTile = 8;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9: two softmax groups, each takes
+                                    // 32 of a block's 64 key columns for all 128 rows (no row reductions
+                                    // are needed in the backward, so the halves are independent)
 constexpr int kMaxMaskWords = 128;
 constexpr uint32_t kTileHalfBytes = 128 * 128;   // 128 rows x 64 bf16
 constexpr uint32_t kKVHalfBytes = 64 * 128;      // 64 keys x 64 bf16
@@ -161,7 +163,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
       mbar_init(&sm.sdp_full[s], 1);
-      mbar_init(&sm.ds_ready[s], 4);         // one arrival per softmax warp
+      mbar_init(&sm.ds_ready[s], 8);         // one arrival per softmax warp
     }
     mbar_init(&sm.dq_final, 1);
     fence_barrier_init();
@@ -269,6 +271,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
     }
   } else {
     const int quad = warp & 3;
+    const int grp = (warp - 2) >> 2;                 // softmax warp group: which 32 key columns
     const int r = quad * 32 + lane;
     const int tl = r >> 4, g = r & 15;
     const int tok = tok0 + tl;
@@ -293,13 +296,14 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       bool selected = valid;
       if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
       const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
-      uint32_t packed[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      uint32_t packed[16];
+      {
+        const int half = grp;                          // this warp group's 32 key columns
         uint32_t sv[32], dpv[32];
         tmem_ld32(tmem + lane_off + s * 128 + half * 32, sv);
         tmem_ld32(tmem + lane_off + s * 128 + 64 + half * 32, dpv);
-        tmem_wait_ld();
+        tmem_wait_ld_dep(sv);
+        tmem_wait_ld_dep(dpv);
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           float ds[2];
@@ -309,10 +313,10 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
             const float d = pr * (__uint_as_float(dpv[c + e]) - dsum);
             ds[e] = (half * 32 + c + e < lim) ? d : 0.f;
           }
-          packed[half * 16 + (c >> 1)] = pack_bf16(ds[0], ds[1]);
+          packed[c >> 1] = pack_bf16(ds[0], ds[1]);
         }
       }
-      tmem_st32(tmem + lane_off + s * 128, packed);
+      tmem_st16(tmem + lane_off + s * 128 + grp * 16, packed);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&sm.ds_ready[s]);
@@ -324,7 +328,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
     if (ok) {
       __nv_bfloat16* orow = p.dq + ((int64_t)(q0 + tok) * p.heads_q + h * kGroup + g) * kHeadDim;
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
+      for (int c = grp * 64; c < grp * 64 + 64; c += 32) {
         uint32_t o[32];
         if (n_blocks > 0) {
           tmem_ld32(tmem_dq + lane_off + c, o);
@@ -434,9 +438,9 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.qdo_full[s], 1);
       mbar_init(&sm.qdo_empty[s], 1);
       mbar_init(&sm.sdp_full[s], 1);
-      mbar_init(&sm.sdp_empty[s], 4);
+      mbar_init(&sm.sdp_empty[s], 8);
     }
-    mbar_init(&sm.pds_ready, 4);
+    mbar_init(&sm.pds_ready, 8);
     mbar_init(&sm.pds_empty, 1);
     mbar_init(&sm.acc_final, 1);
     fence_barrier_init();
@@ -548,6 +552,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
     }
   } else {
     const int quad = warp & 3;
+    const int grp = (warp - 2) >> 2;                 // softmax warp group: which 32 key columns
     const int r = quad * 32 + lane;
     const int tl = r >> 4, g = r & 15;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
@@ -573,13 +578,14 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
                                                abort_flag, p.status, 86));
         if (!ok) break;
         tc_fence_after();
-        uint32_t pp[32], dd[32];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        uint32_t pp[16], dd[16];
+        {
+          const int half = grp;                        // this warp group's 32 key columns
           uint32_t sv[32], dpv[32];
           tmem_ld32(tmem + lane_off + s * 128 + half * 32, sv);
           tmem_ld32(tmem + lane_off + s * 128 + 64 + half * 32, dpv);
-          tmem_wait_ld();
+          tmem_wait_ld_dep(sv);
+          tmem_wait_ld_dep(dpv);
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
             float pr[2], ds[2];
@@ -590,8 +596,8 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
               pr[e] = vis ? x : 0.f;
               ds[e] = vis ? x * (__uint_as_float(dpv[c + e]) - dsum) : 0.f;
             }
-            pp[half * 16 + (c >> 1)] = pack_bf16(pr[0], pr[1]);
-            dd[half * 16 + (c >> 1)] = pack_bf16(ds[0], ds[1]);
+            pp[c >> 1] = pack_bf16(pr[0], pr[1]);
+            dd[c >> 1] = pack_bf16(ds[0], ds[1]);
           }
         }
         tc_fence_before();
@@ -606,8 +612,8 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         uint8_t* prow = sm.pmat + r * 128;
         uint8_t* drow = sm.dsmat + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int pc = (c ^ (r & 7)) << 4;
+        for (int c = 0; c < 4; ++c) {                  // this group's four 16-byte chunks of the row
+          const int pc = ((grp * 4 + c) ^ (r & 7)) << 4;
           *reinterpret_cast<uint4*>(prow + pc) =
               make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
           *reinterpret_cast<uint4*>(drow + pc) =
@@ -627,8 +633,8 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       __nv_bfloat16* dv_base = p.dv + ((int64_t)(k0 + n * kBlockN) * p.heads_k + h) * kHeadDim + d;
       __nv_bfloat16* dk_base = p.dk + ((int64_t)(k0 + n * kBlockN) * p.heads_k + h) * kHeadDim + d;
       const int64_t key_stride = (int64_t)p.heads_k * kHeadDim;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
+      {
+        const int c0 = grp * 32;
         uint32_t a[32], bb[32];
         if (steps > 0) {
           tmem_ld32(tmem_dv + lane_off + c0, a);

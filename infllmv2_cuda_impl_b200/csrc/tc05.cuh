@@ -166,6 +166,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
 // tcgen05.wait::ld that also names the destination registers of the load it completes, so that
 // no use of those registers can be scheduled ahead of the wait.
 __device__ __forceinline__ void tmem_wait_ld_dep(uint32_t (&r)[32]) {
@@ -210,6 +220,21 @@ __device__ __forceinline__ uint64_t umma_desc_noswz16(uint32_t smem_addr) {
   d |= (uint64_t)(128u >> 4) << 16;
   d |= (uint64_t)(256u >> 4) << 32;
   d |= 1ull << 46;                        // layout type 0 = no swizzle
+  return d;
+}
+
+// The same (rows x 16) bf16 K-major operand with the 32-byte swizzle: rows of 32 bytes, the two
+// 16-byte halves of a row swapped when bit 2 of the row index is set; 8-row groups 256 B apart.
+__device__ __forceinline__ uint32_t umma_sw32_off(int row, int col) {
+  return (uint32_t)(row * 32 + (((col >> 3) ^ ((row >> 2) & 1)) << 4) + (col & 7) * 2);
+}
+__device__ __forceinline__ uint64_t umma_desc_sw32(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)1u << 16;
+  d |= (uint64_t)(256u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 6ull << 61;                        // layout type 6 = 32-byte swizzle
   return d;
 }
 

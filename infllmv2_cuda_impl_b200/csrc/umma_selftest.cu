@@ -14,6 +14,8 @@ struct SelfTestParams {
   const __nv_bfloat16* b;   // mode 4: B read with plain loads
   float* d;                 // (128, n) fp32
   int mode;
+  int iters;                // the product is issued this many times (rate measurement)
+  long long* cycles;        // optional: SM cycles from first issue to completion
   int32_t* status;
 };
 
@@ -21,6 +23,7 @@ struct SelfTestParams {
 // mode 1: D(128x128) = A(128x64,  K-major) * Bt(64x128, MN-major)      [the P.V shape, P in smem]
 // mode 2: D(128x128) = A(128x64 in TMEM)   * Bt(64x128, MN-major)      [the P.V shape, P in TMEM]
 // mode 3: D(128x64)  = At(128x128, MN-major)^T * Bt(128x64, MN-major)  [the dO^T.P shape of the backward]
+// mode 5: as mode 4 with the 32-byte swizzle
 // mode 4: D(128x64)  = A(128x16) * B(64x16)^T, both K-major WITHOUT swizzle, written by threads
 //                                                                        [the row-constant K step of stage 1]
 __global__ void __launch_bounds__(128)
@@ -51,8 +54,18 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
-  const int n = (p.mode == 0 || p.mode == 3 || p.mode == 4) ? 64 : 128;
-  if (p.mode == 4) {
+  const int alt = p.mode >= 10 ? 1 : 0;      // rate-only variants: alternate between two accumulators
+  const int mode = p.mode >= 10 ? p.mode - 10 : p.mode;
+  const bool sw32 = p.mode == 5;               // mode 5 = mode 4 with the 32-byte swizzle
+  const int n = (mode == 0 || mode == 3 || mode == 4 || mode == 5) ? 64 : 128;
+  if (sw32) {
+    for (int i = threadIdx.x; i < 128 * 16; i += 128)
+      *reinterpret_cast<__nv_bfloat16*>(sA + umma_sw32_off(i >> 4, i & 15)) = p.a[i];
+    for (int i = threadIdx.x; i < 64 * 16; i += 128)
+      *reinterpret_cast<__nv_bfloat16*>(sB + umma_sw32_off(i >> 4, i & 15)) = p.b[i];
+    fence_proxy_async_smem();
+  }
+  if (mode == 4) {
     for (int i = threadIdx.x; i < 128 * 16; i += 128)
       *reinterpret_cast<__nv_bfloat16*>(sA + umma_noswz16_off(i >> 4, i & 15)) = p.a[i];
     for (int i = threadIdx.x; i < 64 * 16; i += 128)
@@ -60,7 +73,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
     fence_proxy_async_smem();
   }
 
-  if (p.mode == 2) {   // every thread stores its A row into TMEM as packed bf16 pairs
+  if (mode == 2) {   // every thread stores its A row into TMEM as packed bf16 pairs
     uint32_t regs[32];
     const uint32_t* row = reinterpret_cast<const uint32_t*>(p.a + (size_t)threadIdx.x * 64);
 #pragma unroll
@@ -71,22 +84,23 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   }
   __syncthreads();
 
-  if (warp == 0 && elect_one()) {
+  long long t_start = 0;
+  if (warp == 0 && lane == 0) {
     tc_fence_after();
-    if (p.mode == 4) {
+    if (mode == 4 || mode == 5) {
       mbar_arrive(&bar_load);                                 // nothing to fetch
-    } else if (p.mode == 0) {
+    } else if (mode == 0) {
       mbar_expect_tx(&bar_load, 2 * 16384 + 2 * 8192);
       tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);
       tma_load_3d(sA + 16384, &map_a, &bar_load, 64, 0, 0);
       tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);
       tma_load_3d(sB + 8192, &map_b, &bar_load, 64, 0, 0);
-    } else if (p.mode == 3) {
+    } else if (mode == 3) {
       mbar_expect_tx(&bar_load, 2 * 16384 + 16384);
       tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);            // At rows 0..127, M columns 0..63
       tma_load_3d(sA + 16384, &map_a, &bar_load, 64, 0, 0);   //                  M columns 64..127
       tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);            // Bt rows 0..127, N columns 0..63
-    } else if (p.mode == 1) {
+    } else if (mode == 1) {
       mbar_expect_tx(&bar_load, 16384 + 2 * 8192);
       tma_load_3d(sA, &map_a, &bar_load, 0, 0, 0);
       tma_load_3d(sB, &map_b, &bar_load, 0, 0, 0);
@@ -98,19 +112,24 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     if (mbar_wait(&bar_load, 0, &abort_flag, p.status, 1)) {
       tc_fence_after();
-      if (p.mode == 4) {
+      t_start = clock64();
+      for (int it = 0; it < p.iters; ++it) {
+      if (mode == 5) {
+        umma_ss(tmem_d, umma_desc_sw32(smem_u32(sA)), umma_desc_sw32(smem_u32(sB)),
+                umma_idesc_bf16(128, 64, false), false);
+      } else if (mode == 4) {
         umma_ss(tmem_d, umma_desc_noswz16(smem_u32(sA)), umma_desc_noswz16(smem_u32(sB)),
                 umma_idesc_bf16(128, 64, false), false);
-      } else if (p.mode == 0) {
+      } else if (mode == 0) {
         const uint32_t idesc = umma_idesc_bf16(128, 64, false);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + off, 16, 1024),
+          umma_ss(tmem_d + (alt ? (kk & 1) * 64 : 0), umma_desc_sw128(smem_u32(sA) + off, 16, 1024),
                   umma_desc_sw128(smem_u32(sB) + offb, 16, 1024), idesc, kk > 0);
         }
-      } else if (p.mode == 3) {
+      } else if (mode == 3) {
         const uint32_t idesc = umma_idesc_bf16(128, 64, true, true);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
@@ -121,11 +140,13 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t bdesc = umma_desc_sw128(smem_u32(sB) + kk * 2048, 8192, 1024);
-          if (p.mode == 1)
-            umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + kk * 32, 16, 1024), bdesc, idesc, kk > 0);
+          if (mode == 1)
+            umma_ss(tmem_d + (alt ? (kk & 1) * 128 : 0), umma_desc_sw128(smem_u32(sA) + kk * 32, 16, 1024),
+                    bdesc, idesc, kk > 0);
           else
             umma_ts(tmem_d, tmem_a + kk * 8, bdesc, idesc, kk > 0);
         }
+      }
       }
       umma_commit(&bar_mma);
     }
@@ -133,6 +154,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncwarp();
   const bool ok = mbar_wait(&bar_mma, 0, &abort_flag, p.status, 2);
   tc_fence_after();
+  if (threadIdx.x == 0 && p.cycles != nullptr) *p.cycles = clock64() - t_start;
   if (ok) {
     for (int c = 0; c < n; c += 32) {
       uint32_t regs[32];
@@ -157,17 +179,34 @@ using namespace ifv2;
 //   mode 0: a (128,128), b (64,128)  -> d (128,64);  modes 1, 2: a (128,64), b (64,128) -> d (128,128)
 //   mode 3: a (128,128) = At, b (128,64) = Bt -> d = At^T . Bt (128,64)
 //   mode 4: a (128,16), b (64,16) -> d = a . b^T (128,64)
+static int selftest_impl(int mode, const void* a, const void* b, float* d, int32_t* status,
+                         void* stream, int iters, long long* cycles);
+
 extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float* d, int32_t* status,
                                   void* stream) {
-  IFV2_REQUIRE(mode >= 0 && mode <= 4, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0..4");
+  return selftest_impl(mode, a, b, d, status, stream, 1, nullptr);
+}
+
+// Same tile product issued `iters` times back to back (the accumulator is simply overwritten /
+// re-accumulated): `cycles` receives the SM clock count from the first issue to completion, which
+// gives the sustained rate of one MMA shape / operand arrangement on a single SM.
+extern "C" int ifv2_selftest_umma_rate(int mode, const void* a, const void* b, float* d,
+                                       int32_t* status, void* stream, int iters, long long* cycles) {
+  return selftest_impl(mode, a, b, d, status, stream, iters, cycles);
+}
+
+static int selftest_impl(int mode, const void* a, const void* b, float* d, int32_t* status,
+                         void* stream, int iters, long long* cycles) {
+  IFV2_REQUIRE((mode >= 0 && mode <= 5) || mode == 10 || mode == 11, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0..4");
   IFV2_REQUIRE(a && b && d && status, IFV2_ERR_INVALID_ARG, "selftest: null pointer");
   CUtensorMap map_a, map_b;
   int rc;
-  if (mode == 0) {
+  const int base_mode = mode >= 10 ? mode - 10 : mode;
+  if (base_mode == 0) {
     rc = make_tensor_map_bf16_3d(&map_a, a, 128, 128, 1, 256, 256 * 128, 64, 128, 1);
     if (rc) return rc;
     rc = make_tensor_map_bf16_3d(&map_b, b, 128, 64, 1, 256, 256 * 64, 64, 64, 1);
-  } else if (mode == 4) {       // operands are written by threads; the maps are not used
+  } else if (mode == 4 || mode == 5) {       // operands are written by threads; the maps are not used
     rc = make_tensor_map_bf16_3d(&map_a, d, 64, 128, 1, 128, 128 * 128, 64, 128, 1);
     if (rc) return rc;
     rc = make_tensor_map_bf16_3d(&map_b, d, 64, 128, 1, 128, 128 * 128, 64, 128, 1);
@@ -185,7 +224,7 @@ extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float*
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 50 * 1024);
   if (attr != cudaSuccess) return set_error((int)attr, "selftest: %s", cudaGetErrorString(attr));
   SelfTestParams p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, mode,
-                   status};
+                   iters < 1 ? 1 : iters, cycles, status};
   umma_selftest_kernel<<<1, 128, 50 * 1024, (cudaStream_t)stream>>>(map_a, map_b, p);
   return check_launch("umma_selftest");
 }

@@ -133,3 +133,60 @@ def sharded_prefill(q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch
                                local_blocks, ops, stride=stride)
         outs.append(out)
     return torch.cat(outs, dim=0)
+
+
+class StreamedPrefill:
+    """Prefill of one sequence whose q / k / v / compressed k live in pinned HOST memory, result to
+    pinned host memory: the query is processed in chunks (each an ordinary seqlen_q < seqlen_k call,
+    as in `prefill_chunk`), and the host->device copy of chunk i+1, the kernels of chunk i and the
+    device->host copy of chunk i-1 run on three streams, so a step costs about
+    max(copy in, compute, copy out) instead of their sum.  Device buffers are allocated once."""
+
+    def __init__(self, seqlen: int, heads_q: int, heads_k: int, head_dim: int, n_comp: int,
+                 device, chunk_tokens: int = 16384, dtype=torch.bfloat16):
+        if seqlen % chunk_tokens != 0 or chunk_tokens % 64 != 0:
+            raise ValueError("seqlen must be a multiple of chunk_tokens, itself a multiple of 64")
+        self.seqlen, self.chunk = seqlen, chunk_tokens
+        self.device = torch.device(device)
+        self.q = torch.empty(seqlen, heads_q, head_dim, dtype=dtype, device=device)
+        self.k = torch.empty(seqlen, heads_k, head_dim, dtype=dtype, device=device)
+        self.v = torch.empty_like(self.k)
+        self.kc = torch.empty(n_comp, heads_k, head_dim, dtype=dtype, device=device)
+        self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def __call__(self, q_host, k_host, v_host, kc_host, out_host, topk: int, init_blocks: int,
+                 local_blocks: int, ops: Optional[PrefillOps] = None):
+        """Enqueue one full prefill; returns when everything is ENQUEUED (synchronise the device, or
+        the returned event, before reading out_host)."""
+        main = torch.cuda.current_stream(self.device)
+        n = self.seqlen // self.chunk
+        self.s_in.wait_stream(main)
+        self.s_out.wait_stream(main)
+        ev_in = []
+        with torch.cuda.stream(self.s_in):
+            self.kc.copy_(kc_host, non_blocking=True)
+            self.k.copy_(k_host, non_blocking=True)
+            self.v.copy_(v_host, non_blocking=True)
+            for c in range(n):
+                sl = slice(c * self.chunk, (c + 1) * self.chunk)
+                self.q[sl].copy_(q_host[sl], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.s_in)
+                ev_in.append(ev)
+        keep = []
+        for c in range(n):
+            ch = Chunk(c, c * self.chunk, (c + 1) * self.chunk)
+            main.wait_event(ev_in[c])
+            out, _ = prefill_chunk(self.q[ch.start:ch.end], self.kc, self.k, self.v, ch, topk,
+                                   init_blocks, local_blocks, ops)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            self.s_out.wait_event(ev)
+            with torch.cuda.stream(self.s_out):
+                out_host[ch.start:ch.end].copy_(out, non_blocking=True)
+            out.record_stream(self.s_out)
+            keep.append(out)
+        done = torch.cuda.Event()
+        done.record(self.s_out)
+        main.wait_event(done)
+        return done

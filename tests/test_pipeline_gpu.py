@@ -57,3 +57,21 @@ def test_query_chunk_equals_full_run():
         rows = (idx == full_idx[:, ch.start:ch.end]).all(dim=-1).all(dim=0)
         err = (out.float() - full_out[ch.start:ch.end].float()).abs()[rows].max().item()
         assert err <= 2e-2, err
+
+
+def test_streamed_prefill_from_host_equals_resident_run():
+    L, hq, hk, d, topk = 2048, 32, 2, 128, 8
+    q = det_tensor((L, hq, d), 11, 0.5).pin_memory()
+    k = det_tensor((L, hk, d), 12, 0.5).pin_memory()
+    v = det_tensor((L, hk, d), 13).pin_memory()
+    kc = oracle.compress_keys(k, [0, L])[0].pin_memory()
+    out_host = torch.empty_like(q).pin_memory()
+    runner = sharding.StreamedPrefill(L, hq, hk, d, kc.shape[0], DEV, chunk_tokens=512)
+    for _ in range(2):                                   # second call reuses the device buffers
+        runner(q, k, v, kc, out_host, topk, 1, 2)
+        torch.cuda.synchronize()
+    infllm_v2.check_device_status()
+    outs = [sharding.prefill_chunk(q.to(DEV)[s:s + 512], kc.to(DEV), k.to(DEV), v.to(DEV),
+                                   sharding.Chunk(i, s, s + 512), topk, 1, 2)[0]
+            for i, s in enumerate(range(0, L, 512))]
+    assert torch.equal(out_host, torch.cat(outs).cpu())

@@ -8,14 +8,14 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 5])
 def test_umma_tile(lib, mode):
     g = torch.Generator().manual_seed(mode)
     if mode == 0:
         a = torch.randn(128, 128, generator=g).to(torch.bfloat16)
         b = torch.randn(64, 128, generator=g).to(torch.bfloat16)
         ref = a.float() @ b.float().t()
-    elif mode == 4:
+    elif mode in (4, 5):
         a = torch.randn(128, 16, generator=g).to(torch.bfloat16)
         b = torch.randn(64, 16, generator=g).to(torch.bfloat16)
         ref = a.float() @ b.float().t()
