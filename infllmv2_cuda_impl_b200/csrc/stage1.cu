@@ -160,32 +160,43 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
-    if (lane == 0 && n_steps > 0) {
+    // All 32 lanes run the same issue code (descriptors stay in uniform registers); `leader`
+    // enables the MMA / commit instructions in one lane only.
+    if (n_steps > 0) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128, false);
-      const uint32_t q_addr = smem_u32(sm.q[0]);
+      const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
+      const uint64_t kc_desc[2] = {umma_desc_sw128(smem_u32(sm.kc[0][0]), 16, 1024),
+                                   umma_desc_sw128(smem_u32(sm.kc[1][0]), 16, 1024)};
       const uint64_t d_ones = umma_desc_noswz16(smem_u32(sm.ones));
       const uint64_t d_rowc = umma_desc_noswz16(smem_u32(sm.rowc));
-      bool ok = mbar_wait(&sm.q_full, 0, abort_flag, p.status, 51);
+      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full, 0, abort_flag, p.status, 51));
       for (int t = 0; t < n_steps && ok; ++t) {
         const int s = t & 1;
         const uint32_t par = (uint32_t)((t >> 1) & 1);
         const bool pass2 = t >= n_tiles;
-        ok = mbar_wait(&sm.kc_full[s], par, abort_flag, p.status, 52);
-        if (ok && t >= 2) ok = mbar_wait(&sm.acc_empty[s], par ^ 1u, abort_flag, p.status, 53);
-        if (ok && t == n_tiles) ok = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
+        bool w = mbar_wait(&sm.kc_full[s], par, abort_flag, p.status, 52);
+        if (w && t >= 2) w = mbar_wait(&sm.acc_empty[s], par ^ 1u, abort_flag, p.status, 53);
+        if (w && t == n_tiles) w = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
+        ok = __all_sync(0xFFFFFFFFu, w);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t kc_addr = smem_u32(sm.kc[s][0]);
+        if (!pass2) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          const uint64_t dq = umma_desc_sw128(q_addr + off, 16, 1024);
-          const uint64_t dk = umma_desc_sw128(kc_addr + off, 16, 1024);
-          umma_ss(tmem + s * 128, pass2 ? dk : dq, pass2 ? dq : dk, idesc, kk > 0);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+            umma_ss_pred(tmem + s * 128, q_desc + off, kc_desc[s] + off, idesc, kk > 0, leader);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+            umma_ss_pred(tmem + s * 128, kc_desc[s] + off, q_desc + off, idesc, kk > 0, leader);
+          }
+          umma_ss_pred(tmem + s * 128, d_ones, d_rowc, idesc, true, leader);   // + row constant
         }
-        if (pass2) umma_ss(tmem + s * 128, d_ones, d_rowc, idesc, true);   // + row constant
-        umma_commit(&sm.kc_empty[s]);
-        umma_commit(&sm.acc_full[s]);
+        umma_commit_pred(&sm.kc_empty[s], leader);
+        umma_commit_pred(&sm.acc_full[s], leader);
       }
     }
   } else {

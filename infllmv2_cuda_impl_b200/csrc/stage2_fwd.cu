@@ -186,26 +186,33 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
-    if (lane == 0 && n_blocks > 0) {
+    // All 32 lanes run the same issue code (descriptors stay in uniform registers); `leader`
+    // enables the MMA / commit instructions in one lane only.
+    if (n_blocks > 0) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, true);
-      const uint32_t q_addr = smem_u32(sm.q[0]);
-      bool ok = mbar_wait(&sm.q_full, 0, abort_flag, p.status, 21);
+      const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
+      const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024),
+                                  umma_desc_sw128(smem_u32(sm.k[1][0]), 16, 1024)};
+      const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0][0]), kKVHalfBytes, 1024),
+                                  umma_desc_sw128(smem_u32(sm.v[1][0]), kKVHalfBytes, 1024)};
+      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full, 0, abort_flag, p.status, 21));
       auto issue_qk = [&](int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(&sm.k_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 22))
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.k_full[s], (uint32_t)((j >> 1) & 1), abort_flag,
+                                               p.status, 22)))
           return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sm.k[s][0]);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t qoff = (kk >> 2) * kQHalfBytes + (kk & 3) * 32;
           const uint32_t koff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
-          umma_ss(tmem + s * 64, umma_desc_sw128(q_addr + qoff, 16, 1024),
-                  umma_desc_sw128(k_addr + koff, 16, 1024), idesc_qk, kk > 0);
+          umma_ss_pred(tmem + s * 64, q_desc + (qoff >> 4), k_desc[s] + (koff >> 4), idesc_qk,
+                       kk > 0, leader);
         }
-        umma_commit(&sm.k_empty[s]);
-        umma_commit(&sm.s_full[s]);
+        umma_commit_pred(&sm.k_empty[s], leader);
+        umma_commit_pred(&sm.s_full[s], leader);
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -214,19 +221,17 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         const uint32_t par = (uint32_t)((i >> 1) & 1);
         if (i + 1 < n_blocks) ok = issue_qk(i + 1);
         if (!ok) break;
-        ok = mbar_wait(&sm.p_ready[s], par, abort_flag, p.status, 23) &&
-             mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 24);
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.p_ready[s], par, abort_flag, p.status, 23) &&
+                                         mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 24));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sm.v[s][0]);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem_o, tmem + s * 64 + kk * 8,
-                  umma_desc_sw128(v_addr + kk * 2048, kKVHalfBytes, 1024), idesc_pv,
-                  (i > 0) || (kk > 0));
-        umma_commit(&sm.v_empty[s]);
-        umma_commit(&sm.o_done);
-        if (i + 1 == n_blocks) umma_commit(&sm.o_final);
+          umma_ts_pred(tmem_o, tmem + s * 64 + kk * 8, v_desc[s] + ((kk * 2048) >> 4), idesc_pv,
+                       (i > 0) || (kk > 0), leader);
+        umma_commit_pred(&sm.v_empty[s], leader);
+        umma_commit_pred(&sm.o_done, leader);
+        if (i + 1 == n_blocks) umma_commit_pred(&sm.o_final, leader);
       }
     }
   } else {

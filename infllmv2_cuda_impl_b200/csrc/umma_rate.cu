@@ -1,0 +1,120 @@
+// Sustained issue rate of one tcgen05.mma shape / operand arrangement on a single SM.  One CTA,
+// warp 0 issues `iters` groups of four K=16 steps back to back into the same accumulator (operand
+// contents are irrelevant and left as zeros), one commit at the end; the cycle count between the
+// first issue and the completion gives clocks per MMA.  Everything that selects the variant is a
+// template parameter so the issue loop is straight-line code.  Test / tuning hook only.
+#include "tc05.cuh"
+
+namespace ifv2 {
+namespace {
+
+using namespace tc;
+
+enum : int { kSmemK = 0, kSmemMN = 1, kTmem = 2 };
+
+template <int kA, int kB, int kN, int kAccs>
+__global__ void __launch_bounds__(128)
+umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  uint8_t* sA = smem;              // 32 KB
+  uint8_t* sB = smem + 32768;      // 64 KB
+  __shared__ uint64_t bar_mma;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < (32768 + 65536) / 16; i += 128)
+    reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar_mma, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+  const uint32_t tmem_a = tmem + 448;          // 4 K steps x 8 columns
+  long long t_start = 0;
+  if (warp == 0) {
+    const uint32_t leader = (lane == 0) ? 1u : 0u;
+    constexpr uint32_t idesc = umma_idesc_bf16(128, kN, kB == kSmemMN, kA == kSmemMN);
+    // K-major: K step = 32 bytes inside the 128-byte row.  MN-major: K step = 16 rows = 2 KB,
+    // 64-element M/N groups 16 KB apart (64-row tiles stacked group after group).
+    const uint64_t da = (kA == kSmemMN) ? umma_desc_sw128(smem_u32(sA), 16384, 1024)
+                                        : umma_desc_sw128(smem_u32(sA), 16, 1024);
+    const uint64_t db = (kB == kSmemMN) ? umma_desc_sw128(smem_u32(sB), 16384, 1024)
+                                        : umma_desc_sw128(smem_u32(sB), 16, 1024);
+    constexpr uint32_t a_step = (kA == kSmemMN) ? 128 : 2, b_step = (kB == kSmemMN) ? 128 : 2;
+    t_start = clock64();
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint32_t d = tmem + ((kAccs > 1) ? (uint32_t)((kk % kAccs) * kN) : 0u);
+        if (kA == kTmem)
+          umma_ts_pred(d, tmem_a + kk * 8, db + b_step * kk, idesc, kk >= kAccs, leader);
+        else
+          umma_ss_pred(d, da + a_step * kk, db + b_step * kk, idesc, kk >= kAccs, leader);
+      }
+    }
+    umma_commit_pred(&bar_mma, leader);
+  }
+  __syncwarp();
+  mbar_wait(&bar_mma, 0, &abort_flag, status, 2);
+  tc_fence_after();
+  if (threadIdx.x == 0) *cycles = clock64() - t_start;
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+template <int kA, int kB, int kN, int kAccs>
+int launch_rate(int iters, long long* cycles, int32_t* status, cudaStream_t stream) {
+  auto kern = umma_rate_kernel<kA, kB, kN, kAccs>;
+  const int smem = 32768 + 65536 + 1024;
+  cudaError_t attr = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (attr != cudaSuccess) return set_error((int)attr, "umma_rate: %s", cudaGetErrorString(attr));
+  kern<<<1, 128, smem, stream>>>(iters, cycles, status);
+  return check_launch("umma_rate");
+}
+
+}  // namespace
+}  // namespace ifv2
+
+using namespace ifv2;
+
+// kind = 1000 * a + 100 * b + variant, a in {0: smem K-major, 1: smem MN-major, 2: TMEM},
+// b in {0: K-major, 1: MN-major}; variant selects N and the number of accumulators (see below).
+extern "C" int ifv2_umma_rate(int a, int b, int n, int accs, int iters, long long* cycles,
+                              int32_t* status, void* stream) {
+  IFV2_REQUIRE(cycles && status && iters > 0, IFV2_ERR_INVALID_ARG, "umma_rate: bad argument");
+  cudaStream_t s = (cudaStream_t)stream;
+#define IFV2_RATE_CASE(A, B, N, ACCS) \
+  if (a == A && b == B && n == N && accs == ACCS) return launch_rate<A, B, N, ACCS>(iters, cycles, status, s);
+  IFV2_RATE_CASE(0, 0, 64, 1)
+  IFV2_RATE_CASE(0, 0, 128, 1)
+  IFV2_RATE_CASE(0, 0, 256, 1)
+  IFV2_RATE_CASE(0, 1, 64, 1)
+  IFV2_RATE_CASE(0, 1, 128, 1)
+  IFV2_RATE_CASE(0, 1, 256, 1)
+  IFV2_RATE_CASE(0, 1, 128, 2)
+  IFV2_RATE_CASE(1, 0, 64, 1)
+  IFV2_RATE_CASE(1, 0, 128, 1)
+  IFV2_RATE_CASE(1, 1, 64, 1)
+  IFV2_RATE_CASE(1, 1, 128, 1)
+  IFV2_RATE_CASE(2, 0, 64, 1)
+  IFV2_RATE_CASE(2, 0, 128, 1)
+  IFV2_RATE_CASE(2, 0, 256, 1)
+  IFV2_RATE_CASE(2, 1, 64, 1)
+  IFV2_RATE_CASE(2, 1, 128, 1)
+  IFV2_RATE_CASE(2, 1, 256, 1)
+  IFV2_RATE_CASE(2, 1, 128, 2)
+#undef IFV2_RATE_CASE
+  return set_error(IFV2_ERR_INVALID_ARG, "umma_rate: variant not instantiated");
+}
