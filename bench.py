@@ -323,6 +323,28 @@ def _time_ms(fn, reps=5, warmup=2):
     return a.elapsed_time(b) / reps
 
 
+def config4_topk(device, pk, small=False):
+    """The top-k kernel alone at the row width of the 131072-token prefill (2048 block scores per
+    query row): one KV head's rows, scores shaped like the stage-1 output (block 0 and the 32
+    local blocks +inf, blocks past the query's own 0)."""
+    import infllm_v2
+    n_blk = 2048
+    rows = 32768 if small else 131072
+    first = 131072 - rows                        # the last `rows` tokens of the sequence
+    g = torch.Generator(device=device).manual_seed(0)
+    y = torch.rand(1, rows, n_blk, device=device, generator=g).to(torch.bfloat16)
+    bq = (torch.arange(rows, device=device) + first) // BLOCK
+    col = torch.arange(n_blk, device=device)
+    y[0].masked_fill_(col[None, :] > bq[:, None], 0.0)
+    y[0].masked_fill_((col[None, :] <= bq[:, None]) & (col[None, :] + LOCAL_BLOCKS >= bq[:, None]), float("inf"))
+    y[0, :, 0] = float("inf")
+    t = _time_ms(lambda: infllm_v2.infllmv2_topk(y, TOPK, cache_len=first))
+    b = rows * (n_blk * 2 + TOPK * 4)
+    return {"config4_topk_rows": {"rows": rows, "n_blocks": n_blk, "topk_ms": round(t, 4),
+                                  "topk_gbs": round(b / t / 1e6, 1),
+                                  "topk_frac": round(b / t / 1e6 / pk["hbm_gbs"], 4)}}
+
+
 def config3_topk(lens, hk, topk, seed):
     """Block lists of BASELINE config 3: per 64-token query block and KV head, block 0, the 32
     causal-local blocks and uniformly random earlier blocks up to `topk`, ascending, -1 tail."""
@@ -352,6 +374,8 @@ def extra_configs(device, pk, only=None, small=False):
     out = {}
     if only in (None, "selection"):
         out.update(config2_selection(device, pk, small))
+    if only in (None, "topk"):
+        out.update(config4_topk(device, pk, small))
     if only in (None, "train"):
         out.update(config3_train(device, pk, small))
     if only in (None, "decode"):
@@ -553,7 +577,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true",
                     help="run stage 1 and the max-pool as two kernels (the reference's op sequence)")
-    ap.add_argument("--only", default=None, choices=["selection", "train", "decode"],
+    ap.add_argument("--only", default=None, choices=["selection", "topk", "train", "decode"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
     ap.add_argument("--no-extras", action="store_true",

@@ -189,6 +189,10 @@ template <> struct Pack<__nv_bfloat16> {
   static __device__ __forceinline__ int hsum(T2 v) {
     return (int)(__bfloat162float(v.x) + __bfloat162float(v.y));
   }
+  // 0xFFFF in the half of the word whose comparison holds
+  static __device__ __forceinline__ uint32_t ge_mask(T2 a, T2 b) { return __hge2_mask(a, b); }
+  static __device__ __forceinline__ uint32_t gt_mask(T2 a, T2 b) { return __hgt2_mask(a, b); }
+  static __device__ __forceinline__ uint32_t eq_mask(T2 a, T2 b) { return __heq2_mask(a, b); }
 };
 template <> struct Pack<__half> {
   using T2 = __half2;
@@ -199,97 +203,78 @@ template <> struct Pack<__half> {
   static __device__ __forceinline__ int hsum(T2 v) {
     return (int)(__half2float(v.x) + __half2float(v.y));
   }
+  static __device__ __forceinline__ uint32_t ge_mask(T2 a, T2 b) { return __hge2_mask(a, b); }
+  static __device__ __forceinline__ uint32_t gt_mask(T2 a, T2 b) { return __hgt2_mask(a, b); }
+  static __device__ __forceinline__ uint32_t eq_mask(T2 a, T2 b) { return __heq2_mask(a, b); }
 };
 
-template <typename T, int kIters>
-__global__ void __launch_bounds__(kThreads) topk_select_kernel(const TopkParams p) {
+// Selection over the first kIts iterations (256 entries each) of a row held in registers; the
+// iteration count is a template parameter so that the probe and emit loops are straight-line
+// code.  Returns the number of entries emitted, or -1 when a restricted selection turns out not
+// to be equivalent to the full one.
+template <typename T, int kPairs, int kIts>
+__device__ __forceinline__ int topk_row(const typename Pack<T>::T2 (&v)[kPairs],
+                                        typename Pack<T>::T2 tail2, bool restricted, int k_sel,
+                                        int bq, int lane, int32_t* o) {
   using N = Num<T>;
   using P = Pack<T>;
   using T2 = typename P::T2;
-  constexpr int kPairs = kIters * 4;          // packed registers per lane
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t rows = (int64_t)p.heads * p.total_q;
-  const T* score = static_cast<const T*>(p.score);
-  const int n = p.n_blocks;
-  const int k_eff = min(p.k, n);
-  const bool aligned = (p.row_stride % 8 == 0) && (reinterpret_cast<uintptr_t>(p.score) % 16 == 0);
-  const T2 pad2 = P::splat(N::kNegInf);
-
-  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows;
-       row += (int64_t)gridDim.x * kWarps) {
-    const int64_t q = row % p.total_q;
-    int bq;
-    if (p.cu_q != nullptr) {
-      const int b = find_sequence(p.cu_q, p.batch, (int)q);
-      const int cl = p.cache_lens ? p.cache_lens[b] : p.cache_len;
-      bq = (int)((q - p.cu_q[b] + cl) / p.block_size);
+  // ---- bisection for the k_sel-th largest value over ordered keys [-inf, +inf]
+  uint32_t lo = bits_to_ordered(N::kNegInf), hi = bits_to_ordered(N::kPosInf) + 1u;
+  bool exact = false;                     // count(x >= val(lo)) == k_sel: no tie handling needed
+  while (hi - lo > 1u) {
+    const uint32_t mid = (lo + hi) >> 1;
+    const T2 c = P::splat(ordered_to_bits(mid));
+    T2 acc = P::zero();
+#pragma unroll
+    for (int it = 0; it < kIts; ++it) {
+      if (it < kIts) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc = __hadd2(acc, __hge2(v[it * 4 + j], c));
+      }
+    }
+    const int cnt = __reduce_add_sync(0xFFFFFFFFu, P::hsum(acc));
+    if (cnt >= k_sel) {
+      lo = mid;
+      if (cnt == k_sel) { exact = true; break; }
     } else {
-      bq = (int)((q + p.cache_len) / p.block_size);
+      hi = mid;
     }
-    const T* x = score + row * p.row_stride;
-    int32_t* o = p.out + row * p.k;
-
-    // ---- load: element index of (it, lane, slot) is (it*32 + lane)*8 + slot
-    T2 v[kPairs];
+  }
+  const T2 thr = P::splat(ordered_to_bits(lo));
+  if (restricted) {
+    // a later entry above the threshold would have displaced one of the selected ones
+    const float tm = fmaxf(N::to_f(tail2.x), N::to_f(tail2.y));
+    const bool bad = tm > N::to_f(thr.x);
+    if (__any_sync(0xFFFFFFFFu, bad)) return -1;        // redo over the full width
+  }
+  int need = 0;                           // how many entries equal to the threshold to take
+  if (!exact) {
+    T2 acc = P::zero();
 #pragma unroll
-    for (int it = 0; it < kIters; ++it) {
-      const int e0 = (it * 32 + lane) * 8;
-      if (aligned && e0 + 8 <= n) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + e0));
-        const T2* t = reinterpret_cast<const T2*>(&raw);
+    for (int it = 0; it < kIts; ++it) {
+      if (it < kIts) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[it * 4 + j] = t[j];
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          T2 pr = pad2;
-          if (e0 + 2 * j < n) pr.x = __ldg(x + e0 + 2 * j);
-          if (e0 + 2 * j + 1 < n) pr.y = __ldg(x + e0 + 2 * j + 1);
-          v[it * 4 + j] = pr;
-        }
+        for (int j = 0; j < 4; ++j) acc = __hadd2(acc, __hgt2(v[it * 4 + j], thr));
       }
     }
+    need = k_sel - __reduce_add_sync(0xFFFFFFFFu, P::hsum(acc));
+  }
 
-    // ---- bisection for the k-th largest value over ordered keys [-inf, +inf]
-    uint32_t lo = bits_to_ordered(N::kNegInf), hi = bits_to_ordered(N::kPosInf) + 1u;
-    bool exact = false;                       // count(x >= val(lo)) == k_eff: no tie handling needed
-    while (hi - lo > 1u) {
-      const uint32_t mid = (lo + hi) >> 1;
-      const T2 c = P::splat(ordered_to_bits(mid));
-      T2 acc = P::zero();
+  // ---- emit in index order
+  int base_gt = 0, base_tie = 0;          // counts over all earlier iterations
 #pragma unroll
-      for (int j = 0; j < kPairs; ++j) acc = __hadd2(acc, __hge2(v[j], c));
-      const int cnt = __reduce_add_sync(0xFFFFFFFFu, P::hsum(acc));
-      if (cnt >= k_eff) {
-        lo = mid;
-        if (cnt == k_eff) { exact = true; break; }
-      } else {
-        hi = mid;
-      }
-    }
-    const T2 thr = P::splat(ordered_to_bits(lo));
-    int need = 0;                             // how many entries equal to the threshold to take
-    if (!exact) {
-      T2 acc = P::zero();
-#pragma unroll
-      for (int j = 0; j < kPairs; ++j) acc = __hadd2(acc, __hgt2(v[j], thr));
-      need = k_eff - __reduce_add_sync(0xFFFFFFFFu, P::hsum(acc));
-    }
-
-    // ---- emit in index order
-    int base_gt = 0, base_tie = 0;            // counts over all earlier iterations
-#pragma unroll
-    for (int it = 0; it < kIters; ++it) {
-      uint32_t gt_bits = 0, tie_bits = 0;     // bit s: slot s of this lane's 8 elements
+  for (int it = 0; it < kIts; ++it) {
+    if (it < kIts) {
+      uint32_t gt_bits = 0, tie_bits = 0;   // bit s: slot s of this lane's 8 elements
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const T2 pr = v[it * 4 + j];
-        const float a = N::to_f(pr.x), b = N::to_f(pr.y), t = N::to_f(thr.x);
-        if (exact) {
-          gt_bits |= (uint32_t)(a >= t) << (2 * j) | (uint32_t)(b >= t) << (2 * j + 1);
-        } else {
-          gt_bits |= (uint32_t)(a > t) << (2 * j) | (uint32_t)(b > t) << (2 * j + 1);
-          tie_bits |= (uint32_t)(a == t) << (2 * j) | (uint32_t)(b == t) << (2 * j + 1);
+        const uint32_t mg = exact ? P::ge_mask(pr, thr) : P::gt_mask(pr, thr);
+        gt_bits |= ((mg & 1u) | ((mg >> 15) & 2u)) << (2 * j);
+        if (!exact) {
+          const uint32_t me = P::eq_mask(pr, thr);
+          tie_bits |= ((me & 1u) | ((me >> 15) & 2u)) << (2 * j);
         }
       }
       // packed inclusive scan over lanes: low 16 bits = taken-for-sure, high 16 = ties
@@ -305,22 +290,136 @@ __global__ void __launch_bounds__(kThreads) topk_select_kernel(const TopkParams 
       int gt_before = base_gt + (int)(excl & 0xFFFFu);
       int tie_before = base_tie + (int)(excl >> 16);
       const int e0 = (it * 32 + lane) * 8;
-#pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        const bool g = (gt_bits >> s) & 1u, t = (tie_bits >> s) & 1u;
-        if (g || (t && tie_before < need)) {
-          const int pos = gt_before + min(tie_before, need);
+      if (tie_bits == 0u) {               // the common case: walk the few set bits
+        int pos = gt_before + min(tie_before, need);
+        uint32_t sel = gt_bits;
+        while (sel) {
+          const int s = __ffs(sel) - 1;
+          sel &= sel - 1u;
           const int idx = e0 + s;
-          o[pos] = (idx <= bq) ? idx : -1;
+          o[pos++] = (idx <= bq) ? idx : -1;
         }
-        gt_before += g;
-        tie_before += t;
+      } else {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const bool g = (gt_bits >> s) & 1u, t = (tie_bits >> s) & 1u;
+          if (g || (t && tie_before < need)) {
+            const int pos = gt_before + min(tie_before, need);
+            const int idx = e0 + s;
+            o[pos] = (idx <= bq) ? idx : -1;
+          }
+          gt_before += g;
+          tie_before += t;
+        }
       }
       base_gt += (int)(total & 0xFFFFu);
       base_tie += (int)(total >> 16);
     }
-    // unused tail (k > n_blocks, or NaN scores that no probe counts)
-    for (int i = base_gt + min(base_tie, need) + lane; i < p.k; i += 32) o[i] = -1;
+  }
+  return base_gt + min(base_tie, need);
+}
+
+template <typename T, int kIters>
+__global__ void __launch_bounds__(kThreads, (kIters <= 8) ? 2 : 1) topk_select_kernel(const TopkParams p) {
+  using N = Num<T>;
+  using P = Pack<T>;
+  using T2 = typename P::T2;
+  constexpr int kPairs = kIters * 4;          // packed registers per lane
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)p.heads * p.total_q;
+  const T* score = static_cast<const T*>(p.score);
+  const int n = p.n_blocks;
+  const int k_eff = min(p.k, n);
+  const bool aligned = (p.row_stride % 8 == 0) && (reinterpret_cast<uintptr_t>(p.score) % 16 == 0);
+  const T2 pad2 = P::splat(N::kNegInf);
+  const T ninf = N::from_bits(N::kNegInf);
+
+  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows;
+       row += (int64_t)gridDim.x * kWarps) {
+    const int64_t q = row % p.total_q;
+    int bq;
+    if (p.cu_q != nullptr) {
+      const int b = find_sequence(p.cu_q, p.batch, (int)q);
+      const int cl = p.cache_lens ? p.cache_lens[b] : p.cache_len;
+      bq = (int)((q - p.cu_q[b] + cl) / p.block_size);
+    } else {
+      bq = (int)((q + p.cache_len) / p.block_size);
+    }
+    const T* x = score + row * p.row_stride;
+    int32_t* o = p.out + row * p.k;
+
+    // Entries past the query's own block only ever come out as -1.  When none of them beats the
+    // k-th best earlier entry (always the case for stage-1 block scores: later blocks hold 0 or
+    // -inf and ties go to the lower index) the selection can run over the earlier entries alone;
+    // that is checked after the fact, and a row that fails it is redone over the full width.
+    const int head = min(n, bq + 1);
+    int emitted = 0;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      const bool restricted = (attempt == 0) && head < n;
+      const int width = restricted ? head : n;              // entries that take part
+      const int its = (width + 255) >> 8;                   // 256 entries per iteration
+      const int k_sel = min(k_eff, width);
+
+      // ---- load: element index of (it, lane, slot) is (it*32 + lane)*8 + slot
+      T2 v[kPairs];
+#pragma unroll
+      for (int it = 0; it < kIters; ++it) {
+        const int e0 = (it * 32 + lane) * 8;
+        if (aligned && e0 + 8 <= n) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + e0));
+          const T2* t = reinterpret_cast<const T2*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[it * 4 + j] = t[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            T2 pr = pad2;
+            if (e0 + 2 * j < n) pr.x = __ldg(x + e0 + 2 * j);
+            if (e0 + 2 * j + 1 < n) pr.y = __ldg(x + e0 + 2 * j + 1);
+            v[it * 4 + j] = pr;
+          }
+        }
+      }
+      // ---- split off the entries past `width`: their maximum is kept, their slots become -inf
+      T2 tail2 = pad2;
+      if (restricted) {
+#pragma unroll
+        for (int it = 0; it < kIters; ++it) {
+          const int nh = width - (it * 32 + lane) * 8;      // entries of this lane that take part
+          if (nh < 8) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              T2 pr = v[it * 4 + j], tl = pad2;
+              if (2 * j >= nh) { tl.x = pr.x; pr.x = ninf; }
+              if (2 * j + 1 >= nh) { tl.y = pr.y; pr.y = ninf; }
+              tail2 = __hmax2(tail2, tl);
+              v[it * 4 + j] = pr;
+            }
+          }
+        }
+      }
+
+      // ---- bisection + emission over the `its` iterations that take part
+      int got = -1;
+      switch (its) {
+#define IFV2_TOPK_CASE(I)                                                                \
+        case I:                                                                          \
+          if constexpr (I <= kIters)                                                     \
+            got = topk_row<T, kPairs, I>(v, tail2, restricted, k_sel, bq, lane, o);      \
+          break;
+        IFV2_TOPK_CASE(0) IFV2_TOPK_CASE(1) IFV2_TOPK_CASE(2) IFV2_TOPK_CASE(3) IFV2_TOPK_CASE(4)
+        IFV2_TOPK_CASE(5) IFV2_TOPK_CASE(6) IFV2_TOPK_CASE(7) IFV2_TOPK_CASE(8)
+#undef IFV2_TOPK_CASE
+        default:
+          got = topk_row<T, kPairs, kIters>(v, tail2, restricted, k_sel, bq, lane, o);
+          break;
+      }
+      if (got < 0) continue;
+      emitted = got;
+      break;
+    }
+    // unused tail (k > entries that took part, or NaN scores that no probe counts)
+    for (int i = emitted + lane; i < p.k; i += 32) o[i] = -1;
   }
 }
 

@@ -35,6 +35,15 @@ constexpr int kKeysPerTile = 128;
 constexpr uint32_t kHalfBytes = 128 * 128;    // 128 rows x 64 bf16
 constexpr uint32_t kTmemCols = 256;
 constexpr int kPoolSlots = 136;               // 1 halo + 128 keys, padded
+#ifndef IFV2_STAGE1_POLY_STRIDE
+#define IFV2_STAGE1_POLY_STRIDE 8
+#endif
+// every kPolyStride-th exponential of a row runs on the FMA pipe (0: none)
+constexpr int kPolyStride = IFV2_STAGE1_POLY_STRIDE;
+__device__ __forceinline__ float exp2_mixed(float x, int c) {
+  return (kPolyStride > 0 && c % (kPolyStride > 0 ? kPolyStride : 1) == (kPolyStride - 1))
+             ? exp2_fma(x) : exp2f(x);
+}
 
 struct Stage1Params {
   __nv_bfloat16* out;             // scores, may be null when only block scores are wanted
@@ -64,6 +73,18 @@ struct Smem {
   uint32_t tmem_base;
   int abort_flag;
 };
+
+// Optional timeline of the first CTAs (a tuning aid, compiled in only with -DIFV2_S1_TRACE).
+#ifdef IFV2_S1_TRACE
+__device__ long long g_s1_trace[4][4][256][2];   // [CTA][role][step][event] = SM clock
+#define IFV2_TRACE(role, i, ev)                                                         \
+  do {                                                                                  \
+    if (blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (i) < 256) \
+      g_s1_trace[blockIdx.x][role][i][ev] = clock64();                                  \
+  } while (0)
+#else
+#define IFV2_TRACE(role, i, ev) do {} while (0)
+#endif
 
 // Number of leading compressed keys visible to local token i (C integer division, as the
 // reference's device code): key j covers tokens [16j, 16j+32) and the pattern is aligned to the
@@ -147,6 +168,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         if (t >= 2 && !mbar_wait(&sm.kc_empty[s], (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag,
                                  p.status, 41))
           break;
+        IFV2_TRACE(3, t, 0);
         mbar_expect_tx(&sm.kc_full[s], 2 * kHalfBytes);
         tma_load_3d(sm.kc[s][0], &map_kc, &sm.kc_full[s], 0, h, k0 + tile * kKeysPerTile);
         tma_load_3d(sm.kc[s][1], &map_kc, &sm.kc_full[s], 64, h, k0 + tile * kKeysPerTile);
@@ -176,11 +198,13 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const uint32_t par = (uint32_t)((t >> 1) & 1);
         const bool pass2 = t >= n_tiles;
         bool w = mbar_wait(&sm.kc_full[s], par, abort_flag, p.status, 52);
+        IFV2_TRACE(3, t, 1);
         if (w && t >= 2) w = mbar_wait(&sm.acc_empty[s], par ^ 1u, abort_flag, p.status, 53);
         if (w && t == n_tiles) w = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
         ok = __all_sync(0xFFFFFFFFu, w);
         if (!ok) break;
         tc_fence_after();
+        IFV2_TRACE(0, t, 0);
         if (!pass2) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -197,6 +221,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
         umma_commit_pred(&sm.kc_empty[s], leader);
         umma_commit_pred(&sm.acc_full[s], leader);
+        IFV2_TRACE(0, t, 1);
       }
     }
   } else {
@@ -219,6 +244,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                                abort_flag, p.status, 61));
         if (!ok) break;
         tc_fence_after();
+        if (quad == 2) IFV2_TRACE(1 + grp, t, 0);
         // visible columns among this group's 64
         const int lim = min(max(lim_row - t * kKeysPerTile - grp * 64, 0), 64);
         const bool full = __all_sync(0xFFFFFFFFu, lim == 64);
@@ -244,7 +270,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 32; ++c)
-              sum[c & 3] += exp2f(fmaf(__uint_as_float(x[c]), p.scale_log2, neg));
+              sum[c & 3] += exp2_mixed(fmaf(__uint_as_float(x[c]), p.scale_log2, neg), c);
             const float f = (m > -INFINITY) ? exp2f(fmaf(m, p.scale_log2, neg)) : 0.f;
             l = l * f + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
             m = m_new;
@@ -252,6 +278,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
         tc_fence_before();
         mbar_arrive_warp(&sm.acc_empty[s]);
+        if (quad == 2) IFV2_TRACE(1 + grp, t, 1);
       }
       // merge the two column halves of every row, then publish the row constant for pass 2, in
       // units of the raw score: -(m + log2(l) / c), as three bf16 terms
@@ -318,6 +345,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                                abort_flag, p.status, 62));
         if (!ok) break;
         tc_fence_after();
+        if (quad == 2) IFV2_TRACE(1 + grp, t, 0);
         const int key = tile * kKeysPerTile + r;
         float val[kTokPerThread];
         uint32_t buf[2][32];
@@ -332,8 +360,8 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             float a0 = 0.f, a1 = 0.f;
 #pragma unroll
             for (int g = 0; g < 16; g += 2) {
-              a0 += exp2f(__uint_as_float(x[half * 16 + g]) * p.scale_log2);
-              a1 += exp2f(__uint_as_float(x[half * 16 + g + 1]) * p.scale_log2);
+              a0 += exp2_mixed(__uint_as_float(x[half * 16 + g]) * p.scale_log2, g);
+              a1 += exp2_mixed(__uint_as_float(x[half * 16 + g + 1]) * p.scale_log2, g + 1);
             }
             val[ch * 2 + half] = a0 + a1;
           }
@@ -359,6 +387,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // (after the deferred pooling reads: this arrival is what lets a later tile reuse them)
         tc_fence_before();
         mbar_arrive_warp(&sm.acc_empty[s]);
+        if (quad == 2) IFV2_TRACE(1 + grp, t, 1);
       }
       if (ok && kPooled && n_tiles > 0) ok = pool_tile(n_tiles - 1);
       // columns past the last tile are zero (rows are 16-byte aligned: stride % 8 == 0)
@@ -394,6 +423,16 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
+
+#ifdef IFV2_S1_TRACE
+}  // namespace
+}  // namespace ifv2
+extern "C" int ifv2_debug_s1_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, ifv2::g_s1_trace, sizeof(long long) * 4 * 4 * 256 * 2);
+}
+namespace ifv2 {
+namespace {
+#endif
 
 int launch_stage1(const void* q, const void* kc, void* out, void* pooled,
                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,

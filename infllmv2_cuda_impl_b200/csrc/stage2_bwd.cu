@@ -221,34 +221,42 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_blocks > 0) {
+    // All 32 lanes run the same issue code (descriptors stay in uniform registers); `leader`
+    // enables the MMA / commit instructions in one lane only.
+    if (n_blocks > 0) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, true);
-      const uint32_t q_addr = smem_u32(sm.q[0]), do_addr = smem_u32(sm.dout[0]);
-      bool ok = mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 73);
+      const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
+      const uint64_t do_desc = umma_desc_sw128(smem_u32(sm.dout[0]), 16, 1024);
+      const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024);
+      const uint64_t k_desc0_mn = umma_desc_sw128(smem_u32(sm.k[0][0]), kKVHalfBytes, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sm.v[0][0]), 16, 1024);
+      constexpr uint32_t kStage = (2 * kKVHalfBytes) >> 4;     // descriptor address units per ring stage
+      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 73));
       auto issue_sdp = [&](int j) -> bool {
         const int s = j & 1, sk = j % 3;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
-        if (!mbar_wait(&sm.k_full[sk], (uint32_t)((j / 3) & 1), abort_flag, p.status, 74)) return false;
-        if (!mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75)) return false;
+        if (!__all_sync(0xFFFFFFFFu,
+                        mbar_wait(&sm.k_full[sk], (uint32_t)((j / 3) & 1), abort_flag, p.status, 74) &&
+                            mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75)))
+          return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sm.k[sk][0]), v_addr = smem_u32(sm.v[s][0]);
+        const uint64_t k_desc = k_desc0 + (uint32_t)sk * kStage, v_desc = v_desc0 + (uint32_t)s * kStage;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
-          umma_ss(tmem + s * 128, umma_desc_sw128(q_addr + aoff, 16, 1024),
-                  umma_desc_sw128(k_addr + boff, 16, 1024), idesc_s, kk > 0);
+          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
+          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
+          umma_ss_pred(tmem + s * 128, q_desc + aoff, k_desc + boff, idesc_s, kk > 0, leader);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
-          umma_ss(tmem + s * 128 + 64, umma_desc_sw128(do_addr + aoff, 16, 1024),
-                  umma_desc_sw128(v_addr + boff, 16, 1024), idesc_s, kk > 0);
+          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
+          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
+          umma_ss_pred(tmem + s * 128 + 64, do_desc + aoff, v_desc + boff, idesc_s, kk > 0, leader);
         }
-        umma_commit(&sm.v_empty[s]);
-        umma_commit(&sm.sdp_full[s]);
+        umma_commit_pred(&sm.v_empty[s], leader);
+        umma_commit_pred(&sm.sdp_full[s], leader);
         return true;
       };
       if (ok) ok = issue_sdp(0);
@@ -256,17 +264,17 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
         const int s = i & 1;
         if (i + 1 < n_blocks) ok = issue_sdp(i + 1);
         if (!ok) break;
-        ok = mbar_wait(&sm.ds_ready[s], (uint32_t)((i >> 1) & 1), abort_flag, p.status, 76);
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.ds_ready[s], (uint32_t)((i >> 1) & 1), abort_flag,
+                                               p.status, 76));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sm.k[i % 3][0]);
+        const uint64_t k_mn = k_desc0_mn + (uint32_t)(i % 3) * kStage;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem_dq, tmem + s * 128 + kk * 8,
-                  umma_desc_sw128(k_addr + kk * 2048, kKVHalfBytes, 1024), idesc_dq,
-                  (i > 0) || (kk > 0));
-        umma_commit(&sm.k_empty[i % 3]);
-        if (i + 1 == n_blocks) umma_commit(&sm.dq_final);
+          umma_ts_pred(tmem_dq, tmem + s * 128 + kk * 8, k_mn + ((kk * 2048) >> 4), idesc_dq,
+                       (i > 0) || (kk > 0), leader);
+        umma_commit_pred(&sm.k_empty[i % 3], leader);
+        if (i + 1 == n_blocks) umma_commit_pred(&sm.dq_final, leader);
       }
     }
   } else {

@@ -15,6 +15,11 @@
 // columns, shared memory 96 KB, so two CTAs share an SM and fill each other's bubbles.
 // The running max is only raised when it grows by more than 2^8 (the accumulator then needs a
 // rescale); P stays bounded by 256 and the final 1/l normalisation makes the result exact.
+// Measured with the optional timeline below: the tensor pipe is ~70 % busy and what bounds a
+// CTA is the latency of the chain S ready -> P ready -> P.V -> next Q.K^T on each S buffer
+// while the co-resident CTA competes for the tensor pipe and the exponential unit.  Splitting a
+// row over two threads (8 softmax warps, half-row maxima exchanged through shared memory) or
+// giving each S buffer its own warp group did not shorten that chain and ran 8-12 % slower.
 #include "tc05.cuh"
 
 namespace ifv2 {
@@ -56,6 +61,18 @@ struct Smem {
   int n_blocks;
   int abort_flag;
 };
+
+// Optional timeline of the first CTAs (a tuning aid, compiled in only with -DIFV2_FWD_TRACE).
+#ifdef IFV2_FWD_TRACE
+__device__ long long g_fwd_trace[4][3][256][4];   // [CTA][role][block][event] = SM clock
+#define IFV2_TRACE(role, i, ev)                                                         \
+  do {                                                                                  \
+    if (blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (i) < 256) \
+      g_fwd_trace[blockIdx.x][role][i][ev] = clock64();                                 \
+  } while (0)
+#else
+#define IFV2_TRACE(role, i, ev) do {} while (0)
+#endif
 
 // Highest-to-lowest walk over the set bits of the tile's union mask.
 struct BlockWalk {
@@ -204,6 +221,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                                                p.status, 22)))
           return false;
         tc_fence_after();
+        IFV2_TRACE(0, j, 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t qoff = (kk >> 2) * kQHalfBytes + (kk & 3) * 32;
@@ -213,6 +231,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         umma_commit_pred(&sm.k_empty[s], leader);
         umma_commit_pred(&sm.s_full[s], leader);
+        IFV2_TRACE(0, j, 1);
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -221,10 +240,12 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         const uint32_t par = (uint32_t)((i >> 1) & 1);
         if (i + 1 < n_blocks) ok = issue_qk(i + 1);
         if (!ok) break;
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.p_ready[s], par, abort_flag, p.status, 23) &&
-                                         mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 24));
+        // (V landed long ago: its wait goes first so that it is not paid after P is ready)
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 24) &&
+                                         mbar_wait(&sm.p_ready[s], par, abort_flag, p.status, 23));
         if (!ok) break;
         tc_fence_after();
+        IFV2_TRACE(0, i, 2);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts_pred(tmem_o, tmem + s * 64 + kk * 8, v_desc[s] + ((kk * 2048) >> 4), idesc_pv,
@@ -232,6 +253,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         umma_commit_pred(&sm.v_empty[s], leader);
         umma_commit_pred(&sm.o_done, leader);
         if (i + 1 == n_blocks) umma_commit_pred(&sm.o_final, leader);
+        IFV2_TRACE(0, i, 3);
       }
     }
   } else {
@@ -263,6 +285,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[s], par, abort_flag, p.status, 31));
       if (!ok) break;
       tc_fence_after();
+      if (warp == 2) IFV2_TRACE(1, i, 0);
 
       uint32_t raw[2][32];
       tmem_ld32(tmem + lane_off + s * 64, raw[0]);
@@ -304,6 +327,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         tmem_wait_st();
       }
+      if (warp == 2) IFV2_TRACE(1, i, 1);
       // rows that take nothing from this block get an exponent of -inf (P = 0) for every column
       const float neg_m = (lim == 0) ? -INFINITY : -m_ref * p.scale_log2;
       uint32_t packed[32];
@@ -320,8 +344,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       l += sum;
       tmem_st32(tmem + lane_off + s * 64, packed);
       tmem_wait_st();
+      if (warp == 2) IFV2_TRACE(1, i, 2);
       tc_fence_before();
       mbar_arrive_warp(&sm.p_ready[s]);
+      if (warp == 2) IFV2_TRACE(1, i, 3);
     }
 
     // ---- epilogue: O / l -> bf16, lse
@@ -373,6 +399,12 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 }  // namespace ifv2
 
 using namespace ifv2;
+
+#ifdef IFV2_FWD_TRACE
+extern "C" int ifv2_debug_fwd_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_fwd_trace, sizeof(long long) * 4 * 3 * 256 * 4);
+}
+#endif
 
 extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out,
                                     float* lse, const int64_t* fwd_mask, int mask_words,

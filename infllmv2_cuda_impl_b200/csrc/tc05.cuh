@@ -176,6 +176,48 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// 2^x evaluated on the FMA / ALU pipes instead of the special-function unit (which retires only 4
+// lanes per clock per scheduler): x is rounded to the nearest integer n with the 1.5 * 2^23 trick,
+// 2^(x - n) comes from a degree-3 polynomial on [-0.5, 0.5] (relative error 7.5e-5, far below one
+// bf16 ulp), and n is added to the exponent field.  Mixing a fraction of these into a loop of
+// ex2.approx calls raises the exponential throughput of an SM.
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -125.f);
+  const float fl = x + 12582912.f;
+  const float f = x - (fl - 12582912.f);
+  float pl = fmaf(0.055171460f, f, 0.24261086f);
+  pl = fmaf(pl, f, 0.69326097f);
+  pl = fmaf(pl, f, 0.99992812f);
+  return __int_as_float(__float_as_int(pl) + (__float_as_int(fl) << 23));
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// 8-column forms for rarely taken paths that must not raise the register peak.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7])
+      : "memory");
+}
+
 // tcgen05.wait::ld that also names the destination registers of the load it completes, so that
 // no use of those registers can be scheduled ahead of the wait.
 __device__ __forceinline__ void tmem_wait_ld_dep(uint32_t (&r)[32]) {

@@ -78,17 +78,20 @@ def compressed_range(chunk: Chunk, stride: int = 16) -> Tuple[int, int]:
 
 @dataclass
 class PrefillOps:
-    """The five operators of the prefill path; defaults are the CUDA ones."""
+    """The operators of the prefill path; defaults are the CUDA ones.  `block_scores`, when set,
+    replaces stage1 + max_pool by the fused kernel (same block scores, bit for bit)."""
     stage1: Callable
     max_pool: Callable
     topk: Callable
     attn: Callable
+    block_scores: Optional[Callable] = None
 
     @staticmethod
     def cuda() -> "PrefillOps":
         from . import attention, ops
         return PrefillOps(attention.infllmv2_attn_stage1, ops.max_pooling_1d, ops.infllmv2_topk,
-                          attention.infllmv2_attn_varlen_func)
+                          attention.infllmv2_attn_varlen_func,
+                          attention.infllmv2_stage1_block_scores)
 
 
 def prefill_chunk(q_chunk: torch.Tensor, kc: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
@@ -106,8 +109,12 @@ def prefill_chunk(q_chunk: torch.Tensor, kc: torch.Tensor, k: torch.Tensor, v: t
     cu_k = torch.tensor([0, lk], dtype=torch.int32, device=dev)
     cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=dev)
     kc_p = kc[:n_comp]
-    score = ops.stage1(q_chunk, kc_p, kc_p, cu_q, cu_c, cu_c, lq, n_comp, causal=True)
-    pooled = ops.max_pool(score, chunk.start, local_blocks, init_blocks, block_size, stride)
+    if ops.block_scores is not None and block_size == 64 and stride == 16:
+        pooled = ops.block_scores(q_chunk, kc_p, cu_q, cu_c, lq, n_comp, local_blocks, init_blocks,
+                                  cache_len=chunk.start, causal=True)
+    else:
+        score = ops.stage1(q_chunk, kc_p, kc_p, cu_q, cu_c, cu_c, lq, n_comp, causal=True)
+        pooled = ops.max_pool(score, chunk.start, local_blocks, init_blocks, block_size, stride)
     idx = ops.topk(pooled, topk, chunk.start)
     out = ops.attn(q_chunk, k[:lk], v[:lk], cu_q, cu_k, lq, lk, causal=True, topk_idx=idx)
     return out, idx
@@ -155,7 +162,8 @@ class StreamedPrefill:
         self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
     def __call__(self, q_host, k_host, v_host, kc_host, out_host, topk: int, init_blocks: int,
-                 local_blocks: int, ops: Optional[PrefillOps] = None):
+                 local_blocks: int, ops: Optional[PrefillOps] = None, kernel: int = 32,
+                 stride: int = 16):
         """Enqueue one full prefill; returns when everything is ENQUEUED (synchronise the device, or
         the returned event, before reading out_host)."""
         main = torch.cuda.current_stream(self.device)
@@ -164,11 +172,18 @@ class StreamedPrefill:
         self.s_out.wait_stream(main)
         ev_in = []
         with torch.cuda.stream(self.s_in):
-            self.kc.copy_(kc_host, non_blocking=True)
-            self.k.copy_(k_host, non_blocking=True)
-            self.v.copy_(v_host, non_blocking=True)
+            done_c = 0
             for c in range(n):
+                # chunk c only needs the keys before its own end: K / V / compressed K travel
+                # chunk by chunk too, so the first kernels start after 1/n of the input has landed
                 sl = slice(c * self.chunk, (c + 1) * self.chunk)
+                lk = (c + 1) * self.chunk
+                n_c = min(self.kc.shape[0], (lk - kernel) // stride + 1 if lk >= kernel else 0)
+                self.k[sl].copy_(k_host[sl], non_blocking=True)
+                self.v[sl].copy_(v_host[sl], non_blocking=True)
+                if n_c > done_c:
+                    self.kc[done_c:n_c].copy_(kc_host[done_c:n_c], non_blocking=True)
+                    done_c = n_c
                 self.q[sl].copy_(q_host[sl], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.s_in)

@@ -103,3 +103,21 @@ def test_topk_future_blocks_and_varlen():
         bq = tok // 64
         forced = {0} | {b for b in range(max(bq - 2, 0), bq + 1)}
         assert forced <= set(sel[0, tok].tolist()) and sel[0, tok].max() <= bq
+
+
+@pytest.mark.parametrize("tail", ["random", "zero", "neg_inf"])
+@pytest.mark.parametrize("t,n,k", [(700, 600, 64), (520, 2048, 64), (300, 40, 16)])
+def test_topk_causal_restriction(t, n, k, tail):
+    """Entries past the query's own block: arbitrary values there must displace earlier entries
+    exactly as a full-width selection would (and come out as -1); the stage-1 pattern (0 / -inf
+    there) must give the same lists as selecting among the visible blocks only."""
+    g = torch.Generator().manual_seed(t + n + k)
+    y = (torch.randint(0, 40, (2, t, n), generator=g).float() / 16).to(torch.bfloat16)
+    y[:, :, 0] = float("inf")
+    q_block = torch.arange(t) // 64
+    if tail != "random":
+        future = torch.arange(n)[None, :] > q_block[:, None]                 # (t, n)
+        y[:, future] = 0.0 if tail == "zero" else float("-inf")
+    exp = oracle.topk_select(y, k, q_block)
+    got = infllm_v2.infllmv2_topk(y.to(DEV), k)
+    assert torch.equal(got.cpu(), exp)
