@@ -188,8 +188,8 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128, false);
       const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
-      const uint64_t kc_desc[2] = {umma_desc_sw128(smem_u32(sm.kc[0][0]), 16, 1024),
-                                   umma_desc_sw128(smem_u32(sm.kc[1][0]), 16, 1024)};
+      const uint64_t kc_desc0 = umma_desc_sw128(smem_u32(sm.kc[0][0]), 16, 1024);
+      constexpr uint32_t kStage = (2 * kHalfBytes) >> 4;      // descriptor address units per stage
       const uint64_t d_ones = umma_desc_noswz16(smem_u32(sm.ones));
       const uint64_t d_rowc = umma_desc_noswz16(smem_u32(sm.rowc));
       bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full, 0, abort_flag, p.status, 51));
@@ -209,13 +209,13 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-            umma_ss_pred(tmem + s * 128, q_desc + off, kc_desc[s] + off, idesc, kk > 0, leader);
+            umma_ss_pred(tmem + s * 128, q_desc + off, kc_desc0 + s * kStage + off, idesc, kk > 0, leader);
           }
         } else {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-            umma_ss_pred(tmem + s * 128, kc_desc[s] + off, q_desc + off, idesc, kk > 0, leader);
+            umma_ss_pred(tmem + s * 128, kc_desc0 + s * kStage + off, q_desc + off, idesc, kk > 0, leader);
           }
           umma_ss_pred(tmem + s * 128, d_ones, d_rowc, idesc, true, leader);   // + row constant
         }

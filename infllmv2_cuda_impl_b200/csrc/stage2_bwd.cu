@@ -26,6 +26,20 @@ constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9: two so
                                     // are needed in the backward, so the halves are independent)
 constexpr int kMaxMaskWords = 128;
 constexpr uint32_t kTileHalfBytes = 128 * 128;   // 128 rows x 64 bf16
+#ifndef IFV2_DKV_ORDER
+#define IFV2_DKV_ORDER 1
+#endif
+// Optional timeline of the first CTAs of the dK/dV kernel (a tuning aid, -DIFV2_DKV_TRACE).
+#ifdef IFV2_DKV_TRACE
+__device__ long long g_dkv_trace[4][3][256][4];   // [CTA][role][step][event] = SM clock
+#define IFV2_TRACE(role, i, ev)                                                         \
+  do {                                                                                  \
+    if (blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (i) < 256) \
+      g_dkv_trace[blockIdx.x][role][i][ev] = clock64();                                 \
+  } while (0)
+#else
+#define IFV2_TRACE(role, i, ev) do {} while (0)
+#endif
 constexpr uint32_t kKVHalfBytes = 64 * 128;      // 64 keys x 64 bf16
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -498,62 +512,85 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && !never_selected) {
+    // All 32 lanes run the same issue code (descriptors stay in uniform registers); `leader`
+    // enables the MMA / commit instructions in one lane only.
+    if (!never_selected) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);             // K-major x K-major
       constexpr uint32_t idesc_t = umma_idesc_bf16(128, 64, true, true);        // MN-major x MN-major
-      const uint32_t k_addr = smem_u32(sm.k[0]), v_addr = smem_u32(sm.v[0]);
-      const uint32_t p_addr = smem_u32(sm.pmat), ds_addr = smem_u32(sm.dsmat);
+      const uint64_t k_desc = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024);
+      const uint64_t v_desc = umma_desc_sw128(smem_u32(sm.v[0]), 16, 1024);
+      const uint64_t p_desc = umma_desc_sw128(smem_u32(sm.pmat), 16, 1024);
+      const uint64_t ds_desc = umma_desc_sw128(smem_u32(sm.dsmat), 16, 1024);
+      // ring stage s = stage 0 + s * kRing (plain arithmetic keeps the descriptors in registers)
+      const uint64_t q_desc0 = umma_desc_sw128(smem_u32(sm.q[0][0]), 16, 1024);
+      const uint64_t do_desc0 = umma_desc_sw128(smem_u32(sm.dout[0][0]), 16, 1024);
+      const uint64_t q_mn0 = umma_desc_sw128(smem_u32(sm.q[0][0]), kTileHalfBytes, 1024);
+      const uint64_t do_mn0 = umma_desc_sw128(smem_u32(sm.dout[0][0]), kTileHalfBytes, 1024);
+      constexpr uint32_t kRing = (2 * kTileHalfBytes) >> 4;
       OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
       uint32_t bits;
-      bool ok = mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 82);
+      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 82));
       int have = ok ? walk.next(bits) : -1;      // octet of step 0
       auto issue_sdp = [&](int j) -> bool {
         const int s = j & 1;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
-        if (!mbar_wait(&sm.qdo_full[s], par, abort_flag, p.status, 83)) return false;
-        if (j >= 2 && !mbar_wait(&sm.sdp_empty[s], par ^ 1u, abort_flag, p.status, 84)) return false;
+        bool w = mbar_wait(&sm.qdo_full[s], par, abort_flag, p.status, 83);
+        if (w && j >= 2) w = mbar_wait(&sm.sdp_empty[s], par ^ 1u, abort_flag, p.status, 84);
+        if (!__all_sync(0xFFFFFFFFu, w)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sm.q[s][0]), do_addr = smem_u32(sm.dout[s][0]);
+        IFV2_TRACE(0, j, 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
-          umma_ss(tmem + s * 128, umma_desc_sw128(q_addr + aoff, 16, 1024),
-                  umma_desc_sw128(k_addr + boff, 16, 1024), idesc_s, kk > 0);
+          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
+          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
+          umma_ss_pred(tmem + s * 128, q_desc0 + s * kRing + aoff, k_desc + boff, idesc_s, kk > 0, leader);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk >> 2) * kTileHalfBytes + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
-          umma_ss(tmem + s * 128 + 64, umma_desc_sw128(do_addr + aoff, 16, 1024),
-                  umma_desc_sw128(v_addr + boff, 16, 1024), idesc_s, kk > 0);
+          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
+          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
+          umma_ss_pred(tmem + s * 128 + 64, do_desc0 + s * kRing + aoff, v_desc + boff, idesc_s, kk > 0, leader);
         }
-        umma_commit(&sm.sdp_full[s]);
+        umma_commit_pred(&sm.sdp_full[s], leader);
+        IFV2_TRACE(0, j, 1);
+        return true;
+      };
+      // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
+      auto issue_dvdk = [&](int i, bool last) -> bool {
+        const int s = i & 1;
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_ready, (uint32_t)(i & 1), abort_flag, p.status, 85)))
+          return false;
+        tc_fence_after();
+        IFV2_TRACE(0, i, 2);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss_pred(tmem_dv, do_mn0 + s * kRing + ((kk * 2048) >> 4), p_desc + ((kk * 2048) >> 4), idesc_t,
+                       (i > 0) || (kk > 0), leader);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss_pred(tmem_dk, q_mn0 + s * kRing + ((kk * 2048) >> 4), ds_desc + ((kk * 2048) >> 4), idesc_t,
+                       (i > 0) || (kk > 0), leader);
+        umma_commit_pred(&sm.qdo_empty[s], leader);
+        umma_commit_pred(&sm.pds_empty, leader);
+        if (last) umma_commit_pred(&sm.acc_final, leader);
+        IFV2_TRACE(0, i, 3);
         return true;
       };
       int i = 0;
       if (have >= 0) ok = issue_sdp(0);
       while (ok && have >= 0) {
-        const int s = i & 1;
         const int next = walk.next(bits);
+#if IFV2_DKV_ORDER == 0
+        // S / dP of the next step first: it runs under this step's softmax
         if (next >= 0) ok = issue_sdp(i + 1);
-        if (!ok) break;
-        ok = mbar_wait(&sm.pds_ready, (uint32_t)(i & 1), abort_flag, p.status, 85);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(sm.q[s][0]), do_addr = smem_u32(sm.dout[s][0]);
-        // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tmem_dv, umma_desc_sw128(do_addr + kk * 2048, kTileHalfBytes, 1024),
-                  umma_desc_sw128(p_addr + kk * 2048, 16, 1024), idesc_t, (i > 0) || (kk > 0));
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tmem_dk, umma_desc_sw128(q_addr + kk * 2048, kTileHalfBytes, 1024),
-                  umma_desc_sw128(ds_addr + kk * 2048, 16, 1024), idesc_t, (i > 0) || (kk > 0));
-        umma_commit(&sm.qdo_empty[s]);
-        umma_commit(&sm.pds_empty);
-        if (next < 0) umma_commit(&sm.acc_final);
+        if (ok) ok = issue_dvdk(i, next < 0);
+#else
+        // dV / dK first: the Q / dO stage is released one product earlier, which gives the copy
+        // of the tile two steps ahead the time of a whole step to land
+        ok = issue_dvdk(i, next < 0);
+        if (ok && next >= 0) ok = issue_sdp(i + 1);
+#endif
         have = next;
         ++i;
       }
@@ -586,6 +623,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
                                                abort_flag, p.status, 86));
         if (!ok) break;
         tc_fence_after();
+        if (quad == 2) IFV2_TRACE(1 + grp, i, 0);
         uint32_t pp[16], dd[16];
         {
           const int half = grp;                        // this warp group's 32 key columns
@@ -629,6 +667,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         fence_proxy_async_smem();
         mbar_arrive_warp(&sm.pds_ready);
+        if (quad == 2) IFV2_TRACE(1 + grp, i, 1);
       }
     }
     if (ok && steps > 0) {
@@ -672,6 +711,12 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
 }  // namespace ifv2
 
 using namespace ifv2;
+
+#ifdef IFV2_DKV_TRACE
+extern "C" int ifv2_debug_dkv_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_dkv_trace, sizeof(long long) * 4 * 3 * 256 * 4);
+}
+#endif
 
 extern "C" int64_t ifv2_sparse_attn_bwd_workspace_bytes(int64_t total_q, int heads_q, int head_dim) {
   (void)head_dim;

@@ -210,10 +210,11 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, true);
       const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
-      const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024),
-                                  umma_desc_sw128(smem_u32(sm.k[1][0]), 16, 1024)};
-      const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0][0]), kKVHalfBytes, 1024),
-                                  umma_desc_sw128(smem_u32(sm.v[1][0]), kKVHalfBytes, 1024)};
+      // ring stage s = stage 0 + s * kStage: plain arithmetic keeps the descriptors in registers
+      // (a runtime-indexed array of descriptors would live in local memory)
+      const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sm.v[0][0]), kKVHalfBytes, 1024);
+      constexpr uint32_t kStage = (2 * kKVHalfBytes) >> 4;
       bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full, 0, abort_flag, p.status, 21));
       auto issue_qk = [&](int j) -> bool {
         const int s = j & 1;
@@ -226,7 +227,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t qoff = (kk >> 2) * kQHalfBytes + (kk & 3) * 32;
           const uint32_t koff = (kk >> 2) * kKVHalfBytes + (kk & 3) * 32;
-          umma_ss_pred(tmem + s * 64, q_desc + (qoff >> 4), k_desc[s] + (koff >> 4), idesc_qk,
+          umma_ss_pred(tmem + s * 64, q_desc + (qoff >> 4), k_desc0 + s * kStage + (koff >> 4), idesc_qk,
                        kk > 0, leader);
         }
         umma_commit_pred(&sm.k_empty[s], leader);
@@ -248,7 +249,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         IFV2_TRACE(0, i, 2);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts_pred(tmem_o, tmem + s * 64 + kk * 8, v_desc[s] + ((kk * 2048) >> 4), idesc_pv,
+          umma_ts_pred(tmem_o, tmem + s * 64 + kk * 8, v_desc0 + s * kStage + ((kk * 2048) >> 4), idesc_pv,
                        (i > 0) || (kk > 0), leader);
         umma_commit_pred(&sm.v_empty[s], leader);
         umma_commit_pred(&sm.o_done, leader);

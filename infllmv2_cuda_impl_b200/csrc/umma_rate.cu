@@ -12,7 +12,7 @@ using namespace tc;
 
 enum : int { kSmemK = 0, kSmemMN = 1, kTmem = 2 };
 
-template <int kA, int kB, int kN, int kAccs>
+template <int kA, int kB, int kN, int kAccs, int kSteps, bool kRandom>
 __global__ void __launch_bounds__(128)
 umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -24,8 +24,11 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < (32768 + 65536) / 16; i += 128)
-    reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < (32768 + 65536) / 16; i += 128) {
+    // zeros, or bf16 values of magnitude ~1 with varying mantissas (operand contents may matter)
+    const uint32_t w = kRandom ? (0x3F803F80u ^ ((uint32_t)i * 2654435761u & 0x807F807Fu)) : 0u;
+    reinterpret_cast<uint4*>(smem)[i] = make_uint4(w, w ^ 0x00110022u * kRandom, w, w ^ 0x00330044u * kRandom);
+  }
   fence_proxy_async_smem();
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -40,7 +43,7 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
-  const uint32_t tmem_a = tmem + 448;          // 4 K steps x 8 columns
+  const uint32_t tmem_a = tmem + 448;          // up to 8 K steps x 8 columns
   long long t_start = 0;
   if (warp == 0) {
     const uint32_t leader = (lane == 0) ? 1u : 0u;
@@ -55,12 +58,15 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
     t_start = clock64();
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
+      for (int kk = 0; kk < kSteps; ++kk) {
         const uint32_t d = tmem + ((kAccs > 1) ? (uint32_t)((kk % kAccs) * kN) : 0u);
+        // K-major: steps 4..7 continue in the second 64-element K slab (16 KB / 32 KB further)
+        const uint32_t ao = (kA == kSmemMN) ? a_step * kk : ((kk >> 2) * 1024 + (kk & 3) * 2);
+        const uint32_t bo = (kB == kSmemMN) ? b_step * kk : ((kk >> 2) * 2048 + (kk & 3) * 2);
         if (kA == kTmem)
-          umma_ts_pred(d, tmem_a + kk * 8, db + b_step * kk, idesc, kk >= kAccs, leader);
+          umma_ts_pred(d, tmem_a + kk * 8, db + bo, idesc, kk >= kAccs, leader);
         else
-          umma_ss_pred(d, da + a_step * kk, db + b_step * kk, idesc, kk >= kAccs, leader);
+          umma_ss_pred(d, da + ao, db + bo, idesc, kk >= kAccs, leader);
       }
     }
     umma_commit_pred(&bar_mma, leader);
@@ -74,9 +80,9 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
-template <int kA, int kB, int kN, int kAccs>
+template <int kA, int kB, int kN, int kAccs, int kSteps, bool kRandom>
 int launch_rate(int iters, long long* cycles, int32_t* status, cudaStream_t stream) {
-  auto kern = umma_rate_kernel<kA, kB, kN, kAccs>;
+  auto kern = umma_rate_kernel<kA, kB, kN, kAccs, kSteps, kRandom>;
   const int smem = 32768 + 65536 + 1024;
   cudaError_t attr = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (attr != cudaSuccess) return set_error((int)attr, "umma_rate: %s", cudaGetErrorString(attr));
@@ -89,14 +95,19 @@ int launch_rate(int iters, long long* cycles, int32_t* status, cudaStream_t stre
 
 using namespace ifv2;
 
-// kind = 1000 * a + 100 * b + variant, a in {0: smem K-major, 1: smem MN-major, 2: TMEM},
-// b in {0: K-major, 1: MN-major}; variant selects N and the number of accumulators (see below).
-extern "C" int ifv2_umma_rate(int a, int b, int n, int accs, int iters, long long* cycles,
-                              int32_t* status, void* stream) {
+// a in {0: smem K-major, 1: smem MN-major, 2: TMEM}, b in {0: K-major, 1: MN-major}; n = MMA N;
+// accs = accumulators used in turn; steps = K steps per group (4 or 8); random = operand contents.
+extern "C" int ifv2_umma_rate(int a, int b, int n, int accs, int steps, int random, int iters,
+                              long long* cycles, int32_t* status, void* stream) {
   IFV2_REQUIRE(cycles && status && iters > 0, IFV2_ERR_INVALID_ARG, "umma_rate: bad argument");
   cudaStream_t s = (cudaStream_t)stream;
-#define IFV2_RATE_CASE(A, B, N, ACCS) \
-  if (a == A && b == B && n == N && accs == ACCS) return launch_rate<A, B, N, ACCS>(iters, cycles, status, s);
+#define IFV2_RATE_CASE(A, B, N, ACCS)                                                        \
+  if (a == A && b == B && n == N && accs == ACCS) {                                          \
+    if (steps == 4 && !random) return launch_rate<A, B, N, ACCS, 4, false>(iters, cycles, status, s); \
+    if (steps == 8 && !random) return launch_rate<A, B, N, ACCS, 8, false>(iters, cycles, status, s); \
+    if (steps == 8 && random) return launch_rate<A, B, N, ACCS, 8, true>(iters, cycles, status, s);   \
+    if (steps == 4 && random) return launch_rate<A, B, N, ACCS, 4, true>(iters, cycles, status, s);   \
+  }
   IFV2_RATE_CASE(0, 0, 64, 1)
   IFV2_RATE_CASE(0, 0, 128, 1)
   IFV2_RATE_CASE(0, 0, 256, 1)
