@@ -400,15 +400,16 @@ __global__ void __launch_bounds__(kThreads, (kIters <= 8) ? 2 : 1) topk_select_k
       }
 
       // ---- bisection + emission over the `its` iterations that take part
+      // (an even iteration count keeps the number of instantiated bodies, and with it the
+      //  instruction-cache footprint, small; the extra iteration only holds -inf slots)
       int got = -1;
-      switch (its) {
+      switch (min(kIters, (its + 1) & ~1)) {
 #define IFV2_TOPK_CASE(I)                                                                \
         case I:                                                                          \
           if constexpr (I <= kIters)                                                     \
             got = topk_row<T, kPairs, I>(v, tail2, restricted, k_sel, bq, lane, o);      \
           break;
-        IFV2_TOPK_CASE(0) IFV2_TOPK_CASE(1) IFV2_TOPK_CASE(2) IFV2_TOPK_CASE(3) IFV2_TOPK_CASE(4)
-        IFV2_TOPK_CASE(5) IFV2_TOPK_CASE(6) IFV2_TOPK_CASE(7) IFV2_TOPK_CASE(8)
+        IFV2_TOPK_CASE(2) IFV2_TOPK_CASE(4) IFV2_TOPK_CASE(6)
 #undef IFV2_TOPK_CASE
         default:
           got = topk_row<T, kPairs, kIters>(v, tail2, restricted, k_sel, bq, lane, o);

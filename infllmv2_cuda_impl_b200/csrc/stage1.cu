@@ -69,7 +69,9 @@ struct Smem {
   __nv_bfloat16 pool[3][kTokPerTile][kPoolSlots];   // scores of the last three key tiles (pooling is
   __nv_bfloat16 carry[4][kTokPerTile];              // deferred by one tile), and each tile's last key
   float2 stat[128];                  // pass-1 (max, sum) of the second column half, per row
-  uint64_t q_full, kc_full[2], kc_empty[2], acc_full[2], acc_empty[2], rowc_ready, pool_full[3];
+  // acc_full[s] doubles as "the key tile of slot s may be refilled": one commit per step (a
+  // tcgen05.commit costs the issuing warp about as much as two MMAs)
+  uint64_t q_full, kc_full[2], acc_full[2], acc_empty[2], rowc_ready, pool_full[3];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -116,7 +118,10 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
   const int ntok = min(kTokPerTile, lq - tok0);
   const int lim_max = visible_limit(tok0 + ntok - 1, lq, lc, p.causal);    // limits grow with i
-  const int n_tiles = (lim_max + kKeysPerTile - 1) / kKeysPerTile;
+  // (read through a warp broadcast: it tells the compiler that the value is warp-uniform, so the
+  //  MMA issuer's descriptor arithmetic stays in uniform registers instead of being moved there
+  //  operand by operand for every MMA)
+  const int n_tiles = __shfl_sync(0xFFFFFFFFu, (lim_max + kKeysPerTile - 1) / kKeysPerTile, 0);
   const int n_steps = 2 * n_tiles;
 
   if (threadIdx.x == 0) {
@@ -124,7 +129,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     mbar_init(&sm.q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.kc_full[s], 1);
-      mbar_init(&sm.kc_empty[s], 1);
       mbar_init(&sm.acc_full[s], 1);
       mbar_init(&sm.acc_empty[s], 8);       // one arrival per softmax warp
     }
@@ -153,7 +157,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem = __shfl_sync(0xFFFFFFFFu, sm.tmem_base, 0);
   volatile int* abort_flag = &sm.abort_flag;
 
   if (warp == 0) {
@@ -165,7 +169,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       int issued = 0;
       for (int t = 0; t < n_steps; ++t) {
         const int s = t & 1, tile = (t < n_tiles) ? t : t - n_tiles;
-        if (t >= 2 && !mbar_wait(&sm.kc_empty[s], (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag,
+        if (t >= 2 && !mbar_wait(&sm.acc_full[s], (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag,
                                  p.status, 41))
           break;
         IFV2_TRACE(3, t, 0);
@@ -219,7 +223,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           }
           umma_ss_pred(tmem + s * 128, d_ones, d_rowc, idesc, true, leader);   // + row constant
         }
-        umma_commit_pred(&sm.kc_empty[s], leader);
         umma_commit_pred(&sm.acc_full[s], leader);
         IFV2_TRACE(0, t, 1);
       }

@@ -29,17 +29,21 @@ constexpr uint32_t kTileHalfBytes = 128 * 128;   // 128 rows x 64 bf16
 #ifndef IFV2_DKV_ORDER
 #define IFV2_DKV_ORDER 1
 #endif
-// Optional timeline of the first CTAs of the dK/dV kernel (a tuning aid, -DIFV2_DKV_TRACE).
-#ifdef IFV2_DKV_TRACE
-__device__ long long g_dkv_trace[4][3][256][4];   // [CTA][role][step][event] = SM clock
-#define IFV2_TRACE(role, i, ev)                                                         \
-  do {                                                                                  \
-    if (blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (i) < 256) \
-      g_dkv_trace[blockIdx.x][role][i][ev] = clock64();                                 \
+// Optional timeline of the first CTAs of one of the gradient kernels (a tuning aid):
+// -DIFV2_BWD_TRACE=1 records the dK/dV kernel, =2 the dQ kernel.
+#ifdef IFV2_BWD_TRACE
+__device__ long long g_bwd_trace[4][3][256][4];   // [CTA][role][step][event] = SM clock
+#define IFV2_TRACE_AT(which, role, i, ev)                                                   \
+  do {                                                                                      \
+    if (IFV2_BWD_TRACE == which && blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 &&  \
+        lane == 0 && (i) < 256)                                                             \
+      g_bwd_trace[blockIdx.x][role][i][ev] = clock64();                                     \
   } while (0)
 #else
-#define IFV2_TRACE(role, i, ev) do {} while (0)
+#define IFV2_TRACE_AT(which, role, i, ev) do {} while (0)
 #endif
+#define IFV2_TRACE(role, i, ev) IFV2_TRACE_AT(1, role, i, ev)
+#define IFV2_TRACE_DQ(role, i, ev) IFV2_TRACE_AT(2, role, i, ev)
 constexpr uint32_t kKVHalfBytes = 64 * 128;      // 64 keys x 64 bf16
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -120,8 +124,11 @@ struct DqSmem {
   uint8_t k[3][2][kKVHalfBytes];      // [stage][d half]; K lives until dS.K of its block is done,
   uint8_t v[2][2][kKVHalfBytes];      // so it needs one more stage than V to be prefetched in time
   unsigned long long umask[kMaxMaskWords];
-  uint64_t qdo_full, k_full[3], k_empty[3], v_full[2], v_empty[2], sdp_full[2], ds_ready[2];
-  uint64_t dq_final;
+  // One commit per product group (a tcgen05.commit costs the issuing warp about as much as two
+  // MMAs): sdp_full[s] also releases the V tile of slot s, dq_done[k] releases the K tile of ring
+  // slot k and, for the last block, tells the epilogue that dQ is complete.
+  uint64_t qdo_full, k_full[3], dq_done[3], v_full[2], sdp_full[2], ds_ready[2];
+  uint64_t qdo_tmem;   // 8 arrivals: Q and dO have been copied from shared memory into TMEM
   uint32_t tmem_base;
   int n_blocks;
   int abort_flag;
@@ -171,15 +178,14 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
     mbar_init(&sm.qdo_full, 1);
     for (int s = 0; s < 3; ++s) {
       mbar_init(&sm.k_full[s], 1);
-      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.dq_done[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.v_full[s], 1);
-      mbar_init(&sm.v_empty[s], 1);
       mbar_init(&sm.sdp_full[s], 1);
       mbar_init(&sm.ds_ready[s], 8);         // one arrival per softmax warp
     }
-    mbar_init(&sm.dq_final, 1);
+    mbar_init(&sm.qdo_tmem, 8);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -195,9 +201,13 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const int n_blocks = sm.n_blocks;
-  const uint32_t tmem = sm.tmem_base;
+  // (read through a warp broadcast: it tells the compiler that the value is warp-uniform, so the
+  //  MMA issuer's descriptor arithmetic stays in uniform registers instead of being moved there
+  //  operand by operand for every MMA)
+  const int n_blocks = __shfl_sync(0xFFFFFFFFu, sm.n_blocks, 0);
+  const uint32_t tmem = __shfl_sync(0xFFFFFFFFu, sm.tmem_base, 0);
   const uint32_t tmem_dq = tmem + 256;             // [0,128) buffer 0: S | dP, [128,256) buffer 1
+  const uint32_t tmem_q = tmem + 384, tmem_do = tmem + 448;   // A operands: 128 rows x 128 d as bf16 pairs
   volatile int* abort_flag = &sm.abort_flag;
 
   if (warp == 0) {
@@ -213,11 +223,11 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
         const int blk = walk.next();
         const int s = i & 1, sk = i % 3, key = k0 + blk * kBlockN;
         const uint32_t par = (uint32_t)((i >> 1) & 1), park = (uint32_t)((i / 3) & 1);
-        if (i >= 3 && !mbar_wait(&sm.k_empty[sk], park ^ 1u, abort_flag, p.status, 71)) break;
+        if (i >= 3 && !mbar_wait(&sm.dq_done[sk], park ^ 1u, abort_flag, p.status, 71)) break;
         mbar_expect_tx(&sm.k_full[sk], 2 * kKVHalfBytes);
         tma_load_3d(sm.k[sk][0], &map_k, &sm.k_full[sk], 0, h, key);
         tma_load_3d(sm.k[sk][1], &map_k, &sm.k_full[sk], 64, h, key);
-        if (i >= 2 && !mbar_wait(&sm.v_empty[s], par ^ 1u, abort_flag, p.status, 72)) {
+        if (i >= 2 && !mbar_wait(&sm.sdp_full[s], par ^ 1u, abort_flag, p.status, 72)) {
           issued = i + 1;
           break;
         }
@@ -241,13 +251,14 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, true);
-      const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
-      const uint64_t do_desc = umma_desc_sw128(smem_u32(sm.dout[0]), 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024);
       const uint64_t k_desc0_mn = umma_desc_sw128(smem_u32(sm.k[0][0]), kKVHalfBytes, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sm.v[0][0]), 16, 1024);
       constexpr uint32_t kStage = (2 * kKVHalfBytes) >> 4;     // descriptor address units per ring stage
-      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 73));
+      // Q and dO are A operands read from TMEM: the Q.K^T and dO.V^T products then fetch only
+      // their 2 KB key tiles from shared memory per step instead of 6 KB
+      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_tmem, 0, abort_flag, p.status, 73));
+      tc_fence_after();
       auto issue_sdp = [&](int j) -> bool {
         const int s = j & 1, sk = j % 3;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
@@ -256,21 +267,20 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
                             mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75)))
           return false;
         tc_fence_after();
+        IFV2_TRACE_DQ(0, j, 0);
         const uint64_t k_desc = k_desc0 + (uint32_t)sk * kStage, v_desc = v_desc0 + (uint32_t)s * kStage;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
           const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
-          umma_ss_pred(tmem + s * 128, q_desc + aoff, k_desc + boff, idesc_s, kk > 0, leader);
+          umma_ts_pred(tmem + s * 128, tmem_q + kk * 8, k_desc + boff, idesc_s, kk > 0, leader);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
           const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
-          umma_ss_pred(tmem + s * 128 + 64, do_desc + aoff, v_desc + boff, idesc_s, kk > 0, leader);
+          umma_ts_pred(tmem + s * 128 + 64, tmem_do + kk * 8, v_desc + boff, idesc_s, kk > 0, leader);
         }
-        umma_commit_pred(&sm.v_empty[s], leader);
         umma_commit_pred(&sm.sdp_full[s], leader);
+        IFV2_TRACE_DQ(0, j, 1);
         return true;
       };
       if (ok) ok = issue_sdp(0);
@@ -282,13 +292,14 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
                                                p.status, 76));
         if (!ok) break;
         tc_fence_after();
+        IFV2_TRACE_DQ(0, i, 2);
         const uint64_t k_mn = k_desc0_mn + (uint32_t)(i % 3) * kStage;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts_pred(tmem_dq, tmem + s * 128 + kk * 8, k_mn + ((kk * 2048) >> 4), idesc_dq,
                        (i > 0) || (kk > 0), leader);
-        umma_commit_pred(&sm.k_empty[i % 3], leader);
-        if (i + 1 == n_blocks) umma_commit_pred(&sm.dq_final, leader);
+        umma_commit_pred(&sm.dq_done[i % 3], leader);
+        IFV2_TRACE_DQ(0, i, 3);
       }
     }
   } else {
@@ -307,14 +318,38 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
     const float neg_lse = valid ? -p.lse[stat_idx] * kLog2e : -INFINITY;   // +inf lse -> P = 0
     const float dsum = valid ? p.dvec[stat_idx] : 0.f;
     bool ok = true;
+    if (n_blocks > 0) {
+      // group 0 moves this thread's Q row, group 1 its dO row, from the swizzled tiles into TMEM
+      // (row r of a d half: 16-byte chunk c sits at chunk c ^ (r & 7); TMEM column j = d 2j, 2j+1)
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 79));
+      if (ok) {
+        const uint8_t* tile = (grp == 0) ? sm.q[0] : sm.dout[0];
+        const uint32_t dst = ((grp == 0) ? tmem_q : tmem_do) + lane_off;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t regs[32];
+          const uint8_t* rowp = tile + hh * kTileHalfBytes + r * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 w = *reinterpret_cast<const uint4*>(rowp + ((c ^ (r & 7)) << 4));
+            regs[4 * c] = w.x; regs[4 * c + 1] = w.y; regs[4 * c + 2] = w.z; regs[4 * c + 3] = w.w;
+          }
+          tmem_st32(dst + hh * 32, regs);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive_warp(&sm.qdo_tmem);
+      }
+    }
     BlockWalk walk(sm.umask, words);
-    for (int i = 0; i < n_blocks; ++i) {
+    for (int i = 0; i < n_blocks && ok; ++i) {
       const int blk = walk.next();
       const int s = i & 1;
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.sdp_full[s], (uint32_t)((i >> 1) & 1),
                                              abort_flag, p.status, 77));
       if (!ok) break;
       tc_fence_after();
+      if (quad == 2) IFV2_TRACE_DQ(1 + grp, i, 0);
       bool selected = valid;
       if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
       const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
@@ -342,9 +377,13 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&sm.ds_ready[s]);
+      if (quad == 2) IFV2_TRACE_DQ(1 + grp, i, 1);
     }
     if (ok && n_blocks > 0) {
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dq_final, 0, abort_flag, p.status, 78));
+      // the last block's product: S / dP of that block is complete, hence every dQ product up to
+      // block n-3 is too, so this barrier is at most one phase behind and the parity is unambiguous
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dq_done[(n_blocks - 1) % 3],
+                                             (uint32_t)(((n_blocks - 1) / 3) & 1), abort_flag, p.status, 78));
       tc_fence_after();
     }
     if (ok) {
@@ -387,8 +426,10 @@ struct DkvSmem {
   uint8_t dout[2][2][kTileHalfBytes];
   uint8_t pmat[kTileHalfBytes];        // P  (128 rows x 64 keys bf16, 128-byte swizzle)
   uint8_t dsmat[kTileHalfBytes];       // dS
-  uint64_t kv_full, qdo_full[2], qdo_empty[2], sdp_full[2], sdp_empty[2], pds_ready, pds_empty;
-  uint64_t acc_final;
+  // dvdk_done[s]: the dV / dK products of a step in ring slot s are complete -> the Q / dO tiles
+  // of the slot may be refilled, P / dS may be rewritten, and after the last step the accumulators
+  // are final (one commit per product group)
+  uint64_t kv_full, qdo_full[2], dvdk_done[2], sdp_full[2], sdp_empty[2], pds_ready;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -458,13 +499,11 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
     mbar_init(&sm.kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.qdo_full[s], 1);
-      mbar_init(&sm.qdo_empty[s], 1);
+      mbar_init(&sm.dvdk_done[s], 1);
       mbar_init(&sm.sdp_full[s], 1);
       mbar_init(&sm.sdp_empty[s], 8);
     }
     mbar_init(&sm.pds_ready, 8);
-    mbar_init(&sm.pds_empty, 1);
-    mbar_init(&sm.acc_final, 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -474,12 +513,12 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem = __shfl_sync(0xFFFFFFFFu, sm.tmem_base, 0);   // warp-uniform for the compiler
   const uint32_t tmem_dv = tmem + 256, tmem_dk = tmem + 320;   // [128 d lanes x 64 key columns]
   volatile int* abort_flag = &sm.abort_flag;
 
   // every role walks the same octet list; the count is not known up front, so the walk itself
-  // tells each role when to stop and the MMA role signals acc_final after its last step
+  // tells each role when to stop
   if (warp == 0) {
     if (lane == 0 && !never_selected) {
       mbar_expect_tx(&sm.kv_full, 4 * kKVHalfBytes);
@@ -494,7 +533,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         const int m = walk.next(bits);
         if (m < 0) break;
         const int s = i & 1;
-        if (i >= 2 && !mbar_wait(&sm.qdo_empty[s], (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag,
+        if (i >= 2 && !mbar_wait(&sm.dvdk_done[s], (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag,
                                  p.status, 81))
           break;
         mbar_expect_tx(&sm.qdo_full[s], 4 * kTileHalfBytes);
@@ -531,7 +570,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
       uint32_t bits;
       bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 82));
-      int have = ok ? walk.next(bits) : -1;      // octet of step 0
+      int have = __shfl_sync(0xFFFFFFFFu, ok ? walk.next(bits) : -1, 0);      // octet of step 0
       auto issue_sdp = [&](int j) -> bool {
         const int s = j & 1;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
@@ -571,16 +610,14 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int kk = 0; kk < 8; ++kk)
           umma_ss_pred(tmem_dk, q_mn0 + s * kRing + ((kk * 2048) >> 4), ds_desc + ((kk * 2048) >> 4), idesc_t,
                        (i > 0) || (kk > 0), leader);
-        umma_commit_pred(&sm.qdo_empty[s], leader);
-        umma_commit_pred(&sm.pds_empty, leader);
-        if (last) umma_commit_pred(&sm.acc_final, leader);
+        umma_commit_pred(&sm.dvdk_done[s], leader);
         IFV2_TRACE(0, i, 3);
         return true;
       };
       int i = 0;
       if (have >= 0) ok = issue_sdp(0);
       while (ok && have >= 0) {
-        const int next = walk.next(bits);
+        const int next = __shfl_sync(0xFFFFFFFFu, walk.next(bits), 0);   // (uniform for the compiler)
 #if IFV2_DKV_ORDER == 0
         // S / dP of the next step first: it runs under this step's softmax
         if (next >= 0) ok = issue_sdp(i + 1);
@@ -650,7 +687,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         mbar_arrive_warp(&sm.sdp_empty[s]);                  // S / dP of this buffer may be overwritten
         // P and dS of the previous step must have been consumed before the tiles are rewritten
         if (i >= 1) {
-          ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_empty, (uint32_t)((i - 1) & 1),
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dvdk_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1),
                                                  abort_flag, p.status, 87));
           if (!ok) break;
         }
@@ -671,7 +708,8 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
     if (ok && steps > 0) {
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.acc_final, 0, abort_flag, p.status, 88));
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dvdk_done[(steps - 1) & 1],
+                                             (uint32_t)(((steps - 1) >> 1) & 1), abort_flag, p.status, 88));
       tc_fence_after();
     }
     if (ok) {
@@ -712,9 +750,9 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
 
 using namespace ifv2;
 
-#ifdef IFV2_DKV_TRACE
-extern "C" int ifv2_debug_dkv_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_dkv_trace, sizeof(long long) * 4 * 3 * 256 * 4);
+#ifdef IFV2_BWD_TRACE
+extern "C" int ifv2_debug_bwd_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_bwd_trace, sizeof(long long) * 4 * 3 * 256 * 4);
 }
 #endif
 

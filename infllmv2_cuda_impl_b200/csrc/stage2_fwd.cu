@@ -54,9 +54,12 @@ struct Smem {
   uint8_t k[2][2][kKVHalfBytes];      // [stage][d half]
   uint8_t v[2][2][kKVHalfBytes];      // [stage][d half]
   unsigned long long umask[kMaxMaskWords];
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2];
-  uint64_t o_done;    // one arrival per P.V product: phase i completes with block i
-  uint64_t o_final;   // one arrival after the last P.V product (an unambiguous wait for the epilogue)
+  // One tcgen05.commit costs the issuing warp about as much as two MMAs, so every product
+  // signals exactly one barrier and everybody interested waits on that one:
+  //   qk_done[s]: S of ring slot s is complete -> the softmax warps read it, the producer may
+  //               refill the K tile;  pv_done[s]: O holds the block of slot s -> the producer may
+  //               refill the V tile, a rescale or the epilogue may touch O.
+  uint64_t q_full, k_full[2], v_full[2], qk_done[2], pv_done[2], p_ready[2];
   uint32_t tmem_base;
   int n_blocks;
   int abort_flag;
@@ -136,14 +139,11 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
     mbar_init(&sm.q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.k_full[s], 1);
-      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.qk_done[s], 1);
       mbar_init(&sm.v_full[s], 1);
-      mbar_init(&sm.v_empty[s], 1);
-      mbar_init(&sm.s_full[s], 1);
+      mbar_init(&sm.pv_done[s], 1);
       mbar_init(&sm.p_ready[s], 4);          // one arrival per softmax warp
     }
-    mbar_init(&sm.o_done, 1);
-    mbar_init(&sm.o_final, 1);
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -163,8 +163,11 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc_fence_after();
 
-  const int n_blocks = sm.n_blocks;
-  const uint32_t tmem = sm.tmem_base;
+  // (read through a warp broadcast: it tells the compiler that the value is warp-uniform, so the
+  //  MMA issuer's descriptor arithmetic stays in uniform registers instead of being moved there
+  //  operand by operand for every MMA)
+  const int n_blocks = __shfl_sync(0xFFFFFFFFu, sm.n_blocks, 0);
+  const uint32_t tmem = __shfl_sync(0xFFFFFFFFu, sm.tmem_base, 0);
   const uint32_t tmem_o = tmem + 128;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -181,12 +184,12 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         const int blk = walk.next();
         const int s = i & 1, key = k0 + blk * kBlockN;
         const uint32_t par = (uint32_t)((i >> 1) & 1);
-        if (i >= 2) ok = mbar_wait(&sm.k_empty[s], par ^ 1u, abort_flag, p.status, 11);
+        if (i >= 2) ok = mbar_wait(&sm.qk_done[s], par ^ 1u, abort_flag, p.status, 11);
         if (!ok) break;
         mbar_expect_tx(&sm.k_full[s], 2 * kKVHalfBytes);
         tma_load_3d(sm.k[s][0], &map_k, &sm.k_full[s], 0, h, key);
         tma_load_3d(sm.k[s][1], &map_k, &sm.k_full[s], 64, h, key);
-        if (i >= 2) ok = mbar_wait(&sm.v_empty[s], par ^ 1u, abort_flag, p.status, 12);
+        if (i >= 2) ok = mbar_wait(&sm.pv_done[s], par ^ 1u, abort_flag, p.status, 12);
         if (!ok) { issued = i + 1; break; }
         mbar_expect_tx(&sm.v_full[s], 2 * kKVHalfBytes);
         tma_load_3d(sm.v[s][0], &map_v, &sm.v_full[s], 0, h, key);
@@ -230,8 +233,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
           umma_ss_pred(tmem + s * 64, q_desc + (qoff >> 4), k_desc0 + s * kStage + (koff >> 4), idesc_qk,
                        kk > 0, leader);
         }
-        umma_commit_pred(&sm.k_empty[s], leader);
-        umma_commit_pred(&sm.s_full[s], leader);
+        umma_commit_pred(&sm.qk_done[s], leader);
         IFV2_TRACE(0, j, 1);
         return true;
       };
@@ -251,9 +253,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int kk = 0; kk < 4; ++kk)
           umma_ts_pred(tmem_o, tmem + s * 64 + kk * 8, v_desc0 + s * kStage + ((kk * 2048) >> 4), idesc_pv,
                        (i > 0) || (kk > 0), leader);
-        umma_commit_pred(&sm.v_empty[s], leader);
-        umma_commit_pred(&sm.o_done, leader);
-        if (i + 1 == n_blocks) umma_commit_pred(&sm.o_final, leader);
+        umma_commit_pred(&sm.pv_done[s], leader);
         IFV2_TRACE(0, i, 3);
       }
     }
@@ -283,7 +283,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       // only the diagonal / ragged block needs per-element masking; a row that did not select
       // the block is handled by the row-level terms below
       const bool partial = __any_sync(0xFFFFFFFFu, lim > 0 && lim < kBlockN);
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[s], par, abort_flag, p.status, 31));
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qk_done[s], par, abort_flag, p.status, 31));
       if (!ok) break;
       tc_fence_after();
       if (warp == 2) IFV2_TRACE(1, i, 0);
@@ -313,8 +313,11 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         l *= f;
       }
       if (i > 0 && __any_sync(0xFFFFFFFFu, f != 1.f)) {
-        ok = __all_sync(0xFFFFFFFFu,
-                        mbar_wait(&sm.o_done, (uint32_t)((i - 1) & 1), abort_flag, p.status, 32));
+        // the previous block's product (slot (i-1)&1, its ((i-1)>>1)-th use).  S of this block is
+        // complete, so every product up to block i-2 is too: the barrier is at most one phase
+        // behind and the parity wait is unambiguous
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.pv_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1),
+                                               abort_flag, p.status, 32));
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
@@ -353,9 +356,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 
     // ---- epilogue: O / l -> bf16, lse
     if (ok && n_blocks > 0) {
-      // (o_done cannot be used here: two products may still be in flight, and a parity wait
-      //  cannot tell "two phases behind" from "done")
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.o_final, 0, abort_flag, p.status, 33));
+      // the last product; as above, all but the last two are known to be complete
+      ok = __all_sync(0xFFFFFFFFu,
+                      mbar_wait(&sm.pv_done[(n_blocks - 1) & 1],
+                                (uint32_t)(((n_blocks - 1) >> 1) & 1), abort_flag, p.status, 33));
       tc_fence_after();
     }
     if (ok) {

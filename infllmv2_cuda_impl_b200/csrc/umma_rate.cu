@@ -14,13 +14,13 @@ enum : int { kSmemK = 0, kSmemMN = 1, kTmem = 2 };
 
 template <int kA, int kB, int kN, int kAccs, int kSteps, bool kRandom>
 __global__ void __launch_bounds__(128)
-umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
+umma_rate_kernel(int iters, long long* cycles, int32_t* status, int dyn, int commits) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
   uint8_t* sA = smem;              // 32 KB
   uint8_t* sB = smem + 32768;      // 64 KB
-  __shared__ uint64_t bar_mma;
+  __shared__ uint64_t bar_mma, bar_group[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -33,6 +33,8 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(&bar_mma, 1);
+    mbar_init(&bar_group[0], 1);
+    mbar_init(&bar_group[1], 1);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -57,6 +59,9 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
     constexpr uint32_t a_step = (kA == kSmemMN) ? 128 : 2, b_step = (kB == kSmemMN) ? 128 : 2;
     t_start = clock64();
     for (int it = 0; it < iters; ++it) {
+      // dyn != 0: the operand tiles alternate between two ring stages chosen at run time, as in
+      // the attention kernels (the descriptors can then not be hoisted out of the loop)
+      const uint32_t stage = (uint32_t)(it & 1) * (uint32_t)dyn;
 #pragma unroll
       for (int kk = 0; kk < kSteps; ++kk) {
         const uint32_t d = tmem + ((kAccs > 1) ? (uint32_t)((kk % kAccs) * kN) : 0u);
@@ -64,10 +69,12 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
         const uint32_t ao = (kA == kSmemMN) ? a_step * kk : ((kk >> 2) * 1024 + (kk & 3) * 2);
         const uint32_t bo = (kB == kSmemMN) ? b_step * kk : ((kk >> 2) * 2048 + (kk & 3) * 2);
         if (kA == kTmem)
-          umma_ts_pred(d, tmem_a + kk * 8, db + bo, idesc, kk >= kAccs, leader);
+          umma_ts_pred(d, tmem_a + kk * 8, db + stage + bo, idesc, kk >= kAccs, leader);
         else
-          umma_ss_pred(d, da + ao, db + bo, idesc, kk >= kAccs, leader);
+          umma_ss_pred(d, da + stage + ao, db + stage + bo, idesc, kk >= kAccs, leader);
       }
+      // commits per group of K steps, as a pipelined kernel issues them (nobody waits on these)
+      for (int c = 0; c < commits; ++c) umma_commit_pred(&bar_group[c & 1], leader);
     }
     umma_commit_pred(&bar_mma, leader);
   }
@@ -81,12 +88,13 @@ umma_rate_kernel(int iters, long long* cycles, int32_t* status) {
 }
 
 template <int kA, int kB, int kN, int kAccs, int kSteps, bool kRandom>
-int launch_rate(int iters, long long* cycles, int32_t* status, cudaStream_t stream) {
+int launch_rate(int iters, long long* cycles, int32_t* status, cudaStream_t stream, int dyn,
+                int commits) {
   auto kern = umma_rate_kernel<kA, kB, kN, kAccs, kSteps, kRandom>;
   const int smem = 32768 + 65536 + 1024;
   cudaError_t attr = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (attr != cudaSuccess) return set_error((int)attr, "umma_rate: %s", cudaGetErrorString(attr));
-  kern<<<1, 128, smem, stream>>>(iters, cycles, status);
+  kern<<<1, 128, smem, stream>>>(iters, cycles, status, dyn, commits);
   return check_launch("umma_rate");
 }
 
@@ -96,17 +104,19 @@ int launch_rate(int iters, long long* cycles, int32_t* status, cudaStream_t stre
 using namespace ifv2;
 
 // a in {0: smem K-major, 1: smem MN-major, 2: TMEM}, b in {0: K-major, 1: MN-major}; n = MMA N;
-// accs = accumulators used in turn; steps = K steps per group (4 or 8); random = operand contents.
+// accs = accumulators used in turn; steps = K steps per group (4 or 8); random: bit 0 = non-zero
+// operand contents, bits 1..12 = run-time ring-stage stride in descriptor units (0 = fixed tiles),
+// bits 16.. = tcgen05.commit instructions issued after every group of K steps.
 extern "C" int ifv2_umma_rate(int a, int b, int n, int accs, int steps, int random, int iters,
                               long long* cycles, int32_t* status, void* stream) {
   IFV2_REQUIRE(cycles && status && iters > 0, IFV2_ERR_INVALID_ARG, "umma_rate: bad argument");
   cudaStream_t s = (cudaStream_t)stream;
 #define IFV2_RATE_CASE(A, B, N, ACCS)                                                        \
   if (a == A && b == B && n == N && accs == ACCS) {                                          \
-    if (steps == 4 && !random) return launch_rate<A, B, N, ACCS, 4, false>(iters, cycles, status, s); \
-    if (steps == 8 && !random) return launch_rate<A, B, N, ACCS, 8, false>(iters, cycles, status, s); \
-    if (steps == 8 && random) return launch_rate<A, B, N, ACCS, 8, true>(iters, cycles, status, s);   \
-    if (steps == 4 && random) return launch_rate<A, B, N, ACCS, 4, true>(iters, cycles, status, s);   \
+    if (steps == 4 && !(random & 1)) return launch_rate<A, B, N, ACCS, 4, false>(iters, cycles, status, s, (random >> 1) & 0xFFF, random >> 16); \
+    if (steps == 8 && !(random & 1)) return launch_rate<A, B, N, ACCS, 8, false>(iters, cycles, status, s, (random >> 1) & 0xFFF, random >> 16); \
+    if (steps == 8 && (random & 1)) return launch_rate<A, B, N, ACCS, 8, true>(iters, cycles, status, s, (random >> 1) & 0xFFF, random >> 16);   \
+    if (steps == 4 && (random & 1)) return launch_rate<A, B, N, ACCS, 4, true>(iters, cycles, status, s, (random >> 1) & 0xFFF, random >> 16);   \
   }
   IFV2_RATE_CASE(0, 0, 64, 1)
   IFV2_RATE_CASE(0, 0, 128, 1)
