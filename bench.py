@@ -272,13 +272,15 @@ def run_ours(args, rank, world, device):
 def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
     """The same job through the public API starting from pinned HOST buffers and ending with the
     output in pinned host memory: `StreamedPrefill` cuts the query into 16384-token chunks and
-    overlaps copy-in, kernels and copy-out on three streams."""
+    overlaps copy-in, kernels and copy-out on three streams.  With compute ~ tokens^2 and copies ~ tokens
+    the ascending chunk order is copy-bound for the first ~45 % of the sequence; smaller chunks only
+    shorten the fill and drain."""
     from infllmv2_cuda_impl_b200.sharding import StreamedPrefill
     host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v, kc)]
     for h, t in zip(host, (q, k, v, kc)):
         h.copy_(t)
     out_host = torch.empty(q.shape, dtype=q.dtype).pin_memory()
-    chunk = 16384 if seqlen % 16384 == 0 else seqlen
+    chunk = args.e2e_chunk if seqlen % args.e2e_chunk == 0 else seqlen
     runner = StreamedPrefill(seqlen, q.shape[1], k.shape[1], D, kc.shape[0], device, chunk)
     torch.cuda.synchronize()
     steps = max(1, min(args.steps, 3))
@@ -580,6 +582,8 @@ def main():
     ap.add_argument("--only", default=None, choices=["selection", "topk", "train", "decode"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
+    ap.add_argument("--e2e-chunk", type=int, default=8192,
+                    help="query tokens per chunk of the host-to-host (e2e) pipeline")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the secondary configs (selection micro-benchmark, varlen fwd+bwd, decode)")
     args = ap.parse_args()

@@ -26,9 +26,6 @@ constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9: two so
                                     // are needed in the backward, so the halves are independent)
 constexpr int kMaxMaskWords = 128;
 constexpr uint32_t kTileHalfBytes = 128 * 128;   // 128 rows x 64 bf16
-#ifndef IFV2_DKV_ORDER
-#define IFV2_DKV_ORDER 1
-#endif
 // Optional timeline of the first CTAs of one of the gradient kernels (a tuning aid):
 // -DIFV2_BWD_TRACE=1 records the dK/dV kernel, =2 the dQ kernel.
 #ifdef IFV2_BWD_TRACE
@@ -596,7 +593,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         return true;
       };
       // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
-      auto issue_dvdk = [&](int i, bool last) -> bool {
+      auto issue_dvdk = [&](int i) -> bool {
         const int s = i & 1;
         if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_ready, (uint32_t)(i & 1), abort_flag, p.status, 85)))
           return false;
@@ -614,20 +611,20 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         IFV2_TRACE(0, i, 3);
         return true;
       };
+      // dV / dK of a step go first, then S / dP of the next one: the Q / dO slot is released one
+      // product group earlier, which gives the copy of the tile two steps ahead a whole step to
+      // land.  Measured alternatives (timeline of the first CTAs, 65536-token training case):
+      // S / dP first (so that it runs under the softmax of the current step) 4600 clocks per
+      // step, this order 4350, issuing whichever group is ready first 4260 -- all three sit on
+      // the same bound, the 64 KB of Q / dO per step that every SM pulls through L2 (about
+      // 4.5 TB/s over the 148 SMs with one tile in flight per SM; shared memory has no room for
+      // a third slot).
       int i = 0;
       if (have >= 0) ok = issue_sdp(0);
       while (ok && have >= 0) {
         const int next = __shfl_sync(0xFFFFFFFFu, walk.next(bits), 0);   // (uniform for the compiler)
-#if IFV2_DKV_ORDER == 0
-        // S / dP of the next step first: it runs under this step's softmax
-        if (next >= 0) ok = issue_sdp(i + 1);
-        if (ok) ok = issue_dvdk(i, next < 0);
-#else
-        // dV / dK first: the Q / dO stage is released one product earlier, which gives the copy
-        // of the tile two steps ahead the time of a whole step to land
-        ok = issue_dvdk(i, next < 0);
+        ok = issue_dvdk(i);
         if (ok && next >= 0) ok = issue_sdp(i + 1);
-#endif
         have = next;
         ++i;
       }
