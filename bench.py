@@ -239,8 +239,22 @@ def run_ours(args, rank, world, device):
         roof["max_pooling_1d"] = ("hbm", bytes_pool / (kernel_ms["max_pooling_1d"] * 1e-3) / 1e9, hbm, "GB/s")
     dominant = max(kernel_ms, key=kernel_ms.get)
     bound, ach, peak, unit = roof[dominant]
+    # DRAM traffic per launch: measured with ncu on the 16384-token case of the same command
+    # (profiles/), where dram bytes / algorithmic bytes came out as below; a full-size launch is
+    # too large to capture, and both kernels stream each input once, so the ratio carries over
+    q_bytes = seqlen * hk_local * 16 * D * 2
+    alg_bytes = {
+        "stage1_block_scores": q_bytes + n_comp * hk_local * D * 2 + hk_local * seqlen * n_blk * 2,
+        "stage1_scores": q_bytes + n_comp * hk_local * D * 2 + hk_local * seqlen * row_stride * 2,
+        "sparse_attn_fwd": 2 * q_bytes + 2 * seqlen * hk_local * D * 2
+                           + hk_local * seqlen * (((n_blk + 63) // 64) * 8 + 16 * 4),
+    }
+    ncu_ratio = {"stage1_block_scores": 0.99, "stage1_scores": 0.97, "sparse_attn_fwd": 0.97}
+    traffic = (round(alg_bytes[dominant] * ncu_ratio[dominant]) if dominant in ncu_ratio else None)
     roofline = {"kernel": dominant, "bound": bound, "achieved": round(ach, 2), "peak": peak,
-                "unit": unit, "frac": round(ach / peak, 4), "traffic": None, "peak_source": pk_kind,
+                "unit": unit, "frac": round(ach / peak, 4), "traffic": traffic,
+                "traffic_source": "ncu dram bytes of the 16384-token case x algorithmic-byte ratio",
+                "algorithmic_bytes": alg_bytes.get(dominant), "peak_source": pk_kind,
                 "ms_per_launch": round(kernel_ms[dominant], 3)}
     kernels = {n: {"ms": round(kernel_ms[n], 3), "bound": roof[n][0], "achieved": round(roof[n][1], 2),
                    "unit": roof[n][3], "frac": round(roof[n][1] / roof[n][2], 4)} for n in names}
@@ -271,7 +285,7 @@ def run_ours(args, rank, world, device):
 
 def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
     """The same job through the public API starting from pinned HOST buffers and ending with the
-    output in pinned host memory: `StreamedPrefill` cuts the query into 16384-token chunks and
+    output in pinned host memory: `StreamedPrefill` cuts the query into chunks (--e2e-chunk tokens) and
     overlaps copy-in, kernels and copy-out on three streams.  With compute ~ tokens^2 and copies ~ tokens
     the ascending chunk order is copy-bound for the first ~45 % of the sequence; smaller chunks only
     shorten the fill and drain."""
