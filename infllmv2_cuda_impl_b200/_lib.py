@@ -9,7 +9,8 @@ import re
 import threading
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libinfllmv2_b200.so")
+# IFV2_LIBRARY_PATH points at another build of the same library (e.g. one compiled with tuning macros)
+LIB_PATH = os.environ.get("IFV2_LIBRARY_PATH") or os.path.join(_PKG_DIR, "libinfllmv2_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_PKG_DIR), "include", "infllmv2_b200.h")
 
 _lib = None

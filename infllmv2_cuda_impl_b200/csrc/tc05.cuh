@@ -59,14 +59,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // the CTA sees it and gives up too, and all roles fall through to the common teardown.
 constexpr long long kWaitLimitCycles = 1ll << 29;   // ~0.3 s at 1.9 GHz; real waits are microseconds
 
+// try_wait with a suspend-time hint: the warp may sleep in hardware until the phase completes or
+// the hint (nanoseconds) runs out, instead of coming back to the scheduler every few cycles.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
+#ifndef IFV2_WAIT_HINT_NS
+#define IFV2_WAIT_HINT_NS 2000
+#endif
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag, int32_t* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if (IFV2_WAIT_HINT_NS > 0 ? mbar_try_wait_hint(bar, parity, IFV2_WAIT_HINT_NS) : mbar_try_wait(bar, parity))
+      return true;
+    if ((++spins & 15u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
