@@ -14,8 +14,6 @@ struct SelfTestParams {
   const __nv_bfloat16* b;   // mode 4: B read with plain loads
   float* d;                 // (128, n) fp32
   int mode;
-  int iters;                // the product is issued this many times (rate measurement)
-  long long* cycles;        // optional: SM cycles from first issue to completion
   int32_t* status;
 };
 
@@ -54,8 +52,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
-  const int alt = p.mode >= 10 ? 1 : 0;      // rate-only variants: alternate between two accumulators
-  const int mode = p.mode >= 10 ? p.mode - 10 : p.mode;
+  const int mode = p.mode;
   const bool sw32 = p.mode == 5;               // mode 5 = mode 4 with the 32-byte swizzle
   const int n = (mode == 0 || mode == 3 || mode == 4 || mode == 5) ? 64 : 128;
   if (sw32) {
@@ -84,7 +81,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   }
   __syncthreads();
 
-  long long t_start = 0;
   if (warp == 0 && lane == 0) {
     tc_fence_after();
     if (mode == 4 || mode == 5) {
@@ -112,8 +108,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     if (mbar_wait(&bar_load, 0, &abort_flag, p.status, 1)) {
       tc_fence_after();
-      t_start = clock64();
-      for (int it = 0; it < p.iters; ++it) {
       if (mode == 5) {
         umma_ss(tmem_d, umma_desc_sw32(smem_u32(sA)), umma_desc_sw32(smem_u32(sB)),
                 umma_idesc_bf16(128, 64, false), false);
@@ -126,7 +120,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(tmem_d + (alt ? (kk & 1) * 64 : 0), umma_desc_sw128(smem_u32(sA) + off, 16, 1024),
+          umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + off, 16, 1024),
                   umma_desc_sw128(smem_u32(sB) + offb, 16, 1024), idesc, kk > 0);
         }
       } else if (mode == 3) {
@@ -141,12 +135,11 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t bdesc = umma_desc_sw128(smem_u32(sB) + kk * 2048, 8192, 1024);
           if (mode == 1)
-            umma_ss(tmem_d + (alt ? (kk & 1) * 128 : 0), umma_desc_sw128(smem_u32(sA) + kk * 32, 16, 1024),
+            umma_ss(tmem_d, umma_desc_sw128(smem_u32(sA) + kk * 32, 16, 1024),
                     bdesc, idesc, kk > 0);
           else
             umma_ts(tmem_d, tmem_a + kk * 8, bdesc, idesc, kk > 0);
         }
-      }
       }
       umma_commit(&bar_mma);
     }
@@ -154,7 +147,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncwarp();
   const bool ok = mbar_wait(&bar_mma, 0, &abort_flag, p.status, 2);
   tc_fence_after();
-  if (threadIdx.x == 0 && p.cycles != nullptr) *p.cycles = clock64() - t_start;
   if (ok) {
     for (int c = 0; c < n; c += 32) {
       uint32_t regs[32];
@@ -179,30 +171,13 @@ using namespace ifv2;
 //   mode 0: a (128,128), b (64,128)  -> d (128,64);  modes 1, 2: a (128,64), b (64,128) -> d (128,128)
 //   mode 3: a (128,128) = At, b (128,64) = Bt -> d = At^T . Bt (128,64)
 //   mode 4: a (128,16), b (64,16) -> d = a . b^T (128,64)
-static int selftest_impl(int mode, const void* a, const void* b, float* d, int32_t* status,
-                         void* stream, int iters, long long* cycles);
-
 extern "C" int ifv2_selftest_umma(int mode, const void* a, const void* b, float* d, int32_t* status,
                                   void* stream) {
-  return selftest_impl(mode, a, b, d, status, stream, 1, nullptr);
-}
-
-// Same tile product issued `iters` times back to back (the accumulator is simply overwritten /
-// re-accumulated): `cycles` receives the SM clock count from the first issue to completion, which
-// gives the sustained rate of one MMA shape / operand arrangement on a single SM.
-extern "C" int ifv2_selftest_umma_rate(int mode, const void* a, const void* b, float* d,
-                                       int32_t* status, void* stream, int iters, long long* cycles) {
-  return selftest_impl(mode, a, b, d, status, stream, iters, cycles);
-}
-
-static int selftest_impl(int mode, const void* a, const void* b, float* d, int32_t* status,
-                         void* stream, int iters, long long* cycles) {
-  IFV2_REQUIRE((mode >= 0 && mode <= 5) || mode == 10 || mode == 11, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0..4");
+  IFV2_REQUIRE(mode >= 0 && mode <= 5, IFV2_ERR_INVALID_ARG, "selftest: mode must be 0..5");
   IFV2_REQUIRE(a && b && d && status, IFV2_ERR_INVALID_ARG, "selftest: null pointer");
   CUtensorMap map_a, map_b;
   int rc;
-  const int base_mode = mode >= 10 ? mode - 10 : mode;
-  if (base_mode == 0) {
+  if (mode == 0) {
     rc = make_tensor_map_bf16_3d(&map_a, a, 128, 128, 1, 256, 256 * 128, 64, 128, 1);
     if (rc) return rc;
     rc = make_tensor_map_bf16_3d(&map_b, b, 128, 64, 1, 256, 256 * 64, 64, 64, 1);
@@ -224,7 +199,7 @@ static int selftest_impl(int mode, const void* a, const void* b, float* d, int32
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 50 * 1024);
   if (attr != cudaSuccess) return set_error((int)attr, "selftest: %s", cudaGetErrorString(attr));
   SelfTestParams p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, mode,
-                   iters < 1 ? 1 : iters, cycles, status};
+                   status};
   umma_selftest_kernel<<<1, 128, 50 * 1024, (cudaStream_t)stream>>>(map_a, map_b, p);
   return check_launch("umma_selftest");
 }
