@@ -287,8 +287,8 @@ def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
     """The same job through the public API starting from pinned HOST buffers and ending with the
     output in pinned host memory: `StreamedPrefill` cuts the query into chunks (--e2e-chunk tokens) and
     overlaps copy-in, kernels and copy-out on three streams.  With compute ~ tokens^2 and copies ~ tokens
-    the ascending chunk order is copy-bound for the first ~45 % of the sequence; smaller chunks only
-    shorten the fill and drain."""
+    an ascending chunk order is copy-bound for the first ~45 % of the sequence; the default order
+    starts in the middle and alternates outwards, which keeps copies and kernels both busy."""
     from infllmv2_cuda_impl_b200.sharding import StreamedPrefill
     host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v, kc)]
     for h, t in zip(host, (q, k, v, kc)):
@@ -300,7 +300,8 @@ def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
     steps = max(1, min(args.steps, 3))
 
     def one():
-        runner(host[0], host[1], host[2], host[3], out_host, TOPK, INIT_BLOCKS, LOCAL_BLOCKS)
+        runner(host[0], host[1], host[2], host[3], out_host, TOPK, INIT_BLOCKS, LOCAL_BLOCKS,
+               order=(list(range(seqlen // chunk)) if args.e2e_order == "ascending" else None))
 
     one()
     if world > 1:
@@ -321,7 +322,7 @@ def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
     d2h = out_host.numel() * out_host.element_size()
     return {"value": round(seqlen / (ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 3),
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "how": f"pinned host buffers, {seqlen // chunk} query chunks, copy-in / kernels / copy-out overlapped"}
+            "how": f"pinned host buffers, {seqlen // chunk} query chunks ({args.e2e_order}), copy-in / kernels / copy-out overlapped"}
 
 
 # ------------------------------------------------------------------------------ other configs --
@@ -596,6 +597,8 @@ def main():
     ap.add_argument("--only", default=None, choices=["selection", "topk", "train", "decode"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
+    ap.add_argument("--e2e-order", default="middle-out", choices=["middle-out", "ascending"],
+                    help="order in which the host-to-host pipeline processes the query chunks")
     ap.add_argument("--e2e-chunk", type=int, default=8192,
                     help="query tokens per chunk of the host-to-host (e2e) pipeline")
     ap.add_argument("--no-extras", action="store_true",

@@ -161,35 +161,58 @@ class StreamedPrefill:
         self.kc = torch.empty(n_comp, heads_k, head_dim, dtype=dtype, device=device)
         self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
+    @staticmethod
+    def middle_out(n: int) -> List[int]:
+        """Chunk order n/2, n/2-1, n/2+1, ...: the cost of a chunk grows with its index (causal) while
+        its copy does not, so starting with cheap chunks leaves the GPU waiting for copies and
+        starting with the last one pays for the whole K/V up front; alternating around the middle
+        keeps both the copy stream and the kernels busy."""
+        order, lo, hi = [], n // 2 - 1, n // 2
+        while lo >= 0 or hi < n:
+            if hi < n:
+                order.append(hi)
+                hi += 1
+            if lo >= 0:
+                order.append(lo)
+                lo -= 1
+        return order
+
     def __call__(self, q_host, k_host, v_host, kc_host, out_host, topk: int, init_blocks: int,
                  local_blocks: int, ops: Optional[PrefillOps] = None, kernel: int = 32,
-                 stride: int = 16):
+                 stride: int = 16, order: Optional[Sequence[int]] = None):
         """Enqueue one full prefill; returns when everything is ENQUEUED (synchronise the device, or
-        the returned event, before reading out_host)."""
+        the returned event, before reading out_host).  `order`: the sequence in which the query
+        chunks are processed (default `middle_out`); chunks are independent given the keys before
+        their end, which are copied on demand."""
         main = torch.cuda.current_stream(self.device)
         n = self.seqlen // self.chunk
+        order = list(order) if order is not None else self.middle_out(n)
+        if sorted(order) != list(range(n)):
+            raise ValueError("order must be a permutation of the chunk indices")
         self.s_in.wait_stream(main)
         self.s_out.wait_stream(main)
-        ev_in = []
+        ev_in = {}
         with torch.cuda.stream(self.s_in):
-            done_c = 0
-            for c in range(n):
-                # chunk c only needs the keys before its own end: K / V / compressed K travel
-                # chunk by chunk too, so the first kernels start after 1/n of the input has landed
-                sl = slice(c * self.chunk, (c + 1) * self.chunk)
+            kv_done, kc_done = 0, 0                 # tokens / compressed keys already on the device
+            for c in order:
+                # chunk c needs the keys before its own end: K / V / compressed K travel piecewise
+                # too, so the first kernels start after a fraction of the input has landed
                 lk = (c + 1) * self.chunk
+                if lk > kv_done:
+                    self.k[kv_done:lk].copy_(k_host[kv_done:lk], non_blocking=True)
+                    self.v[kv_done:lk].copy_(v_host[kv_done:lk], non_blocking=True)
+                    kv_done = lk
                 n_c = min(self.kc.shape[0], (lk - kernel) // stride + 1 if lk >= kernel else 0)
-                self.k[sl].copy_(k_host[sl], non_blocking=True)
-                self.v[sl].copy_(v_host[sl], non_blocking=True)
-                if n_c > done_c:
-                    self.kc[done_c:n_c].copy_(kc_host[done_c:n_c], non_blocking=True)
-                    done_c = n_c
+                if n_c > kc_done:
+                    self.kc[kc_done:n_c].copy_(kc_host[kc_done:n_c], non_blocking=True)
+                    kc_done = n_c
+                sl = slice(c * self.chunk, (c + 1) * self.chunk)
                 self.q[sl].copy_(q_host[sl], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.s_in)
-                ev_in.append(ev)
+                ev_in[c] = ev
         keep = []
-        for c in range(n):
+        for c in order:
             ch = Chunk(c, c * self.chunk, (c + 1) * self.chunk)
             main.wait_event(ev_in[c])
             out, _ = prefill_chunk(self.q[ch.start:ch.end], self.kc, self.k, self.v, ch, topk,
