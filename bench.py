@@ -110,13 +110,14 @@ class ClockSampler:
 
 def make_inputs(seqlen, hk_local, device, seed):
     """q, k, v ~ N(0,1)/sqrt(128) in bf16 for `hk_local` KV heads (16 query heads each), plus the
-    compressed keys (mean over windows of 32 tokens, stride 16)."""
+    compressed keys (mean over windows of 32 tokens, stride 16: the compress_keys kernel)."""
+    import infllm_v2
     g = torch.Generator(device=device).manual_seed(seed)
     s = 1.0 / math.sqrt(D)
     q = (torch.randn(seqlen, hk_local * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
     k = (torch.randn(seqlen, hk_local, D, device=device, generator=g) * s).to(torch.bfloat16)
     v = (torch.randn(seqlen, hk_local, D, device=device, generator=g) * s).to(torch.bfloat16)
-    kc = k.float().unfold(0, KERNEL, STRIDE).mean(-1).to(torch.bfloat16).contiguous()
+    kc = infllm_v2.compress_keys(k, kernel_size=KERNEL, kernel_stride=STRIDE)[0]
     return q, k, v, kc
 
 
@@ -340,6 +341,22 @@ def _time_ms(fn, reps=5, warmup=2):
     return a.elapsed_time(b) / reps
 
 
+def config4_compress(device, pk, small=False):
+    """Key compression (mean over 32-token windows, stride 16) at the prefill size: the K of the
+    131072-token, 8-KV-head sequence (268 MB, larger than L2) -> 8191 compressed keys."""
+    import infllm_v2
+    L, hk = (65536 if small else 131072), 8
+    g = torch.Generator(device=device).manual_seed(0)
+    k = (torch.randn(L, hk, D, device=device, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+    kc = infllm_v2.compress_keys(k)[0]
+    t = _time_ms(lambda: infllm_v2.compress_keys(k), reps=20, warmup=3)
+    b = k.numel() * 2 + kc.numel() * 2
+    return {"config4_compress_keys": {"tokens": L, "kv_heads": hk, "ms": round(t, 4),
+                                      "gbs": round(b / t / 1e6, 1),
+                                      "frac": round(b / t / 1e6 / pk["hbm_gbs"], 4),
+                                      "note": "268 MB of keys per launch, larger than the 126 MB L2"}}
+
+
 def config4_topk(device, pk, small=False):
     """The top-k kernel alone at the row width of the 131072-token prefill (2048 block scores per
     query row): one KV head's rows, scores shaped like the stage-1 output (block 0 and the 32
@@ -393,6 +410,8 @@ def extra_configs(device, pk, only=None, small=False):
         out.update(config2_selection(device, pk, small))
     if only in (None, "topk"):
         out.update(config4_topk(device, pk, small))
+    if only in (None, "compress"):
+        out.update(config4_compress(device, pk, small))
     if only in (None, "train"):
         out.update(config3_train(device, pk, small))
     if only in (None, "decode"):
@@ -409,7 +428,7 @@ def config2_selection(device, pk, small=False):
     L, hk = (8192 if small else 32768), 2
     q = (torch.randn(L, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
     k = (torch.randn(L, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
-    kc = k.float().unfold(0, KERNEL, STRIDE).mean(-1).to(torch.bfloat16).contiguous()
+    kc = infllm_v2.compress_keys(k, kernel_size=KERNEL, kernel_stride=STRIDE)[0]
     n_comp, n_blk = kc.shape[0], L // BLOCK
     cu_q = torch.tensor([0, L], dtype=torch.int32, device=device)
     cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=device)
@@ -594,7 +613,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true",
                     help="run stage 1 and the max-pool as two kernels (the reference's op sequence)")
-    ap.add_argument("--only", default=None, choices=["selection", "topk", "train", "decode"],
+    ap.add_argument("--only", default=None, choices=["selection", "topk", "compress", "train", "decode"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
     ap.add_argument("--e2e-order", default="middle-out", choices=["middle-out", "ascending"],

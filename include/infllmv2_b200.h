@@ -60,6 +60,28 @@ int ifv2_transpose_blockmask(const int64_t* fwd_words, int64_t* bwd_words, int h
 
 /* ---------------------------------------------------------------- selection kernels -------- */
 
+/* Key compression in front of the stage-1 scorer: compressed key j of a sequence = mean of the keys
+ * of tokens [stride*j, stride*j + kernel) (full windows only), per KV head and feature, fp32
+ * accumulation, bf16 result.  k: (total_k, heads_k, 128) bf16; kc: (total_c, heads_k, 128) bf16.
+ * cu_seqlens_k / cu_seqlens_c: (batch+1) int32 device tables of keys / compressed keys per
+ * sequence (cu_c[b+1]-cu_c[b] = (len_b - kernel)/stride + 1, or 0 when len_b < kernel); both null =
+ * one sequence.  The reference keeps this step in its caller and tests
+ * (tests/test_stage1_compressed_lse.py:11-99, compress_tensor / calc_chunks_with_stride). */
+int ifv2_compress_keys(const void* k, void* kc, const int32_t* cu_seqlens_k,
+                       const int32_t* cu_seqlens_c, int batch, int64_t total_k, int64_t total_c,
+                       int heads_k, int head_dim, int kernel_size, int kernel_stride, void* stream);
+
+/* Decode-time update of a compressed-key cache after one token was appended to every sequence:
+ * a sequence whose new length L satisfies L >= kernel and (L - kernel) % stride == 0 has completed
+ * window j = (L - kernel)/stride, and kc_cache[b, j] is written; other sequences are untouched.
+ * k_cache: (batch, cache_capacity, heads_k, 128); kc_cache: (batch, compressed_capacity, heads_k, 128);
+ * cache_seqlens: (batch) int32 lengths after the append.  No counterpart in the reference (its
+ * caller recompresses). */
+int ifv2_compress_keys_append(const void* k_cache, void* kc_cache, const int32_t* cache_seqlens,
+                              int batch, int64_t cache_capacity, int64_t compressed_capacity,
+                              int heads_k, int head_dim, int kernel_size, int kernel_stride,
+                              void* stream);
+
 /* 1-D max-pool of stage-1 scores to block scores with +inf on the init and causal-local blocks.
  * in: (heads, q_len, k_len) with `in_row_stride` elements between rows (>= k_len);
  * out: (heads, q_len, out_len) contiguous.  dtype: is_bf16 ? bf16 : fp16.

@@ -24,6 +24,10 @@ SIGNATURES = {
     "ifv2_blockmask_to_uint64": [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     "ifv2_uint64_to_bool": [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     "ifv2_transpose_blockmask": [c_void_p, c_void_p, c_int, c_int64, c_int, c_void_p],
+    "ifv2_compress_keys": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int,
+                           c_int, c_int, c_void_p],
+    "ifv2_compress_keys_append": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int,
+                                  c_int, c_int, c_void_p],
     "ifv2_max_pooling_1d": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ifv2_max_pooling_1d_varlen": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -209,3 +209,74 @@ def infllmv2_topk(block_score: torch.Tensor, k: int, cache_len: int = 0,
                   int(block_score.dtype == torch.bfloat16), hk, t, n, row_stride, k, cu_ptr, cl_ptr,
                   batch, cache_len, block_size, _stream(block_score.device))
     return out
+
+
+def compressed_lengths(cu_seqlens_k: torch.Tensor, kernel_size: int = 32,
+                       kernel_stride: int = 16) -> torch.Tensor:
+    """Cumulative number of compressed keys per sequence (int32, same device, no host sync):
+    a sequence of length L has (L - kernel_size) // kernel_stride + 1 full windows, none when
+    L < kernel_size (tests/test_stage1_compressed_lse.py:11-55, calc_chunks_with_stride)."""
+    lens = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).to(torch.int64)
+    n = torch.where(lens >= kernel_size, (lens - kernel_size) // kernel_stride + 1,
+                    torch.zeros_like(lens))
+    cu_c = torch.zeros_like(cu_seqlens_k, dtype=torch.int32)
+    cu_c[1:] = n.cumsum(0).to(torch.int32)
+    return cu_c
+
+
+def compress_keys(k: torch.Tensor, cu_seqlens_k: Optional[torch.Tensor] = None, kernel_size: int = 32,
+                  kernel_stride: int = 16, cu_seqlens_c: Optional[torch.Tensor] = None,
+                  total_c: Optional[int] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Mean-pool keys (total_k, Hk, 128) bf16 into compressed keys (total_c, Hk, 128): window j of
+    a sequence covers its tokens [stride*j, stride*j + kernel), full windows only -- what the
+    reference's tests build with `compress_tensor` (tests/test_stage1_compressed_lse.py:57-99)
+    before calling infllmv2_attn_stage1 (there in (heads, tokens, d) layout).
+
+    Returns (kc, cu_seqlens_c).  Without cu_seqlens_k the input is one sequence and cu_seqlens_c is
+    None.  With it, pass cu_seqlens_c / total_c when known; otherwise they are computed here and
+    total_c costs one device->host read.
+    """
+    _require_cuda(k, "k")
+    if k.dtype != torch.bfloat16 or k.dim() != 3:
+        raise ValueError("k must be (total_k, heads_k, head_dim) bf16")
+    k = k.contiguous()
+    total_k, hk, d = k.shape
+    if cu_seqlens_k is None:
+        total_c = (total_k - kernel_size) // kernel_stride + 1 if total_k >= kernel_size else 0
+        batch, cu_k_ptr, cu_c_ptr = 1, None, None
+    else:
+        assert cu_seqlens_k.dtype == torch.int32
+        cu_seqlens_k = cu_seqlens_k.contiguous()
+        batch = cu_seqlens_k.shape[0] - 1
+        if cu_seqlens_c is None:
+            cu_seqlens_c = compressed_lengths(cu_seqlens_k, kernel_size, kernel_stride)
+        cu_seqlens_c = cu_seqlens_c.contiguous()
+        if total_c is None:
+            total_c = int(cu_seqlens_c[-1].item())
+        cu_k_ptr, cu_c_ptr = cu_seqlens_k.data_ptr(), cu_seqlens_c.data_ptr()
+    kc = torch.empty(total_c, hk, d, dtype=k.dtype, device=k.device)
+    with torch.cuda.device(k.device):
+        _lib.call("ifv2_compress_keys", k.data_ptr(), kc.data_ptr(), cu_k_ptr, cu_c_ptr, batch,
+                  total_k, total_c, hk, d, kernel_size, kernel_stride, _stream(k.device))
+    return kc, cu_seqlens_c
+
+
+def compress_keys_append(k_cache: torch.Tensor, cache_seqlens: torch.Tensor, kc_cache: torch.Tensor,
+                         kernel_size: int = 32, kernel_stride: int = 16) -> None:
+    """Decode-time update, in place: for every sequence whose length (AFTER the append of the new
+    token, `cache_seqlens`) completes a window -- L >= kernel and (L - kernel) % stride == 0 --
+    write that window's mean into kc_cache[b, (L - kernel) // stride].
+    k_cache (B, cap, Hk, 128), kc_cache (B, c_cap, Hk, 128), both bf16 and contiguous."""
+    _require_cuda(k_cache, "k_cache")
+    _require_cuda(kc_cache, "kc_cache")
+    if (k_cache.dtype != torch.bfloat16 or kc_cache.dtype != torch.bfloat16 or k_cache.dim() != 4
+            or kc_cache.dim() != 4 or not k_cache.is_contiguous() or not kc_cache.is_contiguous()):
+        raise ValueError("k_cache / kc_cache must be contiguous (batch, capacity, heads_k, 128) bf16")
+    assert cache_seqlens.dtype == torch.int32 and cache_seqlens.shape[0] == k_cache.shape[0]
+    b, cap, hk, d = k_cache.shape
+    if kc_cache.shape[0] != b or kc_cache.shape[2] != hk or kc_cache.shape[3] != d:
+        raise ValueError("kc_cache does not match k_cache")
+    with torch.cuda.device(k_cache.device):
+        _lib.call("ifv2_compress_keys_append", k_cache.data_ptr(), kc_cache.data_ptr(),
+                  cache_seqlens.contiguous().data_ptr(), b, cap, kc_cache.shape[1], hk, d,
+                  kernel_size, kernel_stride, _stream(k_cache.device))

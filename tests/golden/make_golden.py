@@ -12,6 +12,7 @@ It imports, unmodified, from the reference's tests/ directory:
   tests/test_uint64_to_bool.py::py_uint64_to_bool
   tests/utils.py::convert_topk_to_base_blockmask, prepare_mixed_mask, attention_blocksparse_ref
   tests/test_kvcache_simple.py::naive_attention
+  tests/test_stage1_compressed_lse.py::compress_tensor (+ calc_chunks_with_stride)
 (the `infllm_v2` CUDA module and matplotlib those files import at the top are replaced by
 empty stand-ins; none of the functions above touches them), feeds them seeded inputs and
 stores the expected outputs as small .npz files next to this script (the inputs are recomputed
@@ -49,7 +50,7 @@ def _import_reference(ref_root):
     os.chdir(tempfile.mkdtemp())          # tests/utils.py creates a directory in the cwd on import
     mods = {}
     for m in ("stage1.naive_softmax", "test_topk_to_uint64", "test_blockmask",
-              "test_uint64_to_bool", "utils", "test_kvcache_simple"):
+              "test_uint64_to_bool", "utils", "test_kvcache_simple", "test_stage1_compressed_lse"):
         mods[m] = importlib.import_module(m)
     return mods
 
@@ -217,6 +218,32 @@ def gen_pool_topk(out):
     print("pool/topk: fast forms == literal transliterations / hand KATs")
 
 
+def gen_compress(mods, out):
+    """Key compression (mean over token windows): the reference's test helper on bf16 inputs,
+    packed sequences of ragged lengths, both window shapes."""
+    import oracle
+    ref_fn = mods["test_stage1_compressed_lse"].compress_tensor
+    cases = {}
+    for name, lens, kernel, stride in (("a", [64], 32, 16), ("b", [31, 32, 33, 100], 32, 16),
+                                       ("c", [300, 5, 257], 128, 64), ("d", [47, 48, 49], 32, 16),
+                                       ("e", [10, 20], 32, 16)):
+        seed = 700 + ord(name)
+        total, hk = sum(lens), 2
+        k = torch.from_numpy(det_array((total, hk, 128), seed)).to(torch.bfloat16)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+        ref, cu_ref = ref_fn(k.transpose(0, 1).contiguous(), cu, kernel, stride, hk, 128)
+        ref = ref.transpose(0, 1).contiguous()                     # (total_c, hk, 128)
+        got, cu_c = oracle.compress_keys(k, cu.tolist(), kernel, stride)
+        assert list(cu_ref.tolist()) == cu_c, (cu_ref, cu_c)
+        assert ref.shape == got.shape and torch.equal(ref.view(torch.int16), got.view(torch.int16)), name
+        cases[f"ck_{name}_lens"] = np.array(lens, dtype=np.int64)
+        cases[f"ck_{name}_cfg"] = np.array([kernel, stride, seed, hk], dtype=np.int64)
+        cases[f"ck_{name}_cu_c"] = np.array(cu_c, dtype=np.int64)
+        cases[f"ck_{name}_out"] = ref.float().numpy()
+    print("compress: oracle == reference compress_tensor bit for bit")
+    np.savez_compressed(os.path.join(out, "compress.npz"), **cases)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -227,4 +254,5 @@ if __name__ == "__main__":
     gen_stage1(mods, HERE)
     gen_stage2(mods, HERE)
     gen_pool_topk(HERE)
+    gen_compress(mods, HERE)
     print("golden fixtures written to", HERE)

@@ -130,3 +130,17 @@ def test_backward_oracle_matches_finite_difference():
 
     assert torch.autograd.gradcheck(f, (q.requires_grad_(), k.requires_grad_(), v.requires_grad_()),
                                     eps=1e-6, atol=1e-5)
+
+
+def test_compress_golden(golden_dir):
+    """Key compression against the outputs of the reference's compress_tensor test helper."""
+    g = _load(golden_dir, "compress.npz")
+    for key in [k for k in g.files if k.endswith("_lens")]:
+        base = key[:-5]
+        lens = [int(x) for x in g[key]]
+        kernel, stride, seed, hk = (int(x) for x in g[base + "_cfg"])
+        k = torch.from_numpy(det_array((sum(lens), hk, 128), seed)).to(torch.bfloat16)
+        cu = [0] + list(np.cumsum(lens))
+        got, cu_c = oracle.compress_keys(k, cu, kernel, stride)
+        assert cu_c == [int(x) for x in g[base + "_cu_c"]], key
+        assert np.array_equal(got.float().numpy(), g[base + "_out"]), key
