@@ -357,6 +357,30 @@ def config4_compress(device, pk, small=False):
                                       "note": "268 MB of keys per launch, larger than the 126 MB L2"}}
 
 
+def config4_coarse_lse(device, pk, small=False):
+    """Stage 1 (+ pool) of the prefill with the row sums taken over the coarse compression
+    (kernel 128 / stride 64) instead of the scored keys: the reference's "compressed LSE" mode.
+    Pass 1 then has a quarter of the keys."""
+    import infllm_v2
+    L, hk = (32768 if small else SEQLEN), HK
+    q, k, _, kc = make_inputs(L, hk, device, seed=0)
+    kv = infllm_v2.compress_keys(k, kernel_size=128, kernel_stride=64)[0]
+    cu_q = torch.tensor([0, L], dtype=torch.int32, device=device)
+    cu_c = torch.tensor([0, kc.shape[0]], dtype=torch.int32, device=device)
+    cu_v = torch.tensor([0, kv.shape[0]], dtype=torch.int32, device=device)
+    run = lambda **kw: infllm_v2.infllmv2_stage1_block_scores(q, kc, cu_q, cu_c, L, kc.shape[0],
+                                                              LOCAL_BLOCKS, INIT_BLOCKS, **kw)
+    t_same = _time_ms(lambda: run(), reps=3, warmup=2)
+    t_coarse = _time_ms(lambda: run(lse_keys=kv, cu_seqlens_v=cu_v), reps=3, warmup=2)
+    infllm_v2.check_device_status()
+    fl = 2.0 * D * hk * 16 * visible_compressed(L, kc.shape[0])
+    return {"config4_stage1_compressed_lse": {
+        "tokens": L, "ms_lse_over_scored_keys": round(t_same, 3), "ms_lse_over_coarse_keys": round(t_coarse, 3),
+        "tflops_coarse": round(fl / t_coarse / 1e9, 1),
+        "frac_coarse": round(fl / t_coarse / 1e9 / pk["bf16_tflops_sustained"], 4),
+        "note": "FLOPs counted as one pass over the scored keys in both cases"}}
+
+
 def config4_topk(device, pk, small=False):
     """The top-k kernel alone at the row width of the 131072-token prefill (2048 block scores per
     query row): one KV head's rows, scores shaped like the stage-1 output (block 0 and the 32
@@ -412,6 +436,8 @@ def extra_configs(device, pk, only=None, small=False):
         out.update(config4_topk(device, pk, small))
     if only in (None, "compress"):
         out.update(config4_compress(device, pk, small))
+    if only in (None, "coarse"):
+        out.update(config4_coarse_lse(device, pk, small))
     if only in (None, "train"):
         out.update(config3_train(device, pk, small))
     if only in (None, "decode"):
@@ -613,7 +639,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true",
                     help="run stage 1 and the max-pool as two kernels (the reference's op sequence)")
-    ap.add_argument("--only", default=None, choices=["selection", "topk", "compress", "train", "decode"],
+    ap.add_argument("--only", default=None, choices=["selection", "topk", "compress", "coarse", "train", "decode"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
     ap.add_argument("--e2e-order", default="middle-out", choices=["middle-out", "ascending"],

@@ -119,15 +119,19 @@ int ifv2_topk_select(const void* score, int32_t* out_idx, int is_bf16, int heads
  * softmax_j(scale * q[t, 16h+g] . kc[j, h]) over the compressed keys visible to token t.
  * q: (total_q, heads_q, 128) bf16, kc: (total_c, heads_k, 128) bf16, both dense row-major.
  * out: (heads_k, total_q, out_row_stride) bf16; columns [0, max_seqlen_k) of every row are
- * written (0 where invisible).  status: int32[4] device words, word 0 != 0 after the launch
- * means a bounded wait ran out.
+ * written (0 where invisible).  lse_keys / cu_seqlens_v / total_v: the keys the row maxima and
+ * sums are taken over (the reference's `v` argument): null / null / 0 = the same keys as kc; a
+ * sequence whose count differs from its kc count is treated as the coarse compression (kernel
+ * 128, stride 64) whose log-sum-exp normalises the scores, as flash_fwd_kernel.h:1236-1240 does.
+ * status: int32[4] device words, word 0 != 0 after the launch means a bounded wait ran out.
  * Replaces C.varlen_fwd_stage1: csrc/entry.cu:209-214 -> mha_varlen_fwd_stage1,
  * csrc/flash_attn/flash_api.cpp:784-1049 (+ the GQA transpose, slice and NaN scrub of
  * infllm_v2/infllmv2_sparse_attention.py:554-589). */
-int ifv2_stage1_scores(const void* q, const void* kc, void* out, const int32_t* cu_seqlens_q,
-                       const int32_t* cu_seqlens_k, int batch, int64_t total_q, int64_t total_c,
-                       int heads_q, int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
-                       int64_t out_row_stride, float softmax_scale, int causal,
+int ifv2_stage1_scores(const void* q, const void* kc, const void* lse_keys, void* out,
+                       const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                       const int32_t* cu_seqlens_v, int64_t total_v, int batch, int64_t total_q,
+                       int64_t total_c, int heads_q, int heads_k, int head_dim, int max_seqlen_q,
+                       int max_seqlen_k, int64_t out_row_stride, float softmax_scale, int causal,
                        int32_t* status, void* stream);
 
 /* Stage-1 scorer with the 64-token max-pool fused in: writes block scores
@@ -139,14 +143,15 @@ int ifv2_stage1_scores(const void* q, const void* kc, void* out, const int32_t* 
  * Fuses mha_varlen_fwd_stage1 (csrc/flash_attn/flash_api.cpp:784-1049) with
  * max_pooling_1d_varlen_kernel (csrc/max_pooling_1d.cuh:11-103); the reference runs them as two
  * launches with a (heads_k, total_q, max_seqlen_k) tensor in between. */
-int ifv2_stage1_block_scores(const void* q, const void* kc, void* scores_or_null,
-                             void* block_scores, const int32_t* cu_seqlens_q,
-                             const int32_t* cu_seqlens_k, const int32_t* cache_lens, int batch,
-                             int64_t total_q, int64_t total_c, int heads_q, int heads_k,
-                             int head_dim, int max_seqlen_q, int max_seqlen_k,
-                             int64_t scores_row_stride, int n_blocks, int cache_len,
-                             int local_blocks, int init_blocks, float softmax_scale, int causal,
-                             int32_t* status, void* stream);
+int ifv2_stage1_block_scores(const void* q, const void* kc, const void* lse_keys,
+                             void* scores_or_null, void* block_scores,
+                             const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                             const int32_t* cu_seqlens_v, int64_t total_v,
+                             const int32_t* cache_lens, int batch, int64_t total_q,
+                             int64_t total_c, int heads_q, int heads_k, int head_dim,
+                             int max_seqlen_q, int max_seqlen_k, int64_t scores_row_stride,
+                             int n_blocks, int cache_len, int local_blocks, int init_blocks,
+                             float softmax_scale, int causal, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------- stage 2 ------------------ */
 

@@ -35,12 +35,12 @@ SIGNATURES = {
                                    c_int, c_int, c_int, c_void_p],
     "ifv2_topk_select": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int64, c_int,
                          c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "ifv2_stage1_scores": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
-                           c_int64, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int,
-                           c_void_p, c_void_p],
-    "ifv2_stage1_block_scores": [c_void_p] * 7 + [c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,
-                                                  c_int, c_int64, c_int, c_int, c_int, c_int, c_float,
-                                                  c_int, c_void_p, c_void_p],
+    "ifv2_stage1_scores": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_int64, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
+                           c_int64, c_float, c_int, c_void_p, c_void_p],
+    "ifv2_stage1_block_scores": [c_void_p] * 8 + [c_int64, c_void_p, c_int, c_int64, c_int64, c_int,
+                                                  c_int, c_int, c_int, c_int, c_int64, c_int, c_int,
+                                                  c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ifv2_sparse_attn_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int,
                              c_int, c_int, c_float, c_int, c_void_p, c_void_p],

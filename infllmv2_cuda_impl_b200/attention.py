@@ -92,18 +92,22 @@ def infllmv2_attn_stage1(
     """Stage-1 scores: for every KV head, softmax(q . k_compressed) summed over its 16 query heads.
 
     q: (total_q, nheads, 128) bf16; k: (total_c, nheads_k, 128) bf16 compressed keys;
-    v / cu_seqlens_v: the keys the log-sum-exp is taken over -- must be the same tensor as k
-    (the coarse-LSE mode with a differently compressed v is not built).
+    v / cu_seqlens_v: the keys the log-sum-exp is taken over.  Normally the same tensor as k.
+    A differently compressed v (kernel 128 / stride 64, the reference's "compressed LSE" mode,
+    flash_fwd_kernel.h:1236-1240, oracle tests/stage1/complse_online_softmax.py) makes the row
+    maxima and sums come from v and the returned scores exp(q.k - lse_v), summed over the heads.
     Returns (nheads_k, total_q, max_seqlen_k) bf16; entries a token cannot see are 0.
     The returned tensor is a column slice of a buffer whose rows are padded to a multiple of
     128 elements, like the reference's (infllm_v2/infllmv2_sparse_attention.py:587).
     """
     _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table,
                   "infllmv2_attn_stage1")
-    if v is not None and (v.shape != k.shape):
-        raise NotImplementedError(
-            "infllmv2_attn_stage1: a separately compressed `v` (coarse-LSE mode) is not supported; "
-            "pass the compressed keys as both k and v")
+    lse_keys = None
+    if v is not None and v is not k and (v.shape != k.shape or v.data_ptr() != k.data_ptr()):
+        if v.dtype != k.dtype or v.dim() != 3 or v.shape[1:] != k.shape[1:]:
+            raise ValueError("infllmv2_attn_stage1: v must be (total_v, nheads_k, 128) in k's dtype")
+        assert cu_seqlens_v is not None and cu_seqlens_v.dtype == torch.int32
+        lse_keys = _dense(maybe_contiguous(v))
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
     q, k = _dense(maybe_contiguous(q)), _dense(maybe_contiguous(k))
@@ -114,8 +118,11 @@ def infllmv2_attn_stage1(
     row_stride = max(round_multiple(max_seqlen_k, 128), 128)
     buf = torch.empty(nheads_k, total_q, row_stride, dtype=torch.bfloat16, device=q.device)
     with torch.cuda.device(q.device):
-        _lib.call("ifv2_stage1_scores", q.data_ptr(), k.data_ptr(), buf.data_ptr(),
-                  cu_seqlens_q.contiguous().data_ptr(), cu_seqlens_k.contiguous().data_ptr(), batch,
+        _lib.call("ifv2_stage1_scores", q.data_ptr(), k.data_ptr(),
+                  lse_keys.data_ptr() if lse_keys is not None else None, buf.data_ptr(),
+                  cu_seqlens_q.contiguous().data_ptr(), cu_seqlens_k.contiguous().data_ptr(),
+                  cu_seqlens_v.contiguous().data_ptr() if lse_keys is not None else None,
+                  lse_keys.shape[0] if lse_keys is not None else 0, batch,
                   total_q, k.shape[0], nheads, nheads_k, q.shape[-1], max_seqlen_q, max_seqlen_k,
                   row_stride, float(softmax_scale), int(bool(causal)),
                   _status_words(q.device).data_ptr(), _stream(q.device))
@@ -125,7 +132,8 @@ def infllmv2_attn_stage1(
 def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                  local_blocks, init_blocks, cache_len=0, cache_lens=None,
                                  max_cache_len=None, softmax_scale=None, causal=True,
-                                 block_size=64, stride=16, return_scores=False):
+                                 block_size=64, stride=16, return_scores=False,
+                                 lse_keys=None, cu_seqlens_v=None):
     """Stage 1 and the 64-token max-pool in one kernel (an addition to the reference API).
 
     Returns block scores (nheads_k, total_q, ceil((max_seqlen_q + cache) / 64)) bf16 equal, bit
@@ -133,8 +141,13 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
     (nheads_k, total_q, max_seqlen_k) score tensor is only materialised with return_scores=True
     (then the result is (block_scores, scores)).  cache_lens: optional per-sequence int32 tensor
     (pass max_cache_len to avoid a device->host read); otherwise the scalar cache_len applies.
+    lse_keys / cu_seqlens_v: optional coarser compressed keys for the log-sum-exp (the `v` of
+    infllmv2_attn_stage1).
     """
     _check_common(q, k, 0.0, (-1, -1), 0.0, None, None, "infllmv2_stage1_block_scores")
+    if lse_keys is not None:
+        assert cu_seqlens_v is not None and cu_seqlens_v.dtype == torch.int32
+        lse_keys = _dense(maybe_contiguous(lse_keys))
     if block_size != BLOCK_N or stride != 16:
         raise NotImplementedError("infllmv2_stage1_block_scores: only block_size 64 / stride 16")
     if softmax_scale is None:
@@ -158,8 +171,11 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
         buf = torch.empty(nheads_k, total_q, row_stride, dtype=torch.bfloat16, device=q.device)
     with torch.cuda.device(q.device):
         _lib.call("ifv2_stage1_block_scores", q.data_ptr(), k.data_ptr(),
+                  lse_keys.data_ptr() if lse_keys is not None else None,
                   buf.data_ptr() if buf is not None else None, pooled.data_ptr(),
                   cu_seqlens_q.contiguous().data_ptr(), cu_seqlens_k.contiguous().data_ptr(),
+                  cu_seqlens_v.contiguous().data_ptr() if lse_keys is not None else None,
+                  lse_keys.shape[0] if lse_keys is not None else 0,
                   cache_lens.data_ptr() if cache_lens is not None else None, batch, total_q,
                   k.shape[0], nheads, nheads_k, q.shape[-1], max_seqlen_q, max_seqlen_k, row_stride,
                   n_blocks, int(cache_len), int(local_blocks), int(init_blocks), float(softmax_scale),

@@ -50,6 +50,7 @@ struct Stage1Params {
   __nv_bfloat16* pooled;          // block scores, may be null
   const int32_t* cu_q;
   const int32_t* cu_k;
+  const int32_t* cu_v;            // keys of the row sums (pass 1); null = the keys of pass 2
   const int32_t* cache_lens;      // per sequence, may be null
   int64_t total_q;
   int heads_q, heads_k;
@@ -89,12 +90,13 @@ __device__ long long g_s1_trace[4][4][256][2];   // [CTA][role][step][event] = S
 #endif
 
 // Number of leading compressed keys visible to local token i (C integer division, as the
-// reference's device code): key j covers tokens [16j, 16j+32) and the pattern is aligned to the
-// END of the keys when the query segment is shorter than the keys cover.
-__device__ __forceinline__ int visible_limit(int i, int lq, int lc, int causal) {
+// reference's device code): with compression stride st, key j covers tokens [st*j, st*j + 2*st)
+// and the pattern is aligned to the END of the keys when the query segment is shorter than the
+// keys cover.  st = 16 for the scored keys; the coarse keys of the row sums use 64.
+__device__ __forceinline__ int visible_limit(int i, int lq, int lc, int causal, int st = 16) {
   if (!causal) return lc;
-  const int off = lc - (lq - 15) / 16;
-  return min(lc, max(0, (i + 1) / 16 - 1 + off));
+  const int off = lc - (lq - st + 1) / st;
+  return min(lc, max(0, (i + 1) / st - 1 + off));
 }
 
 __device__ __forceinline__ float bf16_round(float x) {
@@ -104,7 +106,7 @@ __device__ __forceinline__ float bf16_round(float x) {
 template <bool kPooled>
 __global__ void __launch_bounds__(kThreads, 2)
 stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kc,
-              const Stage1Params p) {
+              const __grid_constant__ CUtensorMap map_kv, const Stage1Params p) {
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                       ~(uintptr_t)1023);
@@ -118,11 +120,19 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
   const int ntok = min(kTokPerTile, lq - tok0);
   const int lim_max = visible_limit(tok0 + ntok - 1, lq, lc, p.causal);    // limits grow with i
+  // Pass 1 (row maxima and sums) runs over the keys given as `v`: the same compressed keys, or a
+  // coarser compression (kernel 128 / stride 64) whose log-sum-exp then normalises the scores of
+  // pass 2 -- the reference switches on the key counts (flash_fwd_kernel.h:1236-1240)
+  const int v0 = p.cu_v ? p.cu_v[b] : k0;
+  const int lcv = p.cu_v ? p.cu_v[b + 1] - v0 : lc;
+  const int st1 = (lcv == lc) ? 16 : 64;
+  const int lim_max1 = visible_limit(tok0 + ntok - 1, lq, lcv, p.causal, st1);
   // (read through a warp broadcast: it tells the compiler that the value is warp-uniform, so the
   //  MMA issuer's descriptor arithmetic stays in uniform registers instead of being moved there
   //  operand by operand for every MMA)
   const int n_tiles = __shfl_sync(0xFFFFFFFFu, (lim_max + kKeysPerTile - 1) / kKeysPerTile, 0);
-  const int n_steps = 2 * n_tiles;
+  const int n_tiles1 = __shfl_sync(0xFFFFFFFFu, (lim_max1 + kKeysPerTile - 1) / kKeysPerTile, 0);
+  const int n_steps = n_tiles1 + n_tiles;      // pass-1 tiles, then pass-2 tiles
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
@@ -137,6 +147,7 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_kc);
+    prefetch_tensormap(&map_kv);
   }
   if (warp == 1) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -168,14 +179,19 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       tma_load_3d(sm.q[1], &map_q, &sm.q_full, 64, h * kGroup, q0 + tok0);
       int issued = 0;
       for (int t = 0; t < n_steps; ++t) {
-        const int s = t & 1, tile = (t < n_tiles) ? t : t - n_tiles;
+        const int s = t & 1;
         if (t >= 2 && !mbar_wait(&sm.acc_full[s], (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag,
                                  p.status, 41))
           break;
         IFV2_TRACE(3, t, 0);
         mbar_expect_tx(&sm.kc_full[s], 2 * kHalfBytes);
-        tma_load_3d(sm.kc[s][0], &map_kc, &sm.kc_full[s], 0, h, k0 + tile * kKeysPerTile);
-        tma_load_3d(sm.kc[s][1], &map_kc, &sm.kc_full[s], 64, h, k0 + tile * kKeysPerTile);
+        if (t < n_tiles1) {
+          tma_load_3d(sm.kc[s][0], &map_kv, &sm.kc_full[s], 0, h, v0 + t * kKeysPerTile);
+          tma_load_3d(sm.kc[s][1], &map_kv, &sm.kc_full[s], 64, h, v0 + t * kKeysPerTile);
+        } else {
+          tma_load_3d(sm.kc[s][0], &map_kc, &sm.kc_full[s], 0, h, k0 + (t - n_tiles1) * kKeysPerTile);
+          tma_load_3d(sm.kc[s][1], &map_kc, &sm.kc_full[s], 64, h, k0 + (t - n_tiles1) * kKeysPerTile);
+        }
         issued = t + 1;
       }
       if (*abort_flag) {
@@ -200,11 +216,11 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       for (int t = 0; t < n_steps && ok; ++t) {
         const int s = t & 1;
         const uint32_t par = (uint32_t)((t >> 1) & 1);
-        const bool pass2 = t >= n_tiles;
+        const bool pass2 = t >= n_tiles1;
         bool w = mbar_wait(&sm.kc_full[s], par, abort_flag, p.status, 52);
         IFV2_TRACE(3, t, 1);
         if (w && t >= 2) w = mbar_wait(&sm.acc_empty[s], par ^ 1u, abort_flag, p.status, 53);
-        if (w && t == n_tiles) w = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
+        if (w && t == n_tiles1) w = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
         ok = __all_sync(0xFFFFFFFFu, w);
         if (!ok) break;
         tc_fence_after();
@@ -239,9 +255,9 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     // ---------------- pass 1: running max / sum of this thread's query row
     {
       const int tl = r >> 4;
-      const int lim_row = (tl < ntok) ? visible_limit(tok0 + tl, lq, lc, p.causal) : 0;
+      const int lim_row = (tl < ntok) ? visible_limit(tok0 + tl, lq, lcv, p.causal, st1) : 0;
       float m = -INFINITY, l = 0.f;
-      for (int t = 0; t < n_tiles; ++t) {
+      for (int t = 0; t < n_tiles1; ++t) {
         const int s = t & 1;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.acc_full[s], (uint32_t)((t >> 1) & 1),
                                                abort_flag, p.status, 61));
@@ -294,6 +310,8 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           l = l * ((m > -INFINITY) ? exp2f((m - mm) * p.scale_log2) : 0.f) +
               o.y * ((o.x > -INFINITY) ? exp2f((o.x - mm) * p.scale_log2) : 0.f);
         m = mm;
+        // a row without any visible pass-1 key scores 0 everywhere, as in the reference's oracle
+        // (tests/stage1/complse_online_softmax.py: its NaN row sum is scrubbed to 0)
         const float rc = (l > 0.f) ? -(m + log2f(l) * p.inv_scale_log2) : -30000.f;
         const float t0 = bf16_round(rc), t1 = bf16_round(rc - t0), t2 = bf16_round(rc - t0 - t1);
         *reinterpret_cast<__nv_bfloat16*>(sm.rowc + umma_noswz16_off(r, 0)) = __float2bfloat16_rn(t0);
@@ -342,8 +360,8 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     };
 
     if (ok) {
-      for (int t = n_tiles; t < n_steps; ++t) {
-        const int s = t & 1, tile = t - n_tiles;
+      for (int t = n_tiles1; t < n_steps; ++t) {
+        const int s = t & 1, tile = t - n_tiles1;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.acc_full[s], (uint32_t)((t >> 1) & 1),
                                                abort_flag, p.status, 62));
         if (!ok) break;
@@ -437,8 +455,9 @@ namespace ifv2 {
 namespace {
 #endif
 
-int launch_stage1(const void* q, const void* kc, void* out, void* pooled,
+int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void* pooled,
                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                  const int32_t* cu_seqlens_v, int64_t total_v,
                   const int32_t* cache_lens, int batch, int64_t total_q, int64_t total_c,
                   int heads_q, int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
                   int64_t out_row_stride, int pooled_len, int cache_len, int local_blocks,
@@ -471,7 +490,11 @@ int launch_stage1(const void* q, const void* kc, void* out, void* pooled,
   IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE, "%s: batch or heads_k > 65535",
                what);
 
-  CUtensorMap map_q, map_kc;
+  IFV2_REQUIRE((kv == nullptr) == (cu_seqlens_v == nullptr), IFV2_ERR_INVALID_ARG,
+               "%s: the row-sum keys and their cu_seqlens go together", what);
+  IFV2_REQUIRE(kv == nullptr || (total_v >= 0 && total_v <= INT32_MAX), IFV2_ERR_INVALID_ARG,
+               "%s: bad row-sum key count", what);
+  CUtensorMap map_q, map_kc, map_kv;
   int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, total_q, kHeadDim * 2,
                                    (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerTile);
   if (rc) return rc;
@@ -480,12 +503,18 @@ int launch_stage1(const void* q, const void* kc, void* out, void* pooled,
                                total_c > 0 ? total_c : 1, kHeadDim * 2,
                                (uint64_t)heads_k * kHeadDim * 2, 64, 1, kKeysPerTile);
   if (rc) return rc;
+  const bool own_v = kv != nullptr && total_v > 0;
+  rc = make_tensor_map_bf16_3d(&map_kv, own_v ? kv : (total_c > 0 ? kc : q), kHeadDim, heads_k,
+                               own_v ? total_v : (total_c > 0 ? total_c : 1), kHeadDim * 2,
+                               (uint64_t)heads_k * kHeadDim * 2, 64, 1, kKeysPerTile);
+  if (rc) return rc;
 
   Stage1Params p;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.pooled = static_cast<__nv_bfloat16*>(pooled);
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
+  p.cu_v = cu_seqlens_v;
   p.cache_lens = cache_lens;
   p.total_q = total_q;
   p.heads_q = heads_q;
@@ -508,12 +537,12 @@ int launch_stage1(const void* q, const void* kc, void* out, void* pooled,
     e = cudaFuncSetAttribute(stage1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem);
     if (e != cudaSuccess) return set_error((int)e, "%s: %s", what, cudaGetErrorString(e));
-    stage1_kernel<true><<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_kc, p);
+    stage1_kernel<true><<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_kc, map_kv, p);
   } else {
     e = cudaFuncSetAttribute(stage1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem);
     if (e != cudaSuccess) return set_error((int)e, "%s: %s", what, cudaGetErrorString(e));
-    stage1_kernel<false><<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_kc, p);
+    stage1_kernel<false><<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_kc, map_kv, p);
   }
   return check_launch(what);
 }
@@ -523,23 +552,26 @@ int launch_stage1(const void* q, const void* kc, void* out, void* pooled,
 
 using namespace ifv2;
 
-extern "C" int ifv2_stage1_scores(const void* q, const void* kc, void* out,
+extern "C" int ifv2_stage1_scores(const void* q, const void* kc, const void* lse_keys, void* out,
                                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                  int batch, int64_t total_q, int64_t total_c, int heads_q,
+                                  const int32_t* cu_seqlens_v, int64_t total_v, int batch, int64_t total_q, int64_t total_c, int heads_q,
                                   int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
                                   int64_t out_row_stride, float softmax_scale, int causal,
                                   int32_t* status, void* stream) {
   IFV2_REQUIRE(out != nullptr || total_q == 0 || max_seqlen_k == 0 || max_seqlen_q == 0,
                IFV2_ERR_INVALID_ARG, "stage1_scores: null pointer");
-  return launch_stage1(q, kc, out, nullptr, cu_seqlens_q, cu_seqlens_k, nullptr, batch, total_q,
+  return launch_stage1(q, kc, lse_keys, out, nullptr, cu_seqlens_q, cu_seqlens_k, cu_seqlens_v,
+                       total_v, nullptr, batch, total_q,
                        total_c, heads_q, heads_k, head_dim, max_seqlen_q, max_seqlen_k,
                        out_row_stride, 0, 0, 0, 0, softmax_scale, causal, status, stream,
                        "stage1_scores");
 }
 
-extern "C" int ifv2_stage1_block_scores(const void* q, const void* kc, void* scores_or_null,
-                                        void* block_scores, const int32_t* cu_seqlens_q,
-                                        const int32_t* cu_seqlens_k, const int32_t* cache_lens,
+extern "C" int ifv2_stage1_block_scores(const void* q, const void* kc, const void* lse_keys,
+                                        void* scores_or_null, void* block_scores,
+                                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                        const int32_t* cu_seqlens_v, int64_t total_v,
+                                        const int32_t* cache_lens,
                                         int batch, int64_t total_q, int64_t total_c, int heads_q,
                                         int heads_k, int head_dim, int max_seqlen_q,
                                         int max_seqlen_k, int64_t scores_row_stride, int n_blocks,
@@ -548,7 +580,8 @@ extern "C" int ifv2_stage1_block_scores(const void* q, const void* kc, void* sco
                                         void* stream) {
   IFV2_REQUIRE(block_scores != nullptr || total_q == 0 || max_seqlen_q == 0, IFV2_ERR_INVALID_ARG,
                "stage1_block_scores: null block_scores");
-  return launch_stage1(q, kc, scores_or_null, block_scores, cu_seqlens_q, cu_seqlens_k, cache_lens,
+  return launch_stage1(q, kc, lse_keys, scores_or_null, block_scores, cu_seqlens_q, cu_seqlens_k,
+                       cu_seqlens_v, total_v, cache_lens,
                        batch, total_q, total_c, heads_q, heads_k, head_dim, max_seqlen_q,
                        max_seqlen_k, scores_row_stride, n_blocks, cache_len, local_blocks,
                        init_blocks, softmax_scale, causal, status, stream, "stage1_block_scores");

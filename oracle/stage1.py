@@ -15,13 +15,15 @@ def _cdiv_trunc(a: int, b: int) -> int:
     return q if a >= 0 else -q
 
 
-def stage1_visible_limit(i: torch.Tensor, q_len: int, k_len: int, causal: bool) -> torch.Tensor:
+def stage1_visible_limit(i: torch.Tensor, q_len: int, k_len: int, causal: bool,
+                         stride: int = 16) -> torch.Tensor:
     """Number of leading compressed keys visible to local query token i (mask.h:270-281):
-    key j is visible iff j < limit.  Compressed key j covers tokens [16j, 16j+32)."""
+    key j is visible iff j < limit.  Compressed key j covers tokens [stride*j, stride*j + 2*stride);
+    stride 16 for the scored keys, 64 for the coarse keys of the "compressed LSE" mode."""
     if not causal:
         return torch.full_like(i, k_len)
-    off = k_len - _cdiv_trunc(q_len - 15, 16)
-    lim = (i + 1) // 16 - 1 + off
+    off = k_len - _cdiv_trunc(q_len - stride + 1, stride)
+    lim = (i + 1) // stride - 1 + off
     return lim.clamp(0, k_len)
 
 
@@ -43,31 +45,50 @@ def compress_keys(k: torch.Tensor, cu_seqlens, kernel: int = 32, stride: int = 1
 
 def stage1_scores(q: torch.Tensor, kc: torch.Tensor, cu_seqlens_q, cu_seqlens_k,
                   max_seqlen_k: int, causal: bool, softmax_scale=None,
-                  group: int = 16, chunk: int = 512) -> torch.Tensor:
+                  group: int = 16, chunk: int = 512, lse_keys=None, cu_seqlens_v=None) -> torch.Tensor:
     """q: (T, Hq, d), kc: (sum Lc, Hk, d).  Returns fp32 (Hk, T, max_seqlen_k): for every KV
     head the softmax probabilities over the visible compressed keys, summed over the `group`
-    query heads that share it; invisible / padded columns and rows with no visible key are 0."""
+    query heads that share it; invisible / padded columns and rows with no visible key are 0.
+
+    lse_keys / cu_seqlens_v ("compressed LSE" mode, tests/stage1/complse_online_softmax.py:21-108
+    and flash_fwd_kernel.h:1236-1240): the log-sum-exp of a row is taken over these keys instead
+    -- with the stride-64 visibility rule when a sequence has a different number of them than of
+    scored keys -- and the result is exp(q.k - lse) summed over the heads.  A row that sees no such
+    key scores 0 everywhere (the reference oracle's running sum turns NaN there and NaNs are
+    scrubbed to 0, complse_online_softmax.py:84-85, 104)."""
     t, hq, d = q.shape
     hk = kc.shape[1]
     assert hq == hk * group
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
     cu_q = [int(v) for v in cu_seqlens_q]
     cu_k = [int(v) for v in cu_seqlens_k]
+    cu_v = [int(v) for v in cu_seqlens_v] if lse_keys is not None else cu_k
+    kv_all = lse_keys if lse_keys is not None else kc
     out = torch.zeros(hk, t, max_seqlen_k, dtype=torch.float32)
     for b in range(len(cu_q) - 1):
         q0, q1, k0, k1 = cu_q[b], cu_q[b + 1], cu_k[b], cu_k[b + 1]
-        lq, lc = q1 - q0, k1 - k0
+        v0, v1 = cu_v[b], cu_v[b + 1]
+        lq, lc, lcv = q1 - q0, k1 - k0, v1 - v0
         if lq <= 0 or lc <= 0:
             continue
+        st1 = 16 if lcv == lc else 64
         kb = kc[k0:k1].float().permute(1, 2, 0)                       # (Hk, d, Lc)
+        vb = kv_all[v0:v1].float().permute(1, 2, 0)                   # (Hk, d, Lcv)
         for s in range(0, lq, chunk):
             e = min(lq, s + chunk)
             qb = q[q0 + s:q0 + e].float().view(e - s, hk, group, d).permute(1, 2, 0, 3)
+            rows = torch.arange(s, e)
+            # log-sum-exp over the pass-1 keys
+            s1 = torch.matmul(qb, vb[:, None]) * scale                # (Hk, g, n, Lcv)
+            lim1 = stage1_visible_limit(rows, lq, lcv, causal, st1)
+            s1 = s1.masked_fill((torch.arange(lcv)[None, :] >= lim1[:, None])[None, None], float("-inf"))
+            lse = torch.logsumexp(s1, dim=-1, keepdim=True)           # -inf for a row that sees nothing
+            # scores of the pass-2 keys against that normaliser
             sc = torch.matmul(qb, kb[:, None]) * scale                # (Hk, g, n, Lc)
-            lim = stage1_visible_limit(torch.arange(s, e), lq, lc, causal)
-            hidden = torch.arange(lc)[None, :] >= lim[:, None]        # (n, Lc)
-            sc = sc.masked_fill(hidden[None, None], float("-inf"))
-            p = torch.softmax(sc, dim=-1)
-            p = torch.where(torch.isnan(p), torch.zeros((), dtype=p.dtype), p).sum(dim=1)
+            lim = stage1_visible_limit(rows, lq, lc, causal)
+            hidden = (torch.arange(lc)[None, :] >= lim[:, None])[None, None]
+            p = torch.exp(sc - lse)
+            dead = hidden | torch.isinf(lse) | torch.isnan(p)         # no pass-1 key: 0, not +inf
+            p = torch.where(dead, torch.zeros((), dtype=p.dtype), p).sum(dim=1)
             out[:, q0 + s:q0 + e, :lc] = p
     return out

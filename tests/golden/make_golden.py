@@ -7,6 +7,7 @@ Run where the reference checkout is available:
 
 It imports, unmodified, from the reference's tests/ directory:
   tests/stage1/naive_softmax.py::torch_naive_softmax
+  tests/stage1/complse_online_softmax.py::compresssed_lse_online_softmax
   tests/test_topk_to_uint64.py::topk_to_uint64_numpy
   tests/test_blockmask.py::py_blockmask_to_uint64
   tests/test_uint64_to_bool.py::py_uint64_to_bool
@@ -49,8 +50,9 @@ def _import_reference(ref_root):
     sys.path.insert(0, os.path.join(ref_root, "tests"))
     os.chdir(tempfile.mkdtemp())          # tests/utils.py creates a directory in the cwd on import
     mods = {}
-    for m in ("stage1.naive_softmax", "test_topk_to_uint64", "test_blockmask",
-              "test_uint64_to_bool", "utils", "test_kvcache_simple", "test_stage1_compressed_lse"):
+    for m in ("stage1.naive_softmax", "stage1.complse_online_softmax", "test_topk_to_uint64",
+              "test_blockmask", "test_uint64_to_bool", "utils", "test_kvcache_simple",
+              "test_stage1_compressed_lse"):
         mods[m] = importlib.import_module(m)
     return mods
 
@@ -114,6 +116,23 @@ def gen_stage1(mods, out):
         cases[f"s1_{name}_out"] = ref.numpy()
     assert worst < 2e-6, worst
     print(f"stage1: oracle vs torch_naive_softmax max|diff| = {worst:.2e}")
+    # "compressed LSE" mode: row sums over coarser keys (kernel 128 / stride 64 of the same tokens)
+    complse = mods["stage1.complse_online_softmax"].compresssed_lse_online_softmax
+    worst = 0.0
+    for name, lq, causal in (("ca", 256, True), ("cb", 512, True), ("cc", 256, False), ("cd", 1024, True)):
+        seed = 300 + ord(name[1])
+        lc, lcv = (lq - 32) // 16 + 1, (lq - 128) // 64 + 1
+        q = torch.from_numpy(det_array((lq, 32, 128), seed, 0.5))
+        k = torch.from_numpy(det_array((lc, 2, 128), seed + 1000))
+        kv = torch.from_numpy(det_array((lcv, 2, 128), seed + 2000))
+        ref = complse(q, k, kv, 16, 16, causal=causal)                # (2, lq, lc) fp32
+        got = oracle.stage1_scores(q, k, [0, lq], [0, lc], lc, causal, lse_keys=kv, cu_seqlens_v=[0, lcv])
+        worst = max(worst, (got - ref).abs().max().item() / max(1.0, ref.abs().max().item()))
+        cases[f"s1_{name}_shape"] = np.array([lq, lc, seed, lcv], dtype=np.int64)
+        cases[f"s1_{name}_causal"] = np.bool_(causal)
+        cases[f"s1_{name}_out"] = ref.numpy()
+    assert worst < 1e-5, worst
+    print(f"stage1 compressed-LSE: oracle vs compresssed_lse_online_softmax max rel diff = {worst:.2e}")
     np.savez_compressed(os.path.join(out, "stage1.npz"), **cases)
 
 

@@ -37,7 +37,19 @@ def test_stage1_golden(golden_dir):
     g = np.load(os.path.join(golden_dir, "stage1.npz"))
     for key in [k for k in g.files if k.endswith("_shape")]:
         base = key[:-6]
-        lq, lc, seed = (int(x) for x in g[key])
+        lq, lc, seed = (int(x) for x in g[key][:3])
+        if len(g[key]) == 4:                 # "compressed LSE" case: row sums over coarser keys
+            lcv = int(g[key][3])
+            q = torch.from_numpy(det_array((lq, 32, 128), seed, 0.5)).to(torch.bfloat16)
+            k = torch.from_numpy(det_array((lc, 2, 128), seed + 1000)).to(torch.bfloat16)
+            kv = torch.from_numpy(det_array((lcv, 2, 128), seed + 2000)).to(torch.bfloat16)
+            got = infllm_v2.infllmv2_attn_stage1(q.to(DEV), k.to(DEV), kv.to(DEV), cu([lq], DEV),
+                                                 cu([lc], DEV), cu([lcv], DEV), lq, lc,
+                                                 causal=bool(g[base + "_causal"])).float().cpu()
+            infllm_v2.check_device_status()
+            ok, err = _within(got, g[base + "_out"])
+            assert ok, (base, err)
+            continue
         q = torch.from_numpy(det_array((lq, 32, 128), seed)).to(torch.bfloat16)
         k = torch.from_numpy(det_array((lc, 2, 128), seed + 1000)).to(torch.bfloat16)
         got = _run(q, k, cu([lq]), cu([lc]), lq, lc, bool(g[base + "_causal"]))
@@ -121,3 +133,31 @@ def test_fused_block_scores_query_chunk_with_cache_len():
     plain = infllm_v2.infllmv2_attn_stage1(q[start:], kc, kc, cu([full - start]).to(DEV), cu_ct, cu_ct,
                                            full - start, cu_c[-1], causal=True)
     assert torch.equal(got, infllm_v2.max_pooling_1d(plain, start, 2, 1))
+
+
+@pytest.mark.parametrize("lens,causal", [([1000, 130, 64, 700], True), ([2048], True), ([300, 500], False)])
+def test_stage1_compressed_lse_vs_oracle(lens, causal):
+    """Row sums over a coarser compression of the same keys (kernel 128 / stride 64), packed
+    ragged sequences including ones with no coarse key at all; scores and fused block scores."""
+    hq, hk = 32, 2
+    seed = sum(lens) + 5
+    q = det_tensor((sum(lens), hq, 128), seed, 0.5)
+    k = det_tensor((sum(lens), hk, 128), seed + 1, 0.5)
+    kc, cu_c = oracle.compress_keys(k, cu(lens), 32, 16)
+    kv, cu_v = oracle.compress_keys(k, cu(lens), 128, 64)
+    max_k = int(np.diff(cu_c).max())
+    exp = oracle.stage1_scores(q, kc, cu(lens).tolist(), cu_c, max_k, causal, lse_keys=kv, cu_seqlens_v=cu_v)
+    cq = cu(lens, DEV)
+    ck = torch.tensor(cu_c, dtype=torch.int32, device=DEV)
+    cv = torch.tensor(cu_v, dtype=torch.int32, device=DEV)
+    got = infllm_v2.infllmv2_attn_stage1(q.to(DEV), kc.to(DEV), kv.to(DEV), cq, ck, cv, max(lens), max_k,
+                                         causal=causal)
+    infllm_v2.check_device_status()
+    ok, err = _within(got.float().cpu(), exp)
+    assert ok, err
+    if causal:
+        pooled = infllm_v2.infllmv2_stage1_block_scores(q.to(DEV), kc.to(DEV), cq, ck, max(lens), max_k, 2, 1,
+                                                        lse_keys=kv.to(DEV), cu_seqlens_v=cv)
+        ref = infllm_v2.max_pooling_1d_varlen(got, cq, ck, torch.zeros(len(lens), dtype=torch.int32, device=DEV),
+                                              max(lens), max_k, 2, 1)
+        assert torch.equal(pooled, ref)
