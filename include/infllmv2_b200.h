@@ -228,6 +228,24 @@ int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new, 
                 int64_t cache_capacity, int64_t cache_batch_stride, float softmax_scale,
                 void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ifv2_decode with the cache addressing options of the reference's fwd_kvcache
+ * (csrc/flash_attn/flash_api.cpp:1590-1640, 1773-1797):
+ *  block_table (batch, block_table_stride) int32 or null: paged cache, k_cache / v_cache are then
+ *    (num_pages, page_size, heads_k, 128) and position p of sequence b lives in page
+ *    block_table[b][p / page_size]; page_size a multiple of 64; cache_capacity = the largest
+ *    position + 1 any sequence may use (<= block_table_stride * page_size);
+ *  cache_batch_idx (batch) int32 or null: sequence b uses row cache_batch_idx[b] of the caches;
+ *  cache_leftpad (batch) int32 or null: the keys of sequence b are positions
+ *    [cache_leftpad[b], cache_seqlens[b]); block indices of the mask count from the first key.
+ * As in the reference, a paged cache takes neither of the last two. */
+int ifv2_decode_paged(const void* q, void* k_cache, void* v_cache, const void* k_new,
+                      const void* v_new, void* out, float* lse, const int64_t* mask, int mask_words,
+                      const int32_t* cache_seqlens, int batch, int heads_q, int heads_k,
+                      int head_dim, int64_t cache_capacity, int64_t cache_batch_stride,
+                      const int32_t* block_table, int block_table_stride, int page_size,
+                      const int32_t* cache_batch_idx, const int32_t* cache_leftpad,
+                      float softmax_scale, void* workspace, int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

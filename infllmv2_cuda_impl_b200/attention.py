@@ -339,34 +339,52 @@ def infllmv2_attn_with_kvcache(
 ):
     """Sparse decode step over a KV cache (one new query token per sequence).
 
-    q: (batch, 1, nheads, 128); k_cache, v_cache: (batch, seqlen_cache, nheads_k, 128);
+    q: (batch, 1, nheads, 128); k_cache, v_cache: (batch_cache, seqlen_cache, nheads_k, 128), or
+    (num_pages, page_size, nheads_k, 128) with block_table (batch, max_pages) int32;
     k, v: optional (batch, 1, nheads_k, 128), written in place at cache_seqlens first;
-    cache_seqlens: int or (batch,) int32; topk_idx: int32 (batch, nheads_k, 1, topk) blocks of
-    the cache to attend (None = the whole cache).  A single query token is never causally
-    masked (csrc/flash_attn/flash_api.cpp:1628).  Returns out (batch, 1, nheads, 128)
+    cache_seqlens: int or (batch,) int32; cache_batch_idx (batch,) int32: the cache row each
+    sequence uses; cache_leftpad (batch,) int32: position of each sequence's first key;
+    topk_idx: int32 (batch, nheads_k, 1, topk) blocks of the sequence to attend (None = all of
+    it), counted from its first key.  A single query token is never causally masked
+    (csrc/flash_attn/flash_api.cpp:1628).  Returns out (batch, 1, nheads, 128)
     [, softmax_lse (batch, nheads, 1)].
     """
     assert k_cache.stride(-1) == 1, "k_cache must have contiguous last dimension"
     assert v_cache.stride(-1) == 1, "v_cache must have contiguous last dimension"
-    _check_common(q, k_cache, 0.0, window_size, softcap, alibi_slopes, block_table,
+    _check_common(q, k_cache, 0.0, window_size, softcap, alibi_slopes, None,
                   "infllmv2_attn_with_kvcache")
     if rotary_cos is not None or rotary_sin is not None:
         raise NotImplementedError("infllmv2_attn_with_kvcache: rotary-on-append is not supported")
-    if cache_batch_idx is not None or cache_leftpad is not None:
-        raise NotImplementedError("infllmv2_attn_with_kvcache: cache_batch_idx / cache_leftpad are not supported")
     if q.shape[1] != 1:
         raise NotImplementedError("infllmv2_attn_with_kvcache: only one query token per sequence is supported")
     q, k, v = [maybe_contiguous(x) for x in (q, k, v)]
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
     batch, _, nheads, d = q.shape
-    cap, nheads_k = k_cache.shape[1], k_cache.shape[2]
+    nheads_k = k_cache.shape[2]
+    bt_ptr, bt_stride, page_size = None, 0, 0
+    if block_table is not None:
+        if cache_batch_idx is not None or cache_leftpad is not None:
+            raise NotImplementedError(
+                "infllmv2_attn_with_kvcache: a paged cache takes neither cache_batch_idx nor cache_leftpad")
+        assert block_table.dtype == torch.int32 and block_table.shape[0] == batch
+        block_table = block_table.contiguous()
+        page_size = k_cache.shape[1]
+        if page_size % BLOCK_N != 0:
+            raise NotImplementedError("infllmv2_attn_with_kvcache: page size must be a multiple of 64")
+        bt_ptr, bt_stride = block_table.data_ptr(), block_table.shape[1]
+        cap = bt_stride * page_size
+    else:
+        cap = k_cache.shape[1]
     if cache_seqlens is None:
         cache_seqlens = cap
     if isinstance(cache_seqlens, int):
         cache_seqlens = torch.full((batch,), cache_seqlens, dtype=torch.int32, device=q.device)
     cache_seqlens = cache_seqlens.contiguous()
     assert cache_seqlens.dtype == torch.int32
+    for name, t in (("cache_batch_idx", cache_batch_idx), ("cache_leftpad", cache_leftpad)):
+        if t is not None:
+            assert t.dtype == torch.int32 and t.numel() == batch, f"{name} must be (batch,) int32"
     for c in (k_cache, v_cache):
         if c.stride(2) != d or c.stride(1) != nheads_k * d:
             raise RuntimeError("infllmv2_attn_with_kvcache: caches must be dense in (seqlen, heads, d)")
@@ -382,12 +400,14 @@ def infllmv2_attn_with_kvcache(
     ws_bytes = int(lib.ifv2_decode_workspace_bytes(batch, nheads, d, max_blocks))
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
-        _lib.call("ifv2_decode", q2.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        _lib.call("ifv2_decode_paged", q2.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                   k.contiguous().data_ptr() if k is not None else None,
                   v.contiguous().data_ptr() if v is not None else None, out.data_ptr(),
                   lse.data_ptr(), mask.data_ptr() if mask is not None else None,
                   mask.shape[-1] if mask is not None else 0, cache_seqlens.data_ptr(), batch,
-                  nheads, nheads_k, d, cap, k_cache.stride(0), float(softmax_scale), ws.data_ptr(),
-                  ws_bytes, _stream(q.device))
+                  nheads, nheads_k, d, cap, k_cache.stride(0), bt_ptr, bt_stride, page_size,
+                  cache_batch_idx.contiguous().data_ptr() if cache_batch_idx is not None else None,
+                  cache_leftpad.contiguous().data_ptr() if cache_leftpad is not None else None,
+                  float(softmax_scale), ws.data_ptr(), ws_bytes, _stream(q.device))
     out = out.view(batch, 1, nheads, d)
     return (out, lse.view(batch, nheads, 1)) if return_softmax_lse else out

@@ -34,6 +34,10 @@ struct DecodeParams {
   int new_tokens;                 // 1 when k_new / v_new were appended, else 0
   int heads_q, heads_k;
   int64_t batch_stride;           // elements between sequences in the caches
+  const int32_t* block_table;     // (batch, bt_stride) page of every page_size positions, or null
+  int bt_stride, page_size;
+  const int32_t* cache_batch_idx; // (batch) row of the caches each sequence uses, or null
+  const int32_t* leftpad;         // (batch) position of a sequence's first key, or null
   float scale_log2;
   int splits;                     // CTAs sharing one (sequence, KV head), 1 .. kMaxSplits
   float* partial;                 // (batch, heads_k, splits, 16, kPartialFloats)
@@ -41,18 +45,35 @@ struct DecodeParams {
   float* lse;                     // (batch, heads_q) or null
 };
 
+// Element offset of position `pos` of sequence b (head 0) in a cache: contiguous rows, rows of
+// another sequence slot (cache_batch_idx), or pages of a block table.
+__device__ __forceinline__ int64_t cache_row_offset(const int32_t* block_table, int bt_stride,
+                                                    int page_size, int64_t batch_stride,
+                                                    int64_t row_stride, int b, int slot, int64_t pos) {
+  if (block_table != nullptr) {
+    const int page = __ldg(block_table + (int64_t)b * bt_stride + pos / page_size);
+    return ((int64_t)page * page_size + pos % page_size) * row_stride;
+  }
+  return slot * batch_stride + pos * row_stride;
+}
+
 __global__ void decode_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                                      const __nv_bfloat16* k_new, const __nv_bfloat16* v_new,
                                      const int32_t* cache_seqlens, int heads_k, int64_t capacity,
-                                     int64_t batch_stride) {
+                                     int64_t batch_stride, const int32_t* block_table, int bt_stride,
+                                     int page_size, const int32_t* cache_batch_idx) {
   const int b = blockIdx.x;
   const int64_t pos = cache_seqlens[b];
   if (pos < 0 || pos >= capacity) return;           // no room: the host documents this as an error
   const int n = heads_k * kHeadDim / 8;             // 16-byte vectors per token
+  const int64_t row_stride = (int64_t)heads_k * kHeadDim;
+  const int slot = cache_batch_idx ? cache_batch_idx[b] : b;
+  const int64_t off = cache_row_offset(block_table, bt_stride, page_size, batch_stride, row_stride, b,
+                                       slot, pos);
   const uint4* ks = reinterpret_cast<const uint4*>(k_new + (int64_t)b * heads_k * kHeadDim);
   const uint4* vs = reinterpret_cast<const uint4*>(v_new + (int64_t)b * heads_k * kHeadDim);
-  uint4* kd = reinterpret_cast<uint4*>(k_cache + b * batch_stride + pos * heads_k * kHeadDim);
-  uint4* vd = reinterpret_cast<uint4*>(v_cache + b * batch_stride + pos * heads_k * kHeadDim);
+  uint4* kd = reinterpret_cast<uint4*>(k_cache + off);
+  uint4* vd = reinterpret_cast<uint4*>(v_cache + off);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     kd[i] = ks[i];
     vd[i] = vs[i];
@@ -96,14 +117,13 @@ __device__ __forceinline__ uint8_t* tile_addr(uint8_t* tile, int row, int chunk)
   return tile + row * 256 + ((chunk ^ (row & 7)) << 4);
 }
 
-// one warp copies keys [key0, key0 + kUnit) of one KV head; rows past `len` are not fetched
+// one warp copies the kUnit keys starting at `base` (one KV head); rows >= `rows` are not fetched
 __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* base, int64_t row_stride,
-                                          int key0, int len, int lane) {
+                                          int rows, int lane) {
 #pragma unroll 4
   for (int i = lane; i < kUnit * 16; i += 32) {
     const int row = i >> 4, chunk = i & 15;
-    if (key0 + row < len)
-      cp_async16(tile_addr(tile, row, chunk), base + (int64_t)(key0 + row) * row_stride + chunk * 8);
+    if (row < rows) cp_async16(tile_addr(tile, row, chunk), base + (int64_t)row * row_stride + chunk * 8);
   }
 }
 
@@ -146,16 +166,22 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeP
   uint8_t* k_tile = smem + warp * kWarpSmem;
   uint8_t* v_tile = k_tile + kUnit * 256;
 
-  const int len = p.cache_seqlens[b] + p.new_tokens;
+  const int pad = p.leftpad ? p.leftpad[b] : 0;                 // keys are positions pad .. end-1
+  const int len = p.cache_seqlens[b] + p.new_tokens - pad;
+  const int slot = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
   BlockList list{p.mask ? p.mask + ((int64_t)b * p.heads_k + h) * p.mask_words : nullptr, p.mask_words,
                  (len + kBlockN - 1) / kBlockN};
   const int n = list.count();
   const int per_split = (n + p.splits - 1) / p.splits;
   const int j_begin = split * per_split, j_end = min(n, j_begin + per_split);
 
-  const __nv_bfloat16* kbase = p.k_cache + b * p.batch_stride + (int64_t)h * kHeadDim;
-  const __nv_bfloat16* vbase = p.v_cache + b * p.batch_stride + (int64_t)h * kHeadDim;
   const int64_t row_stride = (int64_t)p.heads_k * kHeadDim;
+  // first row of the 32-key unit that starts at key `k0` (a unit never straddles a page: pages
+  // are multiples of 64 positions and a paged cache has no left padding)
+  auto unit = [&](const __nv_bfloat16* cache, int k0) -> const __nv_bfloat16* {
+    return cache + cache_row_offset(p.block_table, p.bt_stride, p.page_size, p.batch_stride, row_stride,
+                                    b, slot, (int64_t)k0 + pad) + (int64_t)h * kHeadDim;
+  };
 
   // Q fragments of the 16 heads (rows g and g + 8), all 8 k-steps
   uint32_t qf[8][4];
@@ -192,9 +218,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeP
     return bb >= 0 ? bb * kBlockN : -1;
   };
   if (blk >= 0) {
-    load_tile(k_tile, kbase, row_stride, key0, len, lane);
+    load_tile(k_tile, unit(p.k_cache, key0), row_stride, len - key0, lane);
     cp_async_commit();
-    load_tile(v_tile, vbase, row_stride, key0, len, lane);
+    load_tile(v_tile, unit(p.v_cache, key0), row_stride, len - key0, lane);
     cp_async_commit();
   } else {
     key0 = -1;
@@ -220,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeP
       }
     }
     __syncwarp();
-    if (key_next >= 0) load_tile(k_tile, kbase, row_stride, key_next, len, lane);
+    if (key_next >= 0) load_tile(k_tile, unit(p.k_cache, key_next), row_stride, len - key_next, lane);
     cp_async_commit();
 
     // ---- online softmax (rows g and g + 8; a row's scores live in the 4 lanes of a quad)
@@ -293,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeP
       }
     }
     __syncwarp();
-    if (key_next >= 0) load_tile(v_tile, vbase, row_stride, key_next, len, lane);
+    if (key_next >= 0) load_tile(v_tile, unit(p.v_cache, key_next), row_stride, len - key_next, lane);
     cp_async_commit();
     j = jn;
     half = hn;
@@ -396,12 +422,14 @@ extern "C" int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_
   return (int64_t)batch * heads_q * kMaxSplits * kPartialFloats * 4 + 256;
 }
 
-extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new,
-                           const void* v_new, void* out, float* lse, const int64_t* mask,
-                           int mask_words, const int32_t* cache_seqlens, int batch, int heads_q,
-                           int heads_k, int head_dim, int64_t cache_capacity,
-                           int64_t cache_batch_stride, float softmax_scale, void* workspace,
-                           int64_t workspace_bytes, void* stream) {
+static int decode_impl(const void* q, void* k_cache, void* v_cache, const void* k_new,
+                       const void* v_new, void* out, float* lse, const int64_t* mask,
+                       int mask_words, const int32_t* cache_seqlens, int batch, int heads_q,
+                       int heads_k, int head_dim, int64_t cache_capacity,
+                       int64_t cache_batch_stride, const int32_t* block_table,
+                       int block_table_stride, int page_size, const int32_t* cache_batch_idx,
+                       const int32_t* cache_leftpad, float softmax_scale, void* workspace,
+                       int64_t workspace_bytes, void* stream) {
   IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED, "decode: head_dim %d not supported (only 128)",
                head_dim);
   IFV2_REQUIRE(heads_k >= 1 && heads_q == heads_k * kGroup, IFV2_ERR_UNSUPPORTED,
@@ -412,8 +440,17 @@ extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const vo
                "decode: null pointer");
   IFV2_REQUIRE((k_new == nullptr) == (v_new == nullptr), IFV2_ERR_INVALID_ARG,
                "decode: pass both k_new and v_new, or neither");
-  IFV2_REQUIRE(cache_batch_stride >= cache_capacity * heads_k * kHeadDim, IFV2_ERR_INVALID_ARG,
-               "decode: cache_batch_stride smaller than one sequence");
+  if (block_table != nullptr) {
+    IFV2_REQUIRE(page_size >= kBlockN && page_size % kBlockN == 0 && block_table_stride >= 1,
+                 IFV2_ERR_INVALID_ARG, "decode: page size must be a positive multiple of 64");
+    IFV2_REQUIRE(cache_leftpad == nullptr && cache_batch_idx == nullptr, IFV2_ERR_UNSUPPORTED,
+                 "decode: a paged cache takes neither cache_leftpad nor cache_batch_idx");
+    IFV2_REQUIRE(cache_capacity <= (int64_t)block_table_stride * page_size, IFV2_ERR_INVALID_ARG,
+                 "decode: cache_capacity exceeds the block table");
+  } else {
+    IFV2_REQUIRE(cache_batch_stride >= cache_capacity * heads_k * kHeadDim, IFV2_ERR_INVALID_ARG,
+                 "decode: cache_batch_stride smaller than one sequence");
+  }
   IFV2_REQUIRE(mask == nullptr || mask_words >= 1, IFV2_ERR_INVALID_ARG, "decode: mask_words < 1");
   IFV2_REQUIRE(workspace_bytes >= ifv2_decode_workspace_bytes(batch, heads_q, head_dim, 0),
                IFV2_ERR_INVALID_ARG, "decode: workspace too small");
@@ -425,7 +462,8 @@ extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const vo
     decode_append_kernel<<<batch, 128, 0, st>>>(
         static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
         static_cast<const __nv_bfloat16*>(k_new), static_cast<const __nv_bfloat16*>(v_new),
-        cache_seqlens, heads_k, cache_capacity, cache_batch_stride);
+        cache_seqlens, heads_k, cache_capacity, cache_batch_stride, block_table, block_table_stride,
+        page_size, cache_batch_idx);
     int rc = check_launch("decode_append");
     if (rc) return rc;
   }
@@ -440,6 +478,11 @@ extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const vo
   p.heads_q = heads_q;
   p.heads_k = heads_k;
   p.batch_stride = cache_batch_stride;
+  p.block_table = block_table;
+  p.bt_stride = block_table_stride;
+  p.page_size = page_size > 0 ? page_size : 1;
+  p.cache_batch_idx = cache_batch_idx;
+  p.leftpad = cache_leftpad;
   p.scale_log2 = softmax_scale * kLog2e;
   // about four waves of two CTAs per SM over the whole launch
   // (a power of two, so that top-k lists of 32 / 64 blocks divide evenly over CTAs and warps)
@@ -459,4 +502,30 @@ extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const vo
   if (rc) return rc;
   decode_combine_kernel<<<dim3(heads_k, batch), 256, 0, st>>>(p);
   return check_launch("decode_combine");
+}
+
+extern "C" int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new,
+                           const void* v_new, void* out, float* lse, const int64_t* mask,
+                           int mask_words, const int32_t* cache_seqlens, int batch, int heads_q,
+                           int heads_k, int head_dim, int64_t cache_capacity,
+                           int64_t cache_batch_stride, float softmax_scale, void* workspace,
+                           int64_t workspace_bytes, void* stream) {
+  return decode_impl(q, k_cache, v_cache, k_new, v_new, out, lse, mask, mask_words, cache_seqlens,
+                     batch, heads_q, heads_k, head_dim, cache_capacity, cache_batch_stride, nullptr, 0,
+                     0, nullptr, nullptr, softmax_scale, workspace, workspace_bytes, stream);
+}
+
+extern "C" int ifv2_decode_paged(const void* q, void* k_cache, void* v_cache, const void* k_new,
+                                 const void* v_new, void* out, float* lse, const int64_t* mask,
+                                 int mask_words, const int32_t* cache_seqlens, int batch,
+                                 int heads_q, int heads_k, int head_dim, int64_t cache_capacity,
+                                 int64_t cache_batch_stride, const int32_t* block_table,
+                                 int block_table_stride, int page_size,
+                                 const int32_t* cache_batch_idx, const int32_t* cache_leftpad,
+                                 float softmax_scale, void* workspace, int64_t workspace_bytes,
+                                 void* stream) {
+  return decode_impl(q, k_cache, v_cache, k_new, v_new, out, lse, mask, mask_words, cache_seqlens,
+                     batch, heads_q, heads_k, head_dim, cache_capacity, cache_batch_stride, block_table,
+                     block_table_stride, page_size, cache_batch_idx, cache_leftpad, softmax_scale,
+                     workspace, workspace_bytes, stream);
 }

@@ -77,3 +77,81 @@ def test_decode_golden(golden_dir):
         cache_seqlens=torch.full((bsz,), cache + 1, dtype=torch.int32, device=DEV), topk_idx=idx.to(DEV))
     mx, mr = err_stats(out.cpu(), torch.from_numpy(g["dec_out"]))
     assert mx <= MAX_ABS and mr <= MEAN_REL, (mx, mr)
+
+
+def _topk(bsz, hk, lens, k_sel, seed):
+    rng = np.random.default_rng(seed)
+    rows = np.full((bsz, hk, 1, k_sel), -1, np.int32)
+    for b in range(bsz):
+        nblk = (lens[b] + 63) // 64
+        for h in range(hk):
+            pick = np.sort(rng.permutation(nblk)[:k_sel])
+            rows[b, h, 0, :len(pick)] = pick
+    return torch.from_numpy(rows)
+
+
+@pytest.mark.parametrize("page,append", [(64, True), (256, False), (128, True)])
+def test_decode_paged_cache(page, append):
+    """A cache scattered over pages through a block table gives the results (and, with an append,
+    the in-place update) of the same cache laid out contiguously."""
+    bsz, hk, d, cap = 3, 2, 128, 1024
+    lens = [700, 64, 1023 - (1 if append else 0)]
+    q = det_tensor((bsz, 1, hk * 16, d), 41, 0.25)
+    kc, vc = det_tensor((bsz, cap, hk, d), 42, 0.25), det_tensor((bsz, cap, hk, d), 43)
+    kn = det_tensor((bsz, 1, hk, d), 44, 0.25) if append else None
+    vn = det_tensor((bsz, 1, hk, d), 45) if append else None
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    idx = _topk(bsz, hk, [l + (1 if append else 0) for l in lens], 5, 46)
+    ref, ref_lse = oracle.kvcache_decode(q, kc.clone(), vc.clone(), lens_t, idx, kn, vn)
+    # scatter the pages
+    per_seq = cap // page
+    perm = torch.randperm(bsz * per_seq, generator=torch.Generator().manual_seed(3))
+    table = perm.view(bsz, per_seq).to(torch.int32)
+    kp = torch.zeros(bsz * per_seq, page, hk, d, dtype=kc.dtype)
+    vp = torch.zeros_like(kp)
+    for b in range(bsz):
+        for j in range(per_seq):
+            kp[table[b, j]] = kc[b, j * page:(j + 1) * page]
+            vp[table[b, j]] = vc[b, j * page:(j + 1) * page]
+    kp_d, vp_d = kp.to(DEV), vp.to(DEV)
+    out, lse = infllm_v2.infllmv2_attn_with_kvcache(
+        q.to(DEV), kp_d, vp_d, k=None if kn is None else kn.to(DEV), v=None if vn is None else vn.to(DEV),
+        cache_seqlens=lens_t.to(DEV), block_table=table.to(DEV), topk_idx=idx.to(DEV),
+        return_softmax_lse=True)
+    mx, mr = err_stats(out.cpu(), ref)
+    assert mx <= MAX_ABS and mr <= MEAN_REL, (mx, mr)
+    assert (lse.cpu() - ref_lse).abs().max() < 2e-2
+    if append:
+        for b in range(bsz):
+            pg, off = int(table[b, lens[b] // page]), lens[b] % page
+            assert torch.equal(kp_d[pg, off].cpu(), kn[b, 0]) and torch.equal(vp_d[pg, off].cpu(), vn[b, 0])
+    with pytest.raises(NotImplementedError):
+        infllm_v2.infllmv2_attn_with_kvcache(q.to(DEV), kp_d, vp_d, cache_seqlens=lens_t.to(DEV),
+                                             block_table=table.to(DEV),
+                                             cache_leftpad=torch.zeros(bsz, dtype=torch.int32, device=DEV))
+
+
+def test_decode_batch_idx_and_leftpad():
+    """cache_batch_idx picks the cache row of each sequence; cache_leftpad shifts where its keys
+    start (block indices then count from the first key)."""
+    bsz, rows, hk, d, cap = 3, 5, 2, 128, 600
+    q = det_tensor((bsz, 1, hk * 16, d), 51, 0.25)
+    kc, vc = det_tensor((rows, cap, hk, d), 52, 0.25), det_tensor((rows, cap, hk, d), 53)
+    slot = torch.tensor([4, 0, 2], dtype=torch.int32)
+    pad = torch.tensor([0, 37, 130], dtype=torch.int32)
+    end = torch.tensor([500, 300, 599], dtype=torch.int32)          # cache_seqlens: absolute ends
+    n = [int(e - p) for e, p in zip(end, pad)]
+    idx = _topk(bsz, hk, n, 4, 54)
+    # dense equivalent: every sequence's keys moved to the front of its own row
+    kd = torch.zeros(bsz, cap, hk, d, dtype=kc.dtype)
+    vd = torch.zeros_like(kd)
+    for b in range(bsz):
+        kd[b, :n[b]] = kc[slot[b], pad[b]:end[b]]
+        vd[b, :n[b]] = vc[slot[b], pad[b]:end[b]]
+    ref, ref_lse = oracle.kvcache_decode(q, kd, vd, torch.tensor(n, dtype=torch.int32), idx)
+    out, lse = infllm_v2.infllmv2_attn_with_kvcache(
+        q.to(DEV), kc.to(DEV), vc.to(DEV), cache_seqlens=end.to(DEV), cache_batch_idx=slot.to(DEV),
+        cache_leftpad=pad.to(DEV), topk_idx=idx.to(DEV), return_softmax_lse=True)
+    mx, mr = err_stats(out.cpu(), ref)
+    assert mx <= MAX_ABS and mr <= MEAN_REL, (mx, mr)
+    assert (lse.cpu() - ref_lse).abs().max() < 2e-2
