@@ -70,6 +70,63 @@ def gather_sequence(local: torch.Tensor, world: int, group=None) -> torch.Tensor
     return torch.cat(chunks, dim=0)
 
 
+def scatter_sequence_grad(full: torch.Tensor, world: int, rank: int, group=None) -> torch.Tensor:
+    """The reverse of `gather_sequence` for gradients: every rank holds a partial gradient of a
+    whole-sequence tensor (rows in sequence order); the partials are summed and each rank gets the
+    rows of its own two zig-zag chunks, in the order `gather_sequence` takes them.  A
+    reduce-scatter over NCCL; backends without one (gloo) all-reduce and slice."""
+    if world == 1:
+        return full
+    n = 2 * world
+    clen = full.shape[0] // n
+    chunks = full.reshape(n, clen, *full.shape[1:])
+    order = [i for r in range(world) for i in (r, n - 1 - r)]       # rank-major zig-zag order
+    send = chunks[order].contiguous()                                # (2*world, clen, ...)
+    mine = torch.empty((2 * clen,) + tuple(full.shape[1:]), dtype=full.dtype, device=full.device)
+    if dist.get_backend(group) == "nccl":
+        dist.reduce_scatter_tensor(mine, send.view(-1, *full.shape[1:]), group=group)
+    else:
+        dist.all_reduce(send, group=group)
+        mine.copy_(send[2 * rank:2 * rank + 2].reshape(mine.shape))
+    return mine
+
+
+def sharded_attention_fwd_bwd(q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
+                              dout_local: torch.Tensor, topk_idx_local: torch.Tensor, seqlen: int,
+                              world: int, rank: int, attn: Optional[Callable] = None, group=None):
+    """Training step of the block-sparse attention of ONE sequence under query-chunk sharding
+    (the selection that produced `topk_idx_local` carries no gradient, as in the reference's
+    autograd function, infllm_v2/infllmv2_sparse_attention.py:266-385).
+
+    Every rank passes the rows of its two zig-zag chunks: q_local / dout_local (2*clen, Hq, d),
+    k_local / v_local (2*clen, Hk, d), topk_idx_local (Hk, 2*clen, k).  K and V are all-gathered,
+    each chunk runs forward and backward as an ordinary seqlen_q < seqlen_k call (its dK / dV
+    cover the keys before its end), and the partial dK / dV of all ranks are summed and handed
+    back by rows (`scatter_sequence_grad`).  Returns (out_local, dq_local, dk_local, dv_local).
+    `attn`: a differentiable stand-in for infllmv2_attn_varlen_func (tests)."""
+    if attn is None:
+        from . import attention
+        attn = attention.infllmv2_attn_varlen_func
+    chunks = zigzag_chunks(seqlen, world, rank)
+    clen = chunks[0].end - chunks[0].start
+    dev = q_local.device
+    q = q_local.detach().requires_grad_(True)
+    k = gather_sequence(k_local, world, group).detach().requires_grad_(True)
+    v = gather_sequence(v_local, world, group).detach().requires_grad_(True)
+    outs = []
+    for i, ch in enumerate(chunks):
+        cu_q = torch.tensor([0, clen], dtype=torch.int32, device=dev)
+        cu_k = torch.tensor([0, ch.end], dtype=torch.int32, device=dev)
+        idx = topk_idx_local[:, i * clen:(i + 1) * clen].contiguous()
+        outs.append(attn(q[i * clen:(i + 1) * clen], k[:ch.end], v[:ch.end], cu_q, cu_k, clen, ch.end,
+                         causal=True, topk_idx=idx))
+    out = torch.cat(outs, dim=0)
+    out.backward(dout_local.to(out.dtype))
+    dk = scatter_sequence_grad(k.grad, world, rank, group)
+    dv = scatter_sequence_grad(v.grad, world, rank, group)
+    return out.detach(), q.grad, dk, dv
+
+
 def compressed_range(chunk: Chunk, stride: int = 16) -> Tuple[int, int]:
     """Compressed-key slots [lo, hi) that a rank contributes for a chunk: key j (tokens
     [16j, 16j+32)) belongs to the chunk that holds its first token."""

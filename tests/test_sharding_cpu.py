@@ -90,3 +90,44 @@ def test_query_chunk_prefill_world2_matches_unsharded(tmp_path):
         assert (res["out"] - full_out[res["rows"]]).abs().max() < 1e-5
         seen[res["rows"]] = True
     assert bool(seen.all())
+
+
+def _bwd_worker(rank, world, port, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        q, k, v, kc = _inputs()
+        dout = torch.randn(L, HQ, D, generator=torch.Generator().manual_seed(1))
+        idx = _full_topk(q, k, v, kc)
+        rows = torch.cat([torch.arange(c.start, c.end) for c in sharding.zigzag_chunks(L, world, rank)])
+
+        def attn(qc, kk, vv, cu_q, cu_k, lq, lk, causal=True, topk_idx=None):
+            return oracle.sparse_attention_fwd(qc, kk, vv, cu_q, cu_k, topk_idx, causal=causal)[0]
+
+        out, dq, dk, dv = sharding.sharded_attention_fwd_bwd(
+            q[rows].float(), k[rows].float(), v[rows].float(), dout[rows], idx[:, rows], L, world, rank,
+            attn=attn)
+        torch.save({"rows": rows, "out": out, "dq": dq, "dk": dk, "dv": dv},
+                   os.path.join(result_dir, f"b{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _full_topk(q, k, v, kc):
+    return sharding.prefill_chunk(q, kc, k, v, sharding.Chunk(0, 0, L), TOPK, INIT, LOCAL, _oracle_ops())[1]
+
+
+def test_query_chunk_backward_world2_matches_unsharded(tmp_path):
+    """Forward + backward under query-chunk sharding (all-gather of K/V, per-chunk backward,
+    summed and re-scattered dK/dV) against the unsharded oracle gradients."""
+    world = 2
+    mp.spawn(_bwd_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    q, k, v, kc = _inputs()
+    dout = torch.randn(L, HQ, D, generator=torch.Generator().manual_seed(1))
+    idx = _full_topk(q, k, v, kc)
+    out, _, dq, dk, dv = oracle.sparse_attention_fwd_bwd(q, k, v, dout, [0, L], [0, L], idx)
+    for r in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"b{r}.pt"))
+        rows = res["rows"]
+        for name, ref in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
+            assert (res[name] - ref[rows]).abs().max() < 1e-4, (name, r)

@@ -62,3 +62,56 @@ def test_query_chunk_prefill_two_gpus(tmp_path):
         err = (res["out"].float() - full[res["rows"]]).abs().amax(dim=(1, 2))
         # a token whose bf16 block scores tie differently picks another block; nearly all agree
         assert (err <= 2e-2).float().mean().item() > 0.97
+
+
+def _bwd_worker(rank, world, port, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import infllm_v2
+        from infllmv2_cuda_impl_b200 import sharding
+        q, k, v, kc = _inputs()
+        dout = torch.randn(L, HQ, D, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+        idx = torch.load(os.path.join(result_dir, "idx.pt"))
+        rows = torch.cat([torch.arange(c.start, c.end) for c in sharding.zigzag_chunks(L, world, rank)])
+        out, dq, dk, dv = sharding.sharded_attention_fwd_bwd(
+            q[rows].to(dev), k[rows].to(dev), v[rows].to(dev), dout[rows].to(dev), idx[:, rows].to(dev),
+            L, world, rank)
+        infllm_v2.check_device_status()
+        torch.save({"rows": rows, "out": out.cpu(), "dq": dq.cpu(), "dk": dk.cpu(), "dv": dv.cpu()},
+                   os.path.join(result_dir, f"b{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_query_chunk_backward_two_gpus(tmp_path):
+    """Forward + backward under query-chunk sharding over NCCL (all-gather of K / V, per-chunk
+    backward, reduce-scatter of dK / dV) against the same step on one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import infllm_v2
+    from infllmv2_cuda_impl_b200 import sharding
+    q, k, v, kc = _inputs()
+    dev = torch.device("cuda", 0)
+    _, idx = sharding.prefill_chunk(q.to(dev), kc.to(dev), k.to(dev), v.to(dev),
+                                    sharding.Chunk(0, 0, L), TOPK, INIT, LOCAL)
+    torch.save(idx.cpu(), os.path.join(str(tmp_path), "idx.pt"))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_bwd_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    dout = torch.randn(L, HQ, D, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    cu = torch.tensor([0, L], dtype=torch.int32, device=dev)
+    out = infllm_v2.infllmv2_attn_varlen_func(qd, kd, vd, cu, cu, L, L, causal=True, topk_idx=idx)
+    out.backward(dout.to(dev))
+    ref = {"out": out.detach(), "dq": qd.grad, "dk": kd.grad, "dv": vd.grad}
+    for r in range(2):
+        res = torch.load(os.path.join(str(tmp_path), f"b{r}.pt"))
+        for name in ("out", "dq", "dk", "dv"):
+            a, b = res[name].float(), ref[name][res["rows"].to(dev)].float().cpu()
+            tol = 2e-2 * max(1.0, b.abs().max().item())
+            # dK / dV: the sharded sum adds two bf16-rounded partials, the unsharded one rounds once
+            assert (a - b).abs().max().item() <= tol, (name, r, (a - b).abs().max().item())
