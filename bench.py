@@ -570,6 +570,49 @@ def config5_decode(device, pk, small=False):
         "frac": round(bytes_dec / best / 1e6 / pk["hbm_gbs"], 4),
         "tokens_per_s": round(B / (best * 1e-3), 1),
         "note": "stage-2 sparse decode step incl. the uint64 mask build; 268 MB of selected K/V per step"}
+
+    # ---- the whole decode step: stage 1 over the compressed keys of every sequence (one query
+    # token each) -> 64-token max-pool -> top-64 -> sparse attention over the selected blocks
+    n_c = [(int(l) - KERNEL) // STRIDE + 1 for l in lens_t]
+    kc = (torch.randn(sum(n_c), hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    cu_q = torch.arange(B + 1, dtype=torch.int32, device=device)
+    cu_c = torch.tensor([0] + list(torch.tensor(n_c).cumsum(0)), dtype=torch.int32, device=device)
+    max_c, q2 = max(n_c), q.view(B, hk * 16, D)
+    cache_lens = (lens_d - 1).contiguous()               # the query is the last token of its sequence
+
+    def full_step():
+        score = infllm_v2.infllmv2_attn_stage1(q2, kc, kc, cu_q, cu_c, cu_c, 1, max_c, causal=False)
+        pooled = infllm_v2.max_pooling_1d_varlen(score, cu_q, cu_c, cache_lens, 1, max_c, LOCAL_BLOCKS,
+                                                 INIT_BLOCKS, max_cache_len=hi)
+        sel = infllm_v2.infllmv2_topk(pooled, TOPK, cu_seqlens_q=cu_q, cache_lens=cache_lens)
+        return infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d,
+                                                    topk_idx=sel.transpose(0, 1).unsqueeze(2).contiguous())
+
+    full_step()
+    t_full = _time_ms(full_step, reps=10)
+    t_full_graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            full_step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            full_step()
+        t_full_graph = _time_ms(graph.replay, reps=20)
+    except Exception as e:
+        out["config5_full_graph_error"] = repr(e)[:200]
+    best_full = min(t_full, t_full_graph) if t_full_graph else t_full
+    bytes_full = bytes_dec + kc.numel() * 2
+    out["config5_decode_b64_with_selection"] = {
+        "ms": round(best_full, 4), "ms_eager": round(t_full, 4),
+        "ms_cuda_graph": round(t_full_graph, 4) if t_full_graph else None,
+        "gbs": round(bytes_full / best_full / 1e6, 1),
+        "frac": round(bytes_full / best_full / 1e6 / pk["hbm_gbs"], 4),
+        "tokens_per_s": round(B / (best_full * 1e-3), 1),
+        "note": "stage 1 (one token per sequence) + pool + top-k + sparse decode; algorithmic bytes = "
+                "compressed keys once (%d MB) + selected K/V" % (kc.numel() * 2 // 1000000)}
     return out
 
 

@@ -134,6 +134,19 @@ int ifv2_stage1_scores(const void* q, const void* kc, const void* lse_keys, void
                        int max_seqlen_k, int64_t out_row_stride, float softmax_scale, int causal,
                        int32_t* status, void* stream);
 
+/* Stage-1 scorer for decode: exactly ONE query token per sequence (q: (batch, heads_q, 128)), same
+ * output layout and values as ifv2_stage1_scores called with cu_seqlens_q = 0, 1, 2, ...; the
+ * keys of a sequence are split over CTAs so that the launch is bandwidth-bound instead of being
+ * serialised per sequence.  workspace: ifv2_stage1_decode_workspace_bytes(...) bytes, 8-byte
+ * aligned, holds the per-chunk softmax statistics between the two kernels.
+ * Same reference path as ifv2_stage1_scores (mha_varlen_fwd_stage1 with seqlen_q = 1 per
+ * sequence, as the decode caller of infllm_v2/infllmv2_sparse_attention.py:483-606 uses it). */
+int64_t ifv2_stage1_decode_workspace_bytes(int batch, int heads_k, int max_seqlen_k);
+int ifv2_stage1_decode_scores(const void* q, const void* kc, void* out, const int32_t* cu_seqlens_k,
+                              int batch, int64_t total_c, int heads_q, int heads_k, int head_dim,
+                              int max_seqlen_k, int64_t out_row_stride, float softmax_scale,
+                              int causal, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Stage-1 scorer with the 64-token max-pool fused in: writes block scores
  * (heads_k, total_q, n_blocks) bf16 that are bit-identical to ifv2_max_pooling_1d[_varlen]
  * (kernel 5, stride 4, padding 1, block 64) applied to the output of ifv2_stage1_scores, without

@@ -38,6 +38,8 @@ SIGNATURES = {
     "ifv2_stage1_scores": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int64, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                            c_int64, c_float, c_int, c_void_p, c_void_p],
+    "ifv2_stage1_decode_scores": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
+                                  c_int, c_int, c_int64, c_float, c_int, c_void_p, c_int64, c_void_p],
     "ifv2_stage1_block_scores": [c_void_p] * 8 + [c_int64, c_void_p, c_int, c_int64, c_int64, c_int,
                                                   c_int, c_int, c_int, c_int, c_int64, c_int, c_int,
                                                   c_int, c_int, c_float, c_int, c_void_p, c_void_p],
@@ -61,6 +63,7 @@ SIGNATURES = {
 _INT64_RETURNS = {
     "ifv2_sparse_attn_bwd_workspace_bytes": [c_int64, c_int, c_int],
     "ifv2_decode_workspace_bytes": [c_int, c_int, c_int, c_int],
+    "ifv2_stage1_decode_workspace_bytes": [c_int, c_int, c_int],
 }
 
 

@@ -117,6 +117,17 @@ def infllmv2_attn_stage1(
     assert cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32
     row_stride = max(round_multiple(max_seqlen_k, 128), 128)
     buf = torch.empty(nheads_k, total_q, row_stride, dtype=torch.bfloat16, device=q.device)
+    if max_seqlen_q == 1 and total_q == batch and lse_keys is None and max_seqlen_k > 0:
+        # decode: one token per sequence -> the bandwidth-oriented kernel pair (same values)
+        lib = _lib.load()
+        ws_bytes = int(lib.ifv2_stage1_decode_workspace_bytes(batch, nheads_k, max_seqlen_k))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        with torch.cuda.device(q.device):
+            _lib.call("ifv2_stage1_decode_scores", q.data_ptr(), k.data_ptr(), buf.data_ptr(),
+                      cu_seqlens_k.contiguous().data_ptr(), batch, k.shape[0], nheads, nheads_k,
+                      q.shape[-1], max_seqlen_k, row_stride, float(softmax_scale), int(bool(causal)),
+                      ws.data_ptr(), ws_bytes, _stream(q.device))
+        return buf[:, :, :max_seqlen_k]
     with torch.cuda.device(q.device):
         _lib.call("ifv2_stage1_scores", q.data_ptr(), k.data_ptr(),
                   lse_keys.data_ptr() if lse_keys is not None else None, buf.data_ptr(),

@@ -161,3 +161,34 @@ def test_stage1_compressed_lse_vs_oracle(lens, causal):
         ref = infllm_v2.max_pooling_1d_varlen(got, cq, ck, torch.zeros(len(lens), dtype=torch.int32, device=DEV),
                                               max(lens), max_k, 2, 1)
         assert torch.equal(pooled, ref)
+
+
+@pytest.mark.parametrize("lens_c,hk,causal", [([700, 1, 512, 513, 33], 2, False), ([2047, 16], 8, False),
+                                              ([300, 64, 5], 2, True)])
+def test_stage1_decode_path(lens_c, hk, causal):
+    """One query token per sequence takes the chunk-parallel kernel pair: same scores as the
+    oracle, zeros past every sequence's keys, and as the general kernel (forced by giving one
+    sequence two tokens, which leaves the rows of the single-token sequences unchanged)."""
+    bsz = len(lens_c)
+    seed = sum(lens_c) + hk
+    q = det_tensor((bsz, hk * 16, 128), seed, 0.5)
+    kc = det_tensor((sum(lens_c), hk, 128), seed + 1, 0.5)
+    cu_q, cu_c = cu([1] * bsz), cu(lens_c)
+    max_c = max(lens_c)
+    exp = oracle.stage1_scores(q, kc, cu_q.tolist(), cu_c.tolist(), max_c, causal)
+    got = infllm_v2.infllmv2_attn_stage1(q.to(DEV), kc.to(DEV), kc.to(DEV), cu_q.to(DEV), cu_c.to(DEV),
+                                         cu_c.to(DEV), 1, max_c, causal=causal)
+    infllm_v2.check_device_status()
+    assert got.shape == (hk, bsz, max_c)
+    ok, err = _within(got.float().cpu(), exp)
+    assert ok, err
+    for b, n in enumerate(lens_c):                       # nothing but zeros past a sequence's keys
+        assert (got[:, b, n:] == 0).all()
+    if not causal:
+        # the general kernel on the same rows: append a second token to the last sequence
+        q2 = torch.cat([q, q[-1:]], 0)
+        cu_q2 = cu([1] * (bsz - 1) + [2])
+        ref = infllm_v2.infllmv2_attn_stage1(q2.to(DEV), kc.to(DEV), kc.to(DEV), cu_q2.to(DEV), cu_c.to(DEV),
+                                             cu_c.to(DEV), 2, max_c, causal=False)
+        diff = (got.float() - ref[:, :bsz].float()).abs()
+        assert (diff <= torch.maximum(torch.tensor(2e-2, device=DEV), ref[:, :bsz].float().abs() * 2.0 ** -7)).all()
