@@ -9,8 +9,8 @@
 //   kernel 2: merge the chunk stats of the pair, recompute the products, p = exp2(c*s - c*m)/l,
 //             sum the 16 heads with warp shuffles, write the bf16 score row (0 where invisible,
 //             0 up to max_seqlen_k past the last key)
-// The keys are read twice; the second read of a pair's chunk comes from L2 when the whole key set
-// fits there.  Output layout and values are those of the general kernel (ifv2_stage1_scores).
+// The keys are read twice; kernel 2 runs over the grid in reverse so that its first reads hit
+// what kernel 1 left in L2.  Output layout and values are those of the general kernel (ifv2_stage1_scores).
 #include "mma_sync.cuh"
 
 namespace ifv2 {
@@ -90,7 +90,11 @@ __global__ void __launch_bounds__(kThreads) stage1_decode_kernel(const DecodeS1P
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float2 warp_stat[kWarps][16];
   __shared__ float row_const[16];                  // pass 2: -(m + log2 l) per head, log2 units
-  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // Kernel 2 walks the grid backwards: what kernel 1 read last is still in L2 when kernel 2 starts
+  // there, so only the part of the key set that does not fit L2 is fetched from DRAM twice.
+  const int chunk = (kPass == 2) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int h = (kPass == 2) ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
+  const int b = (kPass == 2) ? (int)(gridDim.z - 1 - blockIdx.z) : (int)blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int k0 = p.cu_k[b], lc = p.cu_k[b + 1] - k0;
