@@ -137,8 +137,9 @@ int ifv2_stage1_scores(const void* q, const void* kc, const void* lse_keys, void
 /* Stage-1 scorer for decode: exactly ONE query token per sequence (q: (batch, heads_q, 128)), same
  * output layout and values as ifv2_stage1_scores called with cu_seqlens_q = 0, 1, 2, ...; the
  * keys of a sequence are split over CTAs so that the launch is bandwidth-bound instead of being
- * serialised per sequence.  workspace: ifv2_stage1_decode_workspace_bytes(...) bytes, 8-byte
- * aligned, holds the per-chunk softmax statistics between the two kernels.
+ * serialised per sequence.  workspace: ifv2_stage1_decode_workspace_bytes(...) bytes, 16-byte
+ * aligned; it holds the per-chunk softmax statistics and the unnormalised bf16 exponentials
+ * (32 bytes per key and KV head) between the two kernels, so the keys are read once.
  * Same reference path as ifv2_stage1_scores (mha_varlen_fwd_stage1 with seqlen_q = 1 per
  * sequence, as the decode caller of infllm_v2/infllmv2_sparse_attention.py:483-606 uses it). */
 int64_t ifv2_stage1_decode_workspace_bytes(int batch, int heads_k, int max_seqlen_k);
