@@ -164,6 +164,7 @@ def test_stage1_compressed_lse_vs_oracle(lens, causal):
 
 
 @pytest.mark.parametrize("lens_c,hk,causal", [([700, 1, 512, 513, 33], 2, False), ([2047, 16], 8, False),
+                                              ([40, 0, 1025], 2, False),
                                               ([300, 64, 5], 2, True)])
 def test_stage1_decode_path(lens_c, hk, causal):
     """One query token per sequence takes the chunk-parallel kernel pair: same scores as the
