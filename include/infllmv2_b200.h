@@ -242,6 +242,17 @@ int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new, 
                 int64_t cache_capacity, int64_t cache_batch_stride, float softmax_scale,
                 void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Rotary embedding for a decode step with an append: rotates q (batch, heads_q, 128) and k_new
+ * (batch, heads_k, 128) at position cache_seqlens[b] into q_out / k_out (same shapes, may not
+ * alias the inputs); rotary_cos / rotary_sin: (seqlen_ro, rotary_dim / 2) bf16; interleaved != 0
+ * pairs features (2i, 2i+1), otherwise (i, i + rotary_dim / 2).  The rotated tensors are then
+ * passed to ifv2_decode[_paged] as q and k_new.  Replaces the rotary-on-append branch of
+ * mha_fwd_kvcache (csrc/flash_attn/flash_api.cpp:1773-1797, src/rotary.h). */
+int ifv2_decode_rotary(const void* q, const void* k_new, void* q_out, void* k_out,
+                       const void* rotary_cos, const void* rotary_sin, const int32_t* cache_seqlens,
+                       int batch, int heads_q, int heads_k, int head_dim, int rotary_dim,
+                       int seqlen_ro, int interleaved, void* stream);
+
 /* ifv2_decode with the cache addressing options of the reference's fwd_kvcache
  * (csrc/flash_attn/flash_api.cpp:1590-1640, 1773-1797):
  *  block_table (batch, block_table_stride) int32 or null: paged cache, k_cache / v_cache are then

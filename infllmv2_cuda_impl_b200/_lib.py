@@ -56,6 +56,7 @@ SIGNATURES = {
                                                       c_void_p, c_void_p],
     "ifv2_decode": [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int64,
                                      c_int64, c_float, c_void_p, c_int64, c_void_p],
+    "ifv2_decode_rotary": [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ifv2_decode_paged": [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_float,
                                            c_void_p, c_int64, c_void_p],

@@ -364,8 +364,8 @@ def infllmv2_attn_with_kvcache(
     assert v_cache.stride(-1) == 1, "v_cache must have contiguous last dimension"
     _check_common(q, k_cache, 0.0, window_size, softcap, alibi_slopes, None,
                   "infllmv2_attn_with_kvcache")
-    if rotary_cos is not None or rotary_sin is not None:
-        raise NotImplementedError("infllmv2_attn_with_kvcache: rotary-on-append is not supported")
+    if (rotary_cos is None) != (rotary_sin is None):
+        raise ValueError("infllmv2_attn_with_kvcache: pass both rotary_cos and rotary_sin, or neither")
     if q.shape[1] != 1:
         raise NotImplementedError("infllmv2_attn_with_kvcache: only one query token per sequence is supported")
     q, k, v = [maybe_contiguous(x) for x in (q, k, v)]
@@ -404,6 +404,20 @@ def infllmv2_attn_with_kvcache(
         assert topk_idx.dtype == torch.int32
         mask, _ = topk_to_uint64(topk_idx, cap, BLOCK_N)
     q2 = q.reshape(batch, nheads, d).contiguous()
+    if rotary_cos is not None and k is not None:
+        # as in the reference, the rotation applies to the appended key and to the query, both at
+        # the position of the append; without an append nothing is rotated
+        if rotary_cos.dtype != q.dtype or rotary_cos.shape != rotary_sin.shape or rotary_cos.dim() != 2:
+            raise ValueError("infllmv2_attn_with_kvcache: rotary_cos / rotary_sin must be "
+                             "(seqlen_ro, rotary_dim / 2) in the dtype of q")
+        k2 = k.reshape(batch, nheads_k, d).contiguous()
+        q_rot, k_rot = torch.empty_like(q2), torch.empty_like(k2)
+        with torch.cuda.device(q.device):
+            _lib.call("ifv2_decode_rotary", q2.data_ptr(), k2.data_ptr(), q_rot.data_ptr(), k_rot.data_ptr(),
+                      rotary_cos.contiguous().data_ptr(), rotary_sin.contiguous().data_ptr(),
+                      cache_seqlens.data_ptr(), batch, nheads, nheads_k, d, 2 * rotary_cos.shape[1],
+                      rotary_cos.shape[0], int(bool(rotary_interleaved)), _stream(q.device))
+        q2, k = q_rot, k_rot
     out = torch.empty_like(q2)
     lse = torch.empty(batch, nheads, dtype=torch.float32, device=q.device)
     lib = _lib.load()

@@ -376,6 +376,51 @@ extern "C" int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_
   return (int64_t)batch * heads_q * kMaxSplits * kPartialFloats * 4 + 256;
 }
 
+// Rotary embedding of the decode step's new key and of its query, both at the position the key is
+// appended at (the reference rotates them while it copies them, flash_fwd_kernel.h:787-930 with
+// rotary.h): interleaved pairs (2i, 2i+1) or halves (i, i + rotary_dim/2); features past rotary_dim
+// pass through; fp32 arithmetic, one rounding.  One thread per (row, pair).
+__global__ void decode_rotary_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_new,
+                                     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
+                                     const __nv_bfloat16* __restrict__ cos_t, const __nv_bfloat16* __restrict__ sin_t,
+                                     const int32_t* __restrict__ cache_seqlens, int batch, int heads_q,
+                                     int heads_k, int rotary_dim, int seqlen_ro, int interleaved) {
+  const int rows = heads_q + heads_k;                  // per sequence: query heads, then key heads
+  const int64_t n = (int64_t)batch * rows * (kHeadDim / 2);
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % (kHeadDim / 2));
+    const int r = (int)((idx / (kHeadDim / 2)) % rows);
+    const int b = (int)(idx / ((int64_t)(kHeadDim / 2) * rows));
+    const bool is_q = r < heads_q;
+    const __nv_bfloat16* src = is_q ? q + ((int64_t)b * heads_q + r) * kHeadDim
+                                    : k_new + ((int64_t)b * heads_k + (r - heads_q)) * kHeadDim;
+    __nv_bfloat16* dst = is_q ? q_out + ((int64_t)b * heads_q + r) * kHeadDim
+                              : k_out + ((int64_t)b * heads_k + (r - heads_q)) * kHeadDim;
+    const int half = rotary_dim / 2;
+    // the two features this thread owns
+    int i0, i1;
+    if (i < half) {
+      i0 = interleaved ? 2 * i : i;
+      i1 = interleaved ? 2 * i + 1 : i + half;
+    } else {                                            // pass-through part, two features per thread
+      i0 = rotary_dim + 2 * (i - half);
+      i1 = i0 + 1;
+    }
+    float x0 = __bfloat162float(src[i0]), x1 = __bfloat162float(src[i1]);
+    if (i < half) {
+      const int pos = min(max(cache_seqlens[b], 0), seqlen_ro - 1);
+      const float c = __bfloat162float(cos_t[(int64_t)pos * half + i]);
+      const float sn = __bfloat162float(sin_t[(int64_t)pos * half + i]);
+      const float re = x0 * c - x1 * sn, im = x0 * sn + x1 * c;
+      x0 = re;
+      x1 = im;
+    }
+    dst[i0] = __float2bfloat16_rn(x0);
+    dst[i1] = __float2bfloat16_rn(x1);
+  }
+}
+
 static int decode_impl(const void* q, void* k_cache, void* v_cache, const void* k_new,
                        const void* v_new, void* out, float* lse, const int64_t* mask,
                        int mask_words, const int32_t* cache_seqlens, int batch, int heads_q,
@@ -482,4 +527,29 @@ extern "C" int ifv2_decode_paged(const void* q, void* k_cache, void* v_cache, co
                      batch, heads_q, heads_k, head_dim, cache_capacity, cache_batch_stride, block_table,
                      block_table_stride, page_size, cache_batch_idx, cache_leftpad, softmax_scale,
                      workspace, workspace_bytes, stream);
+}
+
+extern "C" int ifv2_decode_rotary(const void* q, const void* k_new, void* q_out, void* k_out,
+                                  const void* rotary_cos, const void* rotary_sin,
+                                  const int32_t* cache_seqlens, int batch, int heads_q, int heads_k,
+                                  int head_dim, int rotary_dim, int seqlen_ro, int interleaved,
+                                  void* stream) {
+  IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED, "decode_rotary: head_dim %d not supported (only 128)",
+               head_dim);
+  IFV2_REQUIRE(batch >= 0 && heads_q >= 1 && heads_k >= 1 && seqlen_ro >= 1, IFV2_ERR_INVALID_ARG,
+               "decode_rotary: bad size");
+  IFV2_REQUIRE(rotary_dim >= 0 && rotary_dim <= kHeadDim && rotary_dim % 16 == 0, IFV2_ERR_INVALID_ARG,
+               "decode_rotary: rotary_dim must be a multiple of 16 and <= head_dim");
+  if (batch == 0) return IFV2_OK;
+  IFV2_REQUIRE(q && k_new && q_out && k_out && cache_seqlens && (rotary_dim == 0 || (rotary_cos && rotary_sin)),
+               IFV2_ERR_INVALID_ARG, "decode_rotary: null pointer");
+  const int64_t n = (int64_t)batch * (heads_q + heads_k) * (kHeadDim / 2);
+  int64_t blocks = ceil_div64(n, 256);
+  if (blocks > (int64_t)kNumSMs * 8) blocks = (int64_t)kNumSMs * 8;
+  decode_rotary_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_new),
+      static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out),
+      static_cast<const __nv_bfloat16*>(rotary_cos), static_cast<const __nv_bfloat16*>(rotary_sin),
+      cache_seqlens, batch, heads_q, heads_k, rotary_dim, seqlen_ro, interleaved ? 1 : 0);
+  return check_launch("decode_rotary");
 }

@@ -112,3 +112,22 @@ def kvcache_decode(q, k_cache, v_cache, cache_seqlens, topk_idx=None, k_new=None
         outs.append(o)
         lses.append(l)
     return torch.stack(outs, 0), torch.stack(lses, 0)
+
+
+def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """Rotary embedding of rows x (..., d) with per-row cos / sin (..., rotary_dim / 2), the way the
+    reference rotates q and the appended key of a decode step (csrc/flash_attn/src/rotary.h:20-79
+    interleaved, :83-150 contiguous halves): fp32 arithmetic, features past rotary_dim unchanged,
+    result in x's dtype.  No Python twin exists in the reference (parity unpinned for this helper)."""
+    half = cos.shape[-1]
+    xf, c, s_ = x.float(), cos.float(), sin.float()
+    out = xf.clone()
+    if interleaved:
+        x0, x1 = xf[..., 0:2 * half:2], xf[..., 1:2 * half:2]
+        out[..., 0:2 * half:2] = x0 * c - x1 * s_
+        out[..., 1:2 * half:2] = x0 * s_ + x1 * c
+    else:
+        x0, x1 = xf[..., :half], xf[..., half:2 * half]
+        out[..., :half] = x0 * c - x1 * s_
+        out[..., half:2 * half] = x0 * s_ + x1 * c
+    return out.to(x.dtype)

@@ -155,3 +155,33 @@ def test_decode_batch_idx_and_leftpad():
     mx, mr = err_stats(out.cpu(), ref)
     assert mx <= MAX_ABS and mr <= MEAN_REL, (mx, mr)
     assert (lse.cpu() - ref_lse).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("rotary_dim,interleaved", [(128, True), (64, False), (32, True), (128, False)])
+def test_decode_rotary_on_append(rotary_dim, interleaved):
+    """rotary_cos / rotary_sin rotate the appended key and the query at the append position; the
+    result equals the plain call on inputs rotated by the oracle, and the cache receives the
+    rotated key."""
+    bsz, hk, d, cap = 3, 2, 128, 700
+    lens = [5, 300, 640]
+    q = det_tensor((bsz, 1, hk * 16, d), 61, 0.25)
+    kc, vc = det_tensor((bsz, cap, hk, d), 62, 0.25), det_tensor((bsz, cap, hk, d), 63)
+    kn, vn = det_tensor((bsz, 1, hk, d), 64, 0.25), det_tensor((bsz, 1, hk, d), 65)
+    ang = torch.arange(cap)[:, None] * (1.0 / 10000 ** (torch.arange(rotary_dim // 2) / (rotary_dim // 2)))[None, :]
+    cos, sin = torch.cos(ang).to(torch.bfloat16), torch.sin(ang).to(torch.bfloat16)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    idx = _topk(bsz, hk, [l + 1 for l in lens], 4, 66)
+    pos = lens_t.long()
+    q_rot = oracle.apply_rotary(q[:, 0], cos[pos][:, None], sin[pos][:, None], interleaved)[:, None]
+    k_rot = oracle.apply_rotary(kn[:, 0], cos[pos][:, None], sin[pos][:, None], interleaved)[:, None]
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    ref, ref_lse = oracle.kvcache_decode(q_rot, kc_ref, vc_ref, lens_t, idx, k_rot, vn)
+    kc_d, vc_d = kc.to(DEV), vc.to(DEV)
+    out, lse = infllm_v2.infllmv2_attn_with_kvcache(
+        q.to(DEV), kc_d, vc_d, k=kn.to(DEV), v=vn.to(DEV), rotary_cos=cos.to(DEV), rotary_sin=sin.to(DEV),
+        cache_seqlens=lens_t.to(DEV), rotary_interleaved=interleaved, topk_idx=idx.to(DEV),
+        return_softmax_lse=True)
+    mx, mr = err_stats(out.cpu(), ref)
+    assert mx <= MAX_ABS and mr <= MEAN_REL, (mx, mr)
+    assert (lse.cpu() - ref_lse).abs().max() < 2e-2
+    assert torch.equal(kc_d.cpu(), kc_ref) and torch.equal(vc_d.cpu(), vc_ref)     # rotated key in the cache
