@@ -208,6 +208,22 @@ template <> struct Pack<__half> {
   static __device__ __forceinline__ uint32_t eq_mask(T2 a, T2 b) { return __heq2_mask(a, b); }
 };
 
+// Output stores are guarded by the capacity of the row: a slot outside [0, k) is never written
+// (-DIFV2_TOPK_CHECK additionally reports such a slot).
+#ifdef IFV2_TOPK_CHECK
+#define IFV2_TOPK_STORE(pos, val)                                                               \
+  do {                                                                                          \
+    if ((unsigned)(pos) < (unsigned)k_cap) o[(pos)] = (val);                                    \
+    else printf("topk: slot %d outside [0,%d) lane %d k_sel %d need %d exact %d bq %d\n", (int)(pos), k_cap, \
+                lane, k_sel, need, (int)exact, bq);                                             \
+  } while (0)
+#else
+#define IFV2_TOPK_STORE(pos, val)                                  \
+  do {                                                             \
+    if ((unsigned)(pos) < (unsigned)k_cap) o[(pos)] = (val);       \
+  } while (0)
+#endif
+
 // Selection over the first kIts iterations (256 entries each) of a row held in registers; the
 // iteration count is a template parameter so that the probe and emit loops are straight-line
 // code.  Returns the number of entries emitted, or -1 when a restricted selection turns out not
@@ -215,7 +231,7 @@ template <> struct Pack<__half> {
 template <typename T, int kPairs, int kIts>
 __device__ __forceinline__ int topk_row(const typename Pack<T>::T2 (&v)[kPairs],
                                         typename Pack<T>::T2 tail2, bool restricted, int k_sel,
-                                        int bq, int lane, int32_t* o) {
+                                        int bq, int lane, int32_t* o, int k_cap) {
   using N = Num<T>;
   using P = Pack<T>;
   using T2 = typename P::T2;
@@ -297,7 +313,8 @@ __device__ __forceinline__ int topk_row(const typename Pack<T>::T2 (&v)[kPairs],
           const int s = __ffs(sel) - 1;
           sel &= sel - 1u;
           const int idx = e0 + s;
-          o[pos++] = (idx <= bq) ? idx : -1;
+          IFV2_TOPK_STORE(pos, (idx <= bq) ? idx : -1);
+          ++pos;
         }
       } else {
 #pragma unroll
@@ -306,7 +323,7 @@ __device__ __forceinline__ int topk_row(const typename Pack<T>::T2 (&v)[kPairs],
           if (g || (t && tie_before < need)) {
             const int pos = gt_before + min(tie_before, need);
             const int idx = e0 + s;
-            o[pos] = (idx <= bq) ? idx : -1;
+            IFV2_TOPK_STORE(pos, (idx <= bq) ? idx : -1);
           }
           gt_before += g;
           tie_before += t;
@@ -407,12 +424,12 @@ __global__ void __launch_bounds__(kThreads, (kIters <= 8) ? 2 : 1) topk_select_k
 #define IFV2_TOPK_CASE(I)                                                                \
         case I:                                                                          \
           if constexpr (I <= kIters)                                                     \
-            got = topk_row<T, kPairs, I>(v, tail2, restricted, k_sel, bq, lane, o);      \
+            got = topk_row<T, kPairs, I>(v, tail2, restricted, k_sel, bq, lane, o, p.k); \
           break;
         IFV2_TOPK_CASE(2) IFV2_TOPK_CASE(4) IFV2_TOPK_CASE(6)
 #undef IFV2_TOPK_CASE
         default:
-          got = topk_row<T, kPairs, kIters>(v, tail2, restricted, k_sel, bq, lane, o);
+          got = topk_row<T, kPairs, kIters>(v, tail2, restricted, k_sel, bq, lane, o, p.k);
           break;
       }
       if (got < 0) continue;

@@ -490,10 +490,11 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
   IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE, "%s: batch or heads_k > 65535",
                what);
 
-  IFV2_REQUIRE((kv == nullptr) == (cu_seqlens_v == nullptr), IFV2_ERR_INVALID_ARG,
-               "%s: the row-sum keys and their cu_seqlens go together", what);
-  IFV2_REQUIRE(kv == nullptr || (total_v >= 0 && total_v <= INT32_MAX), IFV2_ERR_INVALID_ARG,
-               "%s: bad row-sum key count", what);
+  // separate row-sum keys are announced by their cu_seqlens; the tensor itself may be empty
+  IFV2_REQUIRE(cu_seqlens_v != nullptr || kv == nullptr, IFV2_ERR_INVALID_ARG,
+               "%s: row-sum keys need their cu_seqlens", what);
+  IFV2_REQUIRE(cu_seqlens_v == nullptr || (total_v >= 0 && total_v <= INT32_MAX && (kv || total_v == 0)),
+               IFV2_ERR_INVALID_ARG, "%s: bad row-sum keys", what);
   CUtensorMap map_q, map_kc, map_kv;
   int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, total_q, kHeadDim * 2,
                                    (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerTile);

@@ -163,6 +163,26 @@ def test_stage1_compressed_lse_vs_oracle(lens, causal):
         assert torch.equal(pooled, ref)
 
 
+def test_stage1_compressed_lse_without_any_coarse_key():
+    """Sequences all shorter than the coarse window: the row-sum tensor is empty (its pointer is
+    null), cu_seqlens_v is all zeros and every score is 0, as in the oracle."""
+    lens, hq, hk = [100, 40, 127], 32, 2
+    q = det_tensor((sum(lens), hq, 128), 3, 0.5)
+    k = det_tensor((sum(lens), hk, 128), 4, 0.5)
+    kc, cu_c = oracle.compress_keys(k, cu(lens), 32, 16)
+    kv, cu_v = oracle.compress_keys(k, cu(lens), 128, 64)
+    assert kv.shape[0] == 0 and not any(cu_v)
+    max_k = int(np.diff(cu_c).max())
+    exp = oracle.stage1_scores(q, kc, cu(lens).tolist(), cu_c, max_k, True, lse_keys=kv, cu_seqlens_v=cu_v)
+    assert not exp.any()
+    got = infllm_v2.infllmv2_attn_stage1(q.to(DEV), kc.to(DEV), kv.to(DEV), cu(lens, DEV),
+                                         torch.tensor(cu_c, dtype=torch.int32, device=DEV),
+                                         torch.tensor(cu_v, dtype=torch.int32, device=DEV), max(lens), max_k,
+                                         causal=True)
+    infllm_v2.check_device_status()
+    assert got.shape == exp.shape and not got.float().cpu().any()
+
+
 @pytest.mark.parametrize("lens_c,hk,causal", [([700, 1, 512, 513, 33], 2, False), ([2047, 16], 8, False),
                                               ([40, 0, 1025], 2, False),
                                               ([300, 64, 5], 2, True)])
