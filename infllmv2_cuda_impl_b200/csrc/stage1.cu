@@ -327,8 +327,13 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     int lim_tok[kTokPerThread];
     const int cache_len = p.cache_lens ? p.cache_lens[b] : p.cache_len;
 #pragma unroll
-    for (int j = 0; j < kTokPerThread; ++j)
-      lim_tok[j] = (grp * 4 + j < ntok) ? visible_limit(tok0 + grp * 4 + j, lq, lc, p.causal) : 0;
+    for (int j = 0; j < kTokPerThread; ++j) {
+      // a token without any visible row-sum key scores exactly 0 (the huge negative row constant
+      // alone leaves 2^-125 per polynomial exponential)
+      const int tk = tok0 + grp * 4 + j;
+      lim_tok[j] = (grp * 4 + j < ntok && visible_limit(tk, lq, lcv, p.causal, st1) > 0)
+                       ? visible_limit(tk, lq, lc, p.causal) : 0;
+    }
     __nv_bfloat16* out_base =
         p.out ? p.out + ((int64_t)h * p.total_q + q0 + tok0) * p.out_row_stride : nullptr;
     __nv_bfloat16* pool_base =
