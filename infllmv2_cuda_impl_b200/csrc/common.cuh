@@ -41,4 +41,16 @@ __device__ inline int find_sequence(const int32_t* __restrict__ cu, int batch, i
   return lo;
 }
 
+// Read-only 16-bit loads.  The toolkit's __ldg overloads for __half / __nv_bfloat16 are inline
+// asm without `volatile`, which the compiler treats as a pure computation and may hoist above the
+// bounds check guarding it: the speculated load of a lane that owns no element then reads past
+// the end of the tensor and faults when the tensor ends at a mapping boundary.  The built-in
+// overload for unsigned short is an ordinary load and stays behind its guard.
+__device__ __forceinline__ __nv_bfloat16 ldg16(const __nv_bfloat16* p) {
+  return __ushort_as_bfloat16(__ldg(reinterpret_cast<const unsigned short*>(p)));
+}
+__device__ __forceinline__ __half ldg16(const __half* p) {
+  return __ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(p)));
+}
+
 }  // namespace ifv2

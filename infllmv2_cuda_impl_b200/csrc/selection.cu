@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(kThreads) max_pool_k5s4_kernel(const PoolParam
       }
       // x[8m-1]: the neighbour lane's last element (lane 0 re-reads it; it is in L1)
       float prev = __shfl_up_sync(0xFFFFFFFFu, v[7], 1);
-      if (lane == 0) prev = (e0 >= 1 && e0 - 1 < k_len) ? N::to_f(__ldg(x + e0 - 1)) : ninf;
+      if (lane == 0) prev = (e0 >= 1 && e0 - 1 < k_len) ? N::to_f(ldg16(x + e0 - 1)) : ninf;
       float r0 = fmaxf(fmaxf(prev, v[0]), fmaxf(fmaxf(v[1], v[2]), v[3]));
       float r1 = fmaxf(fmaxf(v[3], v[4]), fmaxf(fmaxf(v[5], v[6]), v[7]));
       const int b0 = 2 * m, b1 = b0 + 1;
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kThreads) max_pool_generic_kernel(const PoolPa
         const int s = max(b * p.stride - p.padding, 0);
         const int e = min(b * p.stride - p.padding + p.kernel, k_len);
         r = -INFINITY;
-        for (int i = s; i < e; ++i) r = fmaxf(r, N::to_f(__ldg(x + i)));
+        for (int i = s; i < e; ++i) r = fmaxf(r, N::to_f(ldg16(x + i)));
       }
       y[b] = N::from_f(r);
     }
@@ -391,8 +391,8 @@ __global__ void __launch_bounds__(kThreads, (kIters <= 8) ? 2 : 1) topk_select_k
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             T2 pr = pad2;
-            if (e0 + 2 * j < n) pr.x = __ldg(x + e0 + 2 * j);
-            if (e0 + 2 * j + 1 < n) pr.y = __ldg(x + e0 + 2 * j + 1);
+            if (e0 + 2 * j < n) pr.x = ldg16(x + e0 + 2 * j);
+            if (e0 + 2 * j + 1 < n) pr.y = ldg16(x + e0 + 2 * j + 1);
             v[it * 4 + j] = pr;
           }
         }

@@ -121,3 +121,29 @@ def test_topk_causal_restriction(t, n, k, tail):
     exp = oracle.topk_select(y, k, q_block)
     got = infllm_v2.infllmv2_topk(y.to(DEV), k)
     assert torch.equal(got.cpu(), exp)
+
+
+def test_inputs_touching_the_ends_of_an_allocation():
+    """Neither kernel reads outside its input: block scores of unaligned width placed at the very
+    end of a device allocation of their own (top-k; lanes that own no element of such a row must
+    not load anything), and scores starting at the very beginning of one (max-pool: the halo
+    element in front of a row's first score does not exist for row 0)."""
+    hk, t, n, k = 4, 307, 5, 1
+    x = _scores((hk, t, n), 77)
+    x[:, :, 0] = float("inf")
+    big = torch.empty(12 << 20, dtype=torch.uint8, device=DEV)          # a mapping of its own
+    tail = big[big.numel() - x.numel() * 2:].view(torch.bfloat16).view(hk, t, n)
+    tail.copy_(x)
+    cu_q = torch.tensor([0, 7, t], dtype=torch.int32, device=DEV)
+    got = infllm_v2.infllmv2_topk(tail, k, cu_seqlens_q=cu_q)
+    torch.cuda.synchronize()
+    qb = torch.cat([torch.arange(7) // 64, torch.arange(t - 7) // 64])
+    assert torch.equal(got.cpu(), oracle.topk_select(x.float(), k, qb))
+
+    s = _scores((2, 200, 24), 78)
+    head = torch.empty(12 << 20, dtype=torch.uint8, device=DEV)
+    view = head[:s.numel() * 2].view(torch.bfloat16).view(2, 200, 24)
+    view.copy_(s)
+    pooled = infllm_v2.max_pooling_1d(view[:, :, :21], 0, 2, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(pooled.cpu(), oracle.max_pooling_1d(s[:, :, :21], 0, 2, 1))
