@@ -82,6 +82,32 @@ int ifv2_compress_keys_append(const void* k_cache, void* kc_cache, const int32_t
                               int heads_k, int head_dim, int kernel_size, int kernel_stride,
                               void* stream);
 
+/* Prefill -> cache: copies the packed rows of every sequence (src: (total, heads_k, 128) bf16,
+ * cu_seqlens: (batch+1)) to rows [0, len_b) of its cache slot (cache: (batch, capacity, heads_k,
+ * 128)); rows past the capacity are dropped.  seqlens_out (may be null): min(len_b, capacity).
+ * Used for keys, values and both compressed-key tensors.  The reference leaves this to its caller
+ * (the k_cache / v_cache tensors of infllm_v2/infllmv2_sparse_attention.py:609-630 arrive filled). */
+int ifv2_cache_fill(const void* src, void* cache, const int32_t* cu_seqlens, int32_t* seqlens_out,
+                    int batch, int64_t total, int64_t capacity, int heads_k, int head_dim,
+                    void* stream);
+
+/* One decode step of cache bookkeeping in one launch: k_new / v_new (batch, heads_k, 128) go to
+ * position cache_seqlens[b] of k_cache / v_cache (batch, capacity, heads_k, 128); a sequence whose
+ * new length L completes a compression window (L >= kernel, (L - kernel) % stride == 0) gets the
+ * mean of its last `kernel` keys written to kc_cache[b, (L - kernel)/stride] (and likewise to
+ * kc2_cache with kernel2 / stride2: the coarse keys of the compressed-LSE mode); either compressed
+ * cache may be null.  Outputs: new_seqlens[b] = L (must not alias cache_seqlens), n_comp[b] /
+ * n_comp2[b] = compressed keys now valid (the seqused_k of the stage-1 scorer), may be null.  A
+ * sequence whose cache is full is left untouched (new_seqlens[b] = cache_seqlens[b]).
+ * Stands in for the in-kernel append of mha_fwd_kvcache (csrc/flash_attn/flash_api.cpp:1549-1843,
+ * knew / vnew) plus the caller-side recompression the reference has no kernel for. */
+int ifv2_decode_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                       void* kc_cache, void* kc2_cache, const int32_t* cache_seqlens,
+                       int32_t* new_seqlens, int32_t* n_comp, int32_t* n_comp2, int batch,
+                       int64_t capacity, int64_t c_capacity, int64_t c2_capacity, int heads_k,
+                       int head_dim, int kernel_size, int kernel_stride, int kernel2_size,
+                       int kernel2_stride, void* stream);
+
 /* 1-D max-pool of stage-1 scores to block scores with +inf on the init and causal-local blocks.
  * in: (heads, q_len, k_len) with `in_row_stride` elements between rows (>= k_len);
  * out: (heads, q_len, out_len) contiguous.  dtype: is_bf16 ? bf16 : fp16.
@@ -123,16 +149,20 @@ int ifv2_topk_select(const void* score, int32_t* out_idx, int is_bf16, int heads
  * sums are taken over (the reference's `v` argument): null / null / 0 = the same keys as kc; a
  * sequence whose count differs from its kc count is treated as the coarse compression (kernel
  * 128, stride 64) whose log-sum-exp normalises the scores, as flash_fwd_kernel.h:1236-1240 does.
+ * seqused_k: optional (batch) int32, the number of keys of each sequence actually in use (the
+ * reference's seqused_k, flash_api.cpp:792, 906-911; block_info.h:24); cu_seqlens_k then only
+ * gives where a sequence's keys start, e.g. b * capacity for a per-sequence cache of compressed
+ * keys.  seqused_v: the same for lse_keys / cu_seqlens_v.
  * status: int32[4] device words, word 0 != 0 after the launch means a bounded wait ran out.
  * Replaces C.varlen_fwd_stage1: csrc/entry.cu:209-214 -> mha_varlen_fwd_stage1,
  * csrc/flash_attn/flash_api.cpp:784-1049 (+ the GQA transpose, slice and NaN scrub of
  * infllm_v2/infllmv2_sparse_attention.py:554-589). */
 int ifv2_stage1_scores(const void* q, const void* kc, const void* lse_keys, void* out,
                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                       const int32_t* cu_seqlens_v, int64_t total_v, int batch, int64_t total_q,
-                       int64_t total_c, int heads_q, int heads_k, int head_dim, int max_seqlen_q,
-                       int max_seqlen_k, int64_t out_row_stride, float softmax_scale, int causal,
-                       int32_t* status, void* stream);
+                       const int32_t* cu_seqlens_v, int64_t total_v, const int32_t* seqused_k,
+                       const int32_t* seqused_v, int batch, int64_t total_q, int64_t total_c, int heads_q, int heads_k,
+                       int head_dim, int max_seqlen_q, int max_seqlen_k, int64_t out_row_stride,
+                       float softmax_scale, int causal, int32_t* status, void* stream);
 
 /* Stage-1 scorer for decode: exactly ONE query token per sequence (q: (batch, heads_q, 128)), same
  * output layout and values as ifv2_stage1_scores called with cu_seqlens_q = 0, 1, 2, ...; the
@@ -144,7 +174,8 @@ int ifv2_stage1_scores(const void* q, const void* kc, const void* lse_keys, void
  * sequence, as the decode caller of infllm_v2/infllmv2_sparse_attention.py:483-606 uses it). */
 int64_t ifv2_stage1_decode_workspace_bytes(int batch, int heads_k, int max_seqlen_k);
 int ifv2_stage1_decode_scores(const void* q, const void* kc, void* out, const int32_t* cu_seqlens_k,
-                              int batch, int64_t total_c, int heads_q, int heads_k, int head_dim,
+                              const int32_t* seqused_k /* may be null */, int batch,
+                              int64_t total_c, int heads_q, int heads_k, int head_dim,
                               int max_seqlen_k, int64_t out_row_stride, float softmax_scale,
                               int causal, void* workspace, int64_t workspace_bytes, void* stream);
 
@@ -161,6 +192,8 @@ int ifv2_stage1_block_scores(const void* q, const void* kc, const void* lse_keys
                              void* scores_or_null, void* block_scores,
                              const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                              const int32_t* cu_seqlens_v, int64_t total_v,
+                             const int32_t* seqused_k /* may be null */,
+                             const int32_t* seqused_v /* may be null */,
                              const int32_t* cache_lens, int batch, int64_t total_q,
                              int64_t total_c, int heads_q, int heads_k, int head_dim,
                              int max_seqlen_q, int max_seqlen_k, int64_t scores_row_stride,

@@ -88,6 +88,7 @@ def infllmv2_attn_stage1(
     q, k, v, cu_seqlens_q, cu_seqlens_k, cu_seqlens_v, max_seqlen_q, max_seqlen_k,
     dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0,
     alibi_slopes=None, deterministic=False, return_attn_probs=True, block_table=None,
+    seqused_k=None, seqused_v=None,
 ):
     """Stage-1 scores: for every KV head, softmax(q . k_compressed) summed over its 16 query heads.
 
@@ -99,6 +100,11 @@ def infllmv2_attn_stage1(
     Returns (nheads_k, total_q, max_seqlen_k) bf16; entries a token cannot see are 0.
     The returned tensor is a column slice of a buffer whose rows are padded to a multiple of
     128 elements, like the reference's (infllm_v2/infllmv2_sparse_attention.py:587).
+    seqused_k: optional (batch,) int32 -- only that many keys of each sequence are used
+    (flash_api.cpp:792, 906-911); cu_seqlens_k then only says where a sequence's keys start, so a
+    per-sequence cache (batch, capacity, nheads_k, 128) can be scored in place as
+    k = cache.view(-1, nheads_k, 128), cu_seqlens_k = arange(batch + 1) * capacity.
+    seqused_v: the same for v / cu_seqlens_v.
     """
     _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table,
                   "infllmv2_attn_stage1")
@@ -115,6 +121,16 @@ def infllmv2_attn_stage1(
     nheads_k = k.shape[1]
     batch = cu_seqlens_q.numel() - 1
     assert cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32
+    used_ptr = None
+    if seqused_k is not None:
+        assert seqused_k.dtype == torch.int32 and seqused_k.numel() == batch
+        seqused_k = seqused_k.contiguous()
+        used_ptr = seqused_k.data_ptr()
+    used_v_ptr = None
+    if seqused_v is not None and lse_keys is not None:
+        assert seqused_v.dtype == torch.int32 and seqused_v.numel() == batch
+        seqused_v = seqused_v.contiguous()
+        used_v_ptr = seqused_v.data_ptr()
     row_stride = max(round_multiple(max_seqlen_k, 128), 128)
     buf = torch.empty(nheads_k, total_q, row_stride, dtype=torch.bfloat16, device=q.device)
     if max_seqlen_q == 1 and total_q == batch and lse_keys is None and max_seqlen_k > 0:
@@ -124,8 +140,8 @@ def infllmv2_attn_stage1(
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
         with torch.cuda.device(q.device):
             _lib.call("ifv2_stage1_decode_scores", q.data_ptr(), k.data_ptr(), buf.data_ptr(),
-                      cu_seqlens_k.contiguous().data_ptr(), batch, k.shape[0], nheads, nheads_k,
-                      q.shape[-1], max_seqlen_k, row_stride, float(softmax_scale), int(bool(causal)),
+                      cu_seqlens_k.contiguous().data_ptr(), used_ptr, batch, k.shape[0], nheads,
+                      nheads_k, q.shape[-1], max_seqlen_k, row_stride, float(softmax_scale), int(bool(causal)),
                       ws.data_ptr(), ws_bytes, _stream(q.device))
         return buf[:, :, :max_seqlen_k]
     with torch.cuda.device(q.device):
@@ -133,7 +149,7 @@ def infllmv2_attn_stage1(
                   lse_keys.data_ptr() if lse_keys is not None else None, buf.data_ptr(),
                   cu_seqlens_q.contiguous().data_ptr(), cu_seqlens_k.contiguous().data_ptr(),
                   cu_seqlens_v.contiguous().data_ptr() if lse_keys is not None else None,
-                  lse_keys.shape[0] if lse_keys is not None else 0, batch,
+                  lse_keys.shape[0] if lse_keys is not None else 0, used_ptr, used_v_ptr, batch,
                   total_q, k.shape[0], nheads, nheads_k, q.shape[-1], max_seqlen_q, max_seqlen_k,
                   row_stride, float(softmax_scale), int(bool(causal)),
                   _status_words(q.device).data_ptr(), _stream(q.device))
@@ -144,7 +160,7 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
                                  local_blocks, init_blocks, cache_len=0, cache_lens=None,
                                  max_cache_len=None, softmax_scale=None, causal=True,
                                  block_size=64, stride=16, return_scores=False,
-                                 lse_keys=None, cu_seqlens_v=None):
+                                 lse_keys=None, cu_seqlens_v=None, seqused_k=None, seqused_v=None):
     """Stage 1 and the 64-token max-pool in one kernel (an addition to the reference API).
 
     Returns block scores (nheads_k, total_q, ceil((max_seqlen_q + cache) / 64)) bf16 equal, bit
@@ -153,7 +169,7 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
     (then the result is (block_scores, scores)).  cache_lens: optional per-sequence int32 tensor
     (pass max_cache_len to avoid a device->host read); otherwise the scalar cache_len applies.
     lse_keys / cu_seqlens_v: optional coarser compressed keys for the log-sum-exp (the `v` of
-    infllmv2_attn_stage1).
+    infllmv2_attn_stage1).  seqused_k / seqused_v: as in infllmv2_attn_stage1.
     """
     _check_common(q, k, 0.0, (-1, -1), 0.0, None, None, "infllmv2_stage1_block_scores")
     if lse_keys is not None:
@@ -187,6 +203,8 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
                   cu_seqlens_q.contiguous().data_ptr(), cu_seqlens_k.contiguous().data_ptr(),
                   cu_seqlens_v.contiguous().data_ptr() if lse_keys is not None else None,
                   lse_keys.shape[0] if lse_keys is not None else 0,
+                  seqused_k.contiguous().data_ptr() if seqused_k is not None else None,
+                  seqused_v.contiguous().data_ptr() if (seqused_v is not None and lse_keys is not None) else None,
                   cache_lens.data_ptr() if cache_lens is not None else None, batch, total_q,
                   k.shape[0], nheads, nheads_k, q.shape[-1], max_seqlen_q, max_seqlen_k, row_stride,
                   n_blocks, int(cache_len), int(local_blocks), int(init_blocks), float(softmax_scale),

@@ -51,6 +51,8 @@ struct Stage1Params {
   const int32_t* cu_q;
   const int32_t* cu_k;
   const int32_t* cu_v;            // keys of the row sums (pass 1); null = the keys of pass 2
+  const int32_t* seqused_k;       // keys in use per sequence (<= its cu_k extent), may be null
+  const int32_t* seqused_v;       // the same for the row-sum keys (needs cu_v), may be null
   const int32_t* cache_lens;      // per sequence, may be null
   int64_t total_q;
   int heads_q, heads_k;
@@ -113,7 +115,8 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.y, h = blockIdx.z;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], lc = p.cu_k[b + 1] - k0;
+  const int k0 = p.cu_k[b];
+  const int lc = p.seqused_k ? max(0, min(p.seqused_k[b], p.cu_k[b + 1] - k0)) : p.cu_k[b + 1] - k0;
   const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTokPerTile;   // long tiles first
   if (tok0 >= lq) return;
   // an earlier CTA gave up on a wait: the launch is already failed, do not pile up more waits
@@ -124,7 +127,8 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   // coarser compression (kernel 128 / stride 64) whose log-sum-exp then normalises the scores of
   // pass 2 -- the reference switches on the key counts (flash_fwd_kernel.h:1236-1240)
   const int v0 = p.cu_v ? p.cu_v[b] : k0;
-  const int lcv = p.cu_v ? p.cu_v[b + 1] - v0 : lc;
+  const int lcv = !p.cu_v ? lc
+                  : p.seqused_v ? max(0, min(p.seqused_v[b], p.cu_v[b + 1] - v0)) : p.cu_v[b + 1] - v0;
   const int st1 = (lcv == lc) ? 16 : 64;
   const int lim_max1 = visible_limit(tok0 + ntok - 1, lq, lcv, p.causal, st1);
   // (read through a warp broadcast: it tells the compiler that the value is warp-uniform, so the
@@ -462,8 +466,8 @@ namespace {
 
 int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void* pooled,
                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                  const int32_t* cu_seqlens_v, int64_t total_v,
-                  const int32_t* cache_lens, int batch, int64_t total_q, int64_t total_c,
+                  const int32_t* cu_seqlens_v, int64_t total_v, const int32_t* seqused_k,
+                  const int32_t* seqused_v, const int32_t* cache_lens, int batch, int64_t total_q, int64_t total_c,
                   int heads_q, int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
                   int64_t out_row_stride, int pooled_len, int cache_len, int local_blocks,
                   int init_blocks, float softmax_scale, int causal, int32_t* status, void* stream,
@@ -498,6 +502,8 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
   // separate row-sum keys are announced by their cu_seqlens; the tensor itself may be empty
   IFV2_REQUIRE(cu_seqlens_v != nullptr || kv == nullptr, IFV2_ERR_INVALID_ARG,
                "%s: row-sum keys need their cu_seqlens", what);
+  IFV2_REQUIRE(seqused_v == nullptr || cu_seqlens_v != nullptr, IFV2_ERR_INVALID_ARG,
+               "%s: seqused_v needs cu_seqlens_v", what);
   IFV2_REQUIRE(cu_seqlens_v == nullptr || (total_v >= 0 && total_v <= INT32_MAX && (kv || total_v == 0)),
                IFV2_ERR_INVALID_ARG, "%s: bad row-sum keys", what);
   CUtensorMap map_q, map_kc, map_kv;
@@ -521,6 +527,8 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
   p.cu_v = cu_seqlens_v;
+  p.seqused_k = seqused_k;
+  p.seqused_v = seqused_v;
   p.cache_lens = cache_lens;
   p.total_q = total_q;
   p.heads_q = heads_q;
@@ -560,14 +568,16 @@ using namespace ifv2;
 
 extern "C" int ifv2_stage1_scores(const void* q, const void* kc, const void* lse_keys, void* out,
                                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                  const int32_t* cu_seqlens_v, int64_t total_v, int batch, int64_t total_q, int64_t total_c, int heads_q,
-                                  int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                  const int32_t* cu_seqlens_v, int64_t total_v,
+                                  const int32_t* seqused_k, const int32_t* seqused_v, int batch,
+                                  int64_t total_q, int64_t total_c, int heads_q, int heads_k, int head_dim,
+                                  int max_seqlen_q, int max_seqlen_k,
                                   int64_t out_row_stride, float softmax_scale, int causal,
                                   int32_t* status, void* stream) {
   IFV2_REQUIRE(out != nullptr || total_q == 0 || max_seqlen_k == 0 || max_seqlen_q == 0,
                IFV2_ERR_INVALID_ARG, "stage1_scores: null pointer");
   return launch_stage1(q, kc, lse_keys, out, nullptr, cu_seqlens_q, cu_seqlens_k, cu_seqlens_v,
-                       total_v, nullptr, batch, total_q,
+                       total_v, seqused_k, seqused_v, nullptr, batch, total_q,
                        total_c, heads_q, heads_k, head_dim, max_seqlen_q, max_seqlen_k,
                        out_row_stride, 0, 0, 0, 0, softmax_scale, causal, status, stream,
                        "stage1_scores");
@@ -577,8 +587,8 @@ extern "C" int ifv2_stage1_block_scores(const void* q, const void* kc, const voi
                                         void* scores_or_null, void* block_scores,
                                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                                         const int32_t* cu_seqlens_v, int64_t total_v,
-                                        const int32_t* cache_lens,
-                                        int batch, int64_t total_q, int64_t total_c, int heads_q,
+                                        const int32_t* seqused_k, const int32_t* seqused_v,
+                                        const int32_t* cache_lens, int batch, int64_t total_q, int64_t total_c, int heads_q,
                                         int heads_k, int head_dim, int max_seqlen_q,
                                         int max_seqlen_k, int64_t scores_row_stride, int n_blocks,
                                         int cache_len, int local_blocks, int init_blocks,
@@ -587,7 +597,7 @@ extern "C" int ifv2_stage1_block_scores(const void* q, const void* kc, const voi
   IFV2_REQUIRE(block_scores != nullptr || total_q == 0 || max_seqlen_q == 0, IFV2_ERR_INVALID_ARG,
                "stage1_block_scores: null block_scores");
   return launch_stage1(q, kc, lse_keys, scores_or_null, block_scores, cu_seqlens_q, cu_seqlens_k,
-                       cu_seqlens_v, total_v, cache_lens,
+                       cu_seqlens_v, total_v, seqused_k, seqused_v, cache_lens,
                        batch, total_q, total_c, heads_q, heads_k, head_dim, max_seqlen_q,
                        max_seqlen_k, scores_row_stride, n_blocks, cache_len, local_blocks,
                        init_blocks, softmax_scale, causal, status, stream, "stage1_block_scores");

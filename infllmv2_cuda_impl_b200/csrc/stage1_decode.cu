@@ -31,6 +31,7 @@ struct DecodeS1Params {
   const __nv_bfloat16* kc;       // (total_c, heads_k, 128)
   __nv_bfloat16* out;            // (heads_k, batch, row_stride)
   const int32_t* cu_k;           // (batch + 1)
+  const int32_t* seqused_k;      // (batch) keys in use per sequence, or null = all of cu_k's extent
   float2* stats;                 // (batch, heads_k, chunks, 16): (max in log2 units, sum of e)
   __nv_bfloat16* e;              // (batch, heads_k, 16, e_stride): exp2(score - chunk max)
   int64_t e_stride;              // chunks * 512
@@ -38,6 +39,11 @@ struct DecodeS1Params {
   int64_t row_stride;
   float scale_log2;
 };
+
+__device__ __forceinline__ int used_keys(const DecodeS1Params& p, int b) {
+  const int extent = p.cu_k[b + 1] - p.cu_k[b];
+  return p.seqused_k ? max(0, min(p.seqused_k[b], extent)) : extent;
+}
 
 // keys visible to the single query token (same rule as the general kernel with Lq = 1)
 __device__ __forceinline__ int decode_limit(int lc, int causal) {
@@ -98,7 +104,7 @@ __global__ void __launch_bounds__(kThreads) stage1_decode_scores_kernel(const De
   const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int k0 = p.cu_k[b], lc = p.cu_k[b + 1] - k0;
+  const int k0 = p.cu_k[b], lc = used_keys(p, b);
   const int lim = decode_limit(lc, p.causal);
   const int c0 = chunk * kChunk;                   // first key of this CTA
   const int64_t pair = (int64_t)b * p.heads_k + h;
@@ -199,7 +205,7 @@ __global__ void __launch_bounds__(kThreads) stage1_decode_scores_kernel(const De
 __global__ void __launch_bounds__(kThreads) stage1_decode_normalise_kernel(const DecodeS1Params p) {
   __shared__ float weight[16];
   const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int lc = p.cu_k[b + 1] - p.cu_k[b];
+  const int lc = used_keys(p, b);
   const int lim = decode_limit(lc, p.causal);
   const int c0 = chunk * kChunk;
   const int64_t pair = (int64_t)b * p.heads_k + h;
@@ -256,7 +262,8 @@ extern "C" int64_t ifv2_stage1_decode_workspace_bytes(int batch, int heads_k, in
 }
 
 extern "C" int ifv2_stage1_decode_scores(const void* q, const void* kc, void* out,
-                                         const int32_t* cu_seqlens_k, int batch, int64_t total_c,
+                                         const int32_t* cu_seqlens_k, const int32_t* seqused_k,
+                                         int batch, int64_t total_c,
                                          int heads_q, int heads_k, int head_dim, int max_seqlen_k,
                                          int64_t out_row_stride, float softmax_scale, int causal,
                                          void* workspace, int64_t workspace_bytes, void* stream) {
@@ -283,6 +290,7 @@ extern "C" int ifv2_stage1_decode_scores(const void* q, const void* kc, void* ou
   p.kc = static_cast<const __nv_bfloat16*>(kc);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.cu_k = cu_seqlens_k;
+  p.seqused_k = seqused_k;
   p.stats = static_cast<float2*>(workspace);
   const int64_t n_chunks = (max_seqlen_k + kChunk - 1) / kChunk;
   const int64_t stats_bytes = (((int64_t)batch * heads_k * n_chunks * 16 * (int64_t)sizeof(float2)) + 255) / 256 * 256;

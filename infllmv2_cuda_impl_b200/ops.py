@@ -280,3 +280,59 @@ def compress_keys_append(k_cache: torch.Tensor, cache_seqlens: torch.Tensor, kc_
         _lib.call("ifv2_compress_keys_append", k_cache.data_ptr(), kc_cache.data_ptr(),
                   cache_seqlens.contiguous().data_ptr(), b, cap, kc_cache.shape[1], hk, d,
                   kernel_size, kernel_stride, _stream(k_cache.device))
+
+
+def cache_fill(src: torch.Tensor, cache: torch.Tensor, cu_seqlens: torch.Tensor,
+               seqlens_out: Optional[torch.Tensor] = None) -> None:
+    """Copy the packed rows of every sequence (src: (total, Hk, 128) bf16, cu_seqlens (B+1) int32)
+    to rows [0, len_b) of its slot of cache (B, capacity, Hk, 128), in place; rows past the
+    capacity are dropped.  seqlens_out (B,) int32, optional: min(len_b, capacity)."""
+    _require_cuda(src, "src")
+    _require_cuda(cache, "cache")
+    if (src.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or src.dim() != 3 or cache.dim() != 4
+            or not cache.is_contiguous() or cache.shape[2:] != src.shape[1:]):
+        raise ValueError("cache_fill: src (total, heads_k, 128) and contiguous cache (batch, capacity, heads_k, 128), bf16")
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() == cache.shape[0] + 1
+    if seqlens_out is not None:
+        assert seqlens_out.dtype == torch.int32 and seqlens_out.is_contiguous() and seqlens_out.numel() == cache.shape[0]
+    src = src.contiguous()
+    with torch.cuda.device(src.device):
+        _lib.call("ifv2_cache_fill", src.data_ptr(), cache.data_ptr(), cu_seqlens.contiguous().data_ptr(),
+                  seqlens_out.data_ptr() if seqlens_out is not None else None, cache.shape[0],
+                  src.shape[0], cache.shape[1], cache.shape[2], cache.shape[3], _stream(src.device))
+
+
+def decode_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  cache_seqlens: torch.Tensor, new_seqlens: torch.Tensor,
+                  kc_cache: Optional[torch.Tensor] = None, n_comp: Optional[torch.Tensor] = None,
+                  kernel_size: int = 32, kernel_stride: int = 16,
+                  kc2_cache: Optional[torch.Tensor] = None, n_comp2: Optional[torch.Tensor] = None,
+                  kernel2_size: int = 128, kernel2_stride: int = 64) -> None:
+    """One decode step of cache bookkeeping, one launch, all in place: k_new / v_new (B, Hk, 128)
+    are written at position cache_seqlens[b] of k_cache / v_cache (B, capacity, Hk, 128); a
+    sequence whose new length completes a compression window gets that window's mean in kc_cache
+    (B, c_capacity, Hk, 128) (and kc2_cache for the second compression); new_seqlens (B,) int32
+    receives the new lengths (a different tensor than cache_seqlens), n_comp / n_comp2 the number
+    of valid compressed keys -- the `seqused_k` of the stage-1 scorer.  A sequence whose cache is
+    full is left as it is."""
+    for name, t in (("k_new", k_new), ("v_new", v_new), ("k_cache", k_cache), ("v_cache", v_cache)):
+        _require_cuda(t, name)
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError(f"decode_append: {name} must be contiguous bf16")
+    b, cap, hk, d = k_cache.shape
+    if v_cache.shape != k_cache.shape or k_new.numel() != b * hk * d or v_new.numel() != b * hk * d:
+        raise ValueError("decode_append: shapes of the new rows and the caches do not match")
+    for t in (cache_seqlens, new_seqlens, n_comp, n_comp2):
+        assert t is None or (t.dtype == torch.int32 and t.is_contiguous() and t.numel() == b)
+    for c in (kc_cache, kc2_cache):
+        if c is not None and (c.dtype != torch.bfloat16 or not c.is_contiguous() or c.dim() != 4
+                              or c.shape[0] != b or c.shape[2:] != k_cache.shape[2:]):
+            raise ValueError("decode_append: a compressed cache must be contiguous (batch, c_capacity, heads_k, 128) bf16")
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    with torch.cuda.device(k_cache.device):
+        _lib.call("ifv2_decode_append", k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(),
+                  v_cache.data_ptr(), ptr(kc_cache), ptr(kc2_cache), cache_seqlens.data_ptr(),
+                  new_seqlens.data_ptr(), ptr(n_comp), ptr(n_comp2), b, cap,
+                  kc_cache.shape[1] if kc_cache is not None else 0,
+                  kc2_cache.shape[1] if kc2_cache is not None else 0, hk, d, kernel_size, kernel_stride,
+                  kernel2_size, kernel2_stride, _stream(k_cache.device))

@@ -1,0 +1,178 @@
+"""Caller-side glue for the hot path: what a model's attention layer does around the operators.
+
+The reference ships operators only; the layer that strings them together lives in the model code
+that imports `infllm_v2` (the calls it makes are the ones the reference's tests replay:
+tests/test_stage1_compressed_lse.py:57-99 for the compression, tests/test_infllmv2.py for stage 2,
+tests/test_kvcache_simple.py for decode).  This module is that layer, for callers that do not
+bring their own:
+
+    prefill / training   compress keys -> stage-1 block scores -> top-k -> block-sparse attention
+                         (selection runs without gradients; attention is differentiable), and
+                         optionally fills a DecodeCache
+    decode               one launch appends the new key / value and updates the compressed keys,
+                         then stage-1 scores over the cache in place (`seqused_k`), max-pool,
+                         top-k and sparse attention over the selected blocks
+
+Short sequences (<= dense_len tokens) attend densely, as the selection cannot drop anything
+useful there.  Everything stays on the caller's stream; the only host <-> device traffic is the
+optional read of the total number of compressed keys when the caller does not pass the lengths.
+"""
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import ops
+from .attention import (infllmv2_attn_stage1, infllmv2_attn_varlen_func, infllmv2_attn_with_kvcache,
+                        infllmv2_stage1_block_scores, GROUP, HEAD_DIM)
+
+__all__ = ["SparseConfig", "DecodeCache", "SparseAttention"]
+
+
+@dataclass
+class SparseConfig:
+    topk: int = 64                 # blocks kept per (token, KV head), forced ones included
+    init_blocks: int = 1           # leading blocks always kept
+    local_blocks: int = 32         # blocks bq-local_blocks .. bq always kept (a 2048-token window)
+    block_size: int = 64
+    kernel_size: int = 32          # key compression of the scorer
+    kernel_stride: int = 16
+    coarse_lse: bool = False       # row sums over a second compression (the "compressed LSE" mode)
+    coarse_kernel_size: int = 128
+    coarse_kernel_stride: int = 64
+    dense_len: int = 8192          # at most this many tokens -> dense attention
+
+    def windows(self, length: int, coarse: bool = False) -> int:
+        k, s = ((self.coarse_kernel_size, self.coarse_kernel_stride) if coarse
+                else (self.kernel_size, self.kernel_stride))
+        return (length - k) // s + 1 if length >= k else 0
+
+
+class DecodeCache:
+    """Per-sequence caches of keys, values and compressed keys at a fixed capacity, plus the
+    small integer tensors a decode step needs (all device-resident; `max_len` is the only host
+    copy of the lengths and is an upper bound)."""
+
+    def __init__(self, batch: int, capacity: int, heads_k: int, config: SparseConfig, device="cuda"):
+        dev = torch.device(device)
+        self.config, self.batch, self.capacity, self.heads_k = config, batch, capacity, heads_k
+        shape = (batch, capacity, heads_k, HEAD_DIM)
+        self.k = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+        self.v = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+        self.c_capacity = max(config.windows(capacity), 1)
+        self.kc = torch.zeros(batch, self.c_capacity, heads_k, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        self.kc2 = self.n_comp2 = self.cu_c2 = None
+        self.c2_capacity = 0
+        if config.coarse_lse:
+            self.c2_capacity = max(config.windows(capacity, coarse=True), 1)
+            self.kc2 = torch.zeros(batch, self.c2_capacity, heads_k, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+            self.n_comp2 = torch.zeros(batch, dtype=torch.int32, device=dev)
+            self.cu_c2 = torch.arange(batch + 1, dtype=torch.int32, device=dev) * self.c2_capacity
+        self.seqlens = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self._spare = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.n_comp = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.cu_q = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+        self.cu_c = self.cu_q * self.c_capacity
+        self.max_len = 0
+
+    def fill(self, k, v, kc, cu_seqlens, cu_seqlens_c, max_seqlen, kc2=None, cu_seqlens_c2=None):
+        """Load the caches from packed prefill tensors (rows past the capacity are dropped)."""
+        ops.cache_fill(k, self.k, cu_seqlens, self.seqlens)
+        ops.cache_fill(v, self.v, cu_seqlens)
+        ops.cache_fill(kc, self.kc, cu_seqlens_c, self.n_comp)
+        if self.kc2 is not None:
+            ops.cache_fill(kc2, self.kc2, cu_seqlens_c2, self.n_comp2)
+        self.max_len = min(int(max_seqlen), self.capacity)
+
+
+class SparseAttention:
+    """Prefill / training and decode on top of the operators, for 16 query heads per KV head
+    and head dimension 128 (the reference build's only configuration)."""
+
+    def __init__(self, config: Optional[SparseConfig] = None):
+        self.config = config or SparseConfig()
+        if self.config.block_size != 64 or self.config.kernel_stride != 16:
+            raise NotImplementedError("block_size 64 over compression stride 16 only, as in the reference")
+
+    # ------------------------------------------------------------------ selection (no gradients)
+    @torch.no_grad()
+    def compress(self, k, cu_seqlens, seqlens: Optional[Sequence[int]] = None, coarse: bool = False):
+        """Compressed keys of packed sequences; `seqlens` (host ints) avoids a device read."""
+        c = self.config
+        ks, st = ((c.coarse_kernel_size, c.coarse_kernel_stride) if coarse else (c.kernel_size, c.kernel_stride))
+        total_c = sum(c.windows(int(l), coarse) for l in seqlens) if seqlens is not None else None
+        return ops.compress_keys(k, cu_seqlens, ks, st, total_c=total_c)
+
+    @torch.no_grad()
+    def select(self, q, kc, cu_seqlens_q, cu_seqlens_c, max_seqlen_q, max_c, kc2=None,
+               cu_seqlens_c2=None, cache_len: int = 0):
+        """Block selection of packed sequences: int32 (Hk, total_q, topk), ascending, -1 padded."""
+        c = self.config
+        pooled = infllmv2_stage1_block_scores(q, kc, cu_seqlens_q, cu_seqlens_c, max_seqlen_q, max_c,
+                                              c.local_blocks, c.init_blocks, cache_len=cache_len,
+                                              lse_keys=kc2, cu_seqlens_v=cu_seqlens_c2)
+        return ops.infllmv2_topk(pooled, c.topk, cache_len=cache_len, cu_seqlens_q=cu_seqlens_q)
+
+    # ------------------------------------------------------------------ prefill / training
+    def prefill(self, q, k, v, cu_seqlens, max_seqlen: int, seqlens: Optional[Sequence[int]] = None,
+                cache: Optional[DecodeCache] = None, softmax_scale: Optional[float] = None):
+        """Causal self-attention over packed sequences: q (total, Hq, 128), k / v (total, Hk, 128)
+        bf16, cu_seqlens (B+1) int32.  Differentiable in q, k, v through the attention itself; the
+        selection sees detached tensors.  With `cache`, the keys, values and compressed keys are
+        also stored for decoding."""
+        c = self.config
+        max_c = c.windows(max_seqlen)
+        need_comp = cache is not None or (max_seqlen > c.dense_len and max_c > 0)
+        kc = cu_c = kc2 = cu_c2 = None
+        if need_comp:
+            kc, cu_c = self.compress(k.detach(), cu_seqlens, seqlens)
+            if c.coarse_lse:
+                kc2, cu_c2 = self.compress(k.detach(), cu_seqlens, seqlens, coarse=True)
+        idx = None
+        if max_seqlen > c.dense_len and max_c > 0:
+            idx = self.select(q.detach(), kc, cu_seqlens, cu_c, max_seqlen, max_c, kc2, cu_c2)
+        out = infllmv2_attn_varlen_func(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen,
+                                        softmax_scale=softmax_scale, causal=True, topk_idx=idx)
+        if cache is not None:
+            cache.fill(k.detach(), v.detach(), kc, cu_seqlens, cu_c, max_seqlen, kc2, cu_c2)
+        return out
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def decode(self, q, k_new, v_new, cache: DecodeCache, softmax_scale: Optional[float] = None):
+        """One token per sequence: q (B, Hq, 128) or (B, 1, Hq, 128); k_new / v_new (B, Hk, 128)
+        or (B, 1, Hk, 128).  Appends to the cache, then attends over it (the new token included).
+        Returns (B, 1, Hq, 128)."""
+        c = self.config
+        b, hk = cache.batch, cache.heads_k
+        if cache.max_len >= cache.capacity:
+            raise RuntimeError("DecodeCache is full")
+        q3 = q.reshape(b, hk * GROUP, HEAD_DIM)
+        ops.decode_append(k_new.reshape(b, hk, HEAD_DIM).contiguous(), v_new.reshape(b, hk, HEAD_DIM).contiguous(),
+                          cache.k, cache.v, cache.seqlens, cache._spare, cache.kc, cache.n_comp,
+                          c.kernel_size, c.kernel_stride, cache.kc2, cache.n_comp2,
+                          c.coarse_kernel_size, c.coarse_kernel_stride)
+        before = cache.seqlens                       # the query's position in its sequence
+        cache.seqlens, cache._spare = cache._spare, before
+        cache.max_len += 1
+        max_c = c.windows(cache.max_len)
+        idx = None
+        if cache.max_len > c.dense_len and max_c > 0:
+            kc_flat = cache.kc.view(-1, hk, HEAD_DIM)
+            if cache.kc2 is not None:
+                score = infllmv2_attn_stage1(q3, kc_flat, cache.kc2.view(-1, hk, HEAD_DIM), cache.cu_q, cache.cu_c,
+                                             cache.cu_c2, 1, max_c, causal=False, seqused_k=cache.n_comp,
+                                             seqused_v=cache.n_comp2)
+            else:
+                score = infllmv2_attn_stage1(q3, kc_flat, kc_flat, cache.cu_q, cache.cu_c, cache.cu_c, 1, max_c,
+                                             causal=False, seqused_k=cache.n_comp)
+            # columns past a sequence's compressed keys hold 0, which never outranks a real block
+            # (ties go to the lower index) and only ever comes out as -1
+            pooled = ops.max_pooling_1d_varlen(score, cache.cu_q, cache.cu_c, before, 1, max_c,
+                                               c.local_blocks, c.init_blocks,
+                                               max_cache_len=cache.max_len - 1)
+            idx = ops.infllmv2_topk(pooled, c.topk, cu_seqlens_q=cache.cu_q, cache_lens=before)
+            idx = idx.permute(1, 0, 2).unsqueeze(2)                    # (B, Hk, 1, topk)
+        return infllmv2_attn_with_kvcache(q3.view(b, 1, hk * GROUP, HEAD_DIM), cache.k, cache.v,
+                                          cache_seqlens=cache.seqlens, softmax_scale=softmax_scale,
+                                          topk_idx=idx)

@@ -28,8 +28,8 @@ def test_version_and_error_text(lib):
     ("ifv2_uint64_to_bool", (8, 8, 4, 200, 2, None), -1),                    # last_dim > 64*words
     ("ifv2_max_pooling_1d", (8, 8, 1, 2, 4, 16, 8, 1, 0, 5, 4, 1, 64, 1, 1, None), -1),  # stride < k_len
     ("ifv2_topk_select", (8, 8, 1, 2, 4, 9000, 9000, 64, None, None, 1, 0, 64, None), -3),  # too many blocks
-    ("ifv2_stage1_scores", (8, 8, None, 8, 8, 8, None, 0, 1, 4, 4, 32, 2, 64, 4, 4, 8, 0.1, 1, 8, None), -2),  # d != 128
-    ("ifv2_stage1_scores", (8, 8, None, 8, 8, 8, None, 0, 1, 4, 4, 24, 2, 128, 4, 4, 8, 0.1, 1, 8, None), -2),  # group != 16
+    ("ifv2_stage1_scores", (8, 8, None, 8, 8, 8, None, 0, None, None, 1, 4, 4, 32, 2, 64, 4, 4, 8, 0.1, 1, 8, None), -2),  # d != 128
+    ("ifv2_stage1_scores", (8, 8, None, 8, 8, 8, None, 0, None, None, 1, 4, 4, 24, 2, 128, 4, 4, 8, 0.1, 1, 8, None), -2),  # group != 16
     ("ifv2_sparse_attn_fwd", (8, 8, 8, 8, 8, None, 0, 8, 8, 1, 4, 4, 32, 2, 96, 4, 4, 0.1, 1, 8, None), -2),
     ("ifv2_sparse_attn_fwd", (8, 8, 8, 8, 8, 8, 999, 8, 8, 1, 4, 4, 32, 2, 128, 4, 4, 0.1, 1, 8, None), -1),
 ])

@@ -1,0 +1,150 @@
+"""GPU: the caller-side layer (compress -> stage 1 -> pool -> top-k -> attention, cache fill,
+decode step) against the oracle composed the same way, and decode against prefill."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import infllm_v2
+from helpers import det_tensor, cu, err_stats
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+HQ, HK, D = 32, 2, 128
+
+
+def _config(**kw):
+    base = dict(topk=4, init_blocks=1, local_blocks=1, dense_len=0)
+    base.update(kw)
+    return infllm_v2.SparseConfig(**base)
+
+
+def _oracle_selection(q, k, lens, cfg, last_only=False):
+    """Selection by the oracle, stage by stage.  Returns (idx, pooled)."""
+    kc, cu_c = oracle.compress_keys(k, cu(lens), cfg.kernel_size, cfg.kernel_stride)
+    kw = {}
+    if cfg.coarse_lse:
+        kv, cu_v = oracle.compress_keys(k, cu(lens), cfg.coarse_kernel_size, cfg.coarse_kernel_stride)
+        kw = dict(lse_keys=kv, cu_seqlens_v=cu_v)
+    max_k = int(np.diff(cu_c).max())
+    s = oracle.stage1_scores(q, kc, cu(lens).tolist(), cu_c, max_k, True, **kw).to(torch.bfloat16)
+    pooled = oracle.max_pooling_1d_varlen(s, cu(lens).tolist(), cu_c, [0] * len(lens), max(lens), max_k,
+                                          cfg.local_blocks, cfg.init_blocks)
+    qb = torch.cat([torch.arange(l) // 64 for l in lens])
+    return oracle.topk_select(pooled.float(), cfg.topk, qb), pooled
+
+
+def test_cache_fill_and_append_match_recompression():
+    """cache_fill places packed rows; 70 decode_append steps keep keys, values and both compressed
+    caches equal to compressing the grown sequences from scratch."""
+    lens, cap = [100, 31, 257], 400
+    cfg = _config(coarse_lse=True)
+    g = torch.Generator().manual_seed(5)
+    steps = 70
+    k_all = [(torch.randn(l + steps, HK, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    v_all = [torch.randn(l + steps, HK, D, generator=g).to(torch.bfloat16) for l in lens]
+    cache = infllm_v2.DecodeCache(len(lens), cap, HK, cfg, DEV)
+    k0 = torch.cat([k[:l] for k, l in zip(k_all, lens)])
+    v0 = torch.cat([v[:l] for v, l in zip(v_all, lens)])
+    kc0, cu_c = oracle.compress_keys(k0, cu(lens), 32, 16)
+    kv0, cu_v = oracle.compress_keys(k0, cu(lens), 128, 64)
+    cache.fill(k0.to(DEV), v0.to(DEV), kc0.to(DEV), cu(lens, DEV), torch.tensor(cu_c, dtype=torch.int32, device=DEV),
+               max(lens), kv0.to(DEV), torch.tensor(cu_v, dtype=torch.int32, device=DEV))
+    assert cache.seqlens.tolist() == lens
+    assert cache.n_comp.tolist() == list(np.diff(cu_c)) and cache.n_comp2.tolist() == list(np.diff(cu_v))
+    for b, l in enumerate(lens):
+        assert torch.equal(cache.k[b, :l].cpu(), k_all[b][:l]) and torch.equal(cache.v[b, :l].cpu(), v_all[b][:l])
+    for s in range(steps):
+        kn = torch.stack([k[l + s] for k, l in zip(k_all, lens)]).to(DEV)
+        vn = torch.stack([v[l + s] for v, l in zip(v_all, lens)]).to(DEV)
+        infllm_v2.decode_append(kn, vn, cache.k, cache.v, cache.seqlens, cache._spare, cache.kc, cache.n_comp,
+                                32, 16, cache.kc2, cache.n_comp2, 128, 64)
+        cache.seqlens, cache._spare = cache._spare, cache.seqlens
+    torch.cuda.synchronize()
+    assert cache.seqlens.tolist() == [l + steps for l in lens]
+    for b, l in enumerate(lens):
+        n = l + steps
+        assert torch.equal(cache.k[b, :n].cpu(), k_all[b]) and torch.equal(cache.v[b, :n].cpu(), v_all[b])
+        for kc_cache, count, (ks, st) in ((cache.kc, cache.n_comp, (32, 16)), (cache.kc2, cache.n_comp2, (128, 64))):
+            ref, _ = oracle.compress_keys(k_all[b], [0, n], ks, st)
+            assert int(count[b]) == ref.shape[0]
+            if ref.shape[0] == 0:
+                continue
+            got = kc_cache[b, :ref.shape[0]].cpu().float()
+            assert (got - ref.float()).abs().max().item() <= 2.0 ** -7      # one bf16 step: summation order
+
+
+@pytest.mark.parametrize("coarse", [False, True])
+def test_prefill_matches_composed_oracle(coarse):
+    lens = [700, 130, 1000]
+    cfg = _config(coarse_lse=coarse)
+    q = det_tensor((sum(lens), HQ, D), 11, 0.5)
+    k = det_tensor((sum(lens), HK, D), 12, 0.5)
+    v = det_tensor((sum(lens), HK, D), 13, 1.0)
+    layer = infllm_v2.SparseAttention(cfg)
+    cq = cu(lens, DEV)
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    out = layer.prefill(qd, kd, vd, cq, max(lens), seqlens=lens)
+    do = det_tensor((sum(lens), HQ, D), 14, 1.0)
+    out.backward(do.to(DEV))
+    infllm_v2.check_device_status()
+    # the layer's own selection, recomputed through its public pieces
+    kc, cu_c = layer.compress(kd.detach(), cq, lens)
+    kc2 = cu_c2 = None
+    if coarse:
+        kc2, cu_c2 = layer.compress(kd.detach(), cq, lens, coarse=True)
+    idx = layer.select(qd.detach(), kc, cq, cu_c, max(lens), cfg.windows(max(lens)), kc2, cu_c2).cpu()
+    exp_idx, _ = _oracle_selection(q, k, lens, cfg)
+    same = (idx == exp_idx).all(-1).float().mean().item()
+    assert same > 0.97, same                   # bf16 block scores that tie differently pick another block
+    ro, _, rdq, rdk, rdv = oracle.sparse_attention_fwd_bwd(q, k, v, do, cu(lens).tolist(), cu(lens).tolist(), idx)
+    for name, a, b in (("out", out, ro), ("dq", qd.grad, rdq), ("dk", kd.grad, rdk), ("dv", vd.grad, rdv)):
+        mx, mr = err_stats(a.detach().float().cpu(), b)
+        assert mx <= 2e-2 * max(1.0, b.abs().max().item()) and mr <= 1e-2, (name, mx, mr)
+
+
+def test_short_sequences_attend_densely():
+    lens = [300, 64]
+    layer = infllm_v2.SparseAttention(_config(dense_len=512))
+    q = det_tensor((sum(lens), HQ, D), 21, 0.5)
+    k = det_tensor((sum(lens), HK, D), 22, 0.5)
+    v = det_tensor((sum(lens), HK, D), 23, 1.0)
+    out = layer.prefill(q.to(DEV), k.to(DEV), v.to(DEV), cu(lens, DEV), max(lens), seqlens=lens)
+    ref, _ = oracle.sparse_attention_fwd(q, k, v, cu(lens).tolist(), cu(lens).tolist(), None)
+    mx, mr = err_stats(out.float().cpu(), ref)
+    assert mx <= 2e-2 and mr <= 1e-2
+
+
+@pytest.mark.parametrize("coarse", [False, True])
+def test_decode_continues_prefill(coarse):
+    """Prefill L tokens into a cache, decode 40 more one at a time: every decoded token equals the
+    last row of a prefill over the sequence grown by that token (same selection rule, same
+    attention), and the decode selection equals the oracle's for that row."""
+    lens, cap, steps = [200, 460, 150], 512, 40
+    cfg = _config(coarse_lse=coarse, topk=5)
+    layer = infllm_v2.SparseAttention(cfg)
+    g = torch.Generator().manual_seed(9)
+    qs = [(torch.randn(l + steps, HQ, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    ks = [(torch.randn(l + steps, HK, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    vs = [torch.randn(l + steps, HK, D, generator=g).to(torch.bfloat16) for l in lens]
+    pack = lambda ts, n: torch.cat([t[:l + n] for t, l in zip(ts, lens)])
+    cache = infllm_v2.DecodeCache(len(lens), cap, HK, cfg, DEV)
+    layer.prefill(pack(qs, 0).to(DEV), pack(ks, 0).to(DEV), pack(vs, 0).to(DEV), cu(lens, DEV), max(lens),
+                  seqlens=lens, cache=cache)
+    agree = []
+    for s in range(steps):
+        qn = torch.stack([q[l + s] for q, l in zip(qs, lens)]).to(DEV)
+        kn = torch.stack([k[l + s] for k, l in zip(ks, lens)]).to(DEV)
+        vn = torch.stack([v[l + s] for v, l in zip(vs, lens)]).to(DEV)
+        out = layer.decode(qn, kn, vn, cache)
+        if s % 13 and s != steps - 1:
+            continue
+        grown = [l + s + 1 for l in lens]
+        full = layer.prefill(pack(qs, s + 1).to(DEV), pack(ks, s + 1).to(DEV), pack(vs, s + 1).to(DEV),
+                             cu(grown, DEV), max(grown), seqlens=grown)
+        last = torch.tensor(np.cumsum(grown) - 1)
+        err = (out[:, 0].float().cpu() - full[last.to(DEV)].float().cpu()).abs().amax(-1)    # (B, Hq)
+        agree.append((err <= 2e-2).float().mean().item())
+    infllm_v2.check_device_status()
+    assert cache.seqlens.tolist() == [l + steps for l in lens]
+    assert np.mean(agree) > 0.9, agree          # a tie that flips selects another block for 16 heads
