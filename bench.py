@@ -613,6 +613,42 @@ def config5_decode(device, pk, small=False):
         "tokens_per_s": round(B / (best_full * 1e-3), 1),
         "note": "stage 1 (one token per sequence) + pool + top-k + sparse decode; algorithmic bytes = "
                 "compressed keys once (%d MB) + selected K/V" % (kc.numel() * 2 // 1000000)}
+
+    # ---- the same step through the caller-side layer: the new token's key / value are appended
+    # and the compressed-key cache is updated (one launch), the compressed keys are scored in place
+    # in their per-sequence cache (seqused_k), then pool, top-k and sparse attention
+    del kc
+    cfg = infllm_v2.SparseConfig(topk=TOPK, init_blocks=INIT_BLOCKS, local_blocks=LOCAL_BLOCKS, dense_len=0)
+    layer = infllm_v2.SparseAttention(cfg)
+    cache = infllm_v2.DecodeCache(B, 64, hk, cfg, device)          # small, then pointed at the big caches
+    cache.capacity, cache.k, cache.v = cap, kcache, vcache
+    cache.c_capacity = cfg.windows(cap)
+    cache.kc = (torch.randn(B, cache.c_capacity, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    cache.cu_c = cache.cu_q * cache.c_capacity
+    cache.seqlens.copy_(lens_d)
+    cache.n_comp.copy_(torch.tensor(n_c, dtype=torch.int32))
+    cache.max_len = hi
+    k_new = (torch.randn(B, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    v_new = (torch.randn(B, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    t_layer = _time_ms(lambda: layer.decode(q2, k_new, v_new, cache), reps=10, warmup=3)
+    infllm_v2.check_device_status()
+    t_layer_graph = None
+    try:
+        step = layer.capture_decode(cache)
+        t_layer_graph = _time_ms(lambda: step(q2, k_new, v_new), reps=20, warmup=3)
+        infllm_v2.check_device_status()
+    except Exception as e:
+        out["config5_layer_graph_error"] = repr(e)[:200]
+    best_layer = min(t_layer, t_layer_graph) if t_layer_graph else t_layer
+    out["config5_decode_b64_layer_step"] = {
+        "ms": round(best_layer, 4), "ms_eager": round(t_layer, 4),
+        "ms_cuda_graph": round(t_layer_graph, 4) if t_layer_graph else None,
+        "gbs": round(bytes_full / best_layer / 1e6, 1),
+        "frac": round(bytes_full / best_layer / 1e6 / pk["hbm_gbs"], 4),
+        "tokens_per_s": round(B / (best_layer * 1e-3), 1),
+        "note": "SparseAttention.decode: token append + compressed-key update + stage 1 over the "
+                "compressed cache in place + pool + top-k + sparse decode; the graph variant includes "
+                "the three input copies and is sized for the cache capacity"}
     return out
 
 

@@ -96,17 +96,19 @@ int ifv2_cache_fill(const void* src, void* cache, const int32_t* cu_seqlens, int
  * new length L completes a compression window (L >= kernel, (L - kernel) % stride == 0) gets the
  * mean of its last `kernel` keys written to kc_cache[b, (L - kernel)/stride] (and likewise to
  * kc2_cache with kernel2 / stride2: the coarse keys of the compressed-LSE mode); either compressed
- * cache may be null.  Outputs: new_seqlens[b] = L (must not alias cache_seqlens), n_comp[b] /
- * n_comp2[b] = compressed keys now valid (the seqused_k of the stage-1 scorer), may be null.  A
- * sequence whose cache is full is left untouched (new_seqlens[b] = cache_seqlens[b]).
+ * cache may be null.  cache_seqlens is updated IN PLACE to L; positions[b] (may be null, must not
+ * alias) receives the old length, i.e. the position of the new token -- the cache_lens of the
+ * pool and top-k kernels; n_comp[b] / n_comp2[b] (may be null) = compressed keys now valid, the
+ * seqused_k of the stage-1 scorer.  All pointers keep their values from step to step, so a decode
+ * step can be replayed from a CUDA graph.  A sequence whose cache is full is left untouched.
  * Stands in for the in-kernel append of mha_fwd_kvcache (csrc/flash_attn/flash_api.cpp:1549-1843,
  * knew / vnew) plus the caller-side recompression the reference has no kernel for. */
 int ifv2_decode_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
-                       void* kc_cache, void* kc2_cache, const int32_t* cache_seqlens,
-                       int32_t* new_seqlens, int32_t* n_comp, int32_t* n_comp2, int batch,
-                       int64_t capacity, int64_t c_capacity, int64_t c2_capacity, int heads_k,
-                       int head_dim, int kernel_size, int kernel_stride, int kernel2_size,
-                       int kernel2_stride, void* stream);
+                       void* kc_cache, void* kc2_cache, int32_t* cache_seqlens, int32_t* positions,
+                       int32_t* n_comp, int32_t* n_comp2, int batch, int64_t capacity,
+                       int64_t c_capacity, int64_t c2_capacity, int heads_k, int head_dim,
+                       int kernel_size, int kernel_stride, int kernel2_size, int kernel2_stride,
+                       void* stream);
 
 /* 1-D max-pool of stage-1 scores to block scores with +inf on the init and causal-local blocks.
  * in: (heads, q_len, k_len) with `in_row_stride` elements between rows (>= k_len);

@@ -74,11 +74,12 @@ struct AppendParams {
   uint4* v_cache;
   uint4* kc_cache;             // (batch, c_cap, heads, 128) or null
   uint4* kc2_cache;            // (batch, c2_cap, heads, 128) or null
-  const int32_t* seqlens;      // (batch) lengths BEFORE the append
-  int32_t* new_seqlens;        // (batch) lengths after it (may alias nothing else)
+  int32_t* seqlens;            // (batch) in: lengths before the append, out: after it
+  int32_t* positions;          // (batch) out: the lengths before the append, or null
   int32_t* n_comp;             // (batch) compressed keys after the append, or null
   int32_t* n_comp2;
   int batch, heads, kernel, stride, kernel2, stride2;
+  int seq_per_block;           // sequences owned by one CTA (all threads of a sequence share a CTA)
   int64_t cap, c_cap, c2_cap;
 };
 
@@ -99,19 +100,23 @@ __device__ __forceinline__ void write_window(const uint4* k_rows, uint4* dst, in
   *dst = mean_bf16x8(acc, (float)kernel);
 }
 
+// The lengths are updated in place: every thread that reads a sequence's length sits in the CTA
+// that later writes it, and a barrier separates the two.
 __global__ void __launch_bounds__(kThreads) decode_append_kernel(const AppendParams p) {
-  const int64_t row_vecs = (int64_t)p.heads * kVecPerRow;
-  const int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  if (idx >= (int64_t)p.batch * row_vecs) return;
-  const int b = (int)(idx / row_vecs);
-  const int64_t r = idx % row_vecs;
-  const int old_len = p.seqlens[b];
+  const int row_vecs = p.heads * kVecPerRow;
+  const int tps = kThreads / p.seq_per_block;            // threads per sequence
+  const int b = blockIdx.x * p.seq_per_block + (int)threadIdx.x / tps;
+  const int r0 = (int)threadIdx.x % tps;
+  const bool valid = (int)threadIdx.x / tps < p.seq_per_block && b < p.batch;
+  const int old_len = valid ? p.seqlens[b] : 0;
+  __syncthreads();
+  if (!valid) return;
   const bool room = old_len >= 0 && old_len < p.cap;      // a full cache is left untouched
   const int len = room ? old_len + 1 : old_len;
-  if (room) {
+  for (int r = r0; room && r < row_vecs; r += tps) {
     const int64_t at = ((int64_t)b * p.cap + old_len) * row_vecs + r;
-    p.k_cache[at] = __ldg(p.k_new + idx);
-    p.v_cache[at] = __ldg(p.v_new + idx);
+    p.k_cache[at] = __ldg(p.k_new + (int64_t)b * row_vecs + r);
+    p.v_cache[at] = __ldg(p.v_new + (int64_t)b * row_vecs + r);
     // plain loads below: the row just written by this thread is among them
     const uint4* k_rows = p.k_cache + (int64_t)b * p.cap * row_vecs + r;
     if (p.kc_cache != nullptr && len >= p.kernel && (len - p.kernel) % p.stride == 0) {
@@ -125,8 +130,9 @@ __global__ void __launch_bounds__(kThreads) decode_append_kernel(const AppendPar
         write_window(k_rows, p.kc2_cache + ((int64_t)b * p.c2_cap + j) * row_vecs + r, len, p.kernel2, row_vecs);
     }
   }
-  if (r == 0) {
-    p.new_seqlens[b] = len;
+  if (r0 == 0) {
+    p.seqlens[b] = len;
+    if (p.positions != nullptr) p.positions[b] = old_len;
     if (p.n_comp != nullptr)
       p.n_comp[b] = (int32_t)min((int64_t)windows(len, p.kernel, p.stride), p.c_cap);
     if (p.n_comp2 != nullptr)
@@ -163,8 +169,8 @@ extern "C" int ifv2_cache_fill(const void* src, void* cache, const int32_t* cu_s
 }
 
 extern "C" int ifv2_decode_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
-                                  void* kc_cache, void* kc2_cache, const int32_t* cache_seqlens,
-                                  int32_t* new_seqlens, int32_t* n_comp, int32_t* n_comp2, int batch,
+                                  void* kc_cache, void* kc2_cache, int32_t* cache_seqlens,
+                                  int32_t* positions, int32_t* n_comp, int32_t* n_comp2, int batch,
                                   int64_t capacity, int64_t c_capacity, int64_t c2_capacity,
                                   int heads_k, int head_dim, int kernel_size, int kernel_stride,
                                   int kernel2_size, int kernel2_stride, void* stream) {
@@ -172,11 +178,10 @@ extern "C" int ifv2_decode_append(const void* k_new, const void* v_new, void* k_
                "decode_append: head_dim %d not supported (only 128)", head_dim);
   IFV2_REQUIRE(batch >= 1 && heads_k >= 1 && capacity >= 1, IFV2_ERR_INVALID_ARG,
                "decode_append: bad size");
-  IFV2_REQUIRE(k_new && v_new && k_cache && v_cache && cache_seqlens && new_seqlens,
-               IFV2_ERR_INVALID_ARG, "decode_append: null pointer");
-  IFV2_REQUIRE(cache_seqlens != new_seqlens, IFV2_ERR_INVALID_ARG,
-               "decode_append: new_seqlens must not alias cache_seqlens (every thread of a "
-               "sequence reads the old length)");
+  IFV2_REQUIRE(k_new && v_new && k_cache && v_cache && cache_seqlens, IFV2_ERR_INVALID_ARG,
+               "decode_append: null pointer");
+  IFV2_REQUIRE(cache_seqlens != positions, IFV2_ERR_INVALID_ARG,
+               "decode_append: positions must not alias cache_seqlens");
   IFV2_REQUIRE(kc_cache == nullptr || (c_capacity >= 1 && kernel_size >= 1 && kernel_stride >= 1),
                IFV2_ERR_INVALID_ARG, "decode_append: bad compression arguments");
   IFV2_REQUIRE(kc2_cache == nullptr || (c2_capacity >= 1 && kernel2_size >= 1 && kernel2_stride >= 1),
@@ -187,14 +192,15 @@ extern "C" int ifv2_decode_append(const void* k_new, const void* v_new, void* k_
                           (const void*)kc_cache, (const void*)kc2_cache})
     IFV2_REQUIRE(reinterpret_cast<uintptr_t>(ptr) % 16 == 0, IFV2_ERR_INVALID_ARG,
                  "decode_append: tensors must be 16-byte aligned");
+  const int row_vecs = heads_k * kVecPerRow;
+  const int spb = row_vecs >= kThreads ? 1 : kThreads / row_vecs;
   AppendParams p{static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new),
                  static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
                  static_cast<uint4*>(kc_cache), static_cast<uint4*>(kc2_cache), cache_seqlens,
-                 new_seqlens, n_comp, n_comp2, batch, heads_k,
+                 positions, n_comp, n_comp2, batch, heads_k,
                  kc_cache ? kernel_size : 1, kc_cache ? kernel_stride : 1,
-                 kc2_cache ? kernel2_size : 1, kc2_cache ? kernel2_stride : 1,
+                 kc2_cache ? kernel2_size : 1, kc2_cache ? kernel2_stride : 1, spb,
                  capacity, c_capacity, c2_capacity};
-  const int64_t n_vec = (int64_t)batch * heads_k * kVecPerRow;
-  decode_append_kernel<<<(int)ceil_div64(n_vec, kThreads), kThreads, 0, (cudaStream_t)stream>>>(p);
+  decode_append_kernel<<<ceil_div(batch, spb), kThreads, 0, (cudaStream_t)stream>>>(p);
   return check_launch("decode_append");
 }

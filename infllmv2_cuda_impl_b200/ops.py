@@ -303,7 +303,7 @@ def cache_fill(src: torch.Tensor, cache: torch.Tensor, cu_seqlens: torch.Tensor,
 
 
 def decode_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                  cache_seqlens: torch.Tensor, new_seqlens: torch.Tensor,
+                  cache_seqlens: torch.Tensor, positions: Optional[torch.Tensor] = None,
                   kc_cache: Optional[torch.Tensor] = None, n_comp: Optional[torch.Tensor] = None,
                   kernel_size: int = 32, kernel_stride: int = 16,
                   kc2_cache: Optional[torch.Tensor] = None, n_comp2: Optional[torch.Tensor] = None,
@@ -311,10 +311,11 @@ def decode_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tenso
     """One decode step of cache bookkeeping, one launch, all in place: k_new / v_new (B, Hk, 128)
     are written at position cache_seqlens[b] of k_cache / v_cache (B, capacity, Hk, 128); a
     sequence whose new length completes a compression window gets that window's mean in kc_cache
-    (B, c_capacity, Hk, 128) (and kc2_cache for the second compression); new_seqlens (B,) int32
-    receives the new lengths (a different tensor than cache_seqlens), n_comp / n_comp2 the number
-    of valid compressed keys -- the `seqused_k` of the stage-1 scorer.  A sequence whose cache is
-    full is left as it is."""
+    (B, c_capacity, Hk, 128) (and kc2_cache for the second compression); cache_seqlens (B,) int32
+    is advanced in place, positions (B,) int32 receives the old lengths (the `cache_lens` of the
+    pool and top-k), n_comp / n_comp2 the number of valid compressed keys (the `seqused_k` of the
+    stage-1 scorer).  No pointer changes from step to step.  A sequence whose cache is full is
+    left as it is."""
     for name, t in (("k_new", k_new), ("v_new", v_new), ("k_cache", k_cache), ("v_cache", v_cache)):
         _require_cuda(t, name)
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
@@ -322,7 +323,7 @@ def decode_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tenso
     b, cap, hk, d = k_cache.shape
     if v_cache.shape != k_cache.shape or k_new.numel() != b * hk * d or v_new.numel() != b * hk * d:
         raise ValueError("decode_append: shapes of the new rows and the caches do not match")
-    for t in (cache_seqlens, new_seqlens, n_comp, n_comp2):
+    for t in (cache_seqlens, positions, n_comp, n_comp2):
         assert t is None or (t.dtype == torch.int32 and t.is_contiguous() and t.numel() == b)
     for c in (kc_cache, kc2_cache):
         if c is not None and (c.dtype != torch.bfloat16 or not c.is_contiguous() or c.dim() != 4
@@ -332,7 +333,7 @@ def decode_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tenso
     with torch.cuda.device(k_cache.device):
         _lib.call("ifv2_decode_append", k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(),
                   v_cache.data_ptr(), ptr(kc_cache), ptr(kc2_cache), cache_seqlens.data_ptr(),
-                  new_seqlens.data_ptr(), ptr(n_comp), ptr(n_comp2), b, cap,
+                  ptr(positions), ptr(n_comp), ptr(n_comp2), b, cap,
                   kc_cache.shape[1] if kc_cache is not None else 0,
                   kc2_cache.shape[1] if kc2_cache is not None else 0, hk, d, kernel_size, kernel_stride,
                   kernel2_size, kernel2_stride, _stream(k_cache.device))

@@ -69,7 +69,7 @@ class DecodeCache:
             self.n_comp2 = torch.zeros(batch, dtype=torch.int32, device=dev)
             self.cu_c2 = torch.arange(batch + 1, dtype=torch.int32, device=dev) * self.c2_capacity
         self.seqlens = torch.zeros(batch, dtype=torch.int32, device=dev)
-        self._spare = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.positions = torch.zeros(batch, dtype=torch.int32, device=dev)   # lengths before the last append
         self.n_comp = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.cu_q = torch.arange(batch + 1, dtype=torch.int32, device=dev)
         self.cu_c = self.cu_q * self.c_capacity
@@ -139,25 +139,27 @@ class SparseAttention:
 
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
-    def decode(self, q, k_new, v_new, cache: DecodeCache, softmax_scale: Optional[float] = None):
+    def decode(self, q, k_new, v_new, cache: DecodeCache, softmax_scale: Optional[float] = None,
+               static_shapes: bool = False):
         """One token per sequence: q (B, Hq, 128) or (B, 1, Hq, 128); k_new / v_new (B, Hk, 128)
         or (B, 1, Hk, 128).  Appends to the cache, then attends over it (the new token included).
-        Returns (B, 1, Hq, 128)."""
+        Returns (B, 1, Hq, 128).  static_shapes: size every intermediate for the cache capacity
+        instead of the current maximum length, so that the step launches the same kernels with the
+        same arguments every time (what a CUDA graph needs; see `capture_decode`)."""
         c = self.config
         b, hk = cache.batch, cache.heads_k
         if cache.max_len >= cache.capacity:
             raise RuntimeError("DecodeCache is full")
         q3 = q.reshape(b, hk * GROUP, HEAD_DIM)
-        ops.decode_append(k_new.reshape(b, hk, HEAD_DIM).contiguous(), v_new.reshape(b, hk, HEAD_DIM).contiguous(),
-                          cache.k, cache.v, cache.seqlens, cache._spare, cache.kc, cache.n_comp,
-                          c.kernel_size, c.kernel_stride, cache.kc2, cache.n_comp2,
-                          c.coarse_kernel_size, c.coarse_kernel_stride)
-        before = cache.seqlens                       # the query's position in its sequence
-        cache.seqlens, cache._spare = cache._spare, before
+        ops.decode_append(k_new.reshape(b, hk, HEAD_DIM), v_new.reshape(b, hk, HEAD_DIM), cache.k, cache.v,
+                          cache.seqlens, cache.positions, cache.kc, cache.n_comp, c.kernel_size,
+                          c.kernel_stride, cache.kc2, cache.n_comp2, c.coarse_kernel_size,
+                          c.coarse_kernel_stride)
         cache.max_len += 1
-        max_c = c.windows(cache.max_len)
+        bound = cache.capacity if static_shapes else cache.max_len       # >= every sequence length
+        max_c = c.windows(bound)
         idx = None
-        if cache.max_len > c.dense_len and max_c > 0:
+        if bound > c.dense_len and max_c > 0:
             kc_flat = cache.kc.view(-1, hk, HEAD_DIM)
             if cache.kc2 is not None:
                 score = infllmv2_attn_stage1(q3, kc_flat, cache.kc2.view(-1, hk, HEAD_DIM), cache.cu_q, cache.cu_c,
@@ -168,11 +170,57 @@ class SparseAttention:
                                              causal=False, seqused_k=cache.n_comp)
             # columns past a sequence's compressed keys hold 0, which never outranks a real block
             # (ties go to the lower index) and only ever comes out as -1
-            pooled = ops.max_pooling_1d_varlen(score, cache.cu_q, cache.cu_c, before, 1, max_c,
-                                               c.local_blocks, c.init_blocks,
-                                               max_cache_len=cache.max_len - 1)
-            idx = ops.infllmv2_topk(pooled, c.topk, cu_seqlens_q=cache.cu_q, cache_lens=before)
+            pooled = ops.max_pooling_1d_varlen(score, cache.cu_q, cache.cu_c, cache.positions, 1, max_c,
+                                               c.local_blocks, c.init_blocks, max_cache_len=bound - 1)
+            idx = ops.infllmv2_topk(pooled, c.topk, cu_seqlens_q=cache.cu_q, cache_lens=cache.positions)
             idx = idx.permute(1, 0, 2).unsqueeze(2)                    # (B, Hk, 1, topk)
         return infllmv2_attn_with_kvcache(q3.view(b, 1, hk * GROUP, HEAD_DIM), cache.k, cache.v,
                                           cache_seqlens=cache.seqlens, softmax_scale=softmax_scale,
                                           topk_idx=idx)
+
+    def capture_decode(self, cache: DecodeCache, softmax_scale: Optional[float] = None):
+        """Capture one decode step for `cache` in a CUDA graph.  Returns `step(q, k_new, v_new)`,
+        which copies its arguments into the graph's input buffers, replays it and returns the
+        graph's output tensor (B, 1, Hq, 128), valid until the next call.  The step is sized for
+        the cache capacity (`static_shapes`); the lengths live on the device and advance with
+        every replay."""
+        b, hk = cache.batch, cache.heads_k
+        dev = cache.k.device
+        q_in = torch.zeros(b, hk * GROUP, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        k_in = torch.zeros(b, hk, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        v_in = torch.zeros(b, hk, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        # one eager step on a side stream (first-use initialisation must not happen under capture),
+        # then the lengths are put back: what the step wrote lies past them
+        saved = (cache.seqlens.clone(), cache.n_comp.clone(),
+                 cache.n_comp2.clone() if cache.n_comp2 is not None else None, cache.max_len)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self.decode(q_in, k_in, v_in, cache, softmax_scale, static_shapes=True)
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+        def restore():
+            cache.seqlens.copy_(saved[0])
+            cache.n_comp.copy_(saved[1])
+            if saved[2] is not None:
+                cache.n_comp2.copy_(saved[2])
+            cache.max_len = saved[3]
+
+        restore()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.decode(q_in, k_in, v_in, cache, softmax_scale, static_shapes=True)
+        cache.max_len = saved[3]                   # capturing does not run the step
+
+        def step(q, k_new, v_new):
+            if cache.max_len >= cache.capacity:
+                raise RuntimeError("DecodeCache is full")
+            q_in.copy_(q.reshape(q_in.shape))
+            k_in.copy_(k_new.reshape(k_in.shape))
+            v_in.copy_(v_new.reshape(v_in.shape))
+            graph.replay()
+            cache.max_len += 1
+            return out
+
+        step.graph, step.inputs = graph, (q_in, k_in, v_in)
+        return step

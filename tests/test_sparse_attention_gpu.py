@@ -57,11 +57,11 @@ def test_cache_fill_and_append_match_recompression():
     for s in range(steps):
         kn = torch.stack([k[l + s] for k, l in zip(k_all, lens)]).to(DEV)
         vn = torch.stack([v[l + s] for v, l in zip(v_all, lens)]).to(DEV)
-        infllm_v2.decode_append(kn, vn, cache.k, cache.v, cache.seqlens, cache._spare, cache.kc, cache.n_comp,
+        infllm_v2.decode_append(kn, vn, cache.k, cache.v, cache.seqlens, cache.positions, cache.kc, cache.n_comp,
                                 32, 16, cache.kc2, cache.n_comp2, 128, 64)
-        cache.seqlens, cache._spare = cache._spare, cache.seqlens
     torch.cuda.synchronize()
     assert cache.seqlens.tolist() == [l + steps for l in lens]
+    assert cache.positions.tolist() == [l + steps - 1 for l in lens]
     for b, l in enumerate(lens):
         n = l + steps
         assert torch.equal(cache.k[b, :n].cpu(), k_all[b]) and torch.equal(cache.v[b, :n].cpu(), v_all[b])
@@ -148,3 +148,30 @@ def test_decode_continues_prefill(coarse):
     infllm_v2.check_device_status()
     assert cache.seqlens.tolist() == [l + steps for l in lens]
     assert np.mean(agree) > 0.9, agree          # a tie that flips selects another block for 16 heads
+
+
+def test_decode_graph_replay_equals_eager_steps():
+    """The captured decode step (sized for the capacity) against eager steps on a twin cache."""
+    lens, cap, steps = [300, 90, 411], 448, 20
+    cfg = _config(topk=5)
+    layer = infllm_v2.SparseAttention(cfg)
+    g = torch.Generator().manual_seed(3)
+    qs = [(torch.randn(l + steps, HQ, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    ks = [(torch.randn(l + steps, HK, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    vs = [torch.randn(l + steps, HK, D, generator=g).to(torch.bfloat16) for l in lens]
+    pack = lambda ts: torch.cat([t[:l] for t, l in zip(ts, lens)]).to(DEV)
+    caches = [infllm_v2.DecodeCache(len(lens), cap, HK, cfg, DEV) for _ in range(2)]
+    for c in caches:
+        layer.prefill(pack(qs), pack(ks), pack(vs), cu(lens, DEV), max(lens), seqlens=lens, cache=c)
+    step = layer.capture_decode(caches[1])
+    assert caches[1].seqlens.tolist() == lens and caches[1].max_len == max(lens)
+    for s in range(steps):
+        qn = torch.stack([q[l + s] for q, l in zip(qs, lens)]).to(DEV)
+        kn = torch.stack([k[l + s] for k, l in zip(ks, lens)]).to(DEV)
+        vn = torch.stack([v[l + s] for v, l in zip(vs, lens)]).to(DEV)
+        eager = layer.decode(qn, kn, vn, caches[0])
+        replayed = step(qn, kn, vn)
+        assert torch.equal(eager, replayed), s
+    infllm_v2.check_device_status()
+    assert caches[1].seqlens.tolist() == [l + steps for l in lens]
+    assert torch.equal(caches[0].kc, caches[1].kc) and torch.equal(caches[0].k, caches[1].k)
