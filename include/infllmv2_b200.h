@@ -141,6 +141,23 @@ int ifv2_topk_select(const void* score, int32_t* out_idx, int is_bf16, int heads
                      const int32_t* cache_lens, int batch, int cache_len, int block_size,
                      void* stream);
 
+/* Block selection of a decode step in one launch: for every (sequence, KV head) row of stage-1
+ * scores (score: (heads, batch, row_stride), one query token per sequence) the 64-token max-pool
+ * (window block_size/stride + 1, stride block_size/stride, padding 1, +inf on the init and
+ * causal-local blocks), the top-k of the n_blocks block scores and the packed block mask
+ * mask[b, h, :] (batch, heads, mask_words) that ifv2_decode / ifv2_decode_paged read.
+ * seqused_c: (batch) number of compressed keys of each sequence (null = max_seqlen_c);
+ * positions: (batch) position of the query token in its sequence (its block is position /
+ * block_size); topk_idx (may be null): (batch, heads, k) int32, ascending, -1 tail.  Results are
+ * identical to ifv2_max_pooling_1d_varlen -> ifv2_topk_select -> ifv2_topk_to_uint64 on the same
+ * row (csrc/max_pooling_1d.cuh:11-103, the tie rule of csrc/topk.cuh:6-42,
+ * csrc/topk_to_uint64.cuh:10-76); the reference runs these (and a torch.topk) as separate
+ * launches. */
+int ifv2_decode_select(const void* score, int is_bf16, int64_t row_stride, const int32_t* seqused_c,
+                       const int32_t* positions, int64_t* mask, int32_t* topk_idx, int batch,
+                       int heads, int max_seqlen_c, int n_blocks, int mask_words, int k,
+                       int local_blocks, int init_blocks, int block_size, int stride, void* stream);
+
 /* ---------------------------------------------------------------- stage 1 ------------------ */
 
 /* Stage-1 scorer: out[h, t, j] = sum over the 16 query heads of KV head h of

@@ -5,7 +5,7 @@ __version__ = "0.1.0"
 
 from .ops import (blockmask_to_uint64, topk_to_uint64, uint64_to_bool, max_pooling_1d,
                   max_pooling_1d_varlen, infllmv2_topk, transpose_blockmask, compress_keys,
-                  compress_keys_append, compressed_lengths, cache_fill, decode_append)
+                  compress_keys_append, compressed_lengths, cache_fill, decode_append, decode_select)
 from .attention import (infllmv2_attn_varlen_func, infllmv2_attn_stage1,
                         infllmv2_attn_with_kvcache, infllmv2_stage1_block_scores,
                         check_device_status)
@@ -15,6 +15,6 @@ __all__ = [
     "blockmask_to_uint64", "topk_to_uint64", "uint64_to_bool", "max_pooling_1d",
     "max_pooling_1d_varlen", "infllmv2_attn_varlen_func", "infllmv2_attn_stage1",
     "infllmv2_attn_with_kvcache", "infllmv2_topk", "infllmv2_stage1_block_scores", "transpose_blockmask", "check_device_status",
-    "compress_keys", "compress_keys_append", "compressed_lengths", "cache_fill", "decode_append",
+    "compress_keys", "compress_keys_append", "compressed_lengths", "cache_fill", "decode_append", "decode_select",
     "SparseConfig", "DecodeCache", "SparseAttention",
 ]

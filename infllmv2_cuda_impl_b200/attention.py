@@ -364,7 +364,7 @@ def infllmv2_attn_with_kvcache(
     cache_batch_idx: Optional[torch.Tensor] = None, cache_leftpad: Optional[torch.Tensor] = None,
     block_table: Optional[torch.Tensor] = None, softmax_scale=None, causal=False,
     window_size=(-1, -1), softcap=0.0, rotary_interleaved=True, alibi_slopes=None, num_splits=0,
-    return_softmax_lse=False, topk_idx=None,
+    return_softmax_lse=False, topk_idx=None, block_mask=None,
 ):
     """Sparse decode step over a KV cache (one new query token per sequence).
 
@@ -374,7 +374,9 @@ def infllmv2_attn_with_kvcache(
     cache_seqlens: int or (batch,) int32; cache_batch_idx (batch,) int32: the cache row each
     sequence uses; cache_leftpad (batch,) int32: position of each sequence's first key;
     topk_idx: int32 (batch, nheads_k, 1, topk) blocks of the sequence to attend (None = all of
-    it), counted from its first key.  A single query token is never causally masked
+    it), counted from its first key.  block_mask (an addition): the same selection already packed
+    into 64-bit words, (batch, nheads_k, 1, words) int64 as ops.decode_select returns it.
+    A single query token is never causally masked
     (csrc/flash_attn/flash_api.cpp:1628).  Returns out (batch, 1, nheads, 128)
     [, softmax_lse (batch, nheads, 1)].
     """
@@ -418,7 +420,14 @@ def infllmv2_attn_with_kvcache(
         if c.stride(2) != d or c.stride(1) != nheads_k * d:
             raise RuntimeError("infllmv2_attn_with_kvcache: caches must be dense in (seqlen, heads, d)")
     mask = None
-    if topk_idx is not None:
+    if block_mask is not None:
+        # an already packed selection (ops.decode_select): (batch, nheads_k, [1,] words) int64
+        words = ((cap + BLOCK_N - 1) // BLOCK_N + 63) // 64
+        if topk_idx is not None or block_mask.dtype != torch.int64 or block_mask.numel() != batch * nheads_k * words:
+            raise ValueError("infllmv2_attn_with_kvcache: block_mask must be (batch, nheads_k, 1, "
+                             f"{words}) int64 and excludes topk_idx")
+        mask = block_mask.contiguous().view(batch, nheads_k, 1, words)
+    elif topk_idx is not None:
         assert topk_idx.dtype == torch.int32
         mask, _ = topk_to_uint64(topk_idx, cap, BLOCK_N)
     q2 = q.reshape(batch, nheads, d).contiguous()

@@ -9,8 +9,7 @@
 //           its compressed-key cache (up to two compressions: 32/16 for the scorer, 128/64 for
 //           the coarse row sums); the new lengths and compressed-key counts are written out so
 //           that the next kernels of the step need no host arithmetic.
-// One thread owns 8 features (16 bytes) of one (sequence, head) row, as in the compression kernel;
-// the thread that writes the new key row is the one that reads it back for the window mean.
+// 16-byte vectors throughout; the append kernel gives a sequence to one CTA.
 #include "common.cuh"
 
 namespace ifv2 {
@@ -79,58 +78,82 @@ struct AppendParams {
   int32_t* n_comp;             // (batch) compressed keys after the append, or null
   int32_t* n_comp2;
   int batch, heads, kernel, stride, kernel2, stride2;
-  int seq_per_block;           // sequences owned by one CTA (all threads of a sequence share a CTA)
   int64_t cap, c_cap, c2_cap;
 };
 
-__device__ __forceinline__ void write_window(const uint4* k_rows, uint4* dst, int len, int kernel,
-                                             int64_t row_vecs) {
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  const uint4* src = k_rows + (int64_t)(len - kernel) * row_vecs;
-  int t = 0;
-  for (; t + 4 <= kernel; t += 4) {
-    const uint4 a = src[(t + 0) * row_vecs], b = src[(t + 1) * row_vecs];
-    const uint4 c = src[(t + 2) * row_vecs], d = src[(t + 3) * row_vecs];
-    acc_bf16x8(acc, a);
-    acc_bf16x8(acc, b);
-    acc_bf16x8(acc, c);
-    acc_bf16x8(acc, d);
+constexpr int kRowsPerPart = 4;      // window rows a thread fetches per round
+
+// Mean of the last `kernel` key rows of one sequence -> dst (one compressed key, all heads).
+// The CTA's threads fetch the rows of a round side by side into shared memory (one trip to
+// memory per round instead of one per row); the rows are then added in token order, the order of
+// compress_keys_kernel, so a window completed during decode equals the one a prefill computes.
+// Called by all threads of the CTA (it synchronises).
+__device__ __forceinline__ void window_mean(const uint4* k_seq, uint4* dst, int len, int kernel,
+                                            int row_vecs, uint4* stage /* [kRowsPerPart * kThreads] */) {
+  const int tid = threadIdx.x;
+  const int cols = min(row_vecs, kThreads);             // vectors of a row handled per pass
+  const int parts = kThreads / cols;                    // thread groups fetching different rows
+  const int part = tid / cols, c = tid % cols;
+  const int rows_per_round = parts * kRowsPerPart;      // rows_per_round * cols <= 4 * kThreads
+  const uint4* first = k_seq + (int64_t)(len - kernel) * row_vecs;
+  for (int c0 = 0; c0 < row_vecs; c0 += cols) {
+    const int r = c0 + c;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int t0 = 0; t0 < kernel; t0 += rows_per_round) {
+      if (part < parts && r < row_vecs) {
+        uint4 v[kRowsPerPart];
+#pragma unroll
+        for (int i = 0; i < kRowsPerPart; ++i) {         // all loads of the round first
+          const int t = t0 + part * kRowsPerPart + i;
+          if (t < kernel) v[i] = first[(int64_t)t * row_vecs + r];
+        }
+#pragma unroll
+        for (int i = 0; i < kRowsPerPart; ++i)
+          if (t0 + part * kRowsPerPart + i < kernel) stage[(part * kRowsPerPart + i) * cols + c] = v[i];
+      }
+      __syncthreads();
+      if (part == 0 && r < row_vecs) {
+        const int rows = min(rows_per_round, kernel - t0);
+        for (int t = 0; t < rows; ++t) acc_bf16x8(acc, stage[t * cols + c]);
+      }
+      __syncthreads();
+    }
+    if (part == 0 && r < row_vecs) dst[r] = mean_bf16x8(acc, (float)kernel);
   }
-  for (; t < kernel; ++t) acc_bf16x8(acc, src[t * row_vecs]);
-  *dst = mean_bf16x8(acc, (float)kernel);
 }
 
-// The lengths are updated in place: every thread that reads a sequence's length sits in the CTA
-// that later writes it, and a barrier separates the two.
+// One CTA per sequence.  The lengths are updated in place: every thread that reads a sequence's
+// length sits in the CTA that later writes it, and a barrier separates the two.
 __global__ void __launch_bounds__(kThreads) decode_append_kernel(const AppendParams p) {
+  __shared__ uint4 stage[kRowsPerPart * kThreads];        // 16 KB
   const int row_vecs = p.heads * kVecPerRow;
-  const int tps = kThreads / p.seq_per_block;            // threads per sequence
-  const int b = blockIdx.x * p.seq_per_block + (int)threadIdx.x / tps;
-  const int r0 = (int)threadIdx.x % tps;
-  const bool valid = (int)threadIdx.x / tps < p.seq_per_block && b < p.batch;
-  const int old_len = valid ? p.seqlens[b] : 0;
+  const int b = blockIdx.x;
+  const int old_len = p.seqlens[b];
   __syncthreads();
-  if (!valid) return;
   const bool room = old_len >= 0 && old_len < p.cap;      // a full cache is left untouched
   const int len = room ? old_len + 1 : old_len;
-  for (int r = r0; room && r < row_vecs; r += tps) {
-    const int64_t at = ((int64_t)b * p.cap + old_len) * row_vecs + r;
-    p.k_cache[at] = __ldg(p.k_new + (int64_t)b * row_vecs + r);
-    p.v_cache[at] = __ldg(p.v_new + (int64_t)b * row_vecs + r);
-    // plain loads below: the row just written by this thread is among them
-    const uint4* k_rows = p.k_cache + (int64_t)b * p.cap * row_vecs + r;
-    if (p.kc_cache != nullptr && len >= p.kernel && (len - p.kernel) % p.stride == 0) {
-      const int64_t j = (len - p.kernel) / p.stride;
-      if (j < p.c_cap)
-        write_window(k_rows, p.kc_cache + ((int64_t)b * p.c_cap + j) * row_vecs + r, len, p.kernel, row_vecs);
+  if (room) {                                             // (uniform over the CTA)
+    for (int r = threadIdx.x; r < row_vecs; r += kThreads) {
+      const int64_t at = ((int64_t)b * p.cap + old_len) * row_vecs + r;
+      p.k_cache[at] = __ldg(p.k_new + (int64_t)b * row_vecs + r);
+      p.v_cache[at] = __ldg(p.v_new + (int64_t)b * row_vecs + r);
     }
-    if (p.kc2_cache != nullptr && len >= p.kernel2 && (len - p.kernel2) % p.stride2 == 0) {
-      const int64_t j = (len - p.kernel2) / p.stride2;
-      if (j < p.c2_cap)
-        write_window(k_rows, p.kc2_cache + ((int64_t)b * p.c2_cap + j) * row_vecs + r, len, p.kernel2, row_vecs);
+    const bool win1 = p.kc_cache != nullptr && len >= p.kernel && (len - p.kernel) % p.stride == 0 &&
+                      (len - p.kernel) / p.stride < p.c_cap;
+    const bool win2 = p.kc2_cache != nullptr && len >= p.kernel2 && (len - p.kernel2) % p.stride2 == 0 &&
+                      (len - p.kernel2) / p.stride2 < p.c2_cap;
+    if (win1 || win2) {
+      __syncthreads();                                    // the new key row is among the rows read
+      const uint4* k_seq = p.k_cache + (int64_t)b * p.cap * row_vecs;
+      if (win1)
+        window_mean(k_seq, p.kc_cache + ((int64_t)b * p.c_cap + (len - p.kernel) / p.stride) * row_vecs,
+                    len, p.kernel, row_vecs, stage);
+      if (win2)
+        window_mean(k_seq, p.kc2_cache + ((int64_t)b * p.c2_cap + (len - p.kernel2) / p.stride2) * row_vecs,
+                    len, p.kernel2, row_vecs, stage);
     }
   }
-  if (r0 == 0) {
+  if (threadIdx.x == 0) {
     p.seqlens[b] = len;
     if (p.positions != nullptr) p.positions[b] = old_len;
     if (p.n_comp != nullptr)
@@ -192,15 +215,14 @@ extern "C" int ifv2_decode_append(const void* k_new, const void* v_new, void* k_
                           (const void*)kc_cache, (const void*)kc2_cache})
     IFV2_REQUIRE(reinterpret_cast<uintptr_t>(ptr) % 16 == 0, IFV2_ERR_INVALID_ARG,
                  "decode_append: tensors must be 16-byte aligned");
-  const int row_vecs = heads_k * kVecPerRow;
-  const int spb = row_vecs >= kThreads ? 1 : kThreads / row_vecs;
+  IFV2_REQUIRE(batch <= 1 << 30, IFV2_ERR_TOO_LARGE, "decode_append: batch too large");
   AppendParams p{static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new),
                  static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
                  static_cast<uint4*>(kc_cache), static_cast<uint4*>(kc2_cache), cache_seqlens,
                  positions, n_comp, n_comp2, batch, heads_k,
                  kc_cache ? kernel_size : 1, kc_cache ? kernel_stride : 1,
-                 kc2_cache ? kernel2_size : 1, kc2_cache ? kernel2_stride : 1, spb,
+                 kc2_cache ? kernel2_size : 1, kc2_cache ? kernel2_stride : 1,
                  capacity, c_capacity, c2_capacity};
-  decode_append_kernel<<<ceil_div(batch, spb), kThreads, 0, (cudaStream_t)stream>>>(p);
+  decode_append_kernel<<<batch, kThreads, 0, (cudaStream_t)stream>>>(p);
   return check_launch("decode_append");
 }

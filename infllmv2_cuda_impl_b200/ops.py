@@ -337,3 +337,35 @@ def decode_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tenso
                   kc_cache.shape[1] if kc_cache is not None else 0,
                   kc2_cache.shape[1] if kc2_cache is not None else 0, hk, d, kernel_size, kernel_stride,
                   kernel2_size, kernel2_stride, _stream(k_cache.device))
+
+
+def decode_select(score: torch.Tensor, positions: torch.Tensor, k: int, max_seqlen_k: int,
+                  local_blocks: int, init_blocks: int, seqused_c: Optional[torch.Tensor] = None,
+                  block_size: int = 64, stride: int = 16, return_topk: bool = False):
+    """Block selection of a decode step in one launch: max-pool of the stage-1 scores of ONE query
+    token per sequence (score: (Hk, B, n_comp) bf16/fp16, e.g. from infllmv2_attn_stage1), top-k
+    and the uint64 block mask (B, Hk, 1, ceil(ceil(max_seqlen_k / block_size) / 64)) int64 that
+    infllmv2_attn_with_kvcache takes as `block_mask`.  positions (B,) int32: position of the query
+    token in its sequence; seqused_c (B,) int32: compressed keys per sequence (default: all
+    columns).  Equal to max_pooling_1d_varlen -> infllmv2_topk -> topk_to_uint64.  With
+    return_topk also returns topk_idx (B, Hk, 1, k) int32."""
+    assert score.dtype == torch.float16 or score.dtype == torch.bfloat16
+    _require_cuda(score, "score")
+    if score.dim() != 3:
+        raise ValueError("score must be (num_heads_k, batch, n_comp)")
+    score, row_stride = _row_view(score)
+    hk, b, n_c = score.shape
+    assert positions.dtype == torch.int32 and positions.numel() == b
+    if seqused_c is not None:
+        assert seqused_c.dtype == torch.int32 and seqused_c.numel() == b
+        seqused_c = seqused_c.contiguous()
+    n_blocks = (max_seqlen_k + block_size - 1) // block_size
+    words = (n_blocks + 63) // 64
+    mask = torch.empty(b, hk, 1, words, dtype=torch.int64, device=score.device)
+    idx = torch.empty(b, hk, 1, k, dtype=torch.int32, device=score.device) if return_topk else None
+    with torch.cuda.device(score.device):
+        _lib.call("ifv2_decode_select", score.data_ptr(), int(score.dtype == torch.bfloat16), row_stride,
+                  seqused_c.data_ptr() if seqused_c is not None else None, positions.contiguous().data_ptr(),
+                  mask.data_ptr(), idx.data_ptr() if idx is not None else None, b, hk, n_c, n_blocks, words,
+                  k, local_blocks, init_blocks, block_size, stride, _stream(score.device))
+    return (mask, idx) if return_topk else mask

@@ -158,7 +158,7 @@ class SparseAttention:
         cache.max_len += 1
         bound = cache.capacity if static_shapes else cache.max_len       # >= every sequence length
         max_c = c.windows(bound)
-        idx = None
+        mask = None
         if bound > c.dense_len and max_c > 0:
             kc_flat = cache.kc.view(-1, hk, HEAD_DIM)
             if cache.kc2 is not None:
@@ -168,15 +168,12 @@ class SparseAttention:
             else:
                 score = infllmv2_attn_stage1(q3, kc_flat, kc_flat, cache.cu_q, cache.cu_c, cache.cu_c, 1, max_c,
                                              causal=False, seqused_k=cache.n_comp)
-            # columns past a sequence's compressed keys hold 0, which never outranks a real block
-            # (ties go to the lower index) and only ever comes out as -1
-            pooled = ops.max_pooling_1d_varlen(score, cache.cu_q, cache.cu_c, cache.positions, 1, max_c,
-                                               c.local_blocks, c.init_blocks, max_cache_len=bound - 1)
-            idx = ops.infllmv2_topk(pooled, c.topk, cu_seqlens_q=cache.cu_q, cache_lens=cache.positions)
-            idx = idx.permute(1, 0, 2).unsqueeze(2)                    # (B, Hk, 1, topk)
+            # pool + top-k + packed mask of the few decode rows in one launch
+            mask = ops.decode_select(score, cache.positions, c.topk, cache.capacity, c.local_blocks,
+                                     c.init_blocks, seqused_c=cache.n_comp)
         return infllmv2_attn_with_kvcache(q3.view(b, 1, hk * GROUP, HEAD_DIM), cache.k, cache.v,
                                           cache_seqlens=cache.seqlens, softmax_scale=softmax_scale,
-                                          topk_idx=idx)
+                                          block_mask=mask)
 
     def capture_decode(self, cache: DecodeCache, softmax_scale: Optional[float] = None):
         """Capture one decode step for `cache` in a CUDA graph.  Returns `step(q, k_new, v_new)`,

@@ -147,3 +147,44 @@ def test_inputs_touching_the_ends_of_an_allocation():
     pooled = infllm_v2.max_pooling_1d(view[:, :, :21], 0, 2, 1)
     torch.cuda.synchronize()
     assert torch.equal(pooled.cpu(), oracle.max_pooling_1d(s[:, :, :21], 0, 2, 1))
+
+
+@pytest.mark.parametrize("hk,b,cap,k,local,init,dtype", [
+    (2, 5, 4096, 8, 2, 1, torch.bfloat16), (1, 3, 131072, 64, 32, 1, torch.bfloat16),
+    (4, 6, 1000, 16, 0, 0, torch.float16), (2, 4, 64 * 70, 96, 1, 2, torch.bfloat16),
+])
+def test_decode_select_equals_pool_topk_pack(hk, b, cap, k, local, init, dtype):
+    """One launch against the three kernels it replaces, bit for bit: ragged lengths (one
+    sequence shorter than a compression window, one at the capacity), heavy ties."""
+    rng = np.random.default_rng(cap + k)
+    lens = rng.integers(40, cap + 1, size=b)
+    lens[0], lens[-1] = 20, cap
+    n_c = np.where(lens >= 32, (lens - 32) // 16 + 1, 0).astype(np.int32)
+    max_c = int(n_c.max())
+    g = torch.Generator().manual_seed(int(cap))
+    score = (torch.randint(0, 12, (hk, b, max_c), generator=g).float() / 8).to(dtype)     # many equal values
+    for i in range(b):
+        score[:, i, n_c[i]:] = 0
+    score = score.to(DEV)
+    if k % 16 == 0:        # rows padded to 128 scores, as the scorer writes them (staged in shared memory)
+        buf = torch.full((hk, b, (max_c + 127) // 128 * 128), float("nan"), dtype=dtype, device=DEV)
+        buf[:, :, :max_c] = score
+        score = buf[:, :, :max_c]
+    positions = torch.tensor(lens - 1, dtype=torch.int32, device=DEV)
+    used = torch.tensor(n_c, device=DEV)
+    mask, idx = infllm_v2.decode_select(score, positions, k, cap, local, init, seqused_c=used, return_topk=True)
+    cu_q = torch.arange(b + 1, dtype=torch.int32, device=DEV)
+    cu_c = torch.tensor(np.concatenate([[0], np.cumsum(n_c)]), dtype=torch.int32, device=DEV)
+    pooled = infllm_v2.max_pooling_1d_varlen(score, cu_q, cu_c, positions, 1, max_c, local, init,
+                                             max_cache_len=cap - 1)
+    assert pooled.shape[-1] == (cap + 63) // 64
+    ref_idx = infllm_v2.infllmv2_topk(pooled, k, cu_seqlens_q=cu_q, cache_lens=positions)
+    ref_idx = ref_idx.permute(1, 0, 2).unsqueeze(2).contiguous()
+    ref_mask, _ = infllm_v2.topk_to_uint64(ref_idx, cap, 64)
+    assert torch.equal(idx, ref_idx)
+    assert torch.equal(mask, ref_mask)
+    # and against the oracle for one row
+    exp = oracle.topk_select(oracle.max_pooling_1d_varlen(score.cpu(), cu_q.tolist(), cu_c.tolist(), (lens - 1).tolist(),
+                                                          1, max_c, local, init).float(), k,
+                             torch.tensor((lens - 1) // 64))
+    assert torch.equal(idx[:, :, 0].cpu().permute(1, 0, 2), exp)
