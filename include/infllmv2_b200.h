@@ -198,6 +198,21 @@ int ifv2_stage1_decode_scores(const void* q, const void* kc, void* out, const in
                               int max_seqlen_k, int64_t out_row_stride, float softmax_scale,
                               int causal, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Decode selection straight from the compressed keys, two launches: the first kernel of
+ * ifv2_stage1_decode_scores, then one kernel that forms each (sequence, KV head) score row in
+ * shared memory and runs ifv2_decode_select's pool / top-k / mask pack on it -- the score row
+ * never reaches HBM.  Arguments as in those two entries (positions, mask, topk_idx, n_blocks,
+ * mask_words, k, local_blocks, init_blocks, block_size, stride as in ifv2_decode_select; the rest
+ * as in ifv2_stage1_decode_scores, same workspace size); max_seqlen_k <= 32768.  Results are
+ * identical to ifv2_stage1_decode_scores followed by ifv2_decode_select. */
+int ifv2_stage1_decode_select(const void* q, const void* kc, const int32_t* cu_seqlens_k,
+                              const int32_t* seqused_k, const int32_t* positions, int64_t* mask,
+                              int32_t* topk_idx, int batch, int64_t total_c, int heads_q,
+                              int heads_k, int head_dim, int max_seqlen_k, int n_blocks,
+                              int mask_words, int k, int local_blocks, int init_blocks,
+                              int block_size, int stride, float softmax_scale, int causal,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Stage-1 scorer with the 64-token max-pool fused in: writes block scores
  * (heads_k, total_q, n_blocks) bf16 that are bit-identical to ifv2_max_pooling_1d[_varlen]
  * (kernel 5, stride 4, padding 1, block 64) applied to the output of ifv2_stage1_scores, without

@@ -156,6 +156,46 @@ def infllmv2_attn_stage1(
     return buf[:, :, :max_seqlen_k]
 
 
+def infllmv2_stage1_decode_select(q, k, cu_seqlens_k, positions, max_seqlen_k, cache_capacity, topk,
+                                  local_blocks, init_blocks, seqused_k=None, softmax_scale=None,
+                                  causal=False, block_size=64, stride=16, return_topk=False):
+    """Block selection of a decode step straight from the compressed keys (an addition to the
+    reference API): stage-1 scores of ONE query token per sequence (q: (B, Hq, 128)), 64-token
+    max-pool, top-k and the packed block mask, in two launches and without the score rows ever
+    reaching HBM.  k / cu_seqlens_k / seqused_k / max_seqlen_k: the compressed keys as in
+    infllmv2_attn_stage1; positions (B,) int32: position of each query token in its sequence;
+    cache_capacity: key capacity of the KV cache the mask is for.  Returns the int64 mask
+    (B, Hk, 1, words) that infllmv2_attn_with_kvcache takes as `block_mask` [, topk_idx
+    (B, Hk, 1, topk) int32]; both equal infllmv2_attn_stage1 -> ops.decode_select."""
+    _check_common(q, k, 0.0, (-1, -1), 0.0, None, None, "infllmv2_stage1_decode_select")
+    q, k = _dense(maybe_contiguous(q)), _dense(maybe_contiguous(k))
+    if q.dim() != 3:
+        raise ValueError("infllmv2_stage1_decode_select: q must be (batch, nheads, 128), one token per sequence")
+    batch, nheads, d = q.shape
+    nheads_k = k.shape[1]
+    assert cu_seqlens_k.dtype == torch.int32 and cu_seqlens_k.numel() == batch + 1
+    assert positions.dtype == torch.int32 and positions.numel() == batch
+    if seqused_k is not None:
+        assert seqused_k.dtype == torch.int32 and seqused_k.numel() == batch
+        seqused_k = seqused_k.contiguous()
+    if softmax_scale is None:
+        softmax_scale = d ** (-0.5)
+    n_blocks = (cache_capacity + block_size - 1) // block_size
+    words = (n_blocks + 63) // 64
+    mask = torch.empty(batch, nheads_k, 1, words, dtype=torch.int64, device=q.device)
+    idx = torch.empty(batch, nheads_k, 1, topk, dtype=torch.int32, device=q.device) if return_topk else None
+    lib = _lib.load()
+    ws_bytes = int(lib.ifv2_stage1_decode_workspace_bytes(batch, nheads_k, max_seqlen_k))
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("ifv2_stage1_decode_select", q.data_ptr(), k.data_ptr(), cu_seqlens_k.contiguous().data_ptr(),
+                  seqused_k.data_ptr() if seqused_k is not None else None, positions.contiguous().data_ptr(),
+                  mask.data_ptr(), idx.data_ptr() if idx is not None else None, batch, k.shape[0], nheads,
+                  nheads_k, d, max_seqlen_k, n_blocks, words, topk, local_blocks, init_blocks, block_size,
+                  stride, float(softmax_scale), int(bool(causal)), ws.data_ptr(), ws_bytes, _stream(q.device))
+    return (mask, idx) if return_topk else mask
+
+
 def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                  local_blocks, init_blocks, cache_len=0, cache_lens=None,
                                  max_cache_len=None, softmax_scale=None, causal=True,

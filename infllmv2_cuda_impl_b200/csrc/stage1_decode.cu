@@ -13,6 +13,7 @@
 // Output layout and values are those of the general kernel (ifv2_stage1_scores); e carries 8
 // mantissa bits, like the bf16 result it ends up in.
 #include "mma_sync.cuh"
+#include "decode_select.cuh"
 
 namespace ifv2 {
 namespace {
@@ -25,6 +26,7 @@ constexpr int kChunk = 512;                       // keys per CTA
 constexpr int kUnitsPerWarp = kChunk / kUnit / kWarps;
 constexpr int kWarpSmem = 2 * kUnit * 256;        // two K tiles per warp (double buffer)
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMaxChunksShared = 64;              // chunk statistics staged in shared memory up to here
 
 struct DecodeS1Params {
   const __nv_bfloat16* q;        // (batch, heads_q, 128): one token per sequence
@@ -215,17 +217,26 @@ __global__ void __launch_bounds__(kThreads) stage1_decode_normalise_kernel(const
     for (int i = c0 + threadIdx.x; i < end; i += kThreads) out_row[i] = __float2bfloat16_rn(0.f);
     return;
   }
+  // all chunk statistics of the pair come in side by side, then 16 threads merge them
+  __shared__ float2 stats_s[kMaxChunksShared][16];
+  const float2* st_g = p.stats + pair * p.chunks * 16;
+  const bool staged = p.chunks <= kMaxChunksShared;
+  if (staged) {
+    for (int i = threadIdx.x; i < p.chunks * 16; i += kThreads) stats_s[i >> 4][i & 15] = __ldg(st_g + i);
+    __syncthreads();
+  }
   if (threadIdx.x < 16) {
-    const float2* st = p.stats + pair * p.chunks * 16 + threadIdx.x;
+    const int hh = threadIdx.x;
+    auto stat = [&](int c) -> float2 { return staged ? stats_s[c][hh] : st_g[c * 16 + hh]; };
     float m = -INFINITY;
-    for (int c = 0; c < p.chunks; ++c) m = fmaxf(m, st[c * 16].x);
+    for (int c = 0; c < p.chunks; ++c) m = fmaxf(m, stat(c).x);
     float l = 0.f;
     for (int c = 0; c < p.chunks; ++c) {
-      const float2 v = st[c * 16];
+      const float2 v = stat(c);
       if (v.x > -INFINITY) l += v.y * exp2f(v.x - m);
     }
-    const float mine = st[chunk * 16].x;
-    weight[threadIdx.x] = (l > 0.f) ? exp2f(mine - m) / l : 0.f;
+    const float mine = stat(chunk).x;
+    weight[hh] = (l > 0.f) ? exp2f(mine - m) / l : 0.f;
   }
   __syncthreads();
   const __nv_bfloat16* e = p.e + pair * 16 * p.e_stride;
@@ -235,8 +246,8 @@ __global__ void __launch_bounds__(kThreads) stage1_decode_normalise_kernel(const
 #pragma unroll
       for (int r = 0; r < 16; ++r) {
         const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(e + r * p.e_stride + i));
-        a0 += v.x * weight[r];
-        a1 += v.y * weight[r];
+        a0 = fmaf(v.x, weight[r], a0);
+        a1 = fmaf(v.y, weight[r], a1);
       }
       if (i + 1 >= lim) a1 = 0.f;
     }
@@ -246,6 +257,96 @@ __global__ void __launch_bounds__(kThreads) stage1_decode_normalise_kernel(const
       out_row[i] = __float2bfloat16_rn(a0);
     }
   }
+}
+
+// Kernel 2, fused with the block selection: one CTA per (sequence, KV head) merges the chunk
+// statistics, forms the pair's whole score row in shared memory (the values kernel 2 would write,
+// bf16-rounded the same way) and goes straight on to max-pool, top-k and the packed block mask
+// (dsel::select_row).  The score row never reaches HBM.
+constexpr int kMaxChunks = 64;                    // 32768 compressed keys
+
+struct DecodeSelectParams {
+  DecodeS1Params s1;
+  const int32_t* positions;     // (batch) position of the query token in its sequence
+  unsigned long long* mask;     // (batch, heads_k, words)
+  int32_t* topk_idx;            // (batch, heads_k, k) or null
+  int block_size;
+  int row_bytes;                // bytes of the score row in shared memory (a multiple of 16)
+  dsel::Args a;
+};
+
+__global__ void __launch_bounds__(dsel::kThreads)
+stage1_decode_select_kernel(const DecodeSelectParams q) {
+  extern __shared__ __align__(16) uint8_t row_smem[];            // the score row, bf16
+  __shared__ dsel::Smem sm;
+  __shared__ float weight[kMaxChunks][16];
+  __shared__ float2 stats_s[kMaxChunks][16];
+  const DecodeS1Params& p = q.s1;
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int lc = used_keys(p, b);
+  const int lim = decode_limit(lc, p.causal);
+  const int64_t pair = (int64_t)b * p.heads_k + h;
+  const int chunks_used = (lim + kChunk - 1) / kChunk;
+  // the chunk statistics come in side by side (one trip to memory), then 16 threads merge them
+  {
+    const float2* st = p.stats + pair * p.chunks * 16;
+    for (int i = tid; i < chunks_used * 16; i += dsel::kThreads) stats_s[i >> 4][i & 15] = __ldg(st + i);
+  }
+  __syncthreads();
+  if (tid < 16) {
+    float m = -INFINITY;
+    for (int c = 0; c < chunks_used; ++c) m = fmaxf(m, stats_s[c][tid].x);
+    float l = 0.f;
+    for (int c = 0; c < chunks_used; ++c) {
+      const float2 v = stats_s[c][tid];
+      if (v.x > -INFINITY) l += v.y * exp2f(v.x - m);
+    }
+    for (int c = 0; c < chunks_used; ++c)
+      weight[c][tid] = (l > 0.f) ? exp2f(stats_s[c][tid].x - m) / l : 0.f;
+  }
+  __syncthreads();
+  __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(row_smem);
+  // staging tile behind the row: 16 head rows x 256 vectors of 8 keys.  A thread copies the 16
+  // vectors of its 8 keys with cp.async (all in flight at once, whatever the register budget) and
+  // is the only reader of what it copied, so a wait on its own copies is all the ordering needed.
+  uint4* tile = reinterpret_cast<uint4*>(row_smem + q.row_bytes);
+  const __nv_bfloat16* e = p.e + pair * 16 * p.e_stride;
+  const int n_vec = (lc + 7) / 8, n_vec_vis = (lim + 7) / 8;      // 8 keys per thread and trip
+  for (int v0 = 0; v0 < n_vec; v0 += dsel::kThreads) {
+    const int v = v0 + tid, i = v * 8;
+    if (v < n_vec_vis) {
+#pragma unroll
+      for (int r = 0; r < 16; ++r) cp_async16(tile + r * dsel::kThreads + tid, e + r * p.e_stride + i);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    if (v >= n_vec) continue;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (v < n_vec_vis) {
+      const float* w = weight[i / kChunk];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const uint4 raw = tile[r * dsel::kThreads + tid];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          acc[2 * j] = fmaf(f.x, w[r], acc[2 * j]);
+          acc[2 * j + 1] = fmaf(f.y, w[r], acc[2 * j + 1]);
+        }
+      }
+    }
+    uint4 out;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o2[j] = __floats2bfloat162_rn(i + 2 * j < lim ? acc[2 * j] : 0.f, i + 2 * j + 1 < lim ? acc[2 * j + 1] : 0.f);
+    reinterpret_cast<uint4*>(row)[v] = out;
+  }
+  __syncthreads();
+  dsel::select_row<__nv_bfloat16>(row, true, lc, q.positions[b] / q.block_size, q.a, sm,
+                                  q.mask + pair * q.a.words,
+                                  q.topk_idx ? q.topk_idx + pair * q.a.k : nullptr);
 }
 
 }  // namespace
@@ -261,34 +362,27 @@ extern "C" int64_t ifv2_stage1_decode_workspace_bytes(int batch, int heads_k, in
   return ((stats + 255) / 256) * 256 + e + 256;
 }
 
-extern "C" int ifv2_stage1_decode_scores(const void* q, const void* kc, void* out,
-                                         const int32_t* cu_seqlens_k, const int32_t* seqused_k,
-                                         int batch, int64_t total_c,
-                                         int heads_q, int heads_k, int head_dim, int max_seqlen_k,
-                                         int64_t out_row_stride, float softmax_scale, int causal,
-                                         void* workspace, int64_t workspace_bytes, void* stream) {
-  IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED,
-               "stage1_decode_scores: head_dim %d not supported (only 128)", head_dim);
+static int fill_decode_params(DecodeS1Params& p, const char* what, const void* q, const void* kc,
+                              const int32_t* cu_seqlens_k, const int32_t* seqused_k, int batch,
+                              int64_t total_c, int heads_q, int heads_k, int head_dim,
+                              int max_seqlen_k, float softmax_scale, int causal, void* workspace,
+                              int64_t workspace_bytes) {
+  IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED, "%s: head_dim %d not supported (only 128)", what,
+               head_dim);
   IFV2_REQUIRE(heads_k >= 1 && heads_q == heads_k * kGroup, IFV2_ERR_UNSUPPORTED,
-               "stage1_decode_scores: heads_q (%d) must be 16 x heads_k (%d)", heads_q, heads_k);
-  IFV2_REQUIRE(batch >= 0 && total_c >= 0 && max_seqlen_k >= 0, IFV2_ERR_INVALID_ARG,
-               "stage1_decode_scores: negative size");
-  if (batch == 0 || max_seqlen_k == 0) return IFV2_OK;
-  IFV2_REQUIRE(softmax_scale > 0.f, IFV2_ERR_INVALID_ARG, "stage1_decode_scores: softmax_scale must be > 0");
-  IFV2_REQUIRE(q && out && cu_seqlens_k && workspace && (kc || total_c == 0), IFV2_ERR_INVALID_ARG,
-               "stage1_decode_scores: null pointer");
-  IFV2_REQUIRE(out_row_stride >= max_seqlen_k && out_row_stride % 2 == 0 &&
-                   reinterpret_cast<uintptr_t>(out) % 4 == 0,
-               IFV2_ERR_INVALID_ARG, "stage1_decode_scores: out_row_stride must be even and >= max_seqlen_k");
+               "%s: heads_q (%d) must be 16 x heads_k (%d)", what, heads_q, heads_k);
+  IFV2_REQUIRE(batch >= 1 && total_c >= 0 && max_seqlen_k >= 1, IFV2_ERR_INVALID_ARG, "%s: bad size", what);
+  IFV2_REQUIRE(softmax_scale > 0.f, IFV2_ERR_INVALID_ARG, "%s: softmax_scale must be > 0", what);
+  IFV2_REQUIRE(q && cu_seqlens_k && workspace && (kc || total_c == 0), IFV2_ERR_INVALID_ARG,
+               "%s: null pointer", what);
   IFV2_REQUIRE(workspace_bytes >= ifv2_stage1_decode_workspace_bytes(batch, heads_k, max_seqlen_k) &&
                    reinterpret_cast<uintptr_t>(workspace) % 16 == 0,
-               IFV2_ERR_INVALID_ARG, "stage1_decode_scores: workspace too small or misaligned");
+               IFV2_ERR_INVALID_ARG, "%s: workspace too small or misaligned", what);
   IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535 && total_c <= INT32_MAX, IFV2_ERR_TOO_LARGE,
-               "stage1_decode_scores: batch, heads_k or key count too large");
-  DecodeS1Params p;
+               "%s: batch, heads_k or key count too large", what);
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.kc = static_cast<const __nv_bfloat16*>(kc);
-  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out = nullptr;
   p.cu_k = cu_seqlens_k;
   p.seqused_k = seqused_k;
   p.stats = static_cast<float2*>(workspace);
@@ -299,20 +393,88 @@ extern "C" int ifv2_stage1_decode_scores(const void* q, const void* kc, void* ou
   p.batch = batch;
   p.heads_q = heads_q;
   p.heads_k = heads_k;
-  p.chunks = (max_seqlen_k + kChunk - 1) / kChunk;
+  p.chunks = (int)n_chunks;
   p.max_seqlen_k = max_seqlen_k;
   p.causal = causal ? 1 : 0;
-  p.row_stride = out_row_stride;
+  p.row_stride = 0;
   p.scale_log2 = softmax_scale * kLog2e;
+  return IFV2_OK;
+}
+
+static int launch_decode_scores(const DecodeS1Params& p, cudaStream_t st) {
   const size_t smem = (size_t)kWarps * kWarpSmem;
-  cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaFuncSetAttribute(stage1_decode_scores_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error((int)e, "stage1_decode_scores: %s", cudaGetErrorString(e));
-  const dim3 grid(p.chunks, heads_k, batch);
-  stage1_decode_scores_kernel<<<grid, kThreads, smem, st>>>(p);
-  int rc = check_launch("stage1_decode_scores");
+  stage1_decode_scores_kernel<<<dim3(p.chunks, p.heads_k, p.batch), kThreads, smem, st>>>(p);
+  return check_launch("stage1_decode_scores");
+}
+
+extern "C" int ifv2_stage1_decode_scores(const void* q, const void* kc, void* out,
+                                         const int32_t* cu_seqlens_k, const int32_t* seqused_k,
+                                         int batch, int64_t total_c,
+                                         int heads_q, int heads_k, int head_dim, int max_seqlen_k,
+                                         int64_t out_row_stride, float softmax_scale, int causal,
+                                         void* workspace, int64_t workspace_bytes, void* stream) {
+  IFV2_REQUIRE(batch >= 0 && max_seqlen_k >= 0, IFV2_ERR_INVALID_ARG, "stage1_decode_scores: negative size");
+  if (batch == 0 || max_seqlen_k == 0) return IFV2_OK;
+  DecodeS1Params p;
+  int rc = fill_decode_params(p, "stage1_decode_scores", q, kc, cu_seqlens_k, seqused_k, batch, total_c,
+                              heads_q, heads_k, head_dim, max_seqlen_k, softmax_scale, causal, workspace,
+                              workspace_bytes);
   if (rc) return rc;
-  stage1_decode_normalise_kernel<<<grid, kThreads, 0, st>>>(p);
+  IFV2_REQUIRE(out != nullptr && out_row_stride >= max_seqlen_k && out_row_stride % 2 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 4 == 0,
+               IFV2_ERR_INVALID_ARG, "stage1_decode_scores: out_row_stride must be even and >= max_seqlen_k");
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.row_stride = out_row_stride;
+  cudaStream_t st = (cudaStream_t)stream;
+  rc = launch_decode_scores(p, st);
+  if (rc) return rc;
+  stage1_decode_normalise_kernel<<<dim3(p.chunks, heads_k, batch), kThreads, 0, st>>>(p);
   return check_launch("stage1_decode_normalise");
+}
+
+extern "C" int ifv2_stage1_decode_select(const void* q, const void* kc, const int32_t* cu_seqlens_k,
+                                         const int32_t* seqused_k, const int32_t* positions,
+                                         int64_t* mask, int32_t* topk_idx, int batch, int64_t total_c,
+                                         int heads_q, int heads_k, int head_dim, int max_seqlen_k,
+                                         int n_blocks, int mask_words, int k, int local_blocks,
+                                         int init_blocks, int block_size, int stride,
+                                         float softmax_scale, int causal, void* workspace,
+                                         int64_t workspace_bytes, void* stream) {
+  IFV2_REQUIRE(batch >= 0 && max_seqlen_k >= 0 && n_blocks >= 0 && mask_words >= 0 && k >= 0 &&
+                   local_blocks >= 0 && init_blocks >= 0,
+               IFV2_ERR_INVALID_ARG, "stage1_decode_select: negative size");
+  IFV2_REQUIRE(block_size >= 1 && stride >= 1 && block_size % stride == 0, IFV2_ERR_INVALID_ARG,
+               "stage1_decode_select: block_size must be a multiple of the compression stride");
+  IFV2_REQUIRE(n_blocks <= dsel::kMaxBlocks && mask_words <= dsel::kMaxBlocks / 64, IFV2_ERR_TOO_LARGE,
+               "stage1_decode_select: more than %d blocks", dsel::kMaxBlocks);
+  IFV2_REQUIRE(max_seqlen_k <= kMaxChunks * kChunk, IFV2_ERR_TOO_LARGE,
+               "stage1_decode_select: more than %d compressed keys per sequence", kMaxChunks * kChunk);
+  if (batch == 0 || mask_words == 0) return IFV2_OK;
+  IFV2_REQUIRE(positions && mask, IFV2_ERR_INVALID_ARG, "stage1_decode_select: null pointer");
+  IFV2_REQUIRE(max_seqlen_k >= 1, IFV2_ERR_INVALID_ARG,
+               "stage1_decode_select: needs at least one compressed key (use ifv2_decode_select on an "
+               "empty score row otherwise)");
+  DecodeSelectParams sp;
+  int rc = fill_decode_params(sp.s1, "stage1_decode_select", q, kc, cu_seqlens_k, seqused_k, batch, total_c,
+                              heads_q, heads_k, head_dim, max_seqlen_k, softmax_scale, causal, workspace,
+                              workspace_bytes);
+  if (rc) return rc;
+  sp.positions = positions;
+  sp.mask = reinterpret_cast<unsigned long long*>(mask);
+  sp.topk_idx = topk_idx;
+  sp.block_size = block_size;
+  sp.a = dsel::Args{n_blocks, mask_words, k, local_blocks, init_blocks, block_size / stride};
+  cudaStream_t st = (cudaStream_t)stream;
+  rc = launch_decode_scores(sp.s1, st);
+  if (rc) return rc;
+  sp.row_bytes = ((max_seqlen_k + 7) / 8) * 16;
+  const size_t smem = (size_t)sp.row_bytes + 16 * dsel::kThreads * sizeof(uint4);     // row + staging tile
+  cudaError_t e = cudaFuncSetAttribute(stage1_decode_select_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+  if (e != cudaSuccess) return set_error((int)e, "stage1_decode_select: %s", cudaGetErrorString(e));
+  stage1_decode_select_kernel<<<dim3(heads_k, batch), dsel::kThreads, smem, st>>>(sp);
+  return check_launch("stage1_decode_select");
 }

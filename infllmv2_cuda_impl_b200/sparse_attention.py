@@ -23,7 +23,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import ops
-from .attention import (infllmv2_attn_stage1, infllmv2_attn_varlen_func, infllmv2_attn_with_kvcache,
+from .attention import (infllmv2_attn_stage1, infllmv2_stage1_decode_select, infllmv2_attn_varlen_func, infllmv2_attn_with_kvcache,
                         infllmv2_stage1_block_scores, GROUP, HEAD_DIM)
 
 __all__ = ["SparseConfig", "DecodeCache", "SparseAttention"]
@@ -165,12 +165,14 @@ class SparseAttention:
                 score = infllmv2_attn_stage1(q3, kc_flat, cache.kc2.view(-1, hk, HEAD_DIM), cache.cu_q, cache.cu_c,
                                              cache.cu_c2, 1, max_c, causal=False, seqused_k=cache.n_comp,
                                              seqused_v=cache.n_comp2)
+                # pool + top-k + packed mask of the few decode rows in one launch
+                mask = ops.decode_select(score, cache.positions, c.topk, cache.capacity, c.local_blocks,
+                                         c.init_blocks, seqused_c=cache.n_comp)
             else:
-                score = infllmv2_attn_stage1(q3, kc_flat, kc_flat, cache.cu_q, cache.cu_c, cache.cu_c, 1, max_c,
-                                             causal=False, seqused_k=cache.n_comp)
-            # pool + top-k + packed mask of the few decode rows in one launch
-            mask = ops.decode_select(score, cache.positions, c.topk, cache.capacity, c.local_blocks,
-                                     c.init_blocks, seqused_c=cache.n_comp)
+                # scores, pool, top-k and mask in two launches; the score rows stay on chip
+                mask = infllmv2_stage1_decode_select(q3, kc_flat, cache.cu_c, cache.positions, max_c,
+                                                     cache.capacity, c.topk, c.local_blocks, c.init_blocks,
+                                                     seqused_k=cache.n_comp)
         return infllmv2_attn_with_kvcache(q3.view(b, 1, hk * GROUP, HEAD_DIM), cache.k, cache.v,
                                           cache_seqlens=cache.seqlens, softmax_scale=softmax_scale,
                                           block_mask=mask)

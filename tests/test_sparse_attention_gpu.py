@@ -175,3 +175,36 @@ def test_decode_graph_replay_equals_eager_steps():
     infllm_v2.check_device_status()
     assert caches[1].seqlens.tolist() == [l + steps for l in lens]
     assert torch.equal(caches[0].kc, caches[1].kc) and torch.equal(caches[0].k, caches[1].k)
+
+
+@pytest.mark.parametrize("cap,topk", [(2048, 8), (40000, 64)])
+def test_stage1_decode_select_equals_scores_then_select(cap, topk):
+    """The two-launch decode selection (scores stay on chip) against scorer -> decode_select, bit
+    for bit, on a per-sequence cache of compressed keys scored in place (seqused_k)."""
+    b, hk = 5, 2
+    rng = np.random.default_rng(cap)
+    lens = rng.integers(40, cap + 1, size=b)
+    lens[0], lens[-1] = 33, cap
+    n_c = np.where(lens >= 32, (lens - 32) // 16 + 1, 0).astype(np.int32)
+    c_cap = (cap - 32) // 16 + 1
+    max_c = int(n_c.max())
+    g = torch.Generator().manual_seed(cap)
+    kc = (torch.randn(b, c_cap, hk, D, generator=g) * 0.6).to(torch.bfloat16).to(DEV)
+    q = (torch.randn(b, hk * 16, D, generator=g) * 0.6).to(torch.bfloat16).to(DEV)
+    used = torch.tensor(n_c, device=DEV)
+    positions = torch.tensor(lens - 1, dtype=torch.int32, device=DEV)
+    cu_q = torch.arange(b + 1, dtype=torch.int32, device=DEV)
+    cu_c = cu_q * c_cap
+    flat = kc.view(-1, hk, D)
+    mask, idx = infllm_v2.infllmv2_stage1_decode_select(q, flat, cu_c, positions, max_c, cap, topk, 2, 1,
+                                                        seqused_k=used, return_topk=True)
+    score = infllm_v2.infllmv2_attn_stage1(q, flat, flat, cu_q, cu_c, cu_c, 1, max_c, causal=False, seqused_k=used)
+    ref_mask, ref_idx = infllm_v2.decode_select(score, positions, topk, cap, 2, 1, seqused_c=used, return_topk=True)
+    infllm_v2.check_device_status()
+    assert torch.equal(idx, ref_idx)
+    assert torch.equal(mask, ref_mask)
+    # the scores themselves against the oracle on the packed keys (seqused_k semantics)
+    packed = torch.cat([kc[i, :n_c[i]] for i in range(b)]).cpu()
+    cu_p = np.concatenate([[0], np.cumsum(n_c)])
+    exp = oracle.stage1_scores(q.cpu(), packed, list(range(b + 1)), cu_p.tolist(), max_c, False)
+    assert (score.float().cpu() - exp).abs().max().item() <= 2e-2
