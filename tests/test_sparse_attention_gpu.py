@@ -115,6 +115,41 @@ def test_short_sequences_attend_densely():
     assert mx <= 2e-2 and mr <= 1e-2
 
 
+@pytest.mark.parametrize("hk,lens,topk,local,init", [(1, [65, 257, 31], 4, 0, 2), (4, [130], 6, 2, 1),
+                                                     (2, [16, 40], 3, 1, 1)])
+def test_decode_other_shapes(hk, lens, topk, local, init):
+    """Other head counts, forced-block settings and sequences that start below one compression
+    window: 24 decoded tokens each against the oracle's dense-with-mask attention under the
+    oracle's own selection for that token (rows whose bf16 block scores tie differently excepted)."""
+    cfg = _config(topk=topk, local_blocks=local, init_blocks=init)
+    layer = infllm_v2.SparseAttention(cfg)
+    steps, cap = 24, 320
+    g = torch.Generator().manual_seed(sum(lens) + hk)
+    qs = [(torch.randn(l + steps, hk * 16, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    ks = [(torch.randn(l + steps, hk, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    vs = [torch.randn(l + steps, hk, D, generator=g).to(torch.bfloat16) for l in lens]
+    pack = lambda ts, n: torch.cat([t[:l + n] for t, l in zip(ts, lens)])
+    cache = infllm_v2.DecodeCache(len(lens), cap, hk, cfg, DEV)
+    layer.prefill(pack(qs, 0).to(DEV), pack(ks, 0).to(DEV), pack(vs, 0).to(DEV), cu(lens, DEV), max(lens),
+                  seqlens=lens, cache=cache)
+    agree = []
+    for s in range(steps):
+        stack = lambda ts: torch.stack([t[l + s] for t, l in zip(ts, lens)])
+        out = layer.decode(stack(qs).to(DEV), stack(ks).to(DEV), stack(vs).to(DEV), cache)
+        if s % 5:
+            continue
+        grown = [l + s + 1 for l in lens]
+        exp_idx, _ = _oracle_selection(pack(qs, s + 1), pack(ks, s + 1), grown, cfg)
+        ref, _ = oracle.sparse_attention_fwd(pack(qs, s + 1), pack(ks, s + 1), pack(vs, s + 1), cu(grown).tolist(),
+                                             cu(grown).tolist(), exp_idx)
+        last = torch.tensor(np.cumsum(grown) - 1)
+        err = (out[:, 0].float().cpu() - ref[last]).abs().amax(-1)
+        agree.append((err <= 2e-2).float().mean().item())
+    infllm_v2.check_device_status()
+    assert cache.seqlens.tolist() == [l + steps for l in lens]
+    assert np.mean(agree) > 0.9, agree
+
+
 @pytest.mark.parametrize("coarse", [False, True])
 def test_decode_continues_prefill(coarse):
     """Prefill L tokens into a cache, decode 40 more one at a time: every decoded token equals the
