@@ -265,7 +265,8 @@ def gen_compress(mods, out):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("INFLLMV2_REFERENCE"), required="INFLLMV2_REFERENCE" not in os.environ,
+                    help="checkout of OpenBMB/infllmv2_cuda_impl (or set INFLLMV2_REFERENCE)")
     args = ap.parse_args()
     torch.set_num_threads(8)
     mods = _import_reference(args.reference)
