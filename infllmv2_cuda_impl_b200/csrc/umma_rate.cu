@@ -139,3 +139,72 @@ extern "C" int ifv2_umma_rate(int a, int b, int n, int accs, int steps, int rand
 #undef IFV2_RATE_CASE
   return set_error(IFV2_ERR_INVALID_ARG, "umma_rate: variant not instantiated");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Throughput of the exponential forms a softmax loop can use, on one SM: 1024 threads each run
+// `iters` rounds of eight independent exponentials and keep a running sum; the clock count of the
+// slowest warp over the number of values gives values per clock per SM.  mode 0: ex2.approx.ftz.f32
+// (one value per instruction), 1: ex2.approx.ftz.bf16x2 (two), 2: ex2.approx.f16x2 (two),
+// 3: the degree-3 polynomial on the FMA pipe (exp2_fma).  Tuning aid only.
+namespace ifv2 {
+namespace {
+
+template <int kMode>
+__global__ void __launch_bounds__(1024) ex2_rate_kernel(int iters, long long* cycles, float* sink) {
+  float x[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = -0.01f * (float)(threadIdx.x % 61) - 0.125f * (float)j;
+  float acc = 0.f;
+  uint32_t pacc = 0;
+  __syncthreads();
+  const long long t0 = clock64();
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (kMode == 0) {
+        acc += exp2f(x[j]);
+      } else if (kMode == 3) {
+        acc += tc::exp2_fma(x[j]);
+      } else {
+        // two values per instruction; the packed results are folded with an xor so that the
+        // measured loop holds the exponential and one cheap integer op per pair
+        uint32_t in, out;
+        if (kMode == 1) {
+          asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(in) : "f"(x[j]), "f"(x[j] - 0.5f));
+          asm volatile("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(out) : "r"(in));
+        } else {
+          asm volatile("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(in) : "f"(x[j]), "f"(x[j] - 0.5f));
+          asm volatile("ex2.approx.f16x2 %0, %1;" : "=r"(out) : "r"(in));
+        }
+        pacc ^= out;
+      }
+      x[j] -= 1e-6f;
+    }
+  }
+  const long long t1 = clock64();
+  __shared__ long long worst;
+  if (threadIdx.x == 0) worst = 0;
+  __syncthreads();
+  atomicMax(reinterpret_cast<unsigned long long*>(&worst), (unsigned long long)(t1 - t0));
+  __syncthreads();
+  if (threadIdx.x == 0) *cycles = worst;
+  if (acc == 123.456f || pacc == 0x12345678u) *sink = acc;      // keep the results alive
+}
+
+}  // namespace
+}  // namespace ifv2
+
+// Values per instruction: 1 for modes 0 and 3, 2 for modes 1 and 2.  cycles: SM clocks of the slowest
+// warp for 1024 threads x iters x 8 instructions.
+extern "C" int ifv2_ex2_rate(int mode, int iters, long long* cycles, float* sink, void* stream) {
+  IFV2_REQUIRE(cycles && sink && iters > 0 && mode >= 0 && mode <= 3, IFV2_ERR_INVALID_ARG,
+               "ex2_rate: bad argument");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (mode) {
+    case 0: ex2_rate_kernel<0><<<1, 1024, 0, s>>>(iters, cycles, sink); break;
+    case 1: ex2_rate_kernel<1><<<1, 1024, 0, s>>>(iters, cycles, sink); break;
+    case 2: ex2_rate_kernel<2><<<1, 1024, 0, s>>>(iters, cycles, sink); break;
+    default: ex2_rate_kernel<3><<<1, 1024, 0, s>>>(iters, cycles, sink); break;
+  }
+  return check_launch("ex2_rate");
+}

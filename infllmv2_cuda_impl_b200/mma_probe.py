@@ -40,6 +40,25 @@ def clocks_per_mma(a, b, n, accs=1, steps=8, nonzero=0, stage_stride=0, commits=
     return (res[1] - res[0]) / 200.0 / steps
 
 
+def exp_values_per_clock(mode):
+    """Exponentials per SM clock of one form (`ifv2_ex2_rate`: 0 ex2.f32, 1 ex2.bf16x2, 2 ex2.f16x2,
+    3 degree-3 polynomial on the FMA pipe), 1024 threads on one SM, two run lengths."""
+    lib = _lib.load()
+    fn = lib.ifv2_ex2_rate
+    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    cyc = torch.zeros(1, dtype=torch.int64, device="cuda")
+    sink = torch.zeros(1, dtype=torch.float32, device="cuda")
+    res = []
+    for iters in (2000, 4000):
+        if fn(mode, iters, cyc.data_ptr(), sink.data_ptr(), None) != 0:
+            raise RuntimeError(lib.ifv2_last_error().decode(errors="replace"))
+        torch.cuda.synchronize()
+        res.append(int(cyc[0]))
+    per_instr = 2 if mode in (1, 2) else 1
+    return 1024 * 2000 * 8 * per_instr / (res[1] - res[0])
+
+
 def main():
     if not torch.cuda.is_available():
         sys.exit("mma_probe needs a GPU")
@@ -55,6 +74,10 @@ def main():
     for a, b, n, steps, commits, clk in rows:
         print(f"{_A[a]} {_B[b]}  {n:4d}  {steps:6d}     {commits:6d}      {clk:7.1f}  "
               f"{128 * n * 32 / clk:9.0f}")
+    print("exponentials per clock per SM:")
+    for mode, name in ((0, "ex2.approx.ftz.f32"), (1, "ex2.approx.ftz.bf16x2 (+ cvt)"), (2, "ex2.approx.f16x2 (+ cvt)"),
+                       (3, "degree-3 polynomial, FMA pipe")):
+        print(f"  {name:32s} {exp_values_per_clock(mode):6.1f}")
 
 
 if __name__ == "__main__":
