@@ -651,6 +651,54 @@ def config5_decode(device, pk, small=False):
     return out
 
 
+def sharded_prefill_bench(device, rank, world, seqlen=SEQLEN, hk=2, reps=5):
+    """Query-chunk-parallel prefill of ONE sequence with fewer KV heads than GPUs (32q/2kv heads):
+    every rank owns two zig-zag query chunks, K / V / compressed K are all-gathered over NCCL into
+    local HBM, then each chunk runs the normal kernels.  Reports the all-gather separately."""
+    from infllmv2_cuda_impl_b200 import sharding
+    import infllm_v2
+    g = torch.Generator(device=device).manual_seed(rank)
+    s = 1.0 / math.sqrt(D)
+    rows = seqlen // world                                     # two chunks of seqlen / (2 world) tokens
+    q = (torch.randn(rows, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    k = (torch.randn(rows, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    v = (torch.randn(rows, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    kc = (torch.randn(rows // STRIDE, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+
+    def gather():
+        return [sharding.gather_sequence(t, world) for t in (k, v, kc)]
+
+    def step():
+        return sharding.sharded_prefill(q, k, v, kc, seqlen, world, rank, TOPK, INIT_BLOCKS, LOCAL_BLOCKS)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / reps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_gather, t_step = timed(gather), timed(step)
+    infllm_v2.check_device_status()
+    gathered = (2 * seqlen * hk * D + (seqlen // STRIDE) * hk * D) * 2
+    return {"sharded_prefill_131072_32q2kv": {
+        "n_gpus": world, "ms_step": round(t_step, 3), "ms_allgather": round(t_gather, 3),
+        "tokens_per_s": round(seqlen / (t_step * 1e-3), 1),
+        "allgather_bytes_per_rank": gathered, "allgather_gbs": round(gathered / t_gather / 1e6, 1),
+        "note": "one sequence, query chunks in zig-zag order over the ranks; step = all-gather of K, V and "
+                "compressed K into local HBM + fused stage 1 / top-k / mask / stage-2 forward per chunk; "
+                "max over ranks"}}
+
+
 # ------------------------------------------------------------------------------ CPU oracle ----
 
 def cpu_sample(seqlen, sample_tokens, threads):
@@ -717,7 +765,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true",
                     help="run stage 1 and the max-pool as two kernels (the reference's op sequence)")
-    ap.add_argument("--only", default=None, choices=["selection", "topk", "compress", "coarse", "train", "decode"],
+    ap.add_argument("--only", default=None, choices=["selection", "topk", "compress", "coarse", "train", "decode", "sharded"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
     ap.add_argument("--e2e-order", default="middle-out", choices=["middle-out", "ascending"],
@@ -747,6 +795,15 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+    if args.only == "sharded":
+        if world < 2:
+            raise SystemExit("--only sharded needs at least two ranks (torchrun)")
+        res = sharded_prefill_bench(device, rank, world, args.seqlen)
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     if args.only is not None:
         print(json.dumps(extra_configs(device, peaks()[0], args.only, args.small)), flush=True)
         return

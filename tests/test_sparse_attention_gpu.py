@@ -243,3 +243,27 @@ def test_stage1_decode_select_equals_scores_then_select(cap, topk):
     cu_p = np.concatenate([[0], np.cumsum(n_c)])
     exp = oracle.stage1_scores(q.cpu(), packed, list(range(b + 1)), cu_p.tolist(), max_c, False)
     assert (score.float().cpu() - exp).abs().max().item() <= 2e-2
+
+
+def test_cache_capacity_limits():
+    """Rows past the capacity are dropped by cache_fill; a full cache is left untouched by
+    decode_append and refused by the layer before anything is launched."""
+    cfg = _config()
+    lens, cap = [100, 40], 64
+    k = det_tensor((sum(lens), HK, D), 71, 0.5)
+    v = det_tensor((sum(lens), HK, D), 72, 1.0)
+    kc, cu_c = oracle.compress_keys(k, cu(lens), 32, 16)
+    cache = infllm_v2.DecodeCache(len(lens), cap, HK, cfg, DEV)
+    cache.fill(k.to(DEV), v.to(DEV), kc.to(DEV), cu(lens, DEV), torch.tensor(cu_c, dtype=torch.int32, device=DEV),
+               max(lens))
+    assert cache.seqlens.tolist() == [64, 40] and cache.max_len == 64
+    assert cache.n_comp.tolist() == [min(5, cache.c_capacity), 1]
+    assert torch.equal(cache.k[0].cpu(), k[:64]) and torch.equal(cache.k[1, :40].cpu(), k[100:])
+    before = cache.k.clone()
+    kn = det_tensor((2, HK, D), 73, 0.5).to(DEV)
+    infllm_v2.decode_append(kn, kn, cache.k, cache.v, cache.seqlens, cache.positions, cache.kc, cache.n_comp)
+    torch.cuda.synchronize()
+    assert cache.seqlens.tolist() == [64, 41] and cache.positions.tolist() == [64, 40]
+    assert torch.equal(cache.k[0], before[0]) and torch.equal(cache.k[1, 40].cpu(), kn[1].cpu())
+    with pytest.raises(RuntimeError):
+        infllm_v2.SparseAttention(cfg).decode(det_tensor((2, HQ, D), 74, 0.5).to(DEV), kn, kn, cache)
