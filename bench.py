@@ -668,8 +668,9 @@ def sharded_prefill_bench(device, rank, world, seqlen=SEQLEN, hk=2, reps=5):
     def gather():
         return [sharding.gather_sequence(t, world) for t in (k, v, kc)]
 
-    def step():
-        return sharding.sharded_prefill(q, k, v, kc, seqlen, world, rank, TOPK, INIT_BLOCKS, LOCAL_BLOCKS)
+    def step(overlap=True):
+        return sharding.sharded_prefill(q, k, v, kc, seqlen, world, rank, TOPK, INIT_BLOCKS, LOCAL_BLOCKS,
+                                        overlap=overlap)
 
     def timed(fn):
         for _ in range(3):
@@ -688,10 +689,12 @@ def sharded_prefill_bench(device, rank, world, seqlen=SEQLEN, hk=2, reps=5):
         return float(t.item())
 
     t_gather, t_step = timed(gather), timed(step)
+    t_serial = timed(lambda: step(False))
     infllm_v2.check_device_status()
     gathered = (2 * seqlen * hk * D + (seqlen // STRIDE) * hk * D) * 2
     return {"sharded_prefill_131072_32q2kv": {
-        "n_gpus": world, "ms_step": round(t_step, 3), "ms_allgather": round(t_gather, 3),
+        "n_gpus": world, "ms_step": round(t_step, 3), "ms_step_gather_first": round(t_serial, 3),
+        "ms_allgather": round(t_gather, 3),
         "tokens_per_s": round(seqlen / (t_step * 1e-3), 1),
         "allgather_bytes_per_rank": gathered, "allgather_gbs": round(gathered / t_gather / 1e6, 1),
         "note": "one sequence, query chunks in zig-zag order over the ranks; step = all-gather of K, V and "

@@ -151,19 +151,16 @@ class PrefillOps:
                           attention.infllmv2_stage1_block_scores)
 
 
-def prefill_chunk(q_chunk: torch.Tensor, kc: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-                  chunk: Chunk, topk: int, init_blocks: int, local_blocks: int,
-                  ops: Optional[PrefillOps] = None, block_size: int = 64, kernel: int = 32,
-                  stride: int = 16) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Full two-stage pipeline for the query tokens [chunk.start, chunk.end) of one sequence
-    against the keys before chunk.end.  kc, k, v hold (at least) the sequence prefix up to
-    chunk.end.  Returns (out_chunk, topk_idx_chunk)."""
+def chunk_selection(q_chunk: torch.Tensor, kc: torch.Tensor, chunk: Chunk, topk: int, init_blocks: int,
+                    local_blocks: int, ops: Optional[PrefillOps] = None, block_size: int = 64,
+                    kernel: int = 32, stride: int = 16) -> torch.Tensor:
+    """Stage 1 + pool + top-k for the query tokens [chunk.start, chunk.end) of one sequence: needs
+    the compressed keys of the prefix up to chunk.end only.  Returns topk_idx (Hk, lq, topk)."""
     ops = ops or PrefillOps.cuda()
     dev = q_chunk.device
     lq, lk = chunk.end - chunk.start, chunk.end
     n_comp = (lk - kernel) // stride + 1 if lk >= kernel else 0
     cu_q = torch.tensor([0, lq], dtype=torch.int32, device=dev)
-    cu_k = torch.tensor([0, lk], dtype=torch.int32, device=dev)
     cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=dev)
     kc_p = kc[:n_comp]
     if ops.block_scores is not None and block_size == 64 and stride == 16:
@@ -172,30 +169,67 @@ def prefill_chunk(q_chunk: torch.Tensor, kc: torch.Tensor, k: torch.Tensor, v: t
     else:
         score = ops.stage1(q_chunk, kc_p, kc_p, cu_q, cu_c, cu_c, lq, n_comp, causal=True)
         pooled = ops.max_pool(score, chunk.start, local_blocks, init_blocks, block_size, stride)
-    idx = ops.topk(pooled, topk, chunk.start)
-    out = ops.attn(q_chunk, k[:lk], v[:lk], cu_q, cu_k, lq, lk, causal=True, topk_idx=idx)
-    return out, idx
+    return ops.topk(pooled, topk, chunk.start)
+
+
+def chunk_attention(q_chunk: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk: Chunk,
+                    idx: torch.Tensor, ops: Optional[PrefillOps] = None) -> torch.Tensor:
+    """Stage 2 for the same chunk against the keys / values of the prefix up to chunk.end."""
+    ops = ops or PrefillOps.cuda()
+    dev = q_chunk.device
+    lq, lk = chunk.end - chunk.start, chunk.end
+    cu_q = torch.tensor([0, lq], dtype=torch.int32, device=dev)
+    cu_k = torch.tensor([0, lk], dtype=torch.int32, device=dev)
+    return ops.attn(q_chunk, k[:lk], v[:lk], cu_q, cu_k, lq, lk, causal=True, topk_idx=idx)
+
+
+def prefill_chunk(q_chunk: torch.Tensor, kc: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                  chunk: Chunk, topk: int, init_blocks: int, local_blocks: int,
+                  ops: Optional[PrefillOps] = None, block_size: int = 64, kernel: int = 32,
+                  stride: int = 16) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Full two-stage pipeline for the query tokens [chunk.start, chunk.end) of one sequence
+    against the keys before chunk.end.  kc, k, v hold (at least) the sequence prefix up to
+    chunk.end.  Returns (out_chunk, topk_idx_chunk)."""
+    idx = chunk_selection(q_chunk, kc, chunk, topk, init_blocks, local_blocks, ops, block_size, kernel, stride)
+    return chunk_attention(q_chunk, k, v, chunk, idx, ops), idx
 
 
 def sharded_prefill(q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
                     kc_local: torch.Tensor, seqlen: int, world: int, rank: int, topk: int,
                     init_blocks: int, local_blocks: int, ops: Optional[PrefillOps] = None,
-                    group=None, stride: int = 16) -> torch.Tensor:
+                    group=None, stride: int = 16, overlap: bool = True) -> torch.Tensor:
     """Query-chunk-parallel prefill of ONE sequence.  Every rank passes the rows of its two
     zig-zag chunks (concatenated): q_local (2*clen, Hq, d), k_local / v_local (2*clen, Hk, d) and
     kc_local (2*clen/stride, Hk, d) -- the compressed keys whose first token lies in the chunk;
     the slot of the sequence's last, incomplete window is padding.  Returns the attention output
-    for the local rows, in the same order."""
+    for the local rows, in the same order.
+
+    The small compressed keys are gathered first and the selection of both chunks starts on them;
+    on CUDA the all-gather of K and V runs on a side stream meanwhile and stage 2 waits for it."""
     chunks = zigzag_chunks(seqlen, world, rank)
-    k = gather_sequence(k_local, world, group)
-    v = gather_sequence(v_local, world, group)
-    kc = gather_sequence(kc_local, world, group)
     clen = chunks[0].end - chunks[0].start
-    outs = []
-    for i, ch in enumerate(chunks):
-        out, _ = prefill_chunk(q_local[i * clen:(i + 1) * clen], kc, k, v, ch, topk, init_blocks,
-                               local_blocks, ops, stride=stride)
-        outs.append(out)
+    kc = gather_sequence(kc_local, world, group)
+    side = ready = None
+    if overlap and q_local.is_cuda and world > 1:
+        cur = torch.cuda.current_stream(q_local.device)
+        side = torch.cuda.Stream(device=q_local.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            k = gather_sequence(k_local, world, group)
+            v = gather_sequence(v_local, world, group)
+            ready = torch.cuda.Event()
+            ready.record(side)
+    else:
+        k = gather_sequence(k_local, world, group)
+        v = gather_sequence(v_local, world, group)
+    idxs = [chunk_selection(q_local[i * clen:(i + 1) * clen], kc, ch, topk, init_blocks, local_blocks, ops,
+                            stride=stride) for i, ch in enumerate(chunks)]
+    if ready is not None:
+        cur.wait_event(ready)
+        k.record_stream(cur)                      # allocated on the side stream, consumed on this one
+        v.record_stream(cur)
+    outs = [chunk_attention(q_local[i * clen:(i + 1) * clen], k, v, ch, idxs[i], ops)
+            for i, ch in enumerate(chunks)]
     return torch.cat(outs, dim=0)
 
 
