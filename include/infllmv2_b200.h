@@ -33,6 +33,21 @@ const char* ifv2_last_error(void);
 /* Library version, for loaders that want to check what they bound. */
 int ifv2_version(void);
 
+/* The status block of the tensor-core kernels (stage 1, stage-2 forward and backward): int32[4]
+ * device words owned by the caller, zero-initialised once.  Every wait inside those kernels is
+ * bounded (about 0.3 s); a wait that runs out stores its site code in
+ *   word 0: the flag of the RUNNING launch.  Each entry point clears it on the stream before it
+ *           launches; thread blocks that start after a failure see it and return at once, so a
+ *           failed launch ends quickly and leaves its outputs undefined;
+ *   word 1: sticky.  It keeps the first failing site of any launch until ifv2_check_status.
+ * A failed launch therefore never disables later launches, and it cannot go unnoticed by a caller
+ * that checks: ifv2_check_status is the ONE entry point that synchronises -- it waits for
+ * `stream`, reads the block, clears it, and returns IFV2_ERR_DEVICE_STATUS (site code in
+ * ifv2_last_error) if any launch since the last check abandoned a wait, else 0.  Call it where
+ * the host synchronises anyway (end of a step, before results are consumed).  No counterpart in
+ * the reference, whose kernels have no waits that can run out. */
+int ifv2_check_status(int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------- bitmask kernels ---------- */
 
 /* Rows of block indices -> rows of 64-bit words (bit idx%64 of word idx/64; indices outside
@@ -172,7 +187,7 @@ int ifv2_decode_select(const void* score, int is_bf16, int64_t row_stride, const
  * reference's seqused_k, flash_api.cpp:792, 906-911; block_info.h:24); cu_seqlens_k then only
  * gives where a sequence's keys start, e.g. b * capacity for a per-sequence cache of compressed
  * keys.  seqused_v: the same for lse_keys / cu_seqlens_v.
- * status: int32[4] device words, word 0 != 0 after the launch means a bounded wait ran out.
+ * status: the int32[4] status block described at ifv2_check_status.
  * Replaces C.varlen_fwd_stage1: csrc/entry.cu:209-214 -> mha_varlen_fwd_stage1,
  * csrc/flash_attn/flash_api.cpp:784-1049 (+ the GQA transpose, slice and NaN scrub of
  * infllm_v2/infllmv2_sparse_attention.py:554-589). */
@@ -280,7 +295,11 @@ int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void* k, const v
  * query row) is a 16 MiB array built into the library and resident on every GPU that loads it.
  * Limit: total_q * heads_q <= 4194304 rows; larger calls return IFV2_ERR_TOO_LARGE.
  * The first call on each device looks the array's device address up (with that device
- * current); make that first call before any stream capture begins.  All calls on a device share
+ * current); make that first call before any stream capture begins.  With CUDA's lazy module
+ * loading the 16 MiB are only reserved when the library's device code is first loaded on a GPU
+ * (its first kernel launch there, or this look-up), so also make that first call -- or any launch
+ * from this library under CUDA_MODULE_LOADING=EAGER -- BEFORE the host engine reserves the rest
+ * of the device memory; afterwards it can fail with an out-of-memory error.  All calls on a device share
  * the array: two calls whose kernels overlap on the GPU (different streams) race on it.  Nothing
  * in it needs clearing between calls.  No cudaMalloc, cudaFree or allocating library routine
  * is called.  This entry point has no counterpart in the reference. */
@@ -301,6 +320,10 @@ int64_t ifv2_decode_workspace_bytes(int batch, int heads_q, int head_dim, int ma
  * 128) bf16 with `cache_batch_stride` elements between sequences; k_new/v_new (batch, heads_k,
  * 128) or null are first written in place at position cache_seqlens[b]; mask: (batch, heads_k,
  * mask_words) words or null; lse: (batch, heads_q) fp32 or null.
+ * A sequence attends positions [0, min(cache_seqlens[b] + new, cache_capacity)): when
+ * cache_seqlens[b] >= cache_capacity the new token has no room, is NOT appended and is not
+ * attended, and a length beyond the capacity reads only the positions that exist (the host cannot
+ * reject this without a device synchronisation, so the kernels define it instead).
  * Replaces C.fwd_kvcache: csrc/entry.cu:209-214 -> mha_fwd_kvcache,
  * csrc/flash_attn/flash_api.cpp:1549-1843. */
 int ifv2_decode(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
@@ -337,6 +360,22 @@ int ifv2_decode_paged(const void* q, void* k_cache, void* v_cache, const void* k
                       const int32_t* block_table, int block_table_stride, int page_size,
                       const int32_t* cache_batch_idx, const int32_t* cache_leftpad,
                       float softmax_scale, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------- self-tests -------------- */
+/* Test infrastructure shipped in the library so that a deployment can check the tensor-core
+ * building blocks on its own GPU; not part of the attention path.  No counterpart in the
+ * reference.
+ * ifv2_selftest_umma: one tile product through TMA + tcgen05 in the operand arrangement `mode`
+ *   (0: Q.K^T shape, 1/2: P.V with P in shared memory / TMEM, 3: MN-major x MN-major,
+ *   4/5: thread-written K-major tiles without / with the 32-byte swizzle); d receives fp32.
+ * ifv2_selftest_wait_timeout: makes a bounded wait run out on purpose, safely: a kernel waits at
+ *   most limit_cycles (<= 2^24) SM clocks on a barrier that nothing arms, stores `site` in the
+ *   status block, frees its tensor memory and returns; result: int32[3] = {abort flag seen by
+ *   the block, kernel reached its end, the wait returned "gave up"}. */
+int ifv2_selftest_umma(int mode, const void* a, const void* b, float* d, int32_t* status,
+                       void* stream);
+int ifv2_selftest_wait_timeout(int32_t* status, int64_t limit_cycles, int site, int32_t* result,
+                               void* stream);
 
 #ifdef __cplusplus
 }

@@ -9,8 +9,7 @@ import re
 import threading
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-# IFV2_LIBRARY_PATH points at another build of the same library (e.g. one compiled with tuning macros)
-LIB_PATH = os.environ.get("IFV2_LIBRARY_PATH") or os.path.join(_PKG_DIR, "libinfllmv2_b200.so")
+LIB_PATH = os.path.join(_PKG_DIR, "libinfllmv2_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_PKG_DIR), "include", "infllmv2_b200.h")
 
 _lib = None
@@ -20,6 +19,9 @@ c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int6
 
 # name -> argtypes, mirroring include/infllmv2_b200.h (every pointer is passed as an address)
 SIGNATURES = {
+    "ifv2_check_status": [c_void_p, c_void_p],
+    "ifv2_selftest_umma": [c_int] + [c_void_p] * 5,
+    "ifv2_selftest_wait_timeout": [c_void_p, c_int64, c_int, c_void_p, c_void_p],
     "ifv2_topk_to_uint64": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     "ifv2_blockmask_to_uint64": [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     "ifv2_uint64_to_bool": [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],

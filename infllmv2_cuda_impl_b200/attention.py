@@ -8,6 +8,7 @@ Features the reference's build compiles out (dropout, softcap, ALiBi, sliding wi
 head_dim != 128, GQA group != 16) raise on the host, as its TORCH_CHECKs do.
 """
 import math
+import os
 from typing import Optional, Tuple, Union
 
 import torch
@@ -20,6 +21,7 @@ GROUP = 16        # query heads per KV head (the reference's m_block_dim)
 HEAD_DIM = 128
 
 _status = {}
+_CHECK_STATUS = os.environ.get("IFV2_CHECK_STATUS", "0") == "1"
 
 
 def _status_words(device) -> torch.Tensor:
@@ -32,16 +34,18 @@ def _status_words(device) -> torch.Tensor:
 
 
 def check_device_status(device=None) -> None:
-    """Synchronise and raise if any kernel launched through this module gave up on a wait.
-    Not called on the hot path; tests, the smoke entry and the benchmark call it."""
+    """Wait for the current stream and raise if any kernel launched through this module since the
+    last check gave up on one of its bounded waits (the outputs of that launch are undefined; later
+    launches ran normally).  Not called on the hot path because it synchronises: tests, the smoke
+    entry and the benchmark call it, and so does the backward of infllmv2_attn_varlen_func when the
+    environment variable IFV2_CHECK_STATUS=1 is set."""
     devices = list(_status) if device is None else [torch.device(device).index or 0]
     for idx in devices:
         if idx in _status:
-            torch.cuda.synchronize(idx)
-            code = int(_status[idx][0].item())
-            if code != 0:
-                _status[idx].zero_()
-                raise _lib.Ifv2Error(f"a kernel on cuda:{idx} abandoned a bounded wait (site {code})")
+            with torch.cuda.device(idx):
+                torch.cuda.synchronize(idx)
+                _lib.call("ifv2_check_status", _status[idx].data_ptr(),
+                          torch.cuda.current_stream(idx).cuda_stream)
 
 
 def _stream(device) -> int:
@@ -373,6 +377,8 @@ class Infllmv2AttnVarlenFunc(torch.autograd.Function):
         dq, dk, dv = _infllmv2_attn_varlen_backward(
             dout, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, ctx.max_seqlen_q,
             ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal, fwd_mask)
+        if _CHECK_STATUS:
+            check_device_status(q.device)
         return (dq, dk, dv) + (None,) * 14
 
 

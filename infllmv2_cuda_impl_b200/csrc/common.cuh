@@ -21,6 +21,9 @@ char* error_buffer();
 int set_error(int code, const char* fmt, ...);
 // Checks the launch of the kernel just enqueued; returns 0 or the positive cudaError_t.
 int check_launch(const char* what);
+// Clears word 0 of a kernel status block (the flag of the launch about to be enqueued) on the
+// stream; word 1 keeps the first failure until ifv2_check_status.  Returns 0 or a cudaError_t.
+int clear_launch_status(int32_t* status, void* stream, const char* what);
 
 #define IFV2_REQUIRE(cond, code, ...)                          \
   do {                                                         \

@@ -38,6 +38,7 @@ struct DecodeParams {
   int mask_words;
   const int32_t* cache_seqlens;
   int new_tokens;                 // 1 when k_new / v_new were appended, else 0
+  int64_t capacity;               // positions a sequence may use; lengths are clamped to it
   int heads_q, heads_k;
   int64_t batch_stride;           // elements between sequences in the caches
   const int32_t* block_table;     // (batch, bt_stride) page of every page_size positions, or null
@@ -126,7 +127,10 @@ __global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM) decode_spli
   uint8_t* v_tile = k_tile + kUnit * 256;
 
   const int pad = p.leftpad ? p.leftpad[b] : 0;                 // keys are positions pad .. end-1
-  const int len = p.cache_seqlens[b] + p.new_tokens - pad;
+  // a length beyond the capacity is a caller error with a defined result: the keys are the
+  // positions that exist, and the new token counts only if the append had room for it
+  const int64_t end = min(max((int64_t)p.cache_seqlens[b], (int64_t)0) + p.new_tokens, p.capacity);
+  const int len = (int)max(end - pad, (int64_t)0);
   const int slot = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
   BlockList list{p.mask ? p.mask + ((int64_t)b * p.heads_k + h) * p.mask_words : nullptr, p.mask_words,
                  (len + kBlockN - 1) / kBlockN};
@@ -479,6 +483,7 @@ static int decode_impl(const void* q, void* k_cache, void* v_cache, const void* 
   p.mask_words = mask_words;
   p.cache_seqlens = cache_seqlens;
   p.new_tokens = k_new != nullptr ? 1 : 0;
+  p.capacity = cache_capacity;
   p.heads_q = heads_q;
   p.heads_k = heads_k;
   p.batch_stride = cache_batch_stride;

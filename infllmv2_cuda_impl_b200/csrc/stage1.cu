@@ -79,18 +79,6 @@ struct Smem {
   int abort_flag;
 };
 
-// Optional timeline of the first CTAs (a tuning aid, compiled in only with -DIFV2_S1_TRACE).
-#ifdef IFV2_S1_TRACE
-__device__ long long g_s1_trace[4][4][256][2];   // [CTA][role][step][event] = SM clock
-#define IFV2_TRACE(role, i, ev)                                                         \
-  do {                                                                                  \
-    if (blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (i) < 256) \
-      g_s1_trace[blockIdx.x][role][i][ev] = clock64();                                  \
-  } while (0)
-#else
-#define IFV2_TRACE(role, i, ev) do {} while (0)
-#endif
-
 // Number of leading compressed keys visible to local token i (C integer division, as the
 // reference's device code): with compression stride st, key j covers tokens [st*j, st*j + 2*st)
 // and the pattern is aligned to the END of the keys when the query segment is shorter than the
@@ -187,7 +175,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         if (t >= 2 && !mbar_wait(&sm.acc_full[s], (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag,
                                  p.status, 41))
           break;
-        IFV2_TRACE(3, t, 0);
         mbar_expect_tx(&sm.kc_full[s], 2 * kHalfBytes);
         if (t < n_tiles1) {
           tma_load_3d(sm.kc[s][0], &map_kv, &sm.kc_full[s], 0, h, v0 + t * kKeysPerTile);
@@ -222,13 +209,11 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const uint32_t par = (uint32_t)((t >> 1) & 1);
         const bool pass2 = t >= n_tiles1;
         bool w = mbar_wait(&sm.kc_full[s], par, abort_flag, p.status, 52);
-        IFV2_TRACE(3, t, 1);
         if (w && t >= 2) w = mbar_wait(&sm.acc_empty[s], par ^ 1u, abort_flag, p.status, 53);
         if (w && t == n_tiles1) w = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
         ok = __all_sync(0xFFFFFFFFu, w);
         if (!ok) break;
         tc_fence_after();
-        IFV2_TRACE(0, t, 0);
         if (!pass2) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -244,7 +229,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           umma_ss_pred(tmem + s * 128, d_ones, d_rowc, idesc, true, leader);   // + row constant
         }
         umma_commit_pred(&sm.acc_full[s], leader);
-        IFV2_TRACE(0, t, 1);
       }
     }
   } else {
@@ -267,7 +251,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                                abort_flag, p.status, 61));
         if (!ok) break;
         tc_fence_after();
-        if (quad == 2) IFV2_TRACE(1 + grp, t, 0);
         // visible columns among this group's 64
         const int lim = min(max(lim_row - t * kKeysPerTile - grp * 64, 0), 64);
         const bool full = __all_sync(0xFFFFFFFFu, lim == 64);
@@ -301,7 +284,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
         tc_fence_before();
         mbar_arrive_warp(&sm.acc_empty[s]);
-        if (quad == 2) IFV2_TRACE(1 + grp, t, 1);
       }
       // merge the two column halves of every row, then publish the row constant for pass 2, in
       // units of the raw score: -(m + log2(l) / c), as three bf16 terms
@@ -375,7 +357,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                                abort_flag, p.status, 62));
         if (!ok) break;
         tc_fence_after();
-        if (quad == 2) IFV2_TRACE(1 + grp, t, 0);
         const int key = tile * kKeysPerTile + r;
         float val[kTokPerThread];
         uint32_t buf[2][32];
@@ -417,7 +398,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // (after the deferred pooling reads: this arrival is what lets a later tile reuse them)
         tc_fence_before();
         mbar_arrive_warp(&sm.acc_empty[s]);
-        if (quad == 2) IFV2_TRACE(1 + grp, t, 1);
       }
       if (ok && kPooled && n_tiles > 0) ok = pool_tile(n_tiles - 1);
       // columns past the last tile are zero (rows are 16-byte aligned: stride % 8 == 0)
@@ -453,16 +433,6 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
-
-#ifdef IFV2_S1_TRACE
-}  // namespace
-}  // namespace ifv2
-extern "C" int ifv2_debug_s1_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, ifv2::g_s1_trace, sizeof(long long) * 4 * 4 * 256 * 2);
-}
-namespace ifv2 {
-namespace {
-#endif
 
 int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void* pooled,
                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
@@ -546,6 +516,8 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
 
   const size_t smem = sizeof(Smem) + 1024;
   dim3 grid((max_seqlen_q + kTokPerTile - 1) / kTokPerTile, batch, heads_k);
+  rc = clear_launch_status(status, stream, what);
+  if (rc) return rc;
   cudaError_t e;
   if (pooled != nullptr) {
     e = cudaFuncSetAttribute(stage1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,

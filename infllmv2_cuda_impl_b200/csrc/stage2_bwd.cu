@@ -26,21 +26,6 @@ constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9: two so
                                     // are needed in the backward, so the halves are independent)
 constexpr int kMaxMaskWords = 128;
 constexpr uint32_t kTileHalfBytes = 128 * 128;   // 128 rows x 64 bf16
-// Optional timeline of the first CTAs of one of the gradient kernels (a tuning aid):
-// -DIFV2_BWD_TRACE=1 records the dK/dV kernel, =2 the dQ kernel.
-#ifdef IFV2_BWD_TRACE
-__device__ long long g_bwd_trace[4][3][256][4];   // [CTA][role][step][event] = SM clock
-#define IFV2_TRACE_AT(which, role, i, ev)                                                   \
-  do {                                                                                      \
-    if (IFV2_BWD_TRACE == which && blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 &&  \
-        lane == 0 && (i) < 256)                                                             \
-      g_bwd_trace[blockIdx.x][role][i][ev] = clock64();                                     \
-  } while (0)
-#else
-#define IFV2_TRACE_AT(which, role, i, ev) do {} while (0)
-#endif
-#define IFV2_TRACE(role, i, ev) IFV2_TRACE_AT(1, role, i, ev)
-#define IFV2_TRACE_DQ(role, i, ev) IFV2_TRACE_AT(2, role, i, ev)
 constexpr uint32_t kKVHalfBytes = 64 * 128;      // 64 keys x 64 bf16
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -264,7 +249,6 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
                             mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75)))
           return false;
         tc_fence_after();
-        IFV2_TRACE_DQ(0, j, 0);
         const uint64_t k_desc = k_desc0 + (uint32_t)sk * kStage, v_desc = v_desc0 + (uint32_t)s * kStage;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -277,7 +261,6 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
           umma_ts_pred(tmem + s * 128 + 64, tmem_do + kk * 8, v_desc + boff, idesc_s, kk > 0, leader);
         }
         umma_commit_pred(&sm.sdp_full[s], leader);
-        IFV2_TRACE_DQ(0, j, 1);
         return true;
       };
       if (ok) ok = issue_sdp(0);
@@ -289,14 +272,12 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
                                                p.status, 76));
         if (!ok) break;
         tc_fence_after();
-        IFV2_TRACE_DQ(0, i, 2);
         const uint64_t k_mn = k_desc0_mn + (uint32_t)(i % 3) * kStage;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts_pred(tmem_dq, tmem + s * 128 + kk * 8, k_mn + ((kk * 2048) >> 4), idesc_dq,
                        (i > 0) || (kk > 0), leader);
         umma_commit_pred(&sm.dq_done[i % 3], leader);
-        IFV2_TRACE_DQ(0, i, 3);
       }
     }
   } else {
@@ -346,7 +327,6 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
                                              abort_flag, p.status, 77));
       if (!ok) break;
       tc_fence_after();
-      if (quad == 2) IFV2_TRACE_DQ(1 + grp, i, 0);
       bool selected = valid;
       if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
       const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
@@ -374,7 +354,6 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&sm.ds_ready[s]);
-      if (quad == 2) IFV2_TRACE_DQ(1 + grp, i, 1);
     }
     if (ok && n_blocks > 0) {
       // the last block's product: S / dP of that block is complete, hence every dQ product up to
@@ -575,7 +554,6 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         if (w && j >= 2) w = mbar_wait(&sm.sdp_empty[s], par ^ 1u, abort_flag, p.status, 84);
         if (!__all_sync(0xFFFFFFFFu, w)) return false;
         tc_fence_after();
-        IFV2_TRACE(0, j, 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
@@ -589,7 +567,6 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
           umma_ss_pred(tmem + s * 128 + 64, do_desc0 + s * kRing + aoff, v_desc + boff, idesc_s, kk > 0, leader);
         }
         umma_commit_pred(&sm.sdp_full[s], leader);
-        IFV2_TRACE(0, j, 1);
         return true;
       };
       // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
@@ -598,7 +575,6 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_ready, (uint32_t)(i & 1), abort_flag, p.status, 85)))
           return false;
         tc_fence_after();
-        IFV2_TRACE(0, i, 2);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ss_pred(tmem_dv, do_mn0 + s * kRing + ((kk * 2048) >> 4), p_desc + ((kk * 2048) >> 4), idesc_t,
@@ -608,7 +584,6 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
           umma_ss_pred(tmem_dk, q_mn0 + s * kRing + ((kk * 2048) >> 4), ds_desc + ((kk * 2048) >> 4), idesc_t,
                        (i > 0) || (kk > 0), leader);
         umma_commit_pred(&sm.dvdk_done[s], leader);
-        IFV2_TRACE(0, i, 3);
         return true;
       };
       // dV / dK of a step go first, then S / dP of the next one: the Q / dO slot is released one
@@ -657,7 +632,6 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
                                                abort_flag, p.status, 86));
         if (!ok) break;
         tc_fence_after();
-        if (quad == 2) IFV2_TRACE(1 + grp, i, 0);
         uint32_t pp[16], dd[16];
         {
           const int half = grp;                        // this warp group's 32 key columns
@@ -701,7 +675,6 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         fence_proxy_async_smem();
         mbar_arrive_warp(&sm.pds_ready);
-        if (quad == 2) IFV2_TRACE(1 + grp, i, 1);
       }
     }
     if (ok && steps > 0) {
@@ -746,12 +719,6 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
 }  // namespace ifv2
 
 using namespace ifv2;
-
-#ifdef IFV2_BWD_TRACE
-extern "C" int ifv2_debug_bwd_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_bwd_trace, sizeof(long long) * 4 * 3 * 256 * 4);
-}
-#endif
 
 extern "C" int64_t ifv2_sparse_attn_bwd_workspace_bytes(int64_t total_q, int heads_q, int head_dim) {
   (void)head_dim;
@@ -822,6 +789,10 @@ extern "C" int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void*
   p.causal = causal ? 1 : 0;
   p.status = status;
 
+  {
+    const int rc0 = clear_launch_status(status, stream, "sparse_attn_bwd");
+    if (rc0) return rc0;
+  }
   if (total_q > 0) {
     const int64_t rows = total_q * heads_q;
     int64_t blocks = ceil_div64(rows, 16);

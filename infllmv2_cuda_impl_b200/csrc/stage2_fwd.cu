@@ -65,18 +65,6 @@ struct Smem {
   int abort_flag;
 };
 
-// Optional timeline of the first CTAs (a tuning aid, compiled in only with -DIFV2_FWD_TRACE).
-#ifdef IFV2_FWD_TRACE
-__device__ long long g_fwd_trace[4][3][256][4];   // [CTA][role][block][event] = SM clock
-#define IFV2_TRACE(role, i, ev)                                                         \
-  do {                                                                                  \
-    if (blockIdx.x < 4 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (i) < 256) \
-      g_fwd_trace[blockIdx.x][role][i][ev] = clock64();                                 \
-  } while (0)
-#else
-#define IFV2_TRACE(role, i, ev) do {} while (0)
-#endif
-
 // Highest-to-lowest walk over the set bits of the tile's union mask.
 struct BlockWalk {
   const unsigned long long* words;
@@ -225,7 +213,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                                                p.status, 22)))
           return false;
         tc_fence_after();
-        IFV2_TRACE(0, j, 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t qoff = (kk >> 2) * kQHalfBytes + (kk & 3) * 32;
@@ -234,7 +221,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                        kk > 0, leader);
         }
         umma_commit_pred(&sm.qk_done[s], leader);
-        IFV2_TRACE(0, j, 1);
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -248,13 +234,11 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                                          mbar_wait(&sm.p_ready[s], par, abort_flag, p.status, 23));
         if (!ok) break;
         tc_fence_after();
-        IFV2_TRACE(0, i, 2);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts_pred(tmem_o, tmem + s * 64 + kk * 8, v_desc0 + s * kStage + ((kk * 2048) >> 4), idesc_pv,
                        (i > 0) || (kk > 0), leader);
         umma_commit_pred(&sm.pv_done[s], leader);
-        IFV2_TRACE(0, i, 3);
       }
     }
   } else {
@@ -286,7 +270,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qk_done[s], par, abort_flag, p.status, 31));
       if (!ok) break;
       tc_fence_after();
-      if (warp == 2) IFV2_TRACE(1, i, 0);
 
       uint32_t raw[2][32];
       tmem_ld32(tmem + lane_off + s * 64, raw[0]);
@@ -331,7 +314,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         tmem_wait_st();
       }
-      if (warp == 2) IFV2_TRACE(1, i, 1);
       // rows that take nothing from this block get an exponent of -inf (P = 0) for every column
       const float neg_m = (lim == 0) ? -INFINITY : -m_ref * p.scale_log2;
       uint32_t packed[32];
@@ -348,10 +330,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       l += sum;
       tmem_st32(tmem + lane_off + s * 64, packed);
       tmem_wait_st();
-      if (warp == 2) IFV2_TRACE(1, i, 2);
       tc_fence_before();
       mbar_arrive_warp(&sm.p_ready[s]);
-      if (warp == 2) IFV2_TRACE(1, i, 3);
     }
 
     // ---- epilogue: O / l -> bf16, lse
@@ -404,12 +384,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 }  // namespace ifv2
 
 using namespace ifv2;
-
-#ifdef IFV2_FWD_TRACE
-extern "C" int ifv2_debug_fwd_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_fwd_trace, sizeof(long long) * 4 * 3 * 256 * 4);
-}
-#endif
 
 extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out,
                                     float* lse, const int64_t* fwd_mask, int mask_words,
@@ -471,6 +445,8 @@ extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error((int)e, "sparse_attn_fwd: %s", cudaGetErrorString(e));
   dim3 grid((max_seqlen_q + kTokPerTile - 1) / kTokPerTile, batch, heads_k);
+  rc = clear_launch_status(status, stream, "sparse_attn_fwd");
+  if (rc) return rc;
   sparse_attn_fwd_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
   return check_launch("sparse_attn_fwd");
 }

@@ -77,8 +77,12 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 #define IFV2_WAIT_HINT_NS 2000
 #endif
 
+// status[0] is the flag of the running launch (the host entry point clears it before launching, and
+// CTAs that start after a failure return at once instead of queueing more waits); status[1] keeps
+// the first failing site until ifv2_check_status reads and clears it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag, int32_t* status, int code) {
+                                          volatile int* abort_flag, int32_t* status, int code,
+                                          long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -87,9 +91,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
       return true;
     if ((++spins & 15u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
+        if (status) {
+          atomicCAS(status, 0, code);
+          atomicCAS(status + 1, 0, code);
+        }
         return false;
       }
     }

@@ -162,12 +162,60 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
+// A bounded wait that is meant to run out: one CTA allocates TMEM, waits with a short cycle limit
+// on an mbarrier that nothing ever arms, records the site in the status block, frees its TMEM and
+// returns normally -- the teardown every pipeline kernel shares, exercised without any fault.
+__global__ void __launch_bounds__(64)
+wait_timeout_selftest_kernel(int32_t* status, long long limit_cycles, int site, int32_t* result) {
+  __shared__ uint64_t never_armed;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&never_armed, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_slot, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+  // warp 1 waits; warp 0 then sees the CTA-wide abort flag exactly as the other roles of a
+  // pipeline kernel do
+  bool ok = true;
+  if (warp == 1) ok = mbar_wait(&never_armed, 0, &abort_flag, status, site, limit_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    result[0] = abort_flag;                 // 1: the wait gave up and told the CTA
+    result[1] = 1;                          // the kernel reached its normal end
+  }
+  if (threadIdx.x == 32) result[2] = ok ? 0 : 1;
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 32);
+}
+
 }  // namespace
 }  // namespace ifv2
 
 using namespace ifv2;
 
-// Test hook (declared here, not part of the public header): runs one tile product.
+extern "C" int ifv2_selftest_wait_timeout(int32_t* status, int64_t limit_cycles, int site,
+                                          int32_t* result, void* stream) {
+  IFV2_REQUIRE(status && result, IFV2_ERR_INVALID_ARG, "selftest_wait_timeout: null pointer");
+  IFV2_REQUIRE(limit_cycles >= 1 && limit_cycles <= (1ll << 24), IFV2_ERR_INVALID_ARG,
+               "selftest_wait_timeout: limit_cycles must be in [1, 2^24] (a few milliseconds at most)");
+  IFV2_REQUIRE(site > 0, IFV2_ERR_INVALID_ARG, "selftest_wait_timeout: site must be > 0");
+  wait_timeout_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status, (long long)limit_cycles,
+                                                                  site, result);
+  return check_launch("selftest_wait_timeout");
+}
+
+// Runs one tile product.
 //   mode 0: a (128,128), b (64,128)  -> d (128,64);  modes 1, 2: a (128,64), b (64,128) -> d (128,128)
 //   mode 3: a (128,128) = At, b (128,64) = Bt -> d = At^T . Bt (128,64)
 //   mode 4: a (128,16), b (64,16) -> d = a . b^T (128,64)

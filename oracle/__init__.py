@@ -12,8 +12,8 @@ extension is missing and never routes through this package.
 Parity pin: the restatements are checked against the reference's own pure-Python oracle
 functions (imported from the reference's tests/ directory when it is present) by
 tests/golden/make_golden.py, which also writes the committed fixtures under tests/golden/.
-The top-k tie rule has no test in the reference ("parity unpinned" for that one function);
-it follows the comparison rule of the reference's bitonic top-k (csrc/topk.cuh:17,26,37).
+The reference has no Python twin of its top-k; that function is pinned by a thread-for-thread
+simulation of the reference's bitonic top-k kernel (csrc/topk.cuh:6-117, oracle/topk.py).
 """
 from .bitmask import (topk_to_uint64, blockmask_to_uint64, uint64_to_bool,
                       transpose_blockmask)

@@ -18,8 +18,9 @@ It imports, unmodified, from the reference's tests/ directory:
 empty stand-ins; none of the functions above touches them), feeds them seeded inputs and
 stores the expected outputs as small .npz files next to this script (the inputs are recomputed
 from tests/golden/inputs.py, a platform-independent integer hash, so they need not be stored).  The max-pool and top-k
-fixtures come from a loop-for-loop transliteration of csrc/max_pooling_1d.cuh:122-159 and
-from the comparison rule of csrc/topk.cuh:17 (the reference has no Python twin of either).
+fixtures come from a loop-for-loop transliteration of csrc/max_pooling_1d.cuh:122-159 and from
+a thread-for-thread simulation of the reference's bitonic top-k kernel, csrc/topk.cuh:6-117
+(the reference has no Python twin of either).
 The fixtures then travel with the repository; nothing at test time reads the reference.
 """
 import argparse
@@ -233,8 +234,33 @@ def gen_pool_topk(out):
     assert np.array_equal(got2, exp2), got2
     cases.update(topk_y=y.numpy(), topk_exp_all=exp5, topk_exp_cut=exp2,
                  topk_bq_cut=np.array([7, 2, 6]))
+    # top-k pin: the reference's own bitonic kernel (csrc/topk.cuh), simulated thread for thread,
+    # on tie-heavy rows with +-inf; the oracle must pick the same blocks in the same order
+    from oracle.topk import bitonic_topk_literal
+    for name, n, top in (("a", 1024, 32), ("b", 256, 16), ("c", 96, 8), ("d", 160, 5), ("e", 64, 1),
+                         ("f", 512, 17), ("g", 32, 32)):
+        x = rng.integers(0, 4, size=(12, n)).astype(np.float32)
+        x[rng.random((12, n)) < 0.04] = np.inf
+        # -inf only where it cannot reach the top (a padded thread of the kernel holds
+        # (-inf, position -1), which would win a tie against a real -inf)
+        low = rng.random((12, n)) < 0.04
+        low[:, :40 if n >= 64 else 0] = False
+        x[low & (np.arange(n)[None, :] >= 32)] = -np.inf
+        x[0] = 1.0                                                  # a row of all-equal scores
+        x[1, : n // 2] = np.inf                                     # more +inf than selected
+        val, pos = bitonic_topk_literal(x, top)
+        n_sel = pos.shape[1]
+        assert np.isfinite(val).any() and (val > -np.inf).all(), name
+        xt = torch.from_numpy(x)
+        order = torch.sort(xt, dim=-1, descending=True, stable=True).indices[:, :n_sel].numpy()
+        assert np.array_equal(pos, order), f"top-k order differs from the reference kernel ({name})"
+        sel = oracle.topk_select(xt[None].to(torch.bfloat16), n_sel, torch.full((12,), n))[0].numpy()
+        assert np.array_equal(np.sort(pos, axis=1), sel), f"top-k set differs from the reference kernel ({name})"
+        cases[f"bitonic_{name}_x"] = x.astype(np.float16)            # values 0..3 and +-inf: exact
+        cases[f"bitonic_{name}_pos"] = pos.astype(np.int32)
     np.savez_compressed(os.path.join(out, "pool_topk.npz"), **cases)
-    print("pool/topk: fast forms == literal transliterations / hand KATs")
+    print("pool/topk: fast forms == literal transliterations / hand KATs; top-k == the reference's "
+          "bitonic kernel simulated thread for thread")
 
 
 def gen_compress(mods, out):

@@ -114,6 +114,27 @@ def test_pool_topk_golden(golden_dir):
                           g["topk_exp_cut"])
 
 
+def test_topk_oracle_equals_reference_bitonic_kernel(golden_dir):
+    """The pin of the top-k oracle: on tie-heavy rows with +-inf it selects the blocks that the
+    reference's bitonic kernel (csrc/topk.cuh:6-117, simulated thread for thread when the fixture
+    was made) selects, in the same order; the simulation itself is re-run here on two of the cases."""
+    from oracle.topk import bitonic_topk_literal
+    g = _load(golden_dir, "pool_topk.npz")
+    names = sorted(k[len("bitonic_"):-2] for k in g.files if k.startswith("bitonic_") and k.endswith("_x"))
+    assert len(names) >= 6
+    for name in names:
+        x = torch.from_numpy(g[f"bitonic_{name}_x"].astype(np.float32))
+        pos = g[f"bitonic_{name}_pos"]
+        n, k = x.shape[1], pos.shape[1]
+        order = torch.sort(x, dim=-1, descending=True, stable=True).indices[:, :k].numpy()
+        assert np.array_equal(order, pos), name
+        sel = oracle.topk_select(x[None], k, torch.full((x.shape[0],), n))[0].numpy()
+        assert np.array_equal(sel, np.sort(pos, axis=1)), name
+        if name in ("b", "c"):
+            _, again = bitonic_topk_literal(x.numpy(), k)
+            assert np.array_equal(again, pos), name
+
+
 def test_pool_varlen_equals_fixed():
     rng = np.random.default_rng(5)
     x = torch.from_numpy(rng.random((2, 150, 9)).astype(np.float32)).to(torch.bfloat16)

@@ -59,6 +59,20 @@ def test_pool_varlen():
     assert torch.equal(got.cpu(), exp)
 
 
+def test_topk_equals_reference_bitonic_kernel(golden_dir):
+    """Tie-heavy rows with +-inf whose expected selection was produced by a thread-for-thread
+    simulation of the reference's bitonic top-k kernel (csrc/topk.cuh), see make_golden.py."""
+    g = np.load(os.path.join(golden_dir, "pool_topk.npz"))
+    names = sorted(k[len("bitonic_"):-2] for k in g.files if k.startswith("bitonic_") and k.endswith("_x"))
+    assert len(names) >= 6
+    for name in names:
+        x = torch.from_numpy(g[f"bitonic_{name}_x"].astype(np.float32))
+        pos = g[f"bitonic_{name}_pos"]
+        n, k = x.shape[1], pos.shape[1]
+        got = infllm_v2.infllmv2_topk(x[None].to(torch.bfloat16).to(DEV), k, cache_len=64 * n)
+        assert np.array_equal(got[0].cpu().numpy(), np.sort(pos, axis=1)), name
+
+
 def test_topk_kats(golden_dir):
     g = np.load(os.path.join(golden_dir, "pool_topk.npz"))
     y = torch.from_numpy(g["topk_y"]).to(torch.bfloat16).to(DEV)          # (1, 3, 8)
@@ -123,30 +137,40 @@ def test_topk_causal_restriction(t, n, k, tail):
     assert torch.equal(got.cpu(), exp)
 
 
-def test_inputs_touching_the_ends_of_an_allocation():
-    """Neither kernel reads outside its input: block scores of unaligned width placed at the very
-    end of a device allocation of their own (top-k; lanes that own no element of such a row must
-    not load anything), and scores starting at the very beginning of one (max-pool: the halo
-    element in front of a row's first score does not exist for row 0)."""
+def _guarded(x, guard_value, guard_elems=4096):
+    """x copied into the middle of a larger device buffer whose elements before and after it hold
+    `guard_value`: a kernel that reads outside its input then computes a wrong result instead of
+    faulting.  Returns the view of x inside the buffer."""
+    buf = torch.full((x.numel() + 2 * guard_elems,), guard_value, dtype=x.dtype, device=DEV)
+    view = buf[guard_elems:guard_elems + x.numel()].view(x.shape)
+    view.copy_(x)
+    return view
+
+
+@pytest.mark.parametrize("guard", [float("inf"), float("nan")])
+def test_neither_kernel_reads_outside_its_input(guard):
+    """Block scores of unaligned width (5 columns: rows start at odd 2-byte offsets, and the lanes
+    of a warp that own no element of such a row must not load anything) and scores whose first
+    row has no element in front of it (max-pool: the halo of block 0).  The input sits between
+    guard regions of +inf / NaN, so a read outside it changes the selected blocks or the pooled
+    maxima and the comparison with the oracle fails."""
     hk, t, n, k = 4, 307, 5, 1
     x = _scores((hk, t, n), 77)
     x[:, :, 0] = float("inf")
-    big = torch.empty(12 << 20, dtype=torch.uint8, device=DEV)          # a mapping of its own
-    tail = big[big.numel() - x.numel() * 2:].view(torch.bfloat16).view(hk, t, n)
-    tail.copy_(x)
     cu_q = torch.tensor([0, 7, t], dtype=torch.int32, device=DEV)
-    got = infllm_v2.infllmv2_topk(tail, k, cu_seqlens_q=cu_q)
-    torch.cuda.synchronize()
+    got = infllm_v2.infllmv2_topk(_guarded(x, guard), k, cu_seqlens_q=cu_q)
     qb = torch.cat([torch.arange(7) // 64, torch.arange(t - 7) // 64])
     assert torch.equal(got.cpu(), oracle.topk_select(x.float(), k, qb))
+    # three selected of five columns: a stray +inf / NaN read past a row's end would displace one
+    got3 = infllm_v2.infllmv2_topk(_guarded(x[-1:, -3:].contiguous(), guard), 3, cache_len=64 * n)
+    assert torch.equal(got3.cpu(), oracle.topk_select(x[-1:, -3:].float(), 3, torch.full((3,), n)))
 
     s = _scores((2, 200, 24), 78)
-    head = torch.empty(12 << 20, dtype=torch.uint8, device=DEV)
-    view = head[:s.numel() * 2].view(torch.bfloat16).view(2, 200, 24)
-    view.copy_(s)
-    pooled = infllm_v2.max_pooling_1d(view[:, :, :21], 0, 2, 1)
-    torch.cuda.synchronize()
-    assert torch.equal(pooled.cpu(), oracle.max_pooling_1d(s[:, :, :21], 0, 2, 1))
+    view = _guarded(s, guard)
+    pooled = infllm_v2.max_pooling_1d(view[:, :, :21], 0, 2, 0)          # no forced first block
+    assert torch.equal(pooled.cpu(), oracle.max_pooling_1d(s[:, :, :21], 0, 2, 0))
+    pooled = infllm_v2.max_pooling_1d(view, 0, 0, 0)
+    assert torch.equal(pooled.cpu(), oracle.max_pooling_1d(s, 0, 0, 0))
 
 
 @pytest.mark.parametrize("hk,b,cap,k,local,init,dtype", [
