@@ -252,13 +252,29 @@ def run_ours(args, rank, world, device):
     }
     ncu_ratio = {"stage1_block_scores": 0.99, "stage1_scores": 0.97, "sparse_attn_fwd": 0.97}
     traffic = (round(alg_bytes[dominant] * ncu_ratio[dominant]) if dominant in ncu_ratio else None)
+    clk = clocks.summary()
     roofline = {"kernel": dominant, "bound": bound, "achieved": round(ach, 2), "peak": peak,
                 "unit": unit, "frac": round(ach / peak, 4), "traffic": traffic,
                 "traffic_source": "ncu dram bytes of the 16384-token case x algorithmic-byte ratio",
                 "algorithmic_bytes": alg_bytes.get(dominant), "peak_source": pk_kind,
                 "ms_per_launch": round(kernel_ms[dominant], 3)}
+    s1_name = "stage1_block_scores" if fused else "stage1_scores"
+    if dominant == s1_name and clk.get("sm_mhz"):
+        # what governs the scorer is the exponential unit, not the tensor pipe: two exponentials per
+        # (query-head row, visible key) pair -- one for the row sums, one for the probability -- on a
+        # unit that retires 16 ex2 per clock per SM (measured on this part: 16.0)
+        n_exp = 2.0 * (hk_local * 16) * v_pairs
+        sfu_peak = 16.0 * 148 * clk["sm_mhz"] * 1e6
+        sfu_ach = n_exp / (kernel_ms[dominant] * 1e-3)
+        roofline.update(bound_alt="sfu", achieved_alt=round(sfu_ach / 1e12, 3), peak_alt=round(sfu_peak / 1e12, 3),
+                        unit_alt="Texp/s", frac_alt=round(sfu_ach / sfu_peak, 4),
+                        alt_note="exponentials per launch / (16 ex2 per clock per SM x 148 SMs x median SM clock "
+                                 "under load); the kernel also evaluates a share of them as polynomials on the "
+                                 "FMA pipe, so this fraction may exceed 1")
     kernels = {n: {"ms": round(kernel_ms[n], 3), "bound": roof[n][0], "achieved": round(roof[n][1], 2),
                    "unit": roof[n][3], "frac": round(roof[n][1] / roof[n][2], 4)} for n in names}
+
+    parity = step_parity(q, k, v, kc, out, idx, seqlen)
 
     # ---- end to end from pinned host memory through the public API
     e2e = run_e2e(args, step, q, k, v, kc, seqlen, world, device)
@@ -274,14 +290,55 @@ def run_ours(args, rank, world, device):
                    "seq_len": seqlen, "global_batch": 1, "kv_heads_per_gpu": hk_local,
                    "parallelism": f"kv-head shards x{world}" if world > 1 else "single GPU",
                    "l2": "inputs (q alone is %.1f GB per GPU) exceed the 126 MB L2" % (q.numel() * 2 / 1e9)},
-        "clocks": clocks.summary(),
+        "clocks": clk,
         "e2e": e2e,
+        "parity": parity,
         "gpu_launches": len(names) * args.steps,
         "roofline": roofline,
         "kernels": kernels,
         "flops_per_step": {"stage1_algorithmic": flops_s1 * world, "stage2_fwd_algorithmic": flops_s2 * world},
     }
     return result
+
+
+def step_parity(q, k, v, kc, out, idx, seqlen):
+    """The timed step's own results against plain fp32 PyTorch on the GPU for sampled tokens (the
+    dense-with-mask attention restated over gathered keys) and against the CPU oracle for the
+    selection of two row chunks.  The checker runs after the timed region; it is not the product."""
+    try:
+        import oracle
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+        import gpu_oracle
+        import infllm_v2
+        dev = q.device
+        toks = torch.tensor(sorted(set([0, 63, 64, seqlen // 3, seqlen // 2 - 1, seqlen // 2] +
+                                       list(range(seqlen - 8, seqlen)))), device=dev)
+        ref, _ = gpu_oracle.attend_rows(q[toks], toks, k, v, idx[:, toks], seqlen)
+        diff = (out[toks].float() - ref).abs()
+        max_abs = diff.max().item()
+        mean_rel = (diff.mean() / ref.abs().mean().clamp_min(1e-12)).item()
+        exact, rows = 0, 0
+        for start in (seqlen // 2, seqlen - 128):
+            start = start // 64 * 64
+            sl = slice(start, start + 128)
+            n_pre = (sl.stop - KERNEL) // STRIDE + 1
+            cu_q = torch.tensor([0, 128], dtype=torch.int32, device=dev)
+            cu_p = torch.tensor([0, n_pre], dtype=torch.int32, device=dev)
+            score = infllm_v2.infllmv2_attn_stage1(q[sl], kc[:n_pre], kc[:n_pre], cu_q, cu_p, cu_p, 128, n_pre,
+                                                   causal=True)
+            pooled = oracle.max_pooling_1d(score.cpu(), start, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
+            ref_idx = oracle.topk_select(pooled, TOPK, (torch.arange(128) + start) // BLOCK)
+            same = (ref_idx == idx[:, sl].cpu()).all(dim=-1)
+            exact += int(same.sum())
+            rows += same.numel()
+        return {"stage2_out_max_abs": round(max_abs, 5), "stage2_out_mean_rel": round(mean_rel, 5),
+                "stage2_tokens_checked": int(toks.numel()), "topk_exact_row_rate": round(exact / rows, 4),
+                "topk_rows_checked": rows,
+                "tolerance": "max-abs <= 2e-2, mean-rel <= 1e-2; top-k rows bit-exact",
+                "pass": bool(max_abs <= 2e-2 and mean_rel <= 1e-2 and exact == rows)}
+    except Exception as e:                              # the headline line must still be printed
+        return {"error": repr(e)[:300]}
 
 
 def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
@@ -321,8 +378,41 @@ def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
         ms = float(t.item())
     h2d = sum(h.numel() * h.element_size() for h in host)
     d2h = out_host.numel() * out_host.element_size()
+
+    # ---- the floor under any host-to-host number: the same bytes moved by bare cudaMemcpyAsync
+    # calls, host->device and device->host at the same time on two streams, all ranks together
+    def bare_copies():
+        main = torch.cuda.current_stream(device)
+        runner.s_in.wait_stream(main)
+        runner.s_out.wait_stream(main)
+        with torch.cuda.stream(runner.s_in):
+            for dst, src in zip((runner.q, runner.k, runner.v, runner.kc), host):
+                dst.copy_(src, non_blocking=True)
+        with torch.cuda.stream(runner.s_out):
+            out_host.copy_(runner.q, non_blocking=True)
+        main.wait_stream(runner.s_in)
+        main.wait_stream(runner.s_out)
+
+    bare_copies()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(2):
+        bare_copies()
+    b.record()
+    torch.cuda.synchronize()
+    copy_ms = a.elapsed_time(b) / 2
+    if world > 1:
+        t = torch.tensor([copy_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        copy_ms = float(t.item())
     return {"value": round(seqlen / (ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 3),
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "copy_floor": {"ms": round(copy_ms, 3), "h2d_gbs_per_rank": round(h2d / copy_ms / 1e6, 1),
+                           "d2h_gbs_per_rank": round(d2h / copy_ms / 1e6, 1),
+                           "how": "the step's input and output bytes as bare pinned copies, both directions "
+                                  "at once, all ranks at once, no kernels; max over ranks"},
             "how": f"pinned host buffers, {seqlen // chunk} query chunks ({args.e2e_order}), copy-in / kernels / copy-out overlapped"}
 
 
@@ -651,19 +741,52 @@ def config5_decode(device, pk, small=False):
     return out
 
 
-def sharded_prefill_bench(device, rank, world, seqlen=SEQLEN, hk=2, reps=5):
+def _timed_max(fn, device, reps=5, warmup=3):
+    """CUDA-event time of fn per call, all ranks between barriers, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / reps], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _zigzag_rows(seqlen, world, rank):
+    from infllmv2_cuda_impl_b200 import sharding
+    chunks = sharding.zigzag_chunks(seqlen, world, rank)
+    rows = torch.cat([torch.arange(c.start, c.end) for c in chunks])
+    kc_rows = torch.cat([torch.arange(*sharding.compressed_range(c)) for c in chunks])
+    return chunks, rows, kc_rows
+
+
+def sharded_prefill_bench(device, rank, world, seqlen=SEQLEN, hk=2, reps=5, pk=None):
     """Query-chunk-parallel prefill of ONE sequence with fewer KV heads than GPUs (32q/2kv heads):
     every rank owns two zig-zag query chunks, K / V / compressed K are all-gathered over NCCL into
-    local HBM, then each chunk runs the normal kernels.  Reports the all-gather separately."""
+    local HBM, then each chunk runs the normal kernels.  The whole sequence is generated from one
+    seed on every rank (each keeps its rows), so rank 0 can also run it unsharded and compare."""
     from infllmv2_cuda_impl_b200 import sharding
     import infllm_v2
-    g = torch.Generator(device=device).manual_seed(rank)
+    g = torch.Generator(device=device).manual_seed(1234)
     s = 1.0 / math.sqrt(D)
-    rows = seqlen // world                                     # two chunks of seqlen / (2 world) tokens
-    q = (torch.randn(rows, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
-    k = (torch.randn(rows, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
-    v = (torch.randn(rows, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
-    kc = (torch.randn(rows // STRIDE, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    q_full = (torch.randn(seqlen, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    k_full = (torch.randn(seqlen, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    v_full = (torch.randn(seqlen, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    kc_full = infllm_v2.compress_keys(k_full)[0]
+    kc_pad = torch.cat([kc_full, kc_full.new_zeros((seqlen // STRIDE - kc_full.shape[0],) + kc_full.shape[1:])])
+    chunks, rows, kc_rows = _zigzag_rows(seqlen, world, rank)
+    rows_d, kc_rows_d = rows.to(device), kc_rows.to(device)
+    q, k, v, kc = q_full[rows_d], k_full[rows_d], v_full[rows_d], kc_pad[kc_rows_d]
+    if rank != 0:
+        del q_full, k_full, v_full, kc_full
+    del kc_pad
 
     def gather():
         return [sharding.gather_sequence(t, world) for t in (k, v, kc)]
@@ -672,61 +795,248 @@ def sharded_prefill_bench(device, rank, world, seqlen=SEQLEN, hk=2, reps=5):
         return sharding.sharded_prefill(q, k, v, kc, seqlen, world, rank, TOPK, INIT_BLOCKS, LOCAL_BLOCKS,
                                         overlap=overlap)
 
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(reps):
-            fn()
-        b.record()
-        dist.barrier()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / reps], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    t_gather, t_step = timed(gather), timed(step)
-    t_serial = timed(lambda: step(False))
+    t_gather = _timed_max(gather, device, reps)
+    t_step = _timed_max(step, device, reps)
+    t_serial = _timed_max(lambda: step(False), device, reps)
+    infllm_v2.check_device_status()
+    out_local = step()
+    # ---- parity: rank 0 runs the same sequence unsharded and compares its own rows
+    ok = torch.ones(1, device=device)
+    parity = None
+    if rank == 0:
+        full, _ = sharding.prefill_chunk(q_full, kc_full, k_full, v_full, sharding.Chunk(0, 0, seqlen), TOPK,
+                                         INIT_BLOCKS, LOCAL_BLOCKS)
+        diff = (out_local.float() - full[rows_d].float()).abs().amax(dim=(1, 2))
+        parity = {"rows": int(rows.numel()), "rows_bit_identical": round(float((diff == 0).float().mean()), 4),
+                  "rows_within_2e-2": round(float((diff <= 2e-2).float().mean()), 4),
+                  "max_abs": round(float(diff.max()), 5)}
+        parity["pass"] = bool(parity["rows_within_2e-2"] >= 0.999)
+        ok[0] = 1.0 if parity["pass"] else 0.0
+        del full
     infllm_v2.check_device_status()
     gathered = (2 * seqlen * hk * D + (seqlen // STRIDE) * hk * D) * 2
-    return {"sharded_prefill_131072_32q2kv": {
+    recv = gathered * (world - 1) // world                     # bytes that cross NVLink into one rank
+    # algorithmic work of the whole sequence: stage 1 over the visible compressed keys, stage 2 over
+    # min(64, bq + 1) selected blocks per token, the diagonal one partly visible
+    n_comp = (seqlen - KERNEL) // STRIDE + 1
+    t_idx = torch.arange(seqlen, dtype=torch.int64)
+    nsel = ((t_idx // BLOCK) + 1).clamp(max=TOPK)
+    pairs = int(((nsel - 1) * BLOCK + t_idx % BLOCK + 1).sum())
+    flops = 2.0 * D * hk * 16 * visible_compressed(seqlen, n_comp) + 4.0 * D * hk * 16 * pairs
+    res = {
         "n_gpus": world, "ms_step": round(t_step, 3), "ms_step_gather_first": round(t_serial, 3),
         "ms_allgather": round(t_gather, 3),
         "tokens_per_s": round(seqlen / (t_step * 1e-3), 1),
-        "allgather_bytes_per_rank": gathered, "allgather_gbs": round(gathered / t_gather / 1e6, 1),
+        "tflops": round(flops / t_step / 1e9, 1),
+        "allgather_bytes_per_rank": gathered, "allgather_received_bytes_per_rank": recv,
+        "allgather_gbs": round(gathered / t_gather / 1e6, 1),
+        "allgather_received_gbs_per_rank": round(recv / t_gather / 1e6, 1),
+        "parity_vs_unsharded_rank0": parity,
         "note": "one sequence, query chunks in zig-zag order over the ranks; step = all-gather of K, V and "
-                "compressed K into local HBM + fused stage 1 / top-k / mask / stage-2 forward per chunk; "
-                "max over ranks"}}
+                "compressed K into local HBM (compressed K first, K / V on a side stream under the selection) "
+                "+ fused stage 1 / top-k / mask / stage-2 forward per chunk; gather_first = everything "
+                "gathered before any kernel; max over ranks"}
+    if pk is not None:
+        res["frac_of_n_gpu_tensor_roofline"] = round(flops / t_step / 1e9 / (world * pk["bf16_tflops_sustained"]), 4)
+    return {f"sharded_prefill_{seqlen}_32q2kv": res}
 
 
-# ------------------------------------------------------------------------------ CPU oracle ----
+def sharded_training_parity(device, rank, world, seqlen=16384, hk=2):
+    """Forward + backward of one sequence under query-chunk sharding (all-gather of K / V, per-chunk
+    backward, reduce-scatter of dK / dV over NCCL) against the same step on rank 0 alone."""
+    from infllmv2_cuda_impl_b200 import sharding
+    import infllm_v2
+    g = torch.Generator(device=device).manual_seed(4321)
+    s = 1.0 / math.sqrt(D)
+    q = (torch.randn(seqlen, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    k = (torch.randn(seqlen, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    v = (torch.randn(seqlen, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    do = torch.randn(seqlen, hk * 16, D, device=device, generator=g).to(torch.bfloat16)
+    kc = infllm_v2.compress_keys(k)[0]
+    # the selection is input to the training step (it carries no gradient): every rank computes the
+    # same lists from the same tensors
+    _, idx = sharding.prefill_chunk(q, kc, k, v, sharding.Chunk(0, 0, seqlen), TOPK, INIT_BLOCKS, LOCAL_BLOCKS)
+    _, rows, _ = _zigzag_rows(seqlen, world, rank)
+    rows_d = rows.to(device)
+    fn = lambda: sharding.sharded_attention_fwd_bwd(q[rows_d], k[rows_d], v[rows_d], do[rows_d],
+                                                    idx[:, rows_d].contiguous(), seqlen, world, rank)
+    out, dq, dk, dv = fn()
+    t = _timed_max(fn, device, reps=3, warmup=1)
+    infllm_v2.check_device_status()
+    res = {"n_gpus": world, "tokens": seqlen, "ms_fwd_bwd_step": round(t, 3)}
+    if rank == 0:
+        qd, kd, vd = (x.detach().clone().requires_grad_(True) for x in (q, k, v))
+        cu = torch.tensor([0, seqlen], dtype=torch.int32, device=device)
+        ref_out = infllm_v2.infllmv2_attn_varlen_func(qd, kd, vd, cu, cu, seqlen, seqlen, causal=True, topk_idx=idx)
+        ref_out.backward(do)
+        worst = {}
+        good = True
+        for name, a, b in (("out", out, ref_out.detach()), ("dq", dq, qd.grad), ("dk", dk, kd.grad), ("dv", dv, vd.grad)):
+            b = b[rows_d].float()
+            err = float((a.float() - b).abs().max())
+            tol = 2e-2 * max(1.0, float(b.abs().max()))
+            worst[name] = round(err, 5)
+            good = good and err <= tol
+        res.update(max_abs_vs_single_gpu=worst, tolerance="2e-2 x max(1, |ref|max)", **{"pass": bool(good)})
+    return {"sharded_training_step_parity": res}
 
-def cpu_sample(seqlen, sample_tokens, threads):
-    """The reference's pure-PyTorch path (fp32, dense attention under the block mask) for the LAST
-    `sample_tokens` query tokens of one `seqlen`-token sequence, all 128 query heads.  Returns
-    seconds.  Keys are scored as a prefix (bottom-right alignment), so the work per token equals
-    that of the full job's most expensive tokens."""
+
+def sharded_decode_bench(device, rank, world, pk):
+    """Decode at batch 64 with the sequences sharded over the ranks (64 / N per GPU, cache lengths
+    uniform in [32768, 131072], 32q/2kv heads): stage 1 over the compressed keys, one-launch pool /
+    top-64 / mask, sparse decode; replayed from a CUDA graph.  No collective: sequences are
+    independent.  Throughput = 64 sequences / the slowest rank's step."""
+    from infllmv2_cuda_impl_b200 import sharding
+    import infllm_v2
+    B, hk, lo, hi = 64, 2, 32768, 131072
+    mine = list(sharding.batch_shard(B, world, rank))
+    lens_all = torch.randint(lo, hi + 1, (B,), generator=torch.Generator().manual_seed(0)).to(torch.int32)
+    lens = lens_all[mine]
+    nb = len(mine)
+    cap = hi + 64
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    s = 1.0 / math.sqrt(D)
+    kcache = (torch.randn(nb, cap, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    vcache = (torch.randn(nb, cap, hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    q = (torch.randn(nb, 1, hk * 16, D, device=device, generator=g) * s).to(torch.bfloat16)
+    n_c = [(int(l) - KERNEL) // STRIDE + 1 for l in lens]
+    kc = (torch.randn(sum(n_c), hk, D, device=device, generator=g) * s).to(torch.bfloat16)
+    cu_q = torch.arange(nb + 1, dtype=torch.int32, device=device)
+    cu_c = torch.tensor([0] + list(torch.tensor(n_c).cumsum(0)), dtype=torch.int32, device=device)
+    lens_d = lens.to(device)
+    positions = (lens_d - 1).contiguous()
+    n_c_dev = torch.tensor(n_c, dtype=torch.int32, device=device)
+    max_c, q2 = max(n_c), q.view(nb, hk * 16, D)
+
+    def full_step():
+        score = infllm_v2.infllmv2_attn_stage1(q2, kc, kc, cu_q, cu_c, cu_c, 1, max_c, causal=False)
+        mask = infllm_v2.decode_select(score, positions, TOPK, cap, LOCAL_BLOCKS, INIT_BLOCKS, seqused_c=n_c_dev)
+        return infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d, block_mask=mask)
+
+    full_step()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        full_step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        full_step()
+    t = _timed_max(graph.replay, device, reps=20, warmup=3)
+    nbytes = torch.tensor([float(nb * hk * TOPK * BLOCK * D * 2 * 2 + kc.numel() * 2)], device=device)
+    dist.all_reduce(nbytes)
+    total = float(nbytes.item())
+    return {"sharded_decode_b64_with_selection": {
+        "n_gpus": world, "sequences_per_gpu": nb, "ms": round(t, 4), "tokens_per_s": round(B / (t * 1e-3), 1),
+        "gbs_all_gpus": round(total / t / 1e6, 1),
+        "frac_of_n_gpu_hbm": round(total / t / 1e6 / (world * pk["hbm_gbs"]), 4),
+        "note": "batch sharded, no collective; CUDA-graph replay; max over ranks"}}
+
+
+def multi_gpu_configs(device, rank, world, pk):
+    """What the path does across GPUs besides the KV-head sharding of the headline step."""
+    out = {}
+    for name, fn in (("sharded_prefill", lambda: sharded_prefill_bench(device, rank, world, SEQLEN, pk=pk)),
+                     ("sharded_training", lambda: sharded_training_parity(device, rank, world)),
+                     ("sharded_decode", lambda: sharded_decode_bench(device, rank, world, pk))):
+        try:
+            out.update(fn())
+        except Exception as e:                               # every rank takes the same branch or none
+            out[name + "_error"] = repr(e)[:300]
+        torch.cuda.empty_cache()
+    return out
+
+
+# ------------------------------------------------------------------------------ CPU baseline --
+
+def _reference_functions():
+    """The reference's own pure-PyTorch functions (its test oracles), when a checkout is reachable
+    through INFLLMV2_REFERENCE or at /root/reference: torch_naive_softmax (stage 1) and
+    convert_topk_to_base_blockmask / prepare_mixed_mask / attention_blocksparse_ref (stage 2).
+    Returns None where there is no checkout (the GPU box): the CPU port in oracle/ is timed then."""
+    import importlib
+    import types
+    root = os.environ.get("INFLLMV2_REFERENCE") or "/root/reference"
+    tests_dir = os.path.join(root, "tests")
+    if not os.path.isdir(tests_dir):
+        return None
+    try:
+        for name in ("matplotlib", "matplotlib.pyplot", "matplotlib.colors", "seaborn"):
+            sys.modules.setdefault(name, types.ModuleType(name))
+        if "infllm_v2" not in sys.modules:            # the reference's tests import its CUDA module
+            stub = types.ModuleType("infllm_v2")
+            for fn in ("infllmv2_attn_stage1", "infllmv2_attn_varlen_func", "infllmv2_attn_with_kvcache",
+                       "topk_to_uint64", "blockmask_to_uint64", "uint64_to_bool", "max_pooling_1d",
+                       "max_pooling_1d_varlen"):
+                setattr(stub, fn, None)
+            sys.modules["infllm_v2"] = stub
+        sys.path.insert(0, tests_dir)
+        cwd = os.getcwd()
+        os.chdir(tempfile.mkdtemp())                  # tests/utils.py creates a directory on import
+        try:
+            ns = importlib.import_module("stage1.naive_softmax")
+            ut = importlib.import_module("utils")
+        finally:
+            os.chdir(cwd)
+        return {"stage1": ns.torch_naive_softmax, "to_blockmask": ut.convert_topk_to_base_blockmask,
+                "mixed_mask": ut.prepare_mixed_mask, "attention": ut.attention_blocksparse_ref}
+    except Exception:
+        return None
+
+
+def cpu_chunk_starts(seqlen, n_chunks, chunk=16):
+    """Starts of `n_chunks` chunks of `chunk` query tokens spread evenly over the sequence (the
+    cost of a token grows with its position, so the sample must not sit at one end)."""
+    return [min(seqlen - chunk, int((i + 0.5) * seqlen / n_chunks) // 64 * 64) for i in range(n_chunks)]
+
+
+def cpu_sample(seqlen, sample_tokens, threads, ref=None):
+    """The reference's pure-PyTorch CPU path (fp32, dense attention under the block mask) for
+    `sample_tokens` query tokens of one `seqlen`-token sequence, all 128 query heads, taken as
+    16-token chunks spread evenly over the sequence; each chunk is scored against the keys before
+    its end (bottom-right alignment), exactly the work those tokens cost inside the full job.
+    `ref`: the reference's own functions (stage 1 and stage 2; pool, top-k and the mask pack have
+    no CPU form in the reference and come from oracle/ either way).  Returns seconds."""
     import oracle
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
     s = 1.0 / math.sqrt(D)
     k = (torch.randn(seqlen, HK, D, generator=g) * s).to(torch.bfloat16)
     v = (torch.randn(seqlen, HK, D, generator=g) * s).to(torch.bfloat16)
-    q = (torch.randn(sample_tokens, HQ, D, generator=g) * s).to(torch.bfloat16)
-    cu_k = [0, seqlen]
-    kc, cu_c = oracle.compress_keys(k, cu_k, KERNEL, STRIDE)       # input preparation, not timed
-    n_comp = cu_c[-1]
+    chunk = 16
+    starts = cpu_chunk_starts(seqlen, max(1, sample_tokens // chunk), chunk)
+    qs = [(torch.randn(chunk, HQ, D, generator=g) * s).to(torch.bfloat16) for _ in starts]
+    kc, _ = oracle.compress_keys(k, [0, seqlen], KERNEL, STRIDE)       # input preparation, not timed
     t0 = time.perf_counter()
-    score = oracle.stage1_scores(q, kc, [0, sample_tokens], cu_c, n_comp, True).to(torch.bfloat16)
-    pooled = oracle.max_pooling_1d(score, seqlen - sample_tokens, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
-    qb = (torch.arange(sample_tokens) + seqlen - sample_tokens) // BLOCK
-    idx = oracle.topk_select(pooled, TOPK, qb)
-    _mask = oracle.topk_to_uint64(idx.numpy(), seqlen, BLOCK)
-    out, _ = oracle.sparse_attention_fwd(q, k, v, [0, sample_tokens], cu_k, idx, causal=True)
+    for st, q in zip(starts, qs):
+        end = st + chunk
+        n_pre = (end - KERNEL) // STRIDE + 1
+        if ref is not None:
+            score = ref["stage1"](q.float(), kc[:n_pre].float(), causal=True).to(torch.bfloat16)
+        else:
+            score = oracle.stage1_scores(q, kc[:n_pre], [0, chunk], [0, n_pre], n_pre, True).to(torch.bfloat16)
+        pooled = oracle.max_pooling_1d(score, st, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
+        idx = oracle.topk_select(pooled, TOPK, (torch.arange(chunk) + st) // BLOCK)
+        _mask = oracle.topk_to_uint64(idx.numpy(), end, BLOCK)
+        if ref is not None:
+            base = ref["to_blockmask"](idx, end, BLOCK, device="cpu")
+            cu_q, cu_k = torch.tensor([0, chunk]), torch.tensor([0, end])
+            mixed = ref["mixed_mask"](base, cu_q, cu_k, chunk, end, 1, nheads=HQ, nheads_k=HK,
+                                      m_block_dim=16, n_block_dim=BLOCK)
+            ref["attention"](q[None], k[None, :end], v[None, :end], mixed, causal=True)
+        else:
+            oracle.sparse_attention_fwd(q, k[:end], v[:end], [0, chunk], [0, end], idx, causal=True)
     return time.perf_counter() - t0
+
+
+def cpu_baseline_object(seqlen, sample_tokens, threads, sec, kind):
+    n = max(1, sample_tokens // 16) * 16
+    how = ("the reference's own torch_naive_softmax + attention_blocksparse_ref" if kind == "reference"
+           else "the CPU port of the reference's PyTorch path (oracle/)")
+    return {"value": round(n / sec, 2), "unit": "tokens/s", "cores": threads, "kind": kind,
+            "sample": f"{n} query tokens in 16-token chunks spread evenly over the {seqlen}-token sequence, "
+                      f"all 128 query heads, fp32, {how}; stage1 + pool + top-64 + mask + dense-with-mask "
+                      f"attention, {sec:.1f} s"}
 
 
 def run_reference(args, rank, world):
@@ -734,13 +1044,14 @@ def run_reference(args, rank, world):
         return None
     threads = os.cpu_count() or 1
     sample = args.cpu_tokens
+    ref = _reference_functions()
+    kind = "reference" if ref is not None else "port"
     for _ in range(min(args.warmup, 1)):
-        cpu_sample(args.seqlen, sample, threads)
-    times = [cpu_sample(args.seqlen, sample, threads) for _ in range(args.steps)]
+        cpu_sample(args.seqlen, sample, threads, ref)
+    times = [cpu_sample(args.seqlen, sample, threads, ref) for _ in range(args.steps)]
     sec = sum(times) / len(times)
-    val = sample / sec
-    desc = (f"last {sample} query tokens of one {args.seqlen}-token sequence, 128q/8kv heads, fp32 "
-            f"pure-PyTorch path (stage1 + pool + top-64 + mask + dense-with-mask attention)")
+    n = max(1, sample // 16) * 16
+    val = n / sec
     return {
         "impl": "reference", "metric": METRIC, "value": round(val, 2), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -748,8 +1059,7 @@ def run_reference(args, rank, world):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"prefill {args.seqlen} tokens, 128q/8kv heads, d128 (CPU sample)",
                    "seq_len": args.seqlen, "global_batch": 1},
-        "cpu_baseline": {"value": round(val, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": desc},
+        "cpu_baseline": cpu_baseline_object(args.seqlen, sample, threads, sec, kind),
         "e2e": {"value": round(val, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -763,8 +1073,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqlen", type=int, default=SEQLEN)
-    ap.add_argument("--cpu-tokens", type=int, default=16,
-                    help="query tokens in the CPU sample (cpu_baseline / --impl reference)")
+    ap.add_argument("--cpu-tokens", type=int, default=128,
+                    help="query tokens in the CPU sample (cpu_baseline / --impl reference), in 16-token chunks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true",
                     help="run stage 1 and the max-pool as two kernels (the reference's op sequence)")
@@ -801,7 +1111,7 @@ def main():
     if args.only == "sharded":
         if world < 2:
             raise SystemExit("--only sharded needs at least two ranks (torchrun)")
-        res = sharded_prefill_bench(device, rank, world, args.seqlen)
+        res = multi_gpu_configs(device, rank, world, peaks()[0])
         if rank == 0:
             print(json.dumps(res), flush=True)
         dist.barrier()
@@ -811,7 +1121,13 @@ def main():
         print(json.dumps(extra_configs(device, peaks()[0], args.only, args.small)), flush=True)
         return
     res = run_ours(args, rank, world, device)
+    multi = None
+    if world > 1 and not args.no_extras and args.seqlen == SEQLEN:
+        torch.cuda.empty_cache()
+        multi = multi_gpu_configs(device, rank, world, peaks()[0])
     if rank == 0:
+        if multi is not None:
+            res["other_configs"] = multi
         if world == 1 and not args.no_extras and args.seqlen == SEQLEN:
             torch.cuda.empty_cache()
             try:
@@ -820,12 +1136,10 @@ def main():
                 res["other_configs"] = {"error": repr(e)[:300]}
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            sec = cpu_sample(args.seqlen, args.cpu_tokens, threads)
-            res["cpu_baseline"] = {
-                "value": round(args.cpu_tokens / sec, 2), "unit": "tokens/s", "cores": threads,
-                "kind": "port",
-                "sample": f"last {args.cpu_tokens} query tokens of the {args.seqlen}-token sequence, all "
-                          f"128 query heads, fp32 pure-PyTorch oracle, {sec:.1f} s"}
+            ref = _reference_functions()
+            sec = cpu_sample(args.seqlen, args.cpu_tokens, threads, ref)
+            res["cpu_baseline"] = cpu_baseline_object(args.seqlen, args.cpu_tokens, threads, sec,
+                                                      "reference" if ref is not None else "port")
         print(json.dumps(res), flush=True)
     if world > 1:
         dist.barrier()

@@ -23,6 +23,22 @@ import torch
 import torch.distributed as dist
 
 
+_cu_cache = {}
+
+
+def _cu_pair(n: int, device) -> torch.Tensor:
+    """int32 [0, n] on `device`, built once per (device, n): creating it per call would be a
+    blocking pageable host->device copy in the middle of a pipelined step."""
+    key = (str(device), int(n))
+    t = _cu_cache.get(key)
+    if t is None:
+        if len(_cu_cache) > 4096:
+            _cu_cache.clear()
+        t = torch.tensor([0, int(n)], dtype=torch.int32, device=device)
+        _cu_cache[key] = t
+    return t
+
+
 def head_shard(num_kv_heads: int, world: int, rank: int) -> slice:
     """KV heads owned by `rank` (query heads are 16x that slice)."""
     if num_kv_heads % world != 0:
@@ -115,8 +131,7 @@ def sharded_attention_fwd_bwd(q_local: torch.Tensor, k_local: torch.Tensor, v_lo
     v = gather_sequence(v_local, world, group).detach().requires_grad_(True)
     outs = []
     for i, ch in enumerate(chunks):
-        cu_q = torch.tensor([0, clen], dtype=torch.int32, device=dev)
-        cu_k = torch.tensor([0, ch.end], dtype=torch.int32, device=dev)
+        cu_q, cu_k = _cu_pair(clen, dev), _cu_pair(ch.end, dev)
         idx = topk_idx_local[:, i * clen:(i + 1) * clen].contiguous()
         outs.append(attn(q[i * clen:(i + 1) * clen], k[:ch.end], v[:ch.end], cu_q, cu_k, clen, ch.end,
                          causal=True, topk_idx=idx))
@@ -160,8 +175,7 @@ def chunk_selection(q_chunk: torch.Tensor, kc: torch.Tensor, chunk: Chunk, topk:
     dev = q_chunk.device
     lq, lk = chunk.end - chunk.start, chunk.end
     n_comp = (lk - kernel) // stride + 1 if lk >= kernel else 0
-    cu_q = torch.tensor([0, lq], dtype=torch.int32, device=dev)
-    cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=dev)
+    cu_q, cu_c = _cu_pair(lq, dev), _cu_pair(n_comp, dev)
     kc_p = kc[:n_comp]
     if ops.block_scores is not None and block_size == 64 and stride == 16:
         pooled = ops.block_scores(q_chunk, kc_p, cu_q, cu_c, lq, n_comp, local_blocks, init_blocks,
@@ -178,8 +192,7 @@ def chunk_attention(q_chunk: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chu
     ops = ops or PrefillOps.cuda()
     dev = q_chunk.device
     lq, lk = chunk.end - chunk.start, chunk.end
-    cu_q = torch.tensor([0, lq], dtype=torch.int32, device=dev)
-    cu_k = torch.tensor([0, lk], dtype=torch.int32, device=dev)
+    cu_q, cu_k = _cu_pair(lq, dev), _cu_pair(lk, dev)
     return ops.attn(q_chunk, k[:lk], v[:lk], cu_q, cu_k, lq, lk, causal=True, topk_idx=idx)
 
 
@@ -251,6 +264,12 @@ class StreamedPrefill:
         self.v = torch.empty_like(self.k)
         self.kc = torch.empty(n_comp, heads_k, head_dim, dtype=dtype, device=device)
         self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        # the per-chunk cu_seqlens tables, created up front (see _cu_pair)
+        for c in range(seqlen // chunk_tokens):
+            lk = (c + 1) * chunk_tokens
+            _cu_pair(chunk_tokens, self.device)
+            _cu_pair(lk, self.device)
+            _cu_pair((lk - 32) // 16 + 1 if lk >= 32 else 0, self.device)
 
     @staticmethod
     def middle_out(n: int) -> List[int]:

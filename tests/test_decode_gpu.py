@@ -185,3 +185,33 @@ def test_decode_rotary_on_append(rotary_dim, interleaved):
     assert mx <= MAX_ABS and mr <= MEAN_REL, (mx, mr)
     assert (lse.cpu() - ref_lse).abs().max() < 2e-2
     assert torch.equal(kc_d.cpu(), kc_ref) and torch.equal(vc_d.cpu(), vc_ref)     # rotated key in the cache
+
+
+def test_decode_full_cache_and_lengths_beyond_the_capacity():
+    """A sequence whose cache is full cannot take the new token: it is neither appended nor
+    attended, so the result equals the call without k / v; a length beyond the capacity attends the
+    positions that exist.  The caches sit between NaN guards, so a read past a sequence's rows
+    would poison the output."""
+    bsz, hk, cap, d = 3, 2, 256, 128
+    hq = hk * 16
+    q = det_tensor((bsz, 1, hq, d), 1, 0.25).to(DEV)
+    guard = torch.full((bsz + 2, cap, hk, d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kc_all, vc_all = guard.clone(), guard.clone()
+    kc, vc = kc_all[1:-1], vc_all[1:-1]
+    kc.copy_(det_tensor((bsz, cap, hk, d), 2, 0.25))
+    vc.copy_(det_tensor((bsz, cap, hk, d), 3))
+    kn = det_tensor((bsz, 1, hk, d), 4, 0.25).to(DEV)
+    vn = det_tensor((bsz, 1, hk, d), 5).to(DEV)
+    full = torch.tensor([cap, cap, 100], dtype=torch.int32, device=DEV)
+    k_before, v_before = kc.clone(), vc.clone()
+    with_new = infllm_v2.infllmv2_attn_with_kvcache(q, kc, vc, k=kn, v=vn, cache_seqlens=full)
+    # sequences 0 and 1 are full: their rows are untouched; sequence 2 took the token
+    assert torch.equal(kc[:2], k_before[:2]) and torch.equal(vc[:2], v_before[:2])
+    assert torch.equal(kc[2, 100], kn[2, 0]) and torch.equal(vc[2, 100], vn[2, 0])
+    without = infllm_v2.infllmv2_attn_with_kvcache(q, kc, vc, cache_seqlens=torch.tensor(
+        [cap, cap, 101], dtype=torch.int32, device=DEV))
+    assert not torch.isnan(with_new.float()).any()
+    assert torch.equal(with_new, without)
+    beyond = infllm_v2.infllmv2_attn_with_kvcache(q, kc, vc, cache_seqlens=torch.tensor(
+        [cap + 1000, cap + 1, 101], dtype=torch.int32, device=DEV))
+    assert torch.equal(beyond, without)
