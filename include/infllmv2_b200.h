@@ -156,6 +156,21 @@ int ifv2_topk_select(const void* score, int32_t* out_idx, int is_bf16, int heads
                      const int32_t* cache_lens, int batch, int cache_len, int block_size,
                      void* stream);
 
+/* ifv2_topk_select with the block mask packed in the same pass: row_mask (heads, total_q,
+ * ceil(k_blocks/64)) receives exactly the words ifv2_topk_to_uint64 would build from the selected
+ * list (bit b of a row = block b selected and not after the row's own block; every word is
+ * written), so the int32 list never has to travel through memory; out_idx may be null.
+ * col_mask (may be null): the column mask (heads, k_blocks, ceil(total_q/64)) of the backward, as
+ * ifv2_transpose_blockmask gives it, produced by that kernel in a second launch of this call.
+ * Stands for the caller-side top-k (README.md:40-42) followed by C.topk_to_uint64
+ * (csrc/topk_to_uint64.cuh:10-52) and the unpack / transpose / pack sequence of
+ * infllm_v2/infllmv2_sparse_attention.py:343-350.  n_blocks, k_blocks <= 8192. */
+int ifv2_topk_select_mask(const void* score, int32_t* out_idx, int64_t* row_mask, int64_t* col_mask,
+                          int is_bf16, int heads, int64_t total_q, int n_blocks, int64_t row_stride,
+                          int k, int k_blocks, const int32_t* cu_seqlens_q,
+                          const int32_t* cache_lens, int batch, int cache_len, int block_size,
+                          void* stream);
+
 /* Block selection of a decode step in one launch: for every (sequence, KV head) row of stage-1
  * scores (score: (heads, batch, row_stride), one query token per sequence) the 64-token max-pool
  * (window block_size/stride + 1, stride block_size/stride, padding 1, +inf on the init and

@@ -37,6 +37,8 @@ SIGNATURES = {
                                    c_int, c_int, c_int, c_void_p],
     "ifv2_topk_select": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int64, c_int,
                          c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ifv2_topk_select_mask": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int64,
+                              c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "ifv2_stage1_scores": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int64, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                            c_int64, c_float, c_int, c_void_p, c_void_p],

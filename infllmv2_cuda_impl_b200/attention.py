@@ -303,11 +303,17 @@ def _bwd(dout, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_
 def _infllmv2_attn_varlen_forward(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
     cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, softmax_scale: float,
-    causal: bool, topk_idx: Optional[torch.Tensor] = None,
+    causal: bool, topk_idx: Optional[torch.Tensor] = None, block_mask: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Returns (out, softmax_lse (nheads_k, total_q*16), fwd_blockmask int64 or an empty tensor)."""
     q, k, v = [_dense(maybe_contiguous(x)) for x in (q, k, v)]
-    if topk_idx is not None:
+    if block_mask is not None:
+        words = ((max_seqlen_k + BLOCK_N - 1) // BLOCK_N + 63) // 64
+        if topk_idx is not None or block_mask.dtype != torch.int64 or \
+                tuple(block_mask.shape) != (k.shape[1], q.shape[0], words):
+            raise ValueError(f"block_mask must be int64 (nheads_k, total_q, {words}) and excludes topk_idx")
+        fwd_mask = block_mask.contiguous()
+    elif topk_idx is not None:
         assert topk_idx.dtype == torch.int32
         fwd_mask, _ = topk_to_uint64(topk_idx, max_seqlen_k, BLOCK_N)
     else:
@@ -321,10 +327,10 @@ def _infllmv2_attn_varlen_forward(
 
 @_infllmv2_attn_varlen_forward.register_fake
 def _(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
-      topk_idx=None):
+      topk_idx=None, block_mask=None):
     words = ((max_seqlen_k + BLOCK_N - 1) // BLOCK_N + 63) // 64
     mask = (q.new_empty((k.shape[1], q.shape[0], words), dtype=torch.int64)
-            if topk_idx is not None else q.new_empty((0,), dtype=torch.int64))
+            if (topk_idx is not None or block_mask is not None) else q.new_empty((0,), dtype=torch.int64))
     return (torch.empty_like(q),
             q.new_empty((k.shape[1], q.shape[0] * GROUP), dtype=torch.float32), mask)
 
@@ -358,14 +364,14 @@ class Infllmv2AttnVarlenFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p,
                 softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic,
-                return_softmax, block_table, topk_idx):
+                return_softmax, block_table, topk_idx, block_mask=None):
         _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table,
                       "infllmv2_attn_varlen_func")
         if softmax_scale is None:
             softmax_scale = q.shape[-1] ** (-0.5)
         out, lse, fwd_mask = _infllmv2_attn_varlen_forward(
             q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
-            topk_idx)
+            topk_idx, block_mask)
         ctx.save_for_backward(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, fwd_mask)
         ctx.max_seqlen_q, ctx.max_seqlen_k = max_seqlen_q, max_seqlen_k
         ctx.softmax_scale, ctx.causal = softmax_scale, causal
@@ -379,27 +385,28 @@ class Infllmv2AttnVarlenFunc(torch.autograd.Function):
             ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal, fwd_mask)
         if _CHECK_STATUS:
             check_device_status(q.device)
-        return (dq, dk, dv) + (None,) * 14
+        return (dq, dk, dv) + (None,) * 15
 
 
 def infllmv2_attn_varlen_func(
     q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p=0.0,
     softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0, alibi_slopes=None,
-    deterministic=False, return_attn_probs=False, block_table=None, topk_idx=None,
+    deterministic=False, return_attn_probs=False, block_table=None, topk_idx=None, block_mask=None,
 ):
     """Block-sparse varlen attention (stage 2), differentiable.
 
     q: (total_q, nheads, 128); k, v: (total_k, nheads_k, 128), bf16, nheads = 16 * nheads_k.
     cu_seqlens_q / cu_seqlens_k: (batch + 1,) int32.  topk_idx: int32 (nheads_k, total_q, topk)
     block indices local to each sequence's keys (64-token blocks, -1 = unused); None = dense
-    attention.  causal=True aligns the diagonal to the bottom right when seqlen_q != seqlen_k.
+    attention.  block_mask (an addition): the same selection already packed, int64 (nheads_k,
+    total_q, ceil(ceil(max_seqlen_k / 64) / 64)) as topk_to_uint64 / infllmv2_topk_mask return it.  causal=True aligns the diagonal to the bottom right when seqlen_q != seqlen_k.
     Rows that see no key return 0.  Returns out (total_q, nheads, 128), or
     (out, softmax_lse (nheads_k, total_q * 16), None) with return_attn_probs=True.
     """
     return Infllmv2AttnVarlenFunc.apply(
         q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale,
         causal, window_size, softcap, alibi_slopes, deterministic, return_attn_probs, block_table,
-        topk_idx)
+        topk_idx, block_mask)
 
 
 # ------------------------------------------------------------------------------------ decode --

@@ -161,7 +161,9 @@ int launch_pool(const PoolParams& p, cudaStream_t st) {
 
 struct TopkParams {
   const void* score;
-  int32_t* out;
+  int32_t* out;                    // (heads, total_q, k) block lists, or null
+  unsigned long long* mask;        // (heads, total_q, mask_words) packed selection, or null
+  int mask_words;
   const int32_t* cu_q;
   const int32_t* cache_lens;
   int batch, heads;
@@ -213,14 +215,14 @@ template <> struct Pack<__half> {
 #ifdef IFV2_TOPK_CHECK
 #define IFV2_TOPK_STORE(pos, val)                                                               \
   do {                                                                                          \
-    if ((unsigned)(pos) < (unsigned)k_cap) o[(pos)] = (val);                                    \
-    else printf("topk: slot %d outside [0,%d) lane %d k_sel %d need %d exact %d bq %d\n", (int)(pos), k_cap, \
+    if (o != nullptr && (unsigned)(pos) < (unsigned)k_cap) o[(pos)] = (val);                    \
+    else if (o != nullptr) printf("topk: slot %d outside [0,%d) lane %d k_sel %d need %d exact %d bq %d\n", (int)(pos), k_cap, \
                 lane, k_sel, need, (int)exact, bq);                                             \
   } while (0)
 #else
 #define IFV2_TOPK_STORE(pos, val)                                  \
   do {                                                             \
-    if ((unsigned)(pos) < (unsigned)k_cap) o[(pos)] = (val);       \
+    if (o != nullptr && (unsigned)(pos) < (unsigned)k_cap) o[(pos)] = (val);   \
   } while (0)
 #endif
 
@@ -231,7 +233,8 @@ template <> struct Pack<__half> {
 template <typename T, int kPairs, int kIts>
 __device__ __forceinline__ int topk_row(const typename Pack<T>::T2 (&v)[kPairs],
                                         typename Pack<T>::T2 tail2, bool restricted, int k_sel,
-                                        int bq, int lane, int32_t* o, int k_cap) {
+                                        int bq, int lane, int32_t* o, int k_cap,
+                                        unsigned long long* mw, int mask_words) {
   using N = Num<T>;
   using P = Pack<T>;
   using T2 = typename P::T2;
@@ -306,6 +309,9 @@ __device__ __forceinline__ int topk_row(const typename Pack<T>::T2 (&v)[kPairs],
       int gt_before = base_gt + (int)(excl & 0xFFFFu);
       int tie_before = base_tie + (int)(excl >> 16);
       const int e0 = (it * 32 + lane) * 8;
+      // slots of this lane that the query may see (index <= bq): only those reach the mask
+      const uint32_t vis_bits = (bq >= e0 + 7) ? 0xFFu : ((bq < e0) ? 0u : ((2u << (bq - e0)) - 1u));
+      uint32_t taken = gt_bits;           // slots selected in this iteration
       if (tie_bits == 0u) {               // the common case: walk the few set bits
         int pos = gt_before + min(tie_before, need);
         uint32_t sel = gt_bits;
@@ -324,10 +330,20 @@ __device__ __forceinline__ int topk_row(const typename Pack<T>::T2 (&v)[kPairs],
             const int pos = gt_before + min(tie_before, need);
             const int idx = e0 + s;
             IFV2_TOPK_STORE(pos, (idx <= bq) ? idx : -1);
+            taken |= 1u << s;
           }
           gt_before += g;
           tie_before += t;
         }
+      }
+      if (mw != nullptr) {
+        // eight lanes own the 64 consecutive entries of one mask word: OR their bytes together
+        unsigned long long wv = (unsigned long long)(taken & vis_bits) << (8 * (lane & 7));
+        wv |= __shfl_xor_sync(0xFFFFFFFFu, wv, 1);
+        wv |= __shfl_xor_sync(0xFFFFFFFFu, wv, 2);
+        wv |= __shfl_xor_sync(0xFFFFFFFFu, wv, 4);
+        const int w = it * 4 + (lane >> 3);
+        if ((lane & 7) == 0 && w < mask_words) mw[w] = wv;
       }
       base_gt += (int)(total & 0xFFFFu);
       base_tie += (int)(total >> 16);
@@ -363,7 +379,8 @@ __global__ void __launch_bounds__(kThreads, (kIters <= 8) ? 2 : 1) topk_select_k
       bq = (int)((q + p.cache_len) / p.block_size);
     }
     const T* x = score + row * p.row_stride;
-    int32_t* o = p.out + row * p.k;
+    int32_t* o = p.out ? p.out + row * p.k : nullptr;
+    unsigned long long* mw = p.mask ? p.mask + row * p.mask_words : nullptr;
 
     // Entries past the query's own block only ever come out as -1.  When none of them beats the
     // k-th best earlier entry (always the case for stage-1 block scores: later blocks hold 0 or
@@ -420,24 +437,33 @@ __global__ void __launch_bounds__(kThreads, (kIters <= 8) ? 2 : 1) topk_select_k
       // (an even iteration count keeps the number of instantiated bodies, and with it the
       //  instruction-cache footprint, small; the extra iteration only holds -inf slots)
       int got = -1;
-      switch (min(kIters, (its + 1) & ~1)) {
+      const int its_used = min(kIters, (its + 1) & ~1);
+      switch (its_used) {
 #define IFV2_TOPK_CASE(I)                                                                \
         case I:                                                                          \
           if constexpr (I <= kIters)                                                     \
-            got = topk_row<T, kPairs, I>(v, tail2, restricted, k_sel, bq, lane, o, p.k); \
+            got = topk_row<T, kPairs, I>(v, tail2, restricted, k_sel, bq, lane, o, p.k,  \
+                                         mw, p.mask_words);                              \
           break;
         IFV2_TOPK_CASE(2) IFV2_TOPK_CASE(4) IFV2_TOPK_CASE(6)
 #undef IFV2_TOPK_CASE
         default:
-          got = topk_row<T, kPairs, kIters>(v, tail2, restricted, k_sel, bq, lane, o, p.k);
+          got = topk_row<T, kPairs, kIters>(v, tail2, restricted, k_sel, bq, lane, o, p.k, mw,
+                                            p.mask_words);
           break;
       }
       if (got < 0) continue;
       emitted = got;
+      // mask words past the iterations that took part hold no selected block
+      if (mw != nullptr) {
+        const int covered = (its_used == 2 || its_used == 4 || its_used == 6 ? its_used : kIters) * 4;
+        for (int w = covered + lane; w < p.mask_words; w += 32) mw[w] = 0ull;
+      }
       break;
     }
     // unused tail (k > entries that took part, or NaN scores that no probe counts)
-    for (int i = emitted + lane; i < p.k; i += 32) o[i] = -1;
+    if (o != nullptr)
+      for (int i = emitted + lane; i < p.k; i += 32) o[i] = -1;
   }
 }
 
@@ -536,8 +562,38 @@ extern "C" int ifv2_topk_select(const void* score, int32_t* out_idx, int is_bf16
   IFV2_REQUIRE(out_idx != nullptr && (score != nullptr || n_blocks == 0), IFV2_ERR_INVALID_ARG,
                "topk_select: null pointer");
   IFV2_REQUIRE(total_q <= INT32_MAX, IFV2_ERR_TOO_LARGE, "topk_select: total_q > 2^31-1");
-  TopkParams p{score, out_idx, cu_seqlens_q, cache_lens, batch, heads, total_q, n_blocks, row_stride,
-               k, cache_len, block_size};
+  TopkParams p{score, out_idx, nullptr, 0, cu_seqlens_q, cache_lens, batch, heads, total_q, n_blocks,
+               row_stride, k, cache_len, block_size};
   return is_bf16 ? launch_topk<__nv_bfloat16>(p, (cudaStream_t)stream)
                  : launch_topk<__half>(p, (cudaStream_t)stream);
+}
+
+extern "C" int ifv2_topk_select_mask(const void* score, int32_t* out_idx, int64_t* row_mask,
+                                     int64_t* col_mask, int is_bf16, int heads, int64_t total_q,
+                                     int n_blocks, int64_t row_stride, int k, int k_blocks,
+                                     const int32_t* cu_seqlens_q, const int32_t* cache_lens, int batch,
+                                     int cache_len, int block_size, void* stream) {
+  IFV2_REQUIRE(heads >= 0 && total_q >= 0 && n_blocks >= 0 && k >= 0 && k_blocks >= 0,
+               IFV2_ERR_INVALID_ARG, "topk_select_mask: negative size");
+  IFV2_REQUIRE(block_size >= 1 && cache_len >= 0, IFV2_ERR_INVALID_ARG,
+               "topk_select_mask: block_size must be >= 1 and cache_len >= 0");
+  IFV2_REQUIRE(row_stride >= n_blocks, IFV2_ERR_INVALID_ARG, "topk_select_mask: row_stride < n_blocks");
+  IFV2_REQUIRE(n_blocks <= 8192 && k_blocks <= 8192, IFV2_ERR_TOO_LARGE,
+               "topk_select_mask: n_blocks = %d / k_blocks = %d exceed the 8192-block limit", n_blocks,
+               k_blocks);
+  IFV2_REQUIRE(cache_lens == nullptr || cu_seqlens_q != nullptr, IFV2_ERR_INVALID_ARG,
+               "topk_select_mask: cache_lens needs cu_seqlens_q");
+  IFV2_REQUIRE(cu_seqlens_q == nullptr || batch >= 1, IFV2_ERR_INVALID_ARG,
+               "topk_select_mask: batch must be >= 1 with cu_seqlens_q");
+  if (heads == 0 || total_q == 0 || k_blocks == 0) return IFV2_OK;
+  IFV2_REQUIRE(row_mask != nullptr && (score != nullptr || n_blocks == 0), IFV2_ERR_INVALID_ARG,
+               "topk_select_mask: null pointer");
+  IFV2_REQUIRE(total_q <= INT32_MAX, IFV2_ERR_TOO_LARGE, "topk_select_mask: total_q > 2^31-1");
+  const int words = (k_blocks + 63) / 64;
+  TopkParams p{score, out_idx, reinterpret_cast<unsigned long long*>(row_mask), words, cu_seqlens_q,
+               cache_lens, batch, heads, total_q, n_blocks, row_stride, k, cache_len, block_size};
+  int rc = is_bf16 ? launch_topk<__nv_bfloat16>(p, (cudaStream_t)stream)
+                   : launch_topk<__half>(p, (cudaStream_t)stream);
+  if (rc != IFV2_OK || col_mask == nullptr) return rc;
+  return ifv2_transpose_blockmask(row_mask, col_mask, heads, total_q, k_blocks, stream);
 }

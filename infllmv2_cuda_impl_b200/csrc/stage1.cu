@@ -1,26 +1,37 @@
 // Stage-1 scorer: group-summed softmax probabilities of the queries against the compressed keys,
 // optionally max-pooled to 64-token block scores in the same kernel.
 //
-// One CTA owns 8 consecutive tokens x the 16 query heads of one KV head (128 rows, fetched by one
-// 3-D TMA box from the caller's (token, head, d) layout) and streams 128-key tiles of the
-// compressed keys twice:
-//   pass 1:  S   = Q . Kc^T   (rows = query rows in TMEM lanes)   -> running max m and sum l per row
-//   pass 2:  S^T = Kc . Q^T   (rows = keys in TMEM lanes)         -> p = exp2(c*s - c*m - log2 l);
-//            because the 16 heads of a token are now 16 adjacent COLUMNS of one thread's row,
-//            the GQA group sum is an in-register sum: no shuffles, no shared memory.
-// Both products use the same two swizzled shared-memory tiles with the operand roles swapped.
+// One CTA (one per SM) owns 16 consecutive tokens x the 16 query heads of one KV head: two 128-row
+// query tiles A and B, each fetched by 3-D TMA boxes from the caller's (token, head, d) layout, and
+// streams 128-key tiles of the compressed keys twice through a 4-slot ring.  Every key tile serves
+// both query tiles, which halves the L2 -> SM key traffic per score against an 8-token CTA:
+//   pass 1:  S = Q_t . Kc^T  (rows = query rows of tile t in TMEM lanes) -> reference point m
+//            and sum l per row
+//   pass 2:  S^T = Kc . Q_t^T  (rows = keys in TMEM lanes)
+//            -> p = exp2(c*s - c*m - log2 l); because the 16 heads of a token are now 16 adjacent
+//            COLUMNS of one thread's row, the GQA group sum is an in-register sum.
+// Both passes use the same swizzled shared-memory tiles with the operand roles swapped.
 // In pass 2 the per-row constant -(c*m + log2 l)/c rides along inside the tensor-core product as
 // one extra 16-wide K step (a tile of ones against a tile holding the constant split into three
 // bf16 terms), so the softmax warps do one multiply and one ex2 per score and nothing else.
+// Pass 1 does not track the running maximum: m is the maximum of the row's first visible 32-key
+// chunk and stays fixed, so a score costs one FMA, one ex2 and one add; the sum is exact for any
+// reference point as long as it stays finite, and a chunk whose sum leaves the fp32 range (a score
+// more than ~100 log2 units above m) is redone with a fresh maximum.
 // The bf16 result row (Hk, token, key) is written straight from registers, columns past the last
 // visible key are zero-filled (no pre-zeroing, slice or NaN scrub).  With pooling enabled each
-// tile's 128 x 8 scores also go through a small shared-memory window and leave as 32 x 8 block
+// tile's 128 x 16 scores also go through a small shared-memory window and leave as 32 x 16 block
 // scores (5-wide / stride-4 max, +inf on the init and causal-local blocks), bit-identical to
 // running the max-pool kernel on the score tensor.
-// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = softmax: two groups of four
-// warps; both groups cover all 128 TMEM lanes and each takes half of every tile's 128 columns
-// (pass 1: 64 of the keys, merged once at the end; pass 2: 4 of the 8 tokens), which doubles the
-// number of warps the MUFU-bound exponential loops can be issued from.
+// The two query tiles are two independent pipelines that share nothing but the key ring: each has
+// its own MMA-issuing warp, its own pair of 128-column accumulator buffers in TMEM, its own eight
+// softmax warps and its own barriers, so the tiles drift out of phase and one tile's exponentials
+// fill the special-function unit while the other waits, loads or pools (a single lock-stepped
+// pipeline leaves the unit idle in those phases).
+// Warp roles: warp 0 = TMA producer, warps 1-2 = MMA issuers (tile A, tile B), warps 3-18 =
+// softmax: per tile two groups of four warps; both groups cover all 128 TMEM lanes and each takes
+// half of every accumulator's 128 columns (pass 1: 64 of the keys, merged once at the end;
+// pass 2: 4 of the tile's 8 tokens).
 #include "tc05.cuh"
 
 namespace ifv2 {
@@ -28,22 +39,34 @@ namespace {
 
 using namespace tc;
 
-constexpr int kTokPerTile = 8;
-constexpr int kThreads = 320;
-constexpr int kSoftmaxThreads = 256;
+constexpr int kTokPerCta = 16;
+constexpr int kTokPerBox = 8;                 // tokens of one 128-row query tile
+constexpr int kHalfThreads = 256;              // softmax threads of one query tile
+constexpr int kSoftmaxThreads = 2 * kHalfThreads;
+constexpr int kThreads = 96 + kSoftmaxThreads; // + TMA warp + two MMA warps
 constexpr int kKeysPerTile = 128;
+constexpr int kStages = 4;                    // key-tile ring
 constexpr uint32_t kHalfBytes = 128 * 128;    // 128 rows x 64 bf16
-constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kTmemCols = 512;
 constexpr int kPoolSlots = 136;               // 1 halo + 128 keys, padded
 #ifndef IFV2_STAGE1_POLY_STRIDE
-#define IFV2_STAGE1_POLY_STRIDE 8
+#define IFV2_STAGE1_POLY_STRIDE 0
 #endif
-// every kPolyStride-th exponential of a row runs on the FMA pipe (0: none)
+// every kPolyStride-th exponential of a row runs as a polynomial on the FMA pipe (0: none).  Measured at
+// 131072 tokens: strides 0, 6 and 8 run within 1 % of each other and 4 is 5 % slower -- the kernel is
+// bound by the per-step chain of its softmax warps, not by the throughput of the exponential unit.
 constexpr int kPolyStride = IFV2_STAGE1_POLY_STRIDE;
 __device__ __forceinline__ float exp2_mixed(float x, int c) {
   return (kPolyStride > 0 && c % (kPolyStride > 0 ? kPolyStride : 1) == (kPolyStride - 1))
              ? exp2_fma(x) : exp2f(x);
 }
+// the same for pass 1, whose argument is not bounded above: past 2^128 the polynomial form must
+// produce inf / NaN (which the overflow check catches), not wrap into the sign bit
+__device__ __forceinline__ float exp2_mixed_unbounded(float x, int c) {
+  return (kPolyStride > 0 && c % (kPolyStride > 0 ? kPolyStride : 1) == (kPolyStride - 1))
+             ? exp2_fma(fminf(x, 128.f)) : exp2f(x);
+}
+constexpr float kSumLimit = 1e30f;            // a chunk sum at or above this is redone with a fresh maximum
 
 struct Stage1Params {
   __nv_bfloat16* out;             // scores, may be null when only block scores are wanted
@@ -65,16 +88,18 @@ struct Stage1Params {
 };
 
 struct Smem {
-  uint8_t q[2][kHalfBytes];          // [d half]
-  uint8_t kc[2][2][kHalfBytes];      // [stage][d half]
-  uint8_t ones[4096];                // 128 x 16 bf16, no swizzle: columns 0..2 = 1
-  uint8_t rowc[4096];                // 128 x 16 bf16, no swizzle: columns 0..2 = row constant (3 terms)
-  __nv_bfloat16 pool[3][kTokPerTile][kPoolSlots];   // scores of the last three key tiles (pooling is
-  __nv_bfloat16 carry[4][kTokPerTile];              // deferred by one tile), and each tile's last key
-  float2 stat[128];                  // pass-1 (max, sum) of the second column half, per row
-  // acc_full[s] doubles as "the key tile of slot s may be refilled": one commit per step (a
-  // tcgen05.commit costs the issuing warp about as much as two MMAs)
-  uint64_t q_full, kc_full[2], acc_full[2], acc_empty[2], rowc_ready, pool_full[3];
+  uint8_t q[2][2][kHalfBytes];         // [query tile][d half]
+  uint8_t kc[kStages][2][kHalfBytes];  // [stage][d half]
+  uint8_t ones[4096];                  // 128 x 16 bf16, no swizzle: columns 0..2 = 1
+  uint8_t rowc[2][4096];               // per query tile, 128 x 16 bf16, no swizzle: columns 0..2 = row constant (3 terms)
+  __nv_bfloat16 pool[2][3][kTokPerBox][kPoolSlots];   // per query tile: scores of the last three key tiles
+  __nv_bfloat16 carry[2][4][kTokPerBox];              // (pooling is deferred by one tile), and each tile's last key
+  float2 stat[2][128];                 // pass-1 (reference point, sum) of the second column half, per row
+  // kc_free[s]: the products of BOTH query tiles that read key slot s are complete (2 arrivals);
+  // per query tile: acc_full[b]: accumulator buffer b holds a step's scores; acc_empty[b]: its 8
+  // softmax warps have read it
+  uint64_t q_full, kc_full[kStages], kc_free[kStages], acc_full[2][2], acc_empty[2][2], rowc_ready[2],
+      pool_full[2][3];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -94,7 +119,7 @@ __device__ __forceinline__ float bf16_round(float x) {
 }
 
 template <bool kPooled>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kc,
               const __grid_constant__ CUtensorMap map_kv, const Stage1Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -105,14 +130,14 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b];
   const int lc = p.seqused_k ? max(0, min(p.seqused_k[b], p.cu_k[b + 1] - k0)) : p.cu_k[b + 1] - k0;
-  const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTokPerTile;   // long tiles first
+  const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTokPerCta;   // long tiles first
   if (tok0 >= lq) return;
-  // an earlier CTA gave up on a wait: the launch is already failed, do not pile up more waits
+  // an earlier CTA of this launch gave up on a wait: do not pile up more waits
   if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
-  const int ntok = min(kTokPerTile, lq - tok0);
+  const int ntok = min(kTokPerCta, lq - tok0);
   const int lim_max = visible_limit(tok0 + ntok - 1, lq, lc, p.causal);    // limits grow with i
-  // Pass 1 (row maxima and sums) runs over the keys given as `v`: the same compressed keys, or a
-  // coarser compression (kernel 128 / stride 64) whose log-sum-exp then normalises the scores of
+  // Pass 1 (row sums) runs over the keys given as `v`: the same compressed keys, or a coarser
+  // compression (kernel 128 / stride 64) whose log-sum-exp then normalises the scores of
   // pass 2 -- the reference switches on the key counts (flash_fwd_kernel.h:1236-1240)
   const int v0 = p.cu_v ? p.cu_v[b] : k0;
   const int lcv = !p.cu_v ? lc
@@ -129,13 +154,18 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
     mbar_init(&sm.q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&sm.kc_full[s], 1);
-      mbar_init(&sm.acc_full[s], 1);
-      mbar_init(&sm.acc_empty[s], 8);       // one arrival per softmax warp
+      mbar_init(&sm.kc_free[s], 2);               // one commit per MMA warp
     }
-    mbar_init(&sm.rowc_ready, 4);
-    for (int s = 0; s < 3; ++s) mbar_init(&sm.pool_full[s], 8);
+    for (int hq = 0; hq < 2; ++hq) {
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(&sm.acc_full[hq][s], 1);
+        mbar_init(&sm.acc_empty[hq][s], 8);       // one arrival per softmax warp of the tile
+      }
+      mbar_init(&sm.rowc_ready[hq], 4);
+      for (int s = 0; s < 3; ++s) mbar_init(&sm.pool_full[hq][s], 8);
+    }
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_kc);
@@ -145,11 +175,9 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     tmem_alloc(&sm.tmem_base, kTmemCols);
     tmem_relinquish();
   }
-  // the tile of ones (columns 0..2) and the zero part of the row-constant tile
-  for (int i = threadIdx.x; i < 4096 / 4; i += kThreads) {
-    reinterpret_cast<uint32_t*>(sm.ones)[i] = 0u;
-    reinterpret_cast<uint32_t*>(sm.rowc)[i] = 0u;
-  }
+  // the tile of ones (columns 0..2) and the zero part of the row-constant tiles
+  for (int i = threadIdx.x; i < 4096 / 4; i += kThreads) reinterpret_cast<uint32_t*>(sm.ones)[i] = 0u;
+  for (int i = threadIdx.x; i < 8192 / 4; i += kThreads) reinterpret_cast<uint32_t*>(sm.rowc)[i] = 0u;
   __syncthreads();
   if (threadIdx.x < 128) {
     const __nv_bfloat16 one = __float2bfloat16_rn(1.f);
@@ -166,14 +194,15 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   if (warp == 0) {
     // ================================================================ TMA producer
     if (lane == 0 && n_steps > 0) {
-      mbar_expect_tx(&sm.q_full, 2 * kHalfBytes);
-      tma_load_3d(sm.q[0], &map_q, &sm.q_full, 0, h * kGroup, q0 + tok0);
-      tma_load_3d(sm.q[1], &map_q, &sm.q_full, 64, h * kGroup, q0 + tok0);
+      mbar_expect_tx(&sm.q_full, 4 * kHalfBytes);
+      for (int tile = 0; tile < 2; ++tile)       // rows past the last token come back as zeros or as
+        for (int dh = 0; dh < 2; ++dh)           // the next sequence's rows; they are never stored
+          tma_load_3d(sm.q[tile][dh], &map_q, &sm.q_full, dh * 64, h * kGroup, q0 + tok0 + tile * kTokPerBox);
       int issued = 0;
       for (int t = 0; t < n_steps; ++t) {
-        const int s = t & 1;
-        if (t >= 2 && !mbar_wait(&sm.acc_full[s], (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag,
-                                 p.status, 41))
+        const int s = t % kStages;
+        if (t >= kStages && !mbar_wait(&sm.kc_free[s], (uint32_t)((t / kStages - 1) & 1), abort_flag,
+                                       p.status, 41))
           break;
         mbar_expect_tx(&sm.kc_full[s], 2 * kHalfBytes);
         if (t < n_tiles1) {
@@ -187,110 +216,136 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
       if (*abort_flag) {
         mbar_wait_drain(&sm.q_full, 0);
-        for (int j = max(0, issued - 2); j < issued; ++j)
-          mbar_wait_drain(&sm.kc_full[j & 1], (uint32_t)((j >> 1) & 1));
+        for (int j = max(0, issued - kStages); j < issued; ++j)
+          mbar_wait_drain(&sm.kc_full[j % kStages], (uint32_t)((j / kStages) & 1));
       }
     }
-  } else if (warp == 1) {
-    // ================================================================ MMA issuer
+  } else if (warp <= 2) {
+    // ================================================================ MMA issuer of query tile hq
     // All 32 lanes run the same issue code (descriptors stay in uniform registers); `leader`
     // enables the MMA / commit instructions in one lane only.
     if (n_steps > 0) {
+      const int hq = __shfl_sync(0xFFFFFFFFu, warp - 1, 0);
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128, false);
-      const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
+      const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q[0][0]), 16, 1024) + (uint32_t)hq * ((2 * kHalfBytes) >> 4);
       const uint64_t kc_desc0 = umma_desc_sw128(smem_u32(sm.kc[0][0]), 16, 1024);
-      constexpr uint32_t kStage = (2 * kHalfBytes) >> 4;      // descriptor address units per stage
+      constexpr uint32_t kStage = (2 * kHalfBytes) >> 4;      // descriptor address units per ring stage
       const uint64_t d_ones = umma_desc_noswz16(smem_u32(sm.ones));
-      const uint64_t d_rowc = umma_desc_noswz16(smem_u32(sm.rowc));
+      const uint64_t d_rowc = umma_desc_noswz16(smem_u32(sm.rowc[0])) + (uint32_t)hq * (4096u >> 4);
+      const uint32_t acc0 = tmem + (uint32_t)hq * 256u;
       bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full, 0, abort_flag, p.status, 51));
       for (int t = 0; t < n_steps && ok; ++t) {
-        const int s = t & 1;
-        const uint32_t par = (uint32_t)((t >> 1) & 1);
+        const int s = t % kStages, ab = t & 1;
         const bool pass2 = t >= n_tiles1;
-        bool w = mbar_wait(&sm.kc_full[s], par, abort_flag, p.status, 52);
-        if (w && t >= 2) w = mbar_wait(&sm.acc_empty[s], par ^ 1u, abort_flag, p.status, 53);
-        if (w && t == n_tiles1) w = mbar_wait(&sm.rowc_ready, 0, abort_flag, p.status, 54);
+        bool w = mbar_wait(&sm.kc_full[s], (uint32_t)((t / kStages) & 1), abort_flag, p.status, 52);
+        if (w && t >= 2)
+          w = mbar_wait(&sm.acc_empty[hq][ab], (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag, p.status, 53);
+        if (w && t == n_tiles1) w = mbar_wait(&sm.rowc_ready[hq], 0, abort_flag, p.status, 54);
         ok = __all_sync(0xFFFFFFFFu, w);
         if (!ok) break;
         tc_fence_after();
+        const uint64_t kc_desc = kc_desc0 + (uint32_t)s * kStage;
+        const uint32_t acc = acc0 + (uint32_t)ab * 128u;
         if (!pass2) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-            umma_ss_pred(tmem + s * 128, q_desc + off, kc_desc0 + s * kStage + off, idesc, kk > 0, leader);
+            umma_ss_pred(acc, q_desc + off, kc_desc + off, idesc, kk > 0, leader);
           }
         } else {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-            umma_ss_pred(tmem + s * 128, kc_desc0 + s * kStage + off, q_desc + off, idesc, kk > 0, leader);
+            umma_ss_pred(acc, kc_desc + off, q_desc + off, idesc, kk > 0, leader);
           }
-          umma_ss_pred(tmem + s * 128, d_ones, d_rowc, idesc, true, leader);   // + row constant
+          umma_ss_pred(acc, d_ones, d_rowc, idesc, true, leader);   // + row constant
         }
-        umma_commit_pred(&sm.acc_full[s], leader);
+        umma_commit_pred(&sm.kc_free[s], leader);
+        umma_commit_pred(&sm.acc_full[hq][ab], leader);
       }
     }
   } else {
     // ================================================================ softmax warps
+    const int hq = (warp - 3) >> 3;                  // query tile
     const int quad = warp & 3;
-    const int grp = (warp - 2) >> 2;                 // which half of the columns this warp takes
+    const int grp = ((warp - 3) >> 2) & 1;           // which half of the accumulator's columns
     const int r = quad * 32 + lane;                  // TMEM lane: pass 1 = query row, pass 2 = key
-    const uint32_t lane_off = ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * 64);
-    const int st = threadIdx.x - 64;                 // 0..255 among the softmax threads
+    const uint32_t lane_off = ((uint32_t)(quad * 32) << 16) + (uint32_t)(hq * 256 + grp * 64);
+    const int st = threadIdx.x - 96 - hq * kHalfThreads;   // 0..255 among the tile's softmax threads
+    const int tokh = tok0 + hq * kTokPerBox;         // first token of this tile
+    const int ntokh = min(max(ntok - hq * kTokPerBox, 0), kTokPerBox);
+    uint64_t* acc_full = sm.acc_full[hq];
+    uint64_t* acc_empty = sm.acc_empty[hq];
+    uint64_t* pool_full = sm.pool_full[hq];
     bool ok = true;
 
-    // ---------------- pass 1: running max / sum of this thread's query row
+    // ---------------- pass 1: sum of this thread's query row over its half of every key tile
     {
       const int tl = r >> 4;
-      const int lim_row = (tl < ntok) ? visible_limit(tok0 + tl, lq, lcv, p.causal, st1) : 0;
+      const int lim_row = (tl < ntokh) ? visible_limit(tokh + tl, lq, lcv, p.causal, st1) : 0;
       float m = -INFINITY, l = 0.f;
       for (int t = 0; t < n_tiles1; ++t) {
-        const int s = t & 1;
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.acc_full[s], (uint32_t)((t >> 1) & 1),
-                                               abort_flag, p.status, 61));
+        const int ab = t & 1;
+        ok = mbar_wait_warp(&acc_full[ab], (uint32_t)((t >> 1) & 1), abort_flag, p.status, 61);
         if (!ok) break;
         tc_fence_after();
         // visible columns among this group's 64
         const int lim = min(max(lim_row - t * kKeysPerTile - grp * 64, 0), 64);
         const bool full = __all_sync(0xFFFFFFFFu, lim == 64);
-        uint32_t buf[2][32];
-        tmem_ld32(tmem + lane_off + s * 128, buf[0]);
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          tmem_wait_ld_dep(buf[ch & 1]);
-          if (ch < 1) tmem_ld32(tmem + lane_off + s * 128 + (ch + 1) * 32, buf[(ch + 1) & 1]);
-          uint32_t (&x)[32] = buf[ch & 1];
-          if (!full) {
-#pragma unroll
-            for (int c = 0; c < 32; ++c)
-              if (ch * 32 + c >= lim) x[c] = 0xFF800000u;                 // -inf
-          }
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(x[c]));
-          const float cm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-          const float m_new = fmaxf(m, cm);
-          if (m_new > -INFINITY) {
-            const float neg = -m_new * p.scale_log2;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int c = 0; c < 32; ++c)
-              sum[c & 3] += exp2_mixed(fmaf(__uint_as_float(x[c]), p.scale_log2, neg), c);
-            const float f = (m > -INFINITY) ? exp2f(fmaf(m, p.scale_log2, neg)) : 0.f;
-            l = l * f + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
-            m = m_new;
-          }
-        }
+        uint32_t x[64];
+        tmem_ld64_wait(tmem + lane_off + ab * 128, x);
+        // the scores are in registers: the accumulator goes back to the MMA warp at once
         tc_fence_before();
-        mbar_arrive_warp(&sm.acc_empty[s]);
+        mbar_arrive_warp(&acc_empty[ab]);
+        if (!full) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (c >= lim) x[c] = 0xFF800000u;                             // -inf
+        }
+        if (m == -INFINITY) {            // no visible score yet: the first one fixes the reference point
+          float mx = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(x[c]));
+          m = mx;
+        }
+        if (m > -INFINITY) {
+          float neg = -m * p.scale_log2;
+          const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg, neg);
+          uint64_t s2[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s2[i] = pack_f32x2(0.f, 0.f);
+#pragma unroll
+          for (int c = 0; c < 64; c += 2) {
+            float a0, a1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(x[c], x[c + 1]), c2, n2), a0, a1);
+            s2[(c >> 1) & 3] = add_f32x2(s2[(c >> 1) & 3], pack_f32x2(exp2_mixed_unbounded(a0, c),
+                                                                      exp2_mixed_unbounded(a1, c + 1)));
+          }
+          float lo, hi;
+          unpack_f32x2(add_f32x2(add_f32x2(s2[0], s2[1]), add_f32x2(s2[2], s2[3])), lo, hi);
+          float cs = lo + hi;
+          if (!(cs < kSumLimit)) {       // a score far above the reference point: move the point to the maximum
+            float mx = m;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(x[c]));
+            l *= exp2f((m - mx) * p.scale_log2);
+            m = mx;
+            neg = -m * p.scale_log2;
+            cs = 0.f;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) cs += exp2f(fmaf(__uint_as_float(x[c]), p.scale_log2, neg));
+          }
+          l += cs;
+        }
       }
-      // merge the two column halves of every row, then publish the row constant for pass 2, in
+      // merge the two key halves of every row, then publish the row constant for pass 2, in
       // units of the raw score: -(m + log2(l) / c), as three bf16 terms
-      if (grp == 1) sm.stat[r] = make_float2(m, l);
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (grp == 1) sm.stat[hq][r] = make_float2(m, l);
+      if (hq == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
       if (grp == 0) {
-        const float2 o = sm.stat[r];
+        const float2 o = sm.stat[hq][r];
         const float mm = fmaxf(m, o.x);
         if (mm > -INFINITY)
           l = l * ((m > -INFINITY) ? exp2f((m - mm) * p.scale_log2) : 0.f) +
@@ -300,51 +355,53 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // (tests/stage1/complse_online_softmax.py: its NaN row sum is scrubbed to 0)
         const float rc = (l > 0.f) ? -(m + log2f(l) * p.inv_scale_log2) : -30000.f;
         const float t0 = bf16_round(rc), t1 = bf16_round(rc - t0), t2 = bf16_round(rc - t0 - t1);
-        *reinterpret_cast<__nv_bfloat16*>(sm.rowc + umma_noswz16_off(r, 0)) = __float2bfloat16_rn(t0);
-        *reinterpret_cast<__nv_bfloat16*>(sm.rowc + umma_noswz16_off(r, 1)) = __float2bfloat16_rn(t1);
-        *reinterpret_cast<__nv_bfloat16*>(sm.rowc + umma_noswz16_off(r, 2)) = __float2bfloat16_rn(t2);
+        uint8_t* rowc = sm.rowc[hq];
+        *reinterpret_cast<__nv_bfloat16*>(rowc + umma_noswz16_off(r, 0)) = __float2bfloat16_rn(t0);
+        *reinterpret_cast<__nv_bfloat16*>(rowc + umma_noswz16_off(r, 1)) = __float2bfloat16_rn(t1);
+        *reinterpret_cast<__nv_bfloat16*>(rowc + umma_noswz16_off(r, 2)) = __float2bfloat16_rn(t2);
         fence_proxy_async_smem();
-        mbar_arrive_warp(&sm.rowc_ready);
+        mbar_arrive_warp(&sm.rowc_ready[hq]);
       }
     }
 
-    // ---------------- pass 2: this thread's key against all 128 query rows
-    constexpr int kTokPerThread = kTokPerTile / 2;           // tokens grp*4 .. grp*4+3
+    // ---------------- pass 2: this thread's key against 4 tokens x 16 heads
+    constexpr int kTokPerThread = kTokPerBox / 2;            // tokens grp*4 .. grp*4+3 of the tile
     int lim_tok[kTokPerThread];
     const int cache_len = p.cache_lens ? p.cache_lens[b] : p.cache_len;
 #pragma unroll
     for (int j = 0; j < kTokPerThread; ++j) {
       // a token without any visible row-sum key scores exactly 0 (the huge negative row constant
       // alone leaves 2^-125 per polynomial exponential)
-      const int tk = tok0 + grp * 4 + j;
-      lim_tok[j] = (grp * 4 + j < ntok && visible_limit(tk, lq, lcv, p.causal, st1) > 0)
+      const int tk = tokh + grp * kTokPerThread + j;
+      lim_tok[j] = (grp * kTokPerThread + j < ntokh && visible_limit(tk, lq, lcv, p.causal, st1) > 0)
                        ? visible_limit(tk, lq, lc, p.causal) : 0;
     }
     __nv_bfloat16* out_base =
-        p.out ? p.out + ((int64_t)h * p.total_q + q0 + tok0) * p.out_row_stride : nullptr;
+        p.out ? p.out + ((int64_t)h * p.total_q + q0 + tokh) * p.out_row_stride : nullptr;
     __nv_bfloat16* pool_base =
-        kPooled ? p.pooled + ((int64_t)h * p.total_q + q0 + tok0) * p.pooled_len : nullptr;
+        kPooled ? p.pooled + ((int64_t)h * p.total_q + q0 + tokh) * p.pooled_len : nullptr;
     const __nv_bfloat16 ninf_b = __float2bfloat16_rn(-INFINITY);
+    __nv_bfloat16 (*pool)[kTokPerBox][kPoolSlots] = sm.pool[hq];
+    __nv_bfloat16 (*carry)[kTokPerBox] = sm.carry[hq];
 
-    // Max-pool of one finished key tile: 32 blocks x 8 tokens, two per thread.  It runs one tile
+    // Max-pool of one finished key tile: 32 blocks x 8 tokens, one per thread.  It runs one tile
     // late, after the next tile's exponentials, so that no warp waits for the others here.
     auto pool_tile = [&](int tile) -> bool {
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pool_full[tile % 3], (uint32_t)((tile / 3) & 1),
-                                             abort_flag, p.status, 63)))
+      if (!mbar_wait_warp(&pool_full[tile % 3], (uint32_t)((tile / 3) & 1), abort_flag, p.status, 63))
         return false;
       {
         const int t8 = st >> 5, bl = st & 31;
         const int blk = tile * 32 + bl;
-        const __nv_bfloat16* w = &sm.pool[tile % 3][t8][4 * bl];          // slots 4bl .. 4bl+4
+        const __nv_bfloat16* w = &pool[tile % 3][t8][4 * bl];             // slots 4bl .. 4bl+4
         float mxv = fmaxf(fmaxf(__bfloat162float(w[1]), __bfloat162float(w[2])),
                           fmaxf(__bfloat162float(w[3]), __bfloat162float(w[4])));
         float first = -INFINITY;                                          // key 4*blk - 1
         if (bl > 0) first = __bfloat162float(w[0]);
-        else if (tile > 0) first = __bfloat162float(sm.carry[(tile - 1) & 3][t8]);
+        else if (tile > 0) first = __bfloat162float(carry[(tile - 1) & 3][t8]);
         mxv = fmaxf(mxv, first);
-        const int bq = (tok0 + t8 + cache_len) / kBlockN;
+        const int bq = (tokh + t8 + cache_len) / kBlockN;
         if (blk < p.init_blocks || (bq >= blk && bq <= blk + p.local_blocks)) mxv = INFINITY;
-        if (t8 < ntok && blk < p.pooled_len)
+        if (t8 < ntokh && blk < p.pooled_len)
           pool_base[(int64_t)t8 * p.pooled_len + blk] = __float2bfloat16_rn(mxv);
       }
       return true;
@@ -352,29 +409,31 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
     if (ok) {
       for (int t = n_tiles1; t < n_steps; ++t) {
-        const int s = t & 1, tile = t - n_tiles1;
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.acc_full[s], (uint32_t)((t >> 1) & 1),
-                                               abort_flag, p.status, 62));
+        const int ab = t & 1, tile = t - n_tiles1;
+        ok = mbar_wait_warp(&acc_full[ab], (uint32_t)((t >> 1) & 1), abort_flag, p.status, 62);
         if (!ok) break;
         tc_fence_after();
         const int key = tile * kKeysPerTile + r;
         float val[kTokPerThread];
-        uint32_t buf[2][32];
-        tmem_ld32(tmem + lane_off + s * 128, buf[0]);
+        uint32_t x[64];                                   // 4 tokens x 16 heads
+        tmem_ld64_wait(tmem + lane_off + ab * 128, x);
+        // the accumulator is in registers now: hand it back before the arithmetic
+        tc_fence_before();
+        mbar_arrive_warp(&acc_empty[ab]);
+        {
+          const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {                  // 32 columns = 2 tokens x 16 heads
-          tmem_wait_ld_dep(buf[ch & 1]);
-          if (ch < 1) tmem_ld32(tmem + lane_off + s * 128 + (ch + 1) * 32, buf[(ch + 1) & 1]);
-          const uint32_t (&x)[32] = buf[ch & 1];
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            float a0 = 0.f, a1 = 0.f;
+          for (int j = 0; j < kTokPerThread; ++j) {
+            uint64_t a2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
 #pragma unroll
             for (int g = 0; g < 16; g += 2) {
-              a0 += exp2_mixed(__uint_as_float(x[half * 16 + g]) * p.scale_log2, g);
-              a1 += exp2_mixed(__uint_as_float(x[half * 16 + g + 1]) * p.scale_log2, g + 1);
+              float y0, y1;
+              unpack_f32x2(mul_f32x2(pack_f32x2(x[j * 16 + g], x[j * 16 + g + 1]), c2), y0, y1);
+              a2[(g >> 1) & 1] = add_f32x2(a2[(g >> 1) & 1], pack_f32x2(exp2_mixed(y0, g), exp2_mixed(y1, g + 1)));
             }
-            val[ch * 2 + half] = a0 + a1;
+            float lo, hi;
+            unpack_f32x2(add_f32x2(a2[0], a2[1]), lo, hi);
+            val[j] = lo + hi;
           }
         }
         if (kPooled && tile > 0) {
@@ -383,21 +442,19 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
 #pragma unroll
         for (int j = 0; j < kTokPerThread; ++j) {
-          const int t8 = grp * 4 + j;
+          const int t8 = grp * kTokPerThread + j;
           // existing but invisible keys score 0; keys past the sequence do not exist (-inf in the pool)
           const __nv_bfloat16 vb = __float2bfloat16_rn((key < lim_tok[j]) ? val[j] : 0.f);
-          if (out_base != nullptr && t8 < ntok && key < p.max_seqlen_k)
+          if (out_base != nullptr && t8 < ntokh && key < p.max_seqlen_k)
             out_base[(int64_t)t8 * p.out_row_stride + key] = vb;
           if (kPooled) {
             const __nv_bfloat16 pv = (key < lc) ? vb : ninf_b;
-            sm.pool[tile % 3][t8][1 + r] = pv;
-            if (r == 127) sm.carry[tile & 3][t8] = pv;
+            pool[tile % 3][t8][1 + r] = pv;
+            if (r == 127) carry[tile & 3][t8] = pv;
           }
         }
-        if (kPooled) mbar_arrive_warp(&sm.pool_full[tile % 3]);
         // (after the deferred pooling reads: this arrival is what lets a later tile reuse them)
-        tc_fence_before();
-        mbar_arrive_warp(&sm.acc_empty[s]);
+        if (kPooled) mbar_arrive_warp(&pool_full[tile % 3]);
       }
       if (ok && kPooled && n_tiles > 0) ok = pool_tile(n_tiles - 1);
       // columns past the last tile are zero (rows are 16-byte aligned: stride % 8 == 0)
@@ -405,22 +462,22 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       if (ok && out_base != nullptr && first < p.max_seqlen_k) {
         const int vec_per_row = (p.max_seqlen_k - first + 7) / 8;   // may spill into row padding
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-        for (int t8 = 0; t8 < ntok; ++t8) {
+        for (int t8 = 0; t8 < ntokh; ++t8) {
           uint4* dst = reinterpret_cast<uint4*>(out_base + (int64_t)t8 * p.out_row_stride + first);
-          for (int i = st; i < vec_per_row; i += kSoftmaxThreads) dst[i] = z;
+          for (int i = st; i < vec_per_row; i += kHalfThreads) dst[i] = z;
         }
       }
       // block scores past the last tile: their keys are invisible (0) or do not exist (-inf);
       // the first such block still sees the last key of the last tile
       if (ok && kPooled) {
         const int first_blk = n_tiles * 32;
-        for (int t8 = 0; t8 < ntok; ++t8) {
-          const int bq = (tok0 + t8 + cache_len) / kBlockN;
-          for (int blk = first_blk + st; blk < p.pooled_len; blk += kSoftmaxThreads) {
+        for (int t8 = 0; t8 < ntokh; ++t8) {
+          const int bq = (tokh + t8 + cache_len) / kBlockN;
+          for (int blk = first_blk + st; blk < p.pooled_len; blk += kHalfThreads) {
             float v = (4 * blk < lc) ? 0.f : -INFINITY;                   // keys 4blk .. 4blk+3
             if (blk > 0 && 4 * blk - 1 < lc)                              // key 4blk - 1
               v = fmaxf(v, (blk == first_blk && n_tiles > 0)
-                               ? __bfloat162float(sm.carry[(n_tiles - 1) & 3][t8]) : 0.f);
+                               ? __bfloat162float(carry[(n_tiles - 1) & 3][t8]) : 0.f);
             if (blk < p.init_blocks || (bq >= blk && bq <= blk + p.local_blocks)) v = INFINITY;
             pool_base[(int64_t)t8 * p.pooled_len + blk] = __float2bfloat16_rn(v);
           }
@@ -478,7 +535,7 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
                IFV2_ERR_INVALID_ARG, "%s: bad row-sum keys", what);
   CUtensorMap map_q, map_kc, map_kv;
   int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, total_q, kHeadDim * 2,
-                                   (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerTile);
+                                   (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerBox);
   if (rc) return rc;
   // an empty key tensor still needs a valid map: point it at q, no tile is ever fetched
   rc = make_tensor_map_bf16_3d(&map_kc, total_c > 0 ? kc : q, kHeadDim, heads_k,
@@ -515,7 +572,7 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
   p.status = status;
 
   const size_t smem = sizeof(Smem) + 1024;
-  dim3 grid((max_seqlen_q + kTokPerTile - 1) / kTokPerTile, batch, heads_k);
+  dim3 grid((max_seqlen_q + kTokPerCta - 1) / kTokPerCta, batch, heads_k);
   rc = clear_launch_status(status, stream, what);
   if (rc) return rc;
   cudaError_t e;

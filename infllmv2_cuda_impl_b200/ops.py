@@ -211,6 +211,55 @@ def infllmv2_topk(block_score: torch.Tensor, k: int, cache_len: int = 0,
     return out
 
 
+def infllmv2_topk_mask(block_score: torch.Tensor, k: int, max_seqlen_k: int, cache_len: int = 0,
+                       cu_seqlens_q: Optional[torch.Tensor] = None,
+                       cache_lens: Optional[torch.Tensor] = None, block_size: int = 64,
+                       return_idx: bool = False, return_col_mask: bool = False):
+    """Top-k of block scores straight to the packed block mask (an addition to the reference API):
+    the selection of `infllmv2_topk` and the words of `topk_to_uint64(idx, max_seqlen_k, block_size)`
+    from one kernel, without the int32 list in between.  Returns (row_mask int64 (Hk, T,
+    ceil(k_blocks / 64)), k_blocks) followed, when asked for, by topk_idx (Hk, T, k) int32 and by
+    the column mask (Hk, k_blocks, ceil(T / 64)) that the backward reads (`transpose_blockmask`
+    of the row mask, run inside the same call).  Pass the row mask to infllmv2_attn_varlen_func
+    as `block_mask`."""
+    assert block_score.dtype == torch.float16 or block_score.dtype == torch.bfloat16
+    _require_cuda(block_score, "block_score")
+    if block_score.dim() != 3:
+        raise ValueError("block_score must be (num_heads, total_q, n_blocks)")
+    block_score, row_stride = _row_view(block_score)
+    hk, t, n = block_score.shape
+    dev = block_score.device
+    k_blocks = (max_seqlen_k + block_size - 1) // block_size
+    words = (k_blocks + 63) // 64
+    mask = torch.empty(hk, t, words, dtype=torch.int64, device=dev)
+    idx = torch.empty(hk, t, k, dtype=torch.int32, device=dev) if return_idx else None
+    col = torch.empty(hk, k_blocks, (t + 63) // 64, dtype=torch.int64, device=dev) if return_col_mask else None
+    batch = 1
+    cu_ptr = cl_ptr = None
+    if cu_seqlens_q is not None:
+        assert cu_seqlens_q.dtype == torch.int32
+        cu_seqlens_q = cu_seqlens_q.contiguous()
+        batch = cu_seqlens_q.shape[0] - 1
+        cu_ptr = cu_seqlens_q.data_ptr()
+        if cache_lens is not None:
+            assert cache_lens.dtype == torch.int32 and cache_lens.shape[0] == batch
+            cache_lens = cache_lens.contiguous()
+            cl_ptr = cache_lens.data_ptr()
+    elif cache_lens is not None:
+        raise ValueError("cache_lens needs cu_seqlens_q")
+    with torch.cuda.device(dev):
+        _lib.call("ifv2_topk_select_mask", block_score.data_ptr(), idx.data_ptr() if idx is not None else None,
+                  mask.data_ptr(), col.data_ptr() if col is not None else None,
+                  int(block_score.dtype == torch.bfloat16), hk, t, n, row_stride, k, k_blocks, cu_ptr, cl_ptr,
+                  batch, cache_len, block_size, _stream(dev))
+    out = (mask, k_blocks)
+    if return_idx:
+        out += (idx,)
+    if return_col_mask:
+        out += (col,)
+    return out
+
+
 def compressed_lengths(cu_seqlens_k: torch.Tensor, kernel_size: int = 32,
                        kernel_stride: int = 16) -> torch.Tensor:
     """Cumulative number of compressed keys per sequence (int32, same device, no host sync):

@@ -39,6 +39,18 @@ def _cu_pair(n: int, device) -> torch.Tensor:
     return t
 
 
+_side_streams = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    """One persistent side stream per device: the caching allocator keeps a pool per stream, so a
+    new stream per call would turn every gather buffer into a fresh cudaMalloc."""
+    key = str(torch.device(device))
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
+
+
 def head_shard(num_kv_heads: int, world: int, rank: int) -> slice:
     """KV heads owned by `rank` (query heads are 16x that slice)."""
     if num_kv_heads % world != 0:
@@ -225,7 +237,7 @@ def sharded_prefill(q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch
     side = ready = None
     if overlap and q_local.is_cuda and world > 1:
         cur = torch.cuda.current_stream(q_local.device)
-        side = torch.cuda.Stream(device=q_local.device)
+        side = _side_stream(q_local.device)
         side.wait_stream(cur)
         with torch.cuda.stream(side):
             k = gather_sequence(k_local, world, group)
