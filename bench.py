@@ -151,35 +151,44 @@ def run_ours(args, rank, world, device):
     cu_q = torch.tensor([0, seqlen], dtype=torch.int32, device=device)
     cu_c = torch.tensor([0, n_comp], dtype=torch.int32, device=device)
     fused = not args.unfused
-    names = (["stage1_block_scores", "topk_select", "topk_to_uint64", "sparse_attn_fwd"] if fused else
+    # default step: stage 1 + pool in one kernel, top-k + mask pack in one kernel, stage 2 (3 launches);
+    # --unfused runs the reference's operator sequence (5 launches)
+    names = (["stage1_block_scores", "topk_select_mask", "sparse_attn_fwd"] if fused else
              ["stage1_scores", "max_pooling_1d", "topk_select", "topk_to_uint64", "sparse_attn_fwd"])
-    n_marks = len(names)                 # marks 0 .. n_marks-1; the last interval is mask + stage 2
+    n_marks = len(names) + 1
 
     def step(events=None):
-        def mark(j):
+        j = [0]
+
+        def mark():
             if events is not None:
-                events[j].record()
-        mark(0)
+                events[j[0]].record()
+            j[0] += 1
+        mark()
         if fused:
-            # stage 1 and the max-pool in one kernel: the 17 GB score tensor never reaches HBM
+            # the 17 GB score tensor never reaches HBM, and neither does the int32 block list
             pooled = infllm_v2.infllmv2_stage1_block_scores(q, kc, cu_q, cu_c, seqlen, n_comp,
                                                             LOCAL_BLOCKS, INIT_BLOCKS, causal=True)
-            mark(1)
+            mark()
+            mask, _ = infllm_v2.infllmv2_topk_mask(pooled, TOPK, seqlen)
+            del pooled
+            mark()
         else:
             score = infllm_v2.infllmv2_attn_stage1(q, kc, kc, cu_q, cu_c, cu_c, seqlen, n_comp, causal=True)
-            mark(1)
+            mark()
             pooled = infllm_v2.max_pooling_1d(score, 0, LOCAL_BLOCKS, INIT_BLOCKS, BLOCK, STRIDE)
             del score
-            mark(2)
-        idx = infllm_v2.infllmv2_topk(pooled, TOPK)
-        del pooled
-        mark(n_marks - 2)
-        # the mask is built inside infllmv2_attn_varlen_func (as in the reference); the last
-        # interval therefore covers topk_to_uint64 + sparse_attn_fwd, split below by a direct call
+            mark()
+            idx = infllm_v2.infllmv2_topk(pooled, TOPK)
+            del pooled
+            mark()
+            mask, _ = infllm_v2.topk_to_uint64(idx, seqlen, BLOCK)
+            del idx
+            mark()
         out = infllm_v2.infllmv2_attn_varlen_func(q, k, v, cu_q, cu_q, seqlen, seqlen, causal=True,
-                                                  topk_idx=idx)
-        mark(n_marks - 1)
-        return out, idx
+                                                  block_mask=mask)
+        mark()
+        return out
 
     for _ in range(args.warmup):
         step()
@@ -192,7 +201,7 @@ def run_ours(args, rank, world, device):
     with ClockSampler(torch.cuda.current_device()) as clocks:
         t0.record()
         for s in range(args.steps):
-            out, idx = step(ev[s])
+            out = step(ev[s])
         t1.record()
         torch.cuda.synchronize()
     infllm_v2.check_device_status()
@@ -204,16 +213,16 @@ def run_ours(args, rank, world, device):
     ms_per_step = total_ms / args.steps
     per_kernel = [sum(ev[s][j].elapsed_time(ev[s][j + 1]) for s in range(args.steps)) / args.steps
                   for j in range(n_marks - 1)]
+    kernel_ms = dict(zip(names, per_kernel))
 
-    # split topk_to_uint64 from the stage-2 kernel (both are inside infllmv2_attn_varlen_func)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(3):
-        infllm_v2.topk_to_uint64(idx, seqlen, BLOCK)
-    b.record()
-    torch.cuda.synchronize()
-    pack_ms = a.elapsed_time(b) / 3
-    kernel_ms = dict(zip(names, per_kernel[:-1] + [pack_ms, max(per_kernel[-1] - pack_ms, 1e-6)]))
+    # ---- outside the timed region: the block lists (for the work count and the parity check) and
+    # the two separate selection kernels that the fused one replaces
+    pooled = infllm_v2.infllmv2_stage1_block_scores(q, kc, cu_q, cu_c, seqlen, n_comp, LOCAL_BLOCKS,
+                                                    INIT_BLOCKS, causal=True)
+    idx = infllm_v2.infllmv2_topk(pooled, TOPK)
+    sel_ms = {"topk_select": _time_ms(lambda: infllm_v2.infllmv2_topk(pooled, TOPK), reps=3, warmup=1),
+              "topk_to_uint64": _time_ms(lambda: infllm_v2.topk_to_uint64(idx, seqlen, BLOCK), reps=3, warmup=1)}
+    del pooled
 
     # ---- algorithmic work of this rank's shard
     pk, pk_kind = peaks()
@@ -227,17 +236,19 @@ def run_ours(args, rank, world, device):
     bytes_topk = hk_local * seqlen * (n_blk * 2 + TOPK * 4)
     bytes_pack = hk_local * seqlen * (TOPK * 4 + ((n_blk + 63) // 64) * 8)
     tens, hbm = pk["bf16_tflops_sustained"], pk["hbm_gbs"]
+    bytes_mask = hk_local * seqlen * (n_blk * 2 + ((n_blk + 63) // 64) * 8)
     roof = {
         "sparse_attn_fwd": ("tensor", flops_s2 / (kernel_ms["sparse_attn_fwd"] * 1e-3) / 1e12, tens, "TFLOP/s"),
-        "topk_select": ("hbm", bytes_topk / (kernel_ms["topk_select"] * 1e-3) / 1e9, hbm, "GB/s"),
-        "topk_to_uint64": ("hbm", bytes_pack / (kernel_ms["topk_to_uint64"] * 1e-3) / 1e9, hbm, "GB/s"),
     }
     if fused:
         roof["stage1_block_scores"] = ("tensor", flops_s1 / (kernel_ms["stage1_block_scores"] * 1e-3) / 1e12,
                                        tens, "TFLOP/s")
+        roof["topk_select_mask"] = ("hbm", bytes_mask / (kernel_ms["topk_select_mask"] * 1e-3) / 1e9, hbm, "GB/s")
     else:
         roof["stage1_scores"] = ("tensor", flops_s1 / (kernel_ms["stage1_scores"] * 1e-3) / 1e12, tens, "TFLOP/s")
         roof["max_pooling_1d"] = ("hbm", bytes_pool / (kernel_ms["max_pooling_1d"] * 1e-3) / 1e9, hbm, "GB/s")
+        roof["topk_select"] = ("hbm", bytes_topk / (kernel_ms["topk_select"] * 1e-3) / 1e9, hbm, "GB/s")
+        roof["topk_to_uint64"] = ("hbm", bytes_pack / (kernel_ms["topk_to_uint64"] * 1e-3) / 1e9, hbm, "GB/s")
     dominant = max(kernel_ms, key=kernel_ms.get)
     bound, ach, peak, unit = roof[dominant]
     # DRAM traffic per launch: measured with ncu on the 16384-token case of the same command
@@ -273,6 +284,11 @@ def run_ours(args, rank, world, device):
                                  "FMA pipe, so this fraction may exceed 1")
     kernels = {n: {"ms": round(kernel_ms[n], 3), "bound": roof[n][0], "achieved": round(roof[n][1], 2),
                    "unit": roof[n][3], "frac": round(roof[n][1] / roof[n][2], 4)} for n in names}
+    if fused:
+        kernels["separate_selection_kernels"] = {
+            "topk_select_ms": round(sel_ms["topk_select"], 3), "topk_to_uint64_ms": round(sel_ms["topk_to_uint64"], 3),
+            "note": "the two launches (and the int32 list between them) that topk_select_mask replaces; "
+                    "timed outside the step"}
 
     parity = step_parity(q, k, v, kc, out, idx, seqlen)
 
@@ -286,7 +302,8 @@ def run_ours(args, rank, world, device):
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"prefill {seqlen} tokens, 128q/8kv heads, d128: stage1 + max-pool + "
                                f"top-64 (1 init + 32 local) + uint64 mask + stage-2 fwd"
-                               + ("" if fused else " [stage 1 and pool as separate kernels]"),
+                               + (" [3 launches: stage 1 + pool, top-k + mask, stage 2]" if fused
+                                  else " [the reference's 5-operator sequence]"),
                    "seq_len": seqlen, "global_batch": 1, "kv_heads_per_gpu": hk_local,
                    "parallelism": f"kv-head shards x{world}" if world > 1 else "single GPU",
                    "l2": "inputs (q alone is %.1f GB per GPU) exceed the 126 MB L2" % (q.numel() * 2 / 1e9)},
@@ -294,6 +311,7 @@ def run_ours(args, rank, world, device):
         "e2e": e2e,
         "parity": parity,
         "gpu_launches": len(names) * args.steps,
+        "gpu_launches_per_step": len(names),
         "roofline": roofline,
         "kernels": kernels,
         "flops_per_step": {"stage1_algorithmic": flops_s1 * world, "stage2_fwd_algorithmic": flops_s2 * world},
@@ -1077,7 +1095,7 @@ def main():
                     help="query tokens in the CPU sample (cpu_baseline / --impl reference), in 16-token chunks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true",
-                    help="run stage 1 and the max-pool as two kernels (the reference's op sequence)")
+                    help="run the reference's operator sequence: stage 1, max-pool, top-k, mask pack, stage 2")
     ap.add_argument("--only", default=None, choices=["selection", "topk", "compress", "coarse", "train", "decode", "sharded"],
                     help="run just one secondary config and print its numbers (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")

@@ -320,7 +320,8 @@ def _infllmv2_attn_varlen_forward(
         fwd_mask = None
     out, lse = _fwd(q, k, v, cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous(), max_seqlen_q,
                     max_seqlen_k, softmax_scale, causal, fwd_mask)
-    if fwd_mask is None:
+    if fwd_mask is None or block_mask is not None:
+        # (an operator output may not alias an input: the caller keeps its own block_mask)
         fwd_mask = torch.empty(0, dtype=torch.int64, device=q.device)
     return out, lse, fwd_mask
 
@@ -330,7 +331,7 @@ def _(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_s
       topk_idx=None, block_mask=None):
     words = ((max_seqlen_k + BLOCK_N - 1) // BLOCK_N + 63) // 64
     mask = (q.new_empty((k.shape[1], q.shape[0], words), dtype=torch.int64)
-            if (topk_idx is not None or block_mask is not None) else q.new_empty((0,), dtype=torch.int64))
+            if (topk_idx is not None and block_mask is None) else q.new_empty((0,), dtype=torch.int64))
     return (torch.empty_like(q),
             q.new_empty((k.shape[1], q.shape[0] * GROUP), dtype=torch.float32), mask)
 
@@ -372,6 +373,8 @@ class Infllmv2AttnVarlenFunc(torch.autograd.Function):
         out, lse, fwd_mask = _infllmv2_attn_varlen_forward(
             q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
             topk_idx, block_mask)
+        if block_mask is not None:
+            fwd_mask = block_mask.contiguous()
         ctx.save_for_backward(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, fwd_mask)
         ctx.max_seqlen_q, ctx.max_seqlen_k = max_seqlen_q, max_seqlen_k
         ctx.softmax_scale, ctx.causal = softmax_scale, causal

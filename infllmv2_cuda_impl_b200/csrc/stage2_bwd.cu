@@ -334,20 +334,16 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       {
         const int half = grp;                          // this warp group's 32 key columns
         uint32_t sv[32], dpv[32];
-        tmem_ld32(tmem + lane_off + s * 128 + half * 32, sv);
-        tmem_ld32(tmem + lane_off + s * 128 + 64 + half * 32, dpv);
-        tmem_wait_ld_dep(sv);
-        tmem_wait_ld_dep(dpv);
+        tmem_ld32x2_wait(tmem + lane_off + s * 128 + half * 32, sv, tmem + lane_off + s * 128 + 64 + half * 32, dpv);
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_lse, neg_lse);
+        const uint64_t md2 = pack_f32x2(-dsum, -dsum);
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float pr = exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, neg_lse));
-            const float d = pr * (__uint_as_float(dpv[c + e]) - dsum);
-            ds[e] = (half * 32 + c + e < lim) ? d : 0.f;
-          }
-          packed[c >> 1] = pack_bf16(ds[0], ds[1]);
+          float y0, y1, d0, d1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(sv[c], sv[c + 1]), c2, n2), y0, y1);
+          unpack_f32x2(mul_f32x2(pack_f32x2(exp2f(y0), exp2f(y1)),
+                                 add_f32x2(pack_f32x2(dpv[c], dpv[c + 1]), md2)), d0, d1);
+          packed[c >> 1] = pack_bf16((half * 32 + c < lim) ? d0 : 0.f, (half * 32 + c + 1 < lim) ? d1 : 0.f);
         }
       }
       tmem_st16(tmem + lane_off + s * 128 + grp * 16, packed);
@@ -636,22 +632,18 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         {
           const int half = grp;                        // this warp group's 32 key columns
           uint32_t sv[32], dpv[32];
-          tmem_ld32(tmem + lane_off + s * 128 + half * 32, sv);
-          tmem_ld32(tmem + lane_off + s * 128 + 64 + half * 32, dpv);
-          tmem_wait_ld_dep(sv);
-          tmem_wait_ld_dep(dpv);
+          tmem_ld32x2_wait(tmem + lane_off + s * 128 + half * 32, sv, tmem + lane_off + s * 128 + 64 + half * 32, dpv);
+          const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_lse, neg_lse);
+          const uint64_t md2 = pack_f32x2(-dsum, -dsum);
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
-            float pr[2], ds[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const bool vis = half * 32 + c + e < lim;
-              const float x = exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, neg_lse));
-              pr[e] = vis ? x : 0.f;
-              ds[e] = vis ? x * (__uint_as_float(dpv[c + e]) - dsum) : 0.f;
-            }
-            pp[c >> 1] = pack_bf16(pr[0], pr[1]);
-            dd[c >> 1] = pack_bf16(ds[0], ds[1]);
+            float y0, y1, d0, d1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(sv[c], sv[c + 1]), c2, n2), y0, y1);
+            const float x0 = exp2f(y0), x1 = exp2f(y1);
+            unpack_f32x2(mul_f32x2(pack_f32x2(x0, x1), add_f32x2(pack_f32x2(dpv[c], dpv[c + 1]), md2)), d0, d1);
+            const bool v0 = half * 32 + c < lim, v1 = half * 32 + c + 1 < lim;
+            pp[c >> 1] = pack_bf16(v0 ? x0 : 0.f, v1 ? x1 : 0.f);
+            dd[c >> 1] = pack_bf16(v0 ? d0 : 0.f, v1 ? d1 : 0.f);
           }
         }
         tc_fence_before();

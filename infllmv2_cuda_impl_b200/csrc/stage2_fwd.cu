@@ -271,22 +271,17 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       if (!ok) break;
       tc_fence_after();
 
-      uint32_t raw[2][32];
-      tmem_ld32(tmem + lane_off + s * 64, raw[0]);
-      tmem_wait_ld_dep(raw[0]);
-      tmem_ld32(tmem + lane_off + s * 64 + 32, raw[1]);
+      uint32_t raw[64];
+      tmem_ld64_wait(tmem + lane_off + s * 64, raw);
+      if (partial) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          if (c >= lim) raw[c] = 0xFF800000u;                              // -inf
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        if (half == 1) tmem_wait_ld_dep(raw[1]);
-        if (partial) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (half * 32 + c >= lim) raw[half][c] = 0xFF800000u;          // -inf
-        }
-#pragma unroll
-        for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(raw[half][c]));
-      }
+      for (int c = 0; c < 64; c += 2)           // two scores per step: a three-input maximum each
+        mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(raw[c]), __uint_as_float(raw[c + 1])));
       const float mx = (lim > 0) ? fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) : -INFINITY;
       // raise the reference max only when it moves by more than the threshold
       float f = 1.f;
@@ -317,16 +312,21 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       // rows that take nothing from this block get an exponent of -inf (P = 0) for every column
       const float neg_m = (lim == 0) ? -INFINITY : -m_ref * p.scale_log2;
       uint32_t packed[32];
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_m, neg_m);
+      uint64_t sum2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sum2[i] = pack_f32x2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = exp2f(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.scale_log2, neg_m));
-        const float p1 =
-            exp2f(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.scale_log2, neg_m));
-        sum4[(c >> 1) & 3] += p0 + p1;
+        float y0, y1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(raw[c], raw[c + 1]), c2, n2), y0, y1);
+        const float p0 = exp2f(y0), p1 = exp2f(y1);
+        sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
         packed[c >> 1] = pack_bf16(p0, p1);
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      float s_lo, s_hi;
+      unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), s_lo, s_hi);
+      const float sum = s_lo + s_hi;
       l += sum;
       tmem_st32(tmem + lane_off + s * 64, packed);
       tmem_wait_st();

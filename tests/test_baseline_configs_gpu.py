@@ -93,6 +93,9 @@ def test_selection_at_32768_tokens():
     words, kb = infllm_v2.topk_to_uint64(idx, L, BLOCK)
     words_ref, kb_ref = oracle.topk_to_uint64(idx_ref.numpy(), L, BLOCK)
     assert kb == kb_ref and np.array_equal(words.cpu().numpy(), words_ref)
+    fused_mask, _, col = infllm_v2.infllmv2_topk_mask(pooled, TOPK, L, return_col_mask=True)
+    assert torch.equal(fused_mask, words)
+    assert np.array_equal(col.cpu().numpy(), oracle.transpose_blockmask(words_ref, kb_ref))
     infllm_v2.check_device_status()
 
 
@@ -151,6 +154,9 @@ def test_prefill_at_131072_tokens_128q_8kv():
     idx = infllm_v2.infllmv2_topk(pooled, TOPK)
     mask, _ = infllm_v2.topk_to_uint64(idx, L, BLOCK)
     assert mask.shape == (hk, L, 32)
+    fused_mask, _ = infllm_v2.infllmv2_topk_mask(pooled, TOPK, L)      # top-k and pack in one kernel
+    assert torch.equal(fused_mask, mask)
+    del fused_mask
     out, lse, _ = infllm_v2.infllmv2_attn_varlen_func(q, k, v, cu_q, cu_q, L, L, causal=True, topk_idx=idx,
                                                       return_attn_probs=True)
     infllm_v2.check_device_status()

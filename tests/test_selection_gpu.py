@@ -212,3 +212,58 @@ def test_decode_select_equals_pool_topk_pack(hk, b, cap, k, local, init, dtype):
                                                           1, max_c, local, init).float(), k,
                              torch.tensor((lens - 1) // 64))
     assert torch.equal(idx[:, :, 0].cpu().permute(1, 0, 2), exp)
+
+
+@pytest.mark.parametrize("hk,t,n,k,max_k,dtype", [
+    (2, 300, 512, 64, 512 * 64, torch.bfloat16), (2, 130, 2048, 64, 2048 * 64, torch.bfloat16),
+    (1, 70, 40, 64, 40 * 64, torch.bfloat16), (2, 100, 384, 16, 384 * 64 - 5, torch.float16),
+    (1, 64, 2049, 64, 2049 * 64, torch.bfloat16), (1, 33, 4100, 64, 4100 * 64, torch.bfloat16),
+    (2, 200, 100, 1, 100 * 64, torch.bfloat16), (1, 50, 257, 64, 300 * 64, torch.bfloat16),
+    (1, 40, 200, 8, 130 * 64, torch.bfloat16),
+])
+def test_topk_mask_equals_topk_then_pack_then_transpose(hk, t, n, k, max_k, dtype):
+    """The fused entry (top-k straight to the packed row mask, column mask in the same call) against
+    the three separate operators, on tie-heavy scores, with the mask narrower / wider than the
+    score rows and queries whose later blocks are cut off."""
+    g = torch.Generator().manual_seed(n + k)
+    y = (torch.randint(0, 12, (hk, t, n), generator=g).float() / 8).to(dtype)
+    y[:, :, 0] = float("inf")
+    y[:, : t // 2, n // 2:] = float("-inf")
+    y[:, 1::3, 3:9] = float("inf")
+    yd = y.to(DEV)
+    for cache_len in (64 * (n - 1), 64 * (n // 3)):            # nothing cut off / most blocks cut off
+        idx = infllm_v2.infllmv2_topk(yd, k, cache_len=cache_len)
+        words, kb = infllm_v2.topk_to_uint64(idx, max_k, 64)
+        col = infllm_v2.transpose_blockmask(words, kb)
+        mask, kb2, idx2, col2 = infllm_v2.infllmv2_topk_mask(yd, k, max_k, cache_len=cache_len, return_idx=True,
+                                                            return_col_mask=True)
+        assert kb2 == kb and torch.equal(idx2, idx)
+        assert torch.equal(mask, words)
+        assert torch.equal(col2, col)
+        only_mask, _ = infllm_v2.infllmv2_topk_mask(yd, k, max_k, cache_len=cache_len)
+        assert torch.equal(only_mask, words)
+
+
+def test_topk_mask_varlen_and_attention_takes_the_mask():
+    lens = [130, 64, 200]
+    t = sum(lens)
+    y = _scores((2, t, 8), 9).to(DEV)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+    cl = torch.tensor([0, 128, 64], dtype=torch.int32, device=DEV)
+    idx = infllm_v2.infllmv2_topk(y, 4, cu_seqlens_q=cu, cache_lens=cl)
+    words, kb = infllm_v2.topk_to_uint64(idx, 8 * 64, 64)
+    mask, kb2 = infllm_v2.infllmv2_topk_mask(y, 4, 8 * 64, cu_seqlens_q=cu, cache_lens=cl)
+    assert kb == kb2 and torch.equal(mask, words)
+    # the attention accepts the packed mask in place of the list, same result bit for bit
+    from helpers import det_tensor
+    L = 512
+    q = det_tensor((L, 32, 128), 1, 0.25).to(DEV)
+    k = det_tensor((L, 2, 128), 2, 0.25).to(DEV)
+    v = det_tensor((L, 2, 128), 3).to(DEV)
+    sc = _scores((2, L, 8), 11).to(DEV)
+    cu1 = torch.tensor([0, L], dtype=torch.int32, device=DEV)
+    idx = infllm_v2.infllmv2_topk(sc, 3)
+    m, _ = infllm_v2.infllmv2_topk_mask(sc, 3, L)
+    a = infllm_v2.infllmv2_attn_varlen_func(q, k, v, cu1, cu1, L, L, causal=True, topk_idx=idx)
+    b = infllm_v2.infllmv2_attn_varlen_func(q, k, v, cu1, cu1, L, L, causal=True, block_mask=m)
+    assert torch.equal(a, b)
