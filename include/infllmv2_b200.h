@@ -264,6 +264,23 @@ int ifv2_stage1_block_scores(const void* q, const void* kc, const void* lse_keys
                              int n_blocks, int cache_len, int local_blocks, int init_blocks,
                              float softmax_scale, int causal, int32_t* status, void* stream);
 
+/* Stage-1 scorer over a PAGED or left-padded cache of compressed keys, the addressing options of
+ * mha_varlen_fwd_stage1 (csrc/flash_attn/flash_api.cpp:906-911, 1001-1008; src/block_info.h:22-24):
+ * kc is (num_pages * page_size, heads_k, 128) rows with block_table (batch, block_table_stride)
+ * naming the page of every page_size compressed keys of a sequence (page_size a multiple of 128;
+ * the reference wants 256), or a packed tensor whose sequences start leftpad_k[b] rows into their
+ * cu_seqlens_k extent.  Writes the scores (scores_or_null, layout of ifv2_stage1_scores) and / or
+ * the block scores (block_scores_or_null, as ifv2_stage1_block_scores); the row sums run over the
+ * scored keys.  Other arguments as in those two entries. */
+int ifv2_stage1_paged(const void* q, const void* kc, void* scores_or_null, void* block_scores_or_null,
+                      const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                      const int32_t* seqused_k, const int32_t* leftpad_k, const int32_t* block_table,
+                      int block_table_stride, int page_size, const int32_t* cache_lens, int batch,
+                      int64_t total_q, int64_t total_c, int heads_q, int heads_k, int head_dim,
+                      int max_seqlen_q, int max_seqlen_k, int64_t scores_row_stride, int n_blocks,
+                      int cache_len, int local_blocks, int init_blocks, float softmax_scale,
+                      int causal, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------- stage 2 ------------------ */
 
 /* Block-sparse varlen attention forward.  q/out: (total_q, heads_q, 128) bf16; k, v:
@@ -279,6 +296,25 @@ int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out,
                          int heads_q, int heads_k, int head_dim, int max_seqlen_q,
                          int max_seqlen_k, float softmax_scale, int causal, int32_t* status,
                          void* stream);
+
+/* ifv2_sparse_attn_fwd with the key addressing options of the reference's varlen forward
+ * (csrc/flash_attn/flash_api.cpp:592-596, 717-742; src/block_info.h:22-24, 40):
+ *  seqused_k (batch) int32 or null: keys of each sequence actually in use;
+ *  leftpad_k (batch) int32 or null: the keys of sequence b start leftpad_k[b] rows into its
+ *    cu_seqlens_k extent (and there are that many fewer); block indices count from the first key;
+ *  block_table (batch, block_table_stride) int32 or null: paged K / V, k and v are then
+ *    (num_pages * page_size, heads_k, 128) rows (total_k = num_pages * page_size) and key position
+ *    p of sequence b lives in page block_table[b][p / page_size]; page_size a multiple of 64 (the
+ *    reference wants 256); cu_seqlens_k (or seqused_k) still gives the key count per sequence.
+ * As in the reference a paged cache takes no leftpad_k, and there is no paged backward. */
+int ifv2_sparse_attn_fwd_paged(const void* q, const void* k, const void* v, void* out, float* lse,
+                               const int64_t* fwd_mask, int mask_words, const int32_t* cu_seqlens_q,
+                               const int32_t* cu_seqlens_k, const int32_t* seqused_k,
+                               const int32_t* leftpad_k, const int32_t* block_table,
+                               int block_table_stride, int page_size, int batch, int64_t total_q,
+                               int64_t total_k, int heads_q, int heads_k, int head_dim,
+                               int max_seqlen_q, int max_seqlen_k, float softmax_scale, int causal,
+                               int32_t* status, void* stream);
 
 /* Bytes of scratch ifv2_sparse_attn_bwd needs (D = rowsum(dO * O), one fp32 per query row). */
 int64_t ifv2_sparse_attn_bwd_workspace_bytes(int64_t total_q, int heads_q, int head_dim);

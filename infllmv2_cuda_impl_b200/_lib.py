@@ -58,6 +58,13 @@ SIGNATURES = {
     "ifv2_sparse_attn_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int,
                              c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "ifv2_sparse_attn_fwd_paged": [c_void_p] * 6 + [c_int] + [c_void_p] * 5 + [c_int, c_int, c_int, c_int64,
+                                                                              c_int64, c_int, c_int, c_int, c_int,
+                                                                              c_int, c_float, c_int, c_void_p,
+                                                                              c_void_p],
+    "ifv2_stage1_paged": [c_void_p] * 9 + [c_int, c_int, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int,
+                                           c_int, c_int, c_int64, c_int, c_int, c_int, c_int, c_float, c_int,
+                                           c_void_p, c_void_p],
     "ifv2_sparse_attn_bwd": [c_void_p] * 9 + [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int,
                                               c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                                               c_float, c_int, c_void_p, c_int64, c_void_p,

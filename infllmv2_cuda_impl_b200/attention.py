@@ -74,7 +74,9 @@ def _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_tab
     if tuple(window_size) != (-1, -1):
         raise RuntimeError(f"{what}: sliding-window attention is not supported (compiled out in the reference)")
     if block_table is not None:
-        raise NotImplementedError(f"{what}: paged KV (block_table) is not supported")
+        if block_table.dtype != torch.int32 or block_table.dim() != 2 or k.dim() != 4:
+            raise ValueError(f"{what}: with block_table (batch, max_pages) int32 the keys are "
+                             "(num_pages, page_size, nheads_k, 128)")
     if q.shape[-1] != HEAD_DIM or k.shape[-1] != HEAD_DIM:
         raise RuntimeError(f"{what}: head_dim must be {HEAD_DIM}")
     if q.shape[-2] != GROUP * k.shape[-2]:
@@ -92,7 +94,7 @@ def infllmv2_attn_stage1(
     q, k, v, cu_seqlens_q, cu_seqlens_k, cu_seqlens_v, max_seqlen_q, max_seqlen_k,
     dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0,
     alibi_slopes=None, deterministic=False, return_attn_probs=True, block_table=None,
-    seqused_k=None, seqused_v=None,
+    seqused_k=None, seqused_v=None, leftpad_k=None,
 ):
     """Stage-1 scores: for every KV head, softmax(q . k_compressed) summed over its 16 query heads.
 
@@ -109,9 +111,17 @@ def infllmv2_attn_stage1(
     per-sequence cache (batch, capacity, nheads_k, 128) can be scored in place as
     k = cache.view(-1, nheads_k, 128), cu_seqlens_k = arange(batch + 1) * capacity.
     seqused_v: the same for v / cu_seqlens_v.
+    block_table: (batch, max_pages) int32 -- k is then a paged cache of compressed keys
+    (num_pages, page_size, nheads_k, 128), page_size a multiple of 128 (the reference wants 256,
+    flash_api.cpp:906-911), and cu_seqlens_k / seqused_k give each sequence's key count; v must be
+    k.  leftpad_k: (batch,) int32 -- the keys of a sequence start that many rows into its
+    cu_seqlens_k extent (flash_api.cpp:1001-1008).
     """
     _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table,
                   "infllmv2_attn_stage1")
+    if block_table is not None or leftpad_k is not None:
+        return _stage1_paged(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale,
+                             causal, block_table, seqused_k, leftpad_k)
     lse_keys = None
     if v is not None and v is not k and (v.shape != k.shape or v.data_ptr() != k.data_ptr()):
         if v.dtype != k.dtype or v.dim() != 3 or v.shape[1:] != k.shape[1:]:
@@ -160,6 +170,57 @@ def infllmv2_attn_stage1(
     return buf[:, :, :max_seqlen_k]
 
 
+def _stage1_paged(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
+                  block_table, seqused_k, leftpad_k, pool_args=None):
+    """Stage 1 over a paged or left-padded compressed-key cache (ifv2_stage1_paged).  pool_args:
+    (n_blocks, cache_len, cache_lens, local_blocks, init_blocks) for fused block scores."""
+    if v is not None and v is not k and v.data_ptr() != k.data_ptr():
+        raise NotImplementedError("infllmv2_attn_stage1: separate row-sum keys are not supported with "
+                                  "block_table / leftpad_k")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    q = _dense(maybe_contiguous(q))
+    total_q, nheads, d = q.shape
+    batch = cu_seqlens_q.numel() - 1
+    bt_ptr, bt_stride, page = None, 0, 0
+    if block_table is not None:
+        if leftpad_k is not None:
+            raise NotImplementedError("infllmv2_attn_stage1: a paged cache takes no leftpad_k")
+        page = k.shape[1]
+        if page % 128 != 0:
+            raise NotImplementedError("infllmv2_attn_stage1: page size must be a multiple of 128 compressed keys")
+        assert block_table.shape[0] == batch
+        block_table = block_table.contiguous()
+        bt_ptr, bt_stride = block_table.data_ptr(), block_table.shape[1]
+        k = k.contiguous().view(-1, k.shape[2], k.shape[3])
+    else:
+        k = _dense(maybe_contiguous(k))
+    nheads_k = k.shape[1]
+    for name, t in (("seqused_k", seqused_k), ("leftpad_k", leftpad_k)):
+        if t is not None:
+            assert t.dtype == torch.int32 and t.numel() == batch, f"{name} must be (batch,) int32"
+    row_stride = max(round_multiple(max_seqlen_k, 128), 128)
+    buf = pooled = None
+    n_blocks = cache_len = local_blocks = init_blocks = 0
+    cache_lens = None
+    if pool_args is None:
+        buf = torch.empty(nheads_k, total_q, row_stride, dtype=torch.bfloat16, device=q.device)
+    else:
+        n_blocks, cache_len, cache_lens, local_blocks, init_blocks = pool_args
+        pooled = torch.empty(nheads_k, total_q, n_blocks, dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("ifv2_stage1_paged", q.data_ptr(), k.data_ptr(), buf.data_ptr() if buf is not None else None,
+                  pooled.data_ptr() if pooled is not None else None, cu_seqlens_q.contiguous().data_ptr(),
+                  cu_seqlens_k.contiguous().data_ptr(),
+                  seqused_k.contiguous().data_ptr() if seqused_k is not None else None,
+                  leftpad_k.contiguous().data_ptr() if leftpad_k is not None else None, bt_ptr, bt_stride, page,
+                  cache_lens.data_ptr() if cache_lens is not None else None, batch, total_q, k.shape[0],
+                  nheads, nheads_k, d, max_seqlen_q, max_seqlen_k, row_stride if buf is not None else 0,
+                  n_blocks, int(cache_len), int(local_blocks), int(init_blocks), float(softmax_scale),
+                  int(bool(causal)), _status_words(q.device).data_ptr(), _stream(q.device))
+    return buf[:, :, :max_seqlen_k] if buf is not None else pooled
+
+
 def infllmv2_stage1_decode_select(q, k, cu_seqlens_k, positions, max_seqlen_k, cache_capacity, topk,
                                   local_blocks, init_blocks, seqused_k=None, softmax_scale=None,
                                   causal=False, block_size=64, stride=16, return_topk=False):
@@ -204,7 +265,8 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
                                  local_blocks, init_blocks, cache_len=0, cache_lens=None,
                                  max_cache_len=None, softmax_scale=None, causal=True,
                                  block_size=64, stride=16, return_scores=False,
-                                 lse_keys=None, cu_seqlens_v=None, seqused_k=None, seqused_v=None):
+                                 lse_keys=None, cu_seqlens_v=None, seqused_k=None, seqused_v=None,
+                                 block_table=None, leftpad_k=None):
     """Stage 1 and the 64-token max-pool in one kernel (an addition to the reference API).
 
     Returns block scores (nheads_k, total_q, ceil((max_seqlen_q + cache) / 64)) bf16 equal, bit
@@ -213,9 +275,28 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
     (then the result is (block_scores, scores)).  cache_lens: optional per-sequence int32 tensor
     (pass max_cache_len to avoid a device->host read); otherwise the scalar cache_len applies.
     lse_keys / cu_seqlens_v: optional coarser compressed keys for the log-sum-exp (the `v` of
-    infllmv2_attn_stage1).  seqused_k / seqused_v: as in infllmv2_attn_stage1.
+    infllmv2_attn_stage1).  seqused_k / seqused_v / block_table / leftpad_k: as in
+    infllmv2_attn_stage1 (a paged or left-padded cache returns the block scores only).
     """
-    _check_common(q, k, 0.0, (-1, -1), 0.0, None, None, "infllmv2_stage1_block_scores")
+    _check_common(q, k, 0.0, (-1, -1), 0.0, None, block_table, "infllmv2_stage1_block_scores")
+    if block_table is not None or leftpad_k is not None:
+        if lse_keys is not None or return_scores:
+            raise NotImplementedError("infllmv2_stage1_block_scores: a paged / left-padded cache takes neither "
+                                      "lse_keys nor return_scores")
+        if block_size != BLOCK_N or stride != 16:
+            raise NotImplementedError("infllmv2_stage1_block_scores: only block_size 64 / stride 16")
+        batch = cu_seqlens_q.numel() - 1
+        if cache_lens is not None:
+            assert cache_lens.dtype == torch.int32 and cache_lens.numel() == batch
+            if max_cache_len is None:
+                max_cache_len = int(cache_lens.max().item())
+            cache_lens = cache_lens.contiguous()
+        else:
+            max_cache_len = cache_len
+        n_blocks = (max_seqlen_q + max_cache_len + BLOCK_N - 1) // BLOCK_N
+        return _stage1_paged(q, k, None, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale,
+                             causal, block_table, seqused_k, leftpad_k,
+                             pool_args=(n_blocks, cache_len, cache_lens, local_blocks, init_blocks))
     if lse_keys is not None:
         assert cu_seqlens_v is not None and cu_seqlens_v.dtype == torch.int32
         lse_keys = _dense(maybe_contiguous(lse_keys))
@@ -259,11 +340,40 @@ def infllmv2_stage1_block_scores(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
 # ------------------------------------------------------------------------------------ stage 2 --
 
 def _fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
-         fwd_mask):
+         fwd_mask, block_table=None, leftpad_k=None, seqused_k=None):
     total_q, nheads, d = q.shape
-    nheads_k = k.shape[1]
     batch = cu_seqlens_q.numel() - 1
     out = torch.empty_like(q)
+    if block_table is not None or leftpad_k is not None or seqused_k is not None:
+        bt_ptr, bt_stride, page = None, 0, 0
+        if block_table is not None:
+            if leftpad_k is not None:
+                raise NotImplementedError("infllmv2_attn_varlen_func: a paged cache takes no leftpad_k")
+            page = k.shape[1]
+            if page % BLOCK_N != 0:
+                raise NotImplementedError("infllmv2_attn_varlen_func: page size must be a multiple of 64")
+            assert block_table.shape[0] == batch
+            block_table = block_table.contiguous()
+            bt_ptr, bt_stride = block_table.data_ptr(), block_table.shape[1]
+            k = k.contiguous().view(-1, k.shape[2], k.shape[3])
+            v = v.contiguous().view(-1, v.shape[2], v.shape[3])
+        for name, t in (("seqused_k", seqused_k), ("leftpad_k", leftpad_k)):
+            if t is not None:
+                assert t.dtype == torch.int32 and t.numel() == batch, f"{name} must be (batch,) int32"
+        nheads_k = k.shape[1]
+        lse = torch.empty(nheads_k, total_q * GROUP, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            _lib.call("ifv2_sparse_attn_fwd_paged", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                      lse.data_ptr(), fwd_mask.data_ptr() if fwd_mask is not None else None,
+                      fwd_mask.shape[-1] if fwd_mask is not None else 0,
+                      cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(),
+                      seqused_k.contiguous().data_ptr() if seqused_k is not None else None,
+                      leftpad_k.contiguous().data_ptr() if leftpad_k is not None else None,
+                      bt_ptr, bt_stride, page, batch, total_q, k.shape[0], nheads, nheads_k, d,
+                      max_seqlen_q, max_seqlen_k, float(softmax_scale), int(bool(causal)),
+                      _status_words(q.device).data_ptr(), _stream(q.device))
+        return out, lse
+    nheads_k = k.shape[1]
     lse = torch.empty(nheads_k, total_q * GROUP, dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
         _lib.call("ifv2_sparse_attn_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
@@ -395,6 +505,7 @@ def infllmv2_attn_varlen_func(
     q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p=0.0,
     softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0, alibi_slopes=None,
     deterministic=False, return_attn_probs=False, block_table=None, topk_idx=None, block_mask=None,
+    leftpad_k=None, seqused_k=None,
 ):
     """Block-sparse varlen attention (stage 2), differentiable.
 
@@ -405,7 +516,39 @@ def infllmv2_attn_varlen_func(
     total_q, ceil(ceil(max_seqlen_k / 64) / 64)) as topk_to_uint64 / infllmv2_topk_mask return it.  causal=True aligns the diagonal to the bottom right when seqlen_q != seqlen_k.
     Rows that see no key return 0.  Returns out (total_q, nheads, 128), or
     (out, softmax_lse (nheads_k, total_q * 16), None) with return_attn_probs=True.
+    block_table (batch, max_pages) int32: k and v are a paged cache (num_pages, page_size, nheads_k,
+    128), page_size a multiple of 64 (the reference wants 256, flash_api.cpp:592-596), and
+    cu_seqlens_k / seqused_k give each sequence's key count.  leftpad_k (batch,) int32: the keys of a
+    sequence start that many rows into its cu_seqlens_k extent; seqused_k (batch,) int32: keys in
+    use per sequence (flash_api.cpp:717-742, block_info.h:22-24).  These three are forward-only, as
+    in the reference, whose backward takes none of them.
     """
+    if block_table is not None or leftpad_k is not None or seqused_k is not None:
+        _check_common(q, k, dropout_p, window_size, softcap, alibi_slopes, block_table,
+                      "infllmv2_attn_varlen_func")
+        if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
+            raise NotImplementedError("infllmv2_attn_varlen_func: block_table / leftpad_k / seqused_k are "
+                                      "forward-only (the reference's backward takes none of them)")
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** (-0.5)
+        q = _dense(maybe_contiguous(q))
+        if block_table is None:
+            k, v = _dense(maybe_contiguous(k)), _dense(maybe_contiguous(v))
+        nheads_k = k.shape[-2]
+        words = ((max_seqlen_k + BLOCK_N - 1) // BLOCK_N + 63) // 64
+        if block_mask is not None:
+            if topk_idx is not None or block_mask.dtype != torch.int64 or \
+                    tuple(block_mask.shape) != (nheads_k, q.shape[0], words):
+                raise ValueError(f"block_mask must be int64 (nheads_k, total_q, {words}) and excludes topk_idx")
+            fwd_mask = block_mask.contiguous()
+        elif topk_idx is not None:
+            assert topk_idx.dtype == torch.int32
+            fwd_mask, _ = topk_to_uint64(topk_idx, max_seqlen_k, BLOCK_N)
+        else:
+            fwd_mask = None
+        out, lse = _fwd(q, k, v, cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous(), max_seqlen_q,
+                        max_seqlen_k, softmax_scale, causal, fwd_mask, block_table, leftpad_k, seqused_k)
+        return (out, lse, None) if return_attn_probs else out
     return Infllmv2AttnVarlenFunc.apply(
         q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale,
         causal, window_size, softcap, alibi_slopes, deterministic, return_attn_probs, block_table,

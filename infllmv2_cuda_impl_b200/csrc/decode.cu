@@ -10,7 +10,15 @@
 // the per-split (max, sum, O) partials are merged by a small second kernel.
 //
 // Launches: [append new K/V in place] -> split kernel -> combine kernel.
+//
+// Tile loads: when the cache rows can be described by one tensor map (16-byte aligned base, batch
+// stride a whole number of rows) a warp's K and V tiles arrive as two TMA boxes each ({64 d, 1 head,
+// 32 keys}, 128-byte swizzle) on a per-warp mbarrier, issued by one lane: the 512 sixteen-byte
+// cp.async requests per tile of the plain path kept the load/store unit at one request per 1.3
+// clocks per SM, which is what held the kernel at half the HBM bandwidth.  Other layouts use cp.async.
+#include <string.h>
 #include "mma_sync.cuh"
+#include "tc05.cuh"
 
 namespace ifv2 {
 namespace {
@@ -50,7 +58,26 @@ struct DecodeParams {
   float* partial;                 // (batch, heads_k, splits, 16, kPartialFloats)
   __nv_bfloat16* out;             // (batch, heads_q, 128)
   float* lse;                     // (batch, heads_q) or null
+  int use_tma;                    // tiles come through the tensor maps given to the kernel
+  int64_t rows_per_slot;          // cache rows between two sequence slots (TMA path, unpaged)
 };
+
+// Row of position `pos` of sequence b in the (rows, heads_k, 128) view of a cache.
+__device__ __forceinline__ int cache_row(const DecodeParams& p, int b, int slot, int64_t pos) {
+  if (p.block_table != nullptr) {
+    const int page = __ldg(p.block_table + (int64_t)b * p.bt_stride + pos / p.page_size);
+    return page * p.page_size + (int)(pos % p.page_size);
+  }
+  return (int)(slot * p.rows_per_slot + pos);
+}
+
+// Tile layout of the TMA path: two 4 KB halves (d 0..63, d 64..127) of 32 rows x 128 bytes, 16-byte
+// chunk c of row r stored at chunk (c ^ (r & 7)) -- the 128-byte swizzle the copy engine applies.
+__device__ __forceinline__ uint8_t* tile_addr_tma(uint8_t* tile, int row, int chunk) {
+  return tile + (chunk >> 3) * 4096 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+constexpr long long kDecodeWaitLimit = 1ll << 28;       // clocks; a copy takes microseconds
 
 // Element offset of position `pos` of sequence b (head 0) in a cache: contiguous rows, rows of
 // another sequence slot (cache_batch_idx), or pages of a block table.
@@ -118,13 +145,28 @@ struct BlockList {
   }
 };
 
-__global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM) decode_split_kernel(const DecodeParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+template <bool kTma>
+__global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM)
+decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                    const DecodeParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t tile_bar[kWarps][2];              // per warp: K tile, V tile landed
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   uint8_t* k_tile = smem + warp * kWarpSmem;
   uint8_t* v_tile = k_tile + kUnit * 256;
+  if (kTma) {
+    if (lane == 0) {
+      tc::mbar_init(&tile_bar[warp][0], 1);
+      tc::mbar_init(&tile_bar[warp][1], 1);
+      tc::fence_barrier_init();
+    }
+    __syncwarp();
+  }
+  uint32_t k_phase = 0, v_phase = 0;                    // parity of the next completion of each barrier
+  bool expired = false;                                 // a bounded wait ran out: the partial is poisoned
 
   const int pad = p.leftpad ? p.leftpad[b] : 0;                 // keys are positions pad .. end-1
   // a length beyond the capacity is a caller error with a defined result: the keys are the
@@ -145,6 +187,48 @@ __global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM) decode_spli
     return cache + cache_row_offset(p.block_table, p.bt_stride, p.page_size, p.batch_stride, row_stride,
                                     b, slot, (int64_t)k0 + pad) + (int64_t)h * kHeadDim;
   };
+
+  // one tile (32 keys x 128 d of this KV head, first key `k0`): TMA boxes on the warp's barrier, or
+  // 16-byte cp.async copies
+  auto fetch = [&](bool is_v, uint8_t* tile, int k0) {
+    if (kTma) {
+      __syncwarp();                              // every lane is done reading the tile being replaced
+      if (lane == 0) {
+        // the tile was read through ldmatrix / written by plain stores: order those before the copy
+        tc::fence_proxy_async_smem();
+        uint64_t* bar = &tile_bar[warp][is_v ? 1 : 0];
+        const int row = cache_row(p, b, slot, (int64_t)k0 + pad);
+        tc::mbar_expect_tx(bar, kUnit * 256);
+        tc::tma_load_3d(tile, is_v ? &map_v : &map_k, bar, 0, h, row);
+        tc::tma_load_3d(tile + 4096, is_v ? &map_v : &map_k, bar, 64, h, row);
+      }
+    } else {
+      load_tile(tile, unit(is_v ? p.v_cache : p.k_cache, k0), row_stride, len - k0, lane);
+      cp_async_commit();
+    }
+  };
+  // wait for the warp's K (or V) tile; cp.async path: `pending` younger groups may stay in flight
+  auto arrived = [&](bool is_v) {
+    if (kTma) {
+      uint64_t* bar = &tile_bar[warp][is_v ? 1 : 0];
+      const uint32_t par = is_v ? v_phase : k_phase;
+      if (!tc::mbar_try_wait(bar, par)) {
+        const long long t0 = clock64();
+        while (!tc::mbar_try_wait_hint(bar, par, 1000)) {
+          if (clock64() - t0 > kDecodeWaitLimit) {     // give up: the result of this warp becomes NaN
+            expired = true;
+            break;
+          }
+        }
+      }
+      if (is_v) v_phase ^= 1u; else k_phase ^= 1u;
+    } else {
+      cp_async_wait<1>();
+    }
+    __syncwarp();
+  };
+  auto kt = [&](int row, int chunk) { return kTma ? tile_addr_tma(k_tile, row, chunk) : tile_addr(k_tile, row, chunk); };
+  auto vt = [&](int row, int chunk) { return kTma ? tile_addr_tma(v_tile, row, chunk) : tile_addr(v_tile, row, chunk); };
 
   // Q fragments of the 16 heads (rows g and g + 8), all 8 k-steps
   uint32_t qf[8][4];
@@ -181,18 +265,15 @@ __global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM) decode_spli
     return bb >= 0 ? bb * kBlockN : -1;
   };
   if (blk >= 0) {
-    load_tile(k_tile, unit(p.k_cache, key0), row_stride, len - key0, lane);
-    cp_async_commit();
-    load_tile(v_tile, unit(p.v_cache, key0), row_stride, len - key0, lane);
-    cp_async_commit();
+    fetch(false, k_tile, key0);
+    fetch(true, v_tile, key0);
   } else {
     key0 = -1;
   }
   while (key0 >= 0) {
     int jn = j, hn = half, bn = blk;
     const int key_next = advance(jn, hn, bn);
-    cp_async_wait<1>();                 // K of this unit has landed (V may still be in flight)
-    __syncwarp();
+    arrived(false);                     // K of this unit has landed (V may still be in flight)
 
     // ---- S = Q . K^T   (16 x 32)
     float s[kUnit / 8][4];
@@ -203,14 +284,14 @@ __global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM) decode_spli
 #pragma unroll
       for (int kp = 0; kp < 4; ++kp) {        // two k-steps (32 d) per ldmatrix.x4
         uint32_t bf[4];
-        ldmatrix_x4(bf, tile_addr(k_tile, nt * 8 + (lane & 7), kp * 4 + (lane >> 3)));
+        ldmatrix_x4(bf, kt(nt * 8 + (lane & 7), kp * 4 + (lane >> 3)));
         mma_bf16(s[nt], qf[2 * kp], bf[0], bf[1]);
         mma_bf16(s[nt], qf[2 * kp + 1], bf[2], bf[3]);
       }
     }
     __syncwarp();
-    if (key_next >= 0) load_tile(k_tile, unit(p.k_cache, key_next), row_stride, len - key_next, lane);
-    cp_async_commit();
+    if (key_next >= 0) fetch(false, k_tile, key_next);
+    else if (!kTma) cp_async_commit();        // (keeps the group count of the waits uniform)
 
     // ---- online softmax (rows g and g + 8; a row's scores live in the 4 lanes of a quad)
     float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -260,13 +341,12 @@ __global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM) decode_spli
 
     // ---- O += P . V   (16 x 128), V rows past `len` were never fetched: their P is 0, but the
     //      stale shared-memory bytes could be NaN, so those rows are zeroed first
-    cp_async_wait<1>();                       // V of this unit has landed
-    __syncwarp();
+    arrived(true);                            // V of this unit has landed
     if (key0 + kUnit > len) {
       for (int i = lane; i < kUnit * 16; i += 32) {
         const int row = i >> 4;
         if (key0 + row >= len)
-          *reinterpret_cast<uint4*>(tile_addr(v_tile, row, i & 15)) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(vt(row, i & 15)) = make_uint4(0u, 0u, 0u, 0u);
       }
       __syncwarp();
     }
@@ -275,21 +355,21 @@ __global__ void __launch_bounds__(kThreads, IFV2_DECODE_CTAS_PER_SM) decode_spli
 #pragma unroll
       for (int np = 0; np < 8; ++np) {        // two 8-wide d tiles per ldmatrix.x4.trans
         uint32_t bf[4];
-        ldmatrix_x4_trans(bf, tile_addr(v_tile, kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                        np * 2 + (lane >> 4)));
+        ldmatrix_x4_trans(bf, vt(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4)));
         mma_bf16(o[2 * np], pf[kk], bf[0], bf[1]);
         mma_bf16(o[2 * np + 1], pf[kk], bf[2], bf[3]);
       }
     }
     __syncwarp();
-    if (key_next >= 0) load_tile(v_tile, unit(p.v_cache, key_next), row_stride, len - key_next, lane);
-    cp_async_commit();
+    if (key_next >= 0) fetch(true, v_tile, key_next);
+    else if (!kTma) cp_async_commit();
     j = jn;
     half = hn;
     blk = bn;
     key0 = key_next;
   }
-  cp_async_wait<0>();
+  if (!kTma) cp_async_wait<0>();
+  if (__any_sync(0xFFFFFFFFu, expired)) l0 = l1 = __int_as_float(0x7FC00000);   // NaN: visible, not silent
   l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
   l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
   l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1);
@@ -501,12 +581,36 @@ static int decode_impl(const void* q, void* k_cache, void* v_cache, const void* 
   p.partial = static_cast<float*>(workspace);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.lse = lse;
-  const size_t smem = (size_t)kWarps * kWarpSmem > (size_t)kWarps * 16 * kPartialFloats * 4
-                          ? (size_t)kWarps * kWarpSmem : (size_t)kWarps * 16 * kPartialFloats * 4;
-  cudaError_t e = cudaFuncSetAttribute(decode_split_kernel,
+  const size_t smem = ((size_t)kWarps * kWarpSmem > (size_t)kWarps * 16 * kPartialFloats * 4
+                           ? (size_t)kWarps * kWarpSmem : (size_t)kWarps * 16 * kPartialFloats * 4) + 1024;
+  // TMA needs the caches as (rows, heads_k, 128) views: 16-byte aligned bases and, without a block
+  // table, a batch stride of whole rows.  The row extent of the maps is only a clipping bound; the
+  // kernel never asks for a row outside the sequences' own positions.
+  const int64_t row_elems = (int64_t)heads_k * kHeadDim;
+  const bool tma_ok = reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0 &&
+                      (block_table != nullptr || cache_batch_stride % row_elems == 0);
+  p.use_tma = tma_ok ? 1 : 0;
+  p.rows_per_slot = tma_ok && block_table == nullptr ? cache_batch_stride / row_elems : 0;
+  CUtensorMap map_k, map_v;
+  if (tma_ok) {
+    const uint64_t rows = 0x7FFFFFFFull;
+    int rc2 = make_tensor_map_bf16_3d(&map_k, k_cache, kHeadDim, heads_k, rows, kHeadDim * 2,
+                                      (uint64_t)row_elems * 2, 64, 1, kUnit);
+    if (rc2) return rc2;
+    rc2 = make_tensor_map_bf16_3d(&map_v, v_cache, kHeadDim, heads_k, rows, kHeadDim * 2,
+                                  (uint64_t)row_elems * 2, 64, 1, kUnit);
+    if (rc2) return rc2;
+  } else {
+    memset(&map_k, 0, sizeof(map_k));
+    memset(&map_v, 0, sizeof(map_v));
+  }
+  cudaError_t e = cudaFuncSetAttribute(tma_ok ? decode_split_kernel<true> : decode_split_kernel<false>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error((int)e, "decode: %s", cudaGetErrorString(e));
-  decode_split_kernel<<<dim3(p.splits, heads_k, batch), kThreads, smem, st>>>(p);
+  if (tma_ok)
+    decode_split_kernel<true><<<dim3(p.splits, heads_k, batch), kThreads, smem, st>>>(map_k, map_v, p);
+  else
+    decode_split_kernel<false><<<dim3(p.splits, heads_k, batch), kThreads, smem, st>>>(map_k, map_v, p);
   int rc = check_launch("decode_split");
   if (rc) return rc;
   decode_combine_kernel<<<dim3(heads_k, batch), 256, 0, st>>>(p);

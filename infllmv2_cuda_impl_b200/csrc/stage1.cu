@@ -77,6 +77,9 @@ struct Stage1Params {
   const int32_t* seqused_k;       // keys in use per sequence (<= its cu_k extent), may be null
   const int32_t* seqused_v;       // the same for the row-sum keys (needs cu_v), may be null
   const int32_t* cache_lens;      // per sequence, may be null
+  const int32_t* leftpad_k;       // scored keys start this many rows into the sequence's extent, or null
+  const int32_t* block_table;     // (batch, bt_stride) page of every page_size scored keys, or null
+  int bt_stride, page_size;
   int64_t total_q;
   int heads_q, heads_k;
   int max_seqlen_k;
@@ -119,7 +122,7 @@ __device__ __forceinline__ float bf16_round(float x) {
 }
 
 template <bool kPooled>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)      // 19 warps: at most 96 registers per thread
 stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kc,
               const __grid_constant__ CUtensorMap map_kv, const Stage1Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -128,8 +131,15 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.y, h = blockIdx.z;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b];
-  const int lc = p.seqused_k ? max(0, min(p.seqused_k[b], p.cu_k[b + 1] - k0)) : p.cu_k[b + 1] - k0;
+  // scored keys of the sequence: rows [k0, k0 + lc) of a packed tensor (optionally starting
+  // `leftpad_k` rows into the sequence's extent), or positions [0, lc) of a paged cache
+  int k0, lc;
+  {
+    const int pad = p.leftpad_k ? p.leftpad_k[b] : 0;
+    const int extent = p.cu_k[b + 1] - p.cu_k[b];
+    k0 = p.block_table ? 0 : p.cu_k[b] + pad;
+    lc = max(0, (p.seqused_k ? min(p.seqused_k[b], extent) : extent) - pad);
+  }
   const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTokPerCta;   // long tiles first
   if (tok0 >= lq) return;
   // an earlier CTA of this launch gave up on a wait: do not pile up more waits
@@ -206,11 +216,20 @@ stage1_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           break;
         mbar_expect_tx(&sm.kc_full[s], 2 * kHalfBytes);
         if (t < n_tiles1) {
-          tma_load_3d(sm.kc[s][0], &map_kv, &sm.kc_full[s], 0, h, v0 + t * kKeysPerTile);
-          tma_load_3d(sm.kc[s][1], &map_kv, &sm.kc_full[s], 64, h, v0 + t * kKeysPerTile);
+          int row = v0 + t * kKeysPerTile;
+          if (p.block_table != nullptr)          // (the row sums then run over the scored keys themselves)
+            row = __ldg(p.block_table + (int64_t)b * p.bt_stride + (t * kKeysPerTile) / p.page_size) * p.page_size +
+                  (t * kKeysPerTile) % p.page_size;
+          tma_load_3d(sm.kc[s][0], &map_kv, &sm.kc_full[s], 0, h, row);
+          tma_load_3d(sm.kc[s][1], &map_kv, &sm.kc_full[s], 64, h, row);
         } else {
-          tma_load_3d(sm.kc[s][0], &map_kc, &sm.kc_full[s], 0, h, k0 + (t - n_tiles1) * kKeysPerTile);
-          tma_load_3d(sm.kc[s][1], &map_kc, &sm.kc_full[s], 64, h, k0 + (t - n_tiles1) * kKeysPerTile);
+          const int pos = (t - n_tiles1) * kKeysPerTile;
+          int row = k0 + pos;
+          if (p.block_table != nullptr)          // a 128-key tile never straddles a page
+            row = __ldg(p.block_table + (int64_t)b * p.bt_stride + pos / p.page_size) * p.page_size +
+                  pos % p.page_size;
+          tma_load_3d(sm.kc[s][0], &map_kc, &sm.kc_full[s], 0, h, row);
+          tma_load_3d(sm.kc[s][1], &map_kc, &sm.kc_full[s], 64, h, row);
         }
         issued = t + 1;
       }
@@ -498,7 +517,8 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
                   int heads_q, int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
                   int64_t out_row_stride, int pooled_len, int cache_len, int local_blocks,
                   int init_blocks, float softmax_scale, int causal, int32_t* status, void* stream,
-                  const char* what) {
+                  const char* what, const int32_t* leftpad_k = nullptr,
+                  const int32_t* block_table = nullptr, int block_table_stride = 0, int page_size = 0) {
   IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED,
                "%s: head_dim %d not supported (only 128, as in the reference build)", what, head_dim);
   IFV2_REQUIRE(heads_k >= 1 && heads_q == heads_k * kGroup, IFV2_ERR_UNSUPPORTED,
@@ -533,6 +553,18 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
                "%s: seqused_v needs cu_seqlens_v", what);
   IFV2_REQUIRE(cu_seqlens_v == nullptr || (total_v >= 0 && total_v <= INT32_MAX && (kv || total_v == 0)),
                IFV2_ERR_INVALID_ARG, "%s: bad row-sum keys", what);
+  if (block_table != nullptr) {
+    IFV2_REQUIRE(page_size >= kKeysPerTile && page_size % kKeysPerTile == 0 && block_table_stride >= 1,
+                 IFV2_ERR_INVALID_ARG, "%s: page size must be a positive multiple of 128 compressed keys", what);
+    IFV2_REQUIRE(leftpad_k == nullptr, IFV2_ERR_UNSUPPORTED,
+                 "%s: a paged cache takes no leftpad_k (as in the reference)", what);
+    IFV2_REQUIRE(cu_seqlens_v == nullptr, IFV2_ERR_UNSUPPORTED,
+                 "%s: separate row-sum keys are not supported with a paged cache", what);
+    IFV2_REQUIRE((int64_t)block_table_stride * page_size >= max_seqlen_k, IFV2_ERR_INVALID_ARG,
+                 "%s: the block table covers fewer than max_seqlen_k keys", what);
+  }
+  IFV2_REQUIRE(leftpad_k == nullptr || cu_seqlens_v == nullptr, IFV2_ERR_UNSUPPORTED,
+               "%s: leftpad_k is not supported together with separate row-sum keys", what);
   CUtensorMap map_q, map_kc, map_kv;
   int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, total_q, kHeadDim * 2,
                                    (uint64_t)heads_q * kHeadDim * 2, 64, kGroup, kTokPerBox);
@@ -557,6 +589,10 @@ int launch_stage1(const void* q, const void* kc, const void* kv, void* out, void
   p.seqused_k = seqused_k;
   p.seqused_v = seqused_v;
   p.cache_lens = cache_lens;
+  p.leftpad_k = leftpad_k;
+  p.block_table = block_table;
+  p.bt_stride = block_table_stride;
+  p.page_size = page_size > 0 ? page_size : 1;
   p.total_q = total_q;
   p.heads_q = heads_q;
   p.heads_k = heads_k;
@@ -630,4 +666,24 @@ extern "C" int ifv2_stage1_block_scores(const void* q, const void* kc, const voi
                        batch, total_q, total_c, heads_q, heads_k, head_dim, max_seqlen_q,
                        max_seqlen_k, scores_row_stride, n_blocks, cache_len, local_blocks,
                        init_blocks, softmax_scale, causal, status, stream, "stage1_block_scores");
+}
+
+extern "C" int ifv2_stage1_paged(const void* q, const void* kc, void* scores_or_null,
+                                 void* block_scores_or_null, const int32_t* cu_seqlens_q,
+                                 const int32_t* cu_seqlens_k, const int32_t* seqused_k,
+                                 const int32_t* leftpad_k, const int32_t* block_table,
+                                 int block_table_stride, int page_size, const int32_t* cache_lens,
+                                 int batch, int64_t total_q, int64_t total_c, int heads_q, int heads_k,
+                                 int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                 int64_t scores_row_stride, int n_blocks, int cache_len,
+                                 int local_blocks, int init_blocks, float softmax_scale, int causal,
+                                 int32_t* status, void* stream) {
+  IFV2_REQUIRE(scores_or_null != nullptr || block_scores_or_null != nullptr || total_q == 0 ||
+                   max_seqlen_q == 0,
+               IFV2_ERR_INVALID_ARG, "stage1_paged: no output given");
+  return launch_stage1(q, kc, nullptr, scores_or_null, block_scores_or_null, cu_seqlens_q, cu_seqlens_k,
+                       nullptr, 0, seqused_k, nullptr, cache_lens, batch, total_q, total_c, heads_q,
+                       heads_k, head_dim, max_seqlen_q, max_seqlen_k, scores_row_stride, n_blocks,
+                       cache_len, local_blocks, init_blocks, softmax_scale, causal, status, stream,
+                       "stage1_paged", leftpad_k, block_table, block_table_stride, page_size);
 }

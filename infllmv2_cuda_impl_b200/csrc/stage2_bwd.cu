@@ -396,12 +396,12 @@ struct DkvSmem {
   uint8_t v[2][kKVHalfBytes];
   uint8_t q[2][2][kTileHalfBytes];     // [stage][d half]
   uint8_t dout[2][2][kTileHalfBytes];
-  uint8_t pmat[kTileHalfBytes];        // P  (128 rows x 64 keys bf16, 128-byte swizzle)
-  uint8_t dsmat[kTileHalfBytes];       // dS
+  uint8_t pmat[2][kTileHalfBytes];     // P  (128 rows x 64 keys bf16, 128-byte swizzle), double-buffered:
+  uint8_t dsmat[2][kTileHalfBytes];    // dS  the softmax warps write step i+1 while the products of step i read
   // dvdk_done[s]: the dV / dK products of a step in ring slot s are complete -> the Q / dO tiles
-  // of the slot may be refilled, P / dS may be rewritten, and after the last step the accumulators
-  // are final (one commit per product group)
-  uint64_t kv_full, qdo_full[2], dvdk_done[2], sdp_full[2], sdp_empty[2], pds_ready;
+  // of the slot may be refilled, the P / dS tiles of the slot may be rewritten, and after the last
+  // step the accumulators are final (one commit per product group)
+  uint64_t kv_full, qdo_full[2], dvdk_done[2], sdp_full[2], sdp_empty[2], pds_ready[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -475,7 +475,8 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.sdp_full[s], 1);
       mbar_init(&sm.sdp_empty[s], 8);
     }
-    mbar_init(&sm.pds_ready, 8);
+    mbar_init(&sm.pds_ready[0], 8);
+    mbar_init(&sm.pds_ready[1], 8);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -531,8 +532,9 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       constexpr uint32_t idesc_t = umma_idesc_bf16(128, 64, true, true);        // MN-major x MN-major
       const uint64_t k_desc = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024);
       const uint64_t v_desc = umma_desc_sw128(smem_u32(sm.v[0]), 16, 1024);
-      const uint64_t p_desc = umma_desc_sw128(smem_u32(sm.pmat), 16, 1024);
-      const uint64_t ds_desc = umma_desc_sw128(smem_u32(sm.dsmat), 16, 1024);
+      const uint64_t p_desc0 = umma_desc_sw128(smem_u32(sm.pmat[0]), 16, 1024);
+      const uint64_t ds_desc0 = umma_desc_sw128(smem_u32(sm.dsmat[0]), 16, 1024);
+      constexpr uint32_t kPds = kTileHalfBytes >> 4;            // descriptor address units per P / dS buffer
       // ring stage s = stage 0 + s * kRing (plain arithmetic keeps the descriptors in registers)
       const uint64_t q_desc0 = umma_desc_sw128(smem_u32(sm.q[0][0]), 16, 1024);
       const uint64_t do_desc0 = umma_desc_sw128(smem_u32(sm.dout[0][0]), 16, 1024);
@@ -568,9 +570,10 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
       auto issue_dvdk = [&](int i) -> bool {
         const int s = i & 1;
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_ready, (uint32_t)(i & 1), abort_flag, p.status, 85)))
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_ready[s], (uint32_t)((i >> 1) & 1), abort_flag, p.status, 85)))
           return false;
         tc_fence_after();
+        const uint64_t p_desc = p_desc0 + (uint32_t)s * kPds, ds_desc = ds_desc0 + (uint32_t)s * kPds;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ss_pred(tmem_dv, do_mn0 + s * kRing + ((kk * 2048) >> 4), p_desc + ((kk * 2048) >> 4), idesc_t,
@@ -583,13 +586,11 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         return true;
       };
       // dV / dK of a step go first, then S / dP of the next one: the Q / dO slot is released one
-      // product group earlier, which gives the copy of the tile two steps ahead a whole step to
-      // land.  Measured alternatives (timeline of the first CTAs, 65536-token training case):
-      // S / dP first (so that it runs under the softmax of the current step) 4600 clocks per
-      // step, this order 4350, issuing whichever group is ready first 4260 -- all three sit on
-      // the same bound, the 64 KB of Q / dO per step that every SM pulls through L2 (about
-      // 4.5 TB/s over the 148 SMs with one tile in flight per SM; shared memory has no room for
-      // a third slot).
+      // product group earlier, which gives the copy of the tile two steps ahead most of a step to
+      // land.  What bounds the kernel is that copy: 64 KB of Q / dO per step and SM through L2 with
+      // two slots (shared memory has no room for a third), about 4.3 TB/s over the 148 SMs;
+      // issuing S / dP first, or double-buffering P / dS so that the softmax warps never wait for
+      // the products, changes the step time by less than 3 %.
       int i = 0;
       if (have >= 0) ok = issue_sdp(0);
       while (ok && have >= 0) {
@@ -648,15 +649,15 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         tc_fence_before();
         mbar_arrive_warp(&sm.sdp_empty[s]);                  // S / dP of this buffer may be overwritten
-        // P and dS of the previous step must have been consumed before the tiles are rewritten
-        if (i >= 1) {
-          ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dvdk_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1),
+        // the products of step i - 2 must have consumed this slot's P and dS before they are rewritten
+        if (i >= 2) {
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dvdk_done[s], (uint32_t)(((i >> 1) & 1) ^ 1),
                                                  abort_flag, p.status, 87));
           if (!ok) break;
         }
         // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk (c ^ (r & 7))
-        uint8_t* prow = sm.pmat + r * 128;
-        uint8_t* drow = sm.dsmat + r * 128;
+        uint8_t* prow = sm.pmat[s] + r * 128;
+        uint8_t* drow = sm.dsmat[s] + r * 128;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {                  // this group's four 16-byte chunks of the row
           const int pc = ((grp * 4 + c) ^ (r & 7)) << 4;
@@ -666,7 +667,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
               make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
         }
         fence_proxy_async_smem();
-        mbar_arrive_warp(&sm.pds_ready);
+        mbar_arrive_warp(&sm.pds_ready[s]);
       }
     }
     if (ok && steps > 0) {

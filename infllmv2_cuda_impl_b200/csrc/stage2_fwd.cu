@@ -42,6 +42,10 @@ struct FwdParams {
   int mask_words;
   const int32_t* cu_q;
   const int32_t* cu_k;
+  const int32_t* seqused_k;       // keys in use per sequence, or null (then the cu_k extent)
+  const int32_t* leftpad_k;       // keys of a sequence start this many rows into its cu_k extent, or null
+  const int32_t* block_table;     // (batch, bt_stride) page of every page_size key positions, or null
+  int bt_stride, page_size;
   int64_t total_q;
   int heads_q, heads_k;
   float scale, scale_log2;
@@ -92,7 +96,12 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.y, h = blockIdx.z;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
+  // keys of the sequence: rows [k0, k0 + lk) of a packed tensor (optionally starting `leftpad_k`
+  // rows into the sequence's extent, block_info.h:22-24, 40), or positions [0, lk) of a paged
+  // cache whose pages the block table names
+  const int pad = p.leftpad_k ? p.leftpad_k[b] : 0;
+  const int k0 = p.block_table ? 0 : p.cu_k[b] + pad;
+  const int lk = max(0, (p.seqused_k ? p.seqused_k[b] : p.cu_k[b + 1] - p.cu_k[b]) - pad);
   const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTokPerTile;   // long tiles first
   if (tok0 >= lq) return;
   // an earlier CTA gave up on a wait: the launch is already failed, do not pile up more waits
@@ -170,7 +179,13 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       bool ok = true;
       for (int i = 0; i < n_blocks && ok; ++i) {
         const int blk = walk.next();
-        const int s = i & 1, key = k0 + blk * kBlockN;
+        const int s = i & 1;
+        int key = k0 + blk * kBlockN;
+        if (p.block_table != nullptr) {          // a 64-key block never straddles a page
+          const int pos = blk * kBlockN;
+          key = __ldg(p.block_table + (int64_t)b * p.bt_stride + pos / p.page_size) * p.page_size +
+                pos % p.page_size;
+        }
         const uint32_t par = (uint32_t)((i >> 1) & 1);
         if (i >= 2) ok = mbar_wait(&sm.qk_done[s], par ^ 1u, abort_flag, p.status, 11);
         if (!ok) break;
@@ -271,9 +286,12 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       if (!ok) break;
       tc_fence_after();
 
+      // keys of this block that exist: in the ragged last block of a sequence the K / V rows past
+      // them hold the next sequence's keys or whatever an unused part of a cache page contains
+      const int nk = lk - blk * kBlockN;
       uint32_t raw[64];
       tmem_ld64_wait(tmem + lane_off + s * 64, raw);
-      if (partial) {
+      if (partial || nk < kBlockN) {         // (every row of a ragged block: its scores may be NaN)
 #pragma unroll
         for (int c = 0; c < 64; ++c)
           if (c >= lim) raw[c] = 0xFF800000u;                              // -inf
@@ -327,6 +345,18 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       float s_lo, s_hi;
       unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), s_lo, s_hi);
       const float sum = s_lo + s_hi;
+      // The V rows past the last key of a ragged block have P = 0, but 0 x inf or 0 x NaN is not 0,
+      // so those rows are cleared before the product reads them.
+      if (nk < kBlockN) {
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 34));
+        if (!ok) break;
+        const int t128 = threadIdx.x - 64;                   // 0..127 among the softmax threads
+        for (int i = t128; i < (kBlockN - nk) * 16; i += 128) {
+          const int row = nk + (i >> 4), half = (i >> 3) & 1, chunk = i & 7;
+          *reinterpret_cast<uint4*>(sm.v[s][half] + row * 128 + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();
+      }
       l += sum;
       tmem_st32(tmem + lane_off + s * 64, packed);
       tmem_wait_st();
@@ -385,13 +415,15 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 
 using namespace ifv2;
 
-extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out,
-                                    float* lse, const int64_t* fwd_mask, int mask_words,
-                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                    int batch, int64_t total_q, int64_t total_k, int heads_q,
-                                    int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
-                                    float softmax_scale, int causal, int32_t* status,
-                                    void* stream) {
+static int sparse_attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
+                                float* lse, const int64_t* fwd_mask, int mask_words,
+                                const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                const int32_t* seqused_k, const int32_t* leftpad_k,
+                                const int32_t* block_table, int block_table_stride, int page_size,
+                                int batch, int64_t total_q, int64_t total_k, int heads_q,
+                                int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                float softmax_scale, int causal, int32_t* status,
+                                void* stream) {
   IFV2_REQUIRE(head_dim == kHeadDim, IFV2_ERR_UNSUPPORTED,
                "sparse_attn_fwd: head_dim %d not supported (only 128, as in the reference build)",
                head_dim);
@@ -413,6 +445,14 @@ extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v,
                mask_words, kMaxMaskWords);
   IFV2_REQUIRE(batch <= 65535 && heads_k <= 65535, IFV2_ERR_TOO_LARGE,
                "sparse_attn_fwd: batch or heads_k > 65535");
+  if (block_table != nullptr) {
+    IFV2_REQUIRE(page_size >= kBlockN && page_size % kBlockN == 0 && block_table_stride >= 1,
+                 IFV2_ERR_INVALID_ARG, "sparse_attn_fwd: page size must be a positive multiple of 64");
+    IFV2_REQUIRE(leftpad_k == nullptr, IFV2_ERR_UNSUPPORTED,
+                 "sparse_attn_fwd: a paged cache takes no leftpad_k (as in the reference)");
+    IFV2_REQUIRE((int64_t)block_table_stride * page_size >= max_seqlen_k, IFV2_ERR_INVALID_ARG,
+                 "sparse_attn_fwd: the block table covers fewer than max_seqlen_k positions");
+  }
 
   CUtensorMap map_q, map_k, map_v;
   int rc = make_tensor_map_bf16_3d(&map_q, q, kHeadDim, heads_q, total_q, kHeadDim * 2,
@@ -432,6 +472,11 @@ extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v,
   p.mask_words = mask_words;
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
+  p.seqused_k = seqused_k;
+  p.leftpad_k = leftpad_k;
+  p.block_table = block_table;
+  p.bt_stride = block_table_stride;
+  p.page_size = page_size > 0 ? page_size : 1;
   p.total_q = total_q;
   p.heads_q = heads_q;
   p.heads_k = heads_k;
@@ -449,4 +494,31 @@ extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v,
   if (rc) return rc;
   sparse_attn_fwd_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
   return check_launch("sparse_attn_fwd");
+}
+
+extern "C" int ifv2_sparse_attn_fwd(const void* q, const void* k, const void* v, void* out,
+                                    float* lse, const int64_t* fwd_mask, int mask_words,
+                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                    int batch, int64_t total_q, int64_t total_k, int heads_q,
+                                    int heads_k, int head_dim, int max_seqlen_q, int max_seqlen_k,
+                                    float softmax_scale, int causal, int32_t* status,
+                                    void* stream) {
+  return sparse_attn_fwd_impl(q, k, v, out, lse, fwd_mask, mask_words, cu_seqlens_q, cu_seqlens_k,
+                              nullptr, nullptr, nullptr, 0, 0, batch, total_q, total_k, heads_q, heads_k,
+                              head_dim, max_seqlen_q, max_seqlen_k, softmax_scale, causal, status, stream);
+}
+
+extern "C" int ifv2_sparse_attn_fwd_paged(const void* q, const void* k, const void* v, void* out,
+                                          float* lse, const int64_t* fwd_mask, int mask_words,
+                                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                          const int32_t* seqused_k, const int32_t* leftpad_k,
+                                          const int32_t* block_table, int block_table_stride,
+                                          int page_size, int batch, int64_t total_q, int64_t total_k,
+                                          int heads_q, int heads_k, int head_dim, int max_seqlen_q,
+                                          int max_seqlen_k, float softmax_scale, int causal,
+                                          int32_t* status, void* stream) {
+  return sparse_attn_fwd_impl(q, k, v, out, lse, fwd_mask, mask_words, cu_seqlens_q, cu_seqlens_k,
+                              seqused_k, leftpad_k, block_table, block_table_stride, page_size, batch,
+                              total_q, total_k, heads_q, heads_k, head_dim, max_seqlen_q, max_seqlen_k,
+                              softmax_scale, causal, status, stream);
 }

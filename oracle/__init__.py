@@ -21,11 +21,11 @@ from .pooling import max_pooling_1d, max_pooling_1d_varlen
 from .topk import topk_select
 from .stage1 import stage1_scores, stage1_visible_limit, compress_keys
 from .attention import (expand_topk_mask, sparse_attention_fwd, sparse_attention_fwd_bwd,
-                        kvcache_decode, apply_rotary)
+                        kvcache_decode, apply_rotary, apply_rotary_literal)
 
 __all__ = [
     "topk_to_uint64", "blockmask_to_uint64", "uint64_to_bool", "transpose_blockmask",
     "max_pooling_1d", "max_pooling_1d_varlen", "topk_select",
     "stage1_scores", "stage1_visible_limit", "compress_keys",
-    "expand_topk_mask", "sparse_attention_fwd", "sparse_attention_fwd_bwd", "kvcache_decode", "apply_rotary",
+    "expand_topk_mask", "sparse_attention_fwd", "sparse_attention_fwd_bwd", "kvcache_decode", "apply_rotary", "apply_rotary_literal",
 ]

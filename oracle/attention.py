@@ -118,7 +118,8 @@ def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interlea
     """Rotary embedding of rows x (..., d) with per-row cos / sin (..., rotary_dim / 2), the way the
     reference rotates q and the appended key of a decode step (csrc/flash_attn/src/rotary.h:20-79
     interleaved, :83-150 contiguous halves): fp32 arithmetic, features past rotary_dim unchanged,
-    result in x's dtype.  No Python twin exists in the reference (parity unpinned for this helper)."""
+    result in x's dtype.  Pinned by `apply_rotary_literal`, an element-by-element restatement of the
+    two device loops (tests/golden/make_golden.py asserts equality, fixtures rotary_* in stage2.npz)."""
     half = cos.shape[-1]
     xf, c, s_ = x.float(), cos.float(), sin.float()
     out = xf.clone()
@@ -131,3 +132,34 @@ def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interlea
         out[..., :half] = x0 * c - x1 * s_
         out[..., half:2 * half] = x0 * s_ + x1 * c
     return out.to(x.dtype)
+
+
+def apply_rotary_literal(x, cos, sin, interleaved: bool):
+    """Element-by-element restatement of the reference's two rotary copy loops, the pin of
+    `apply_rotary`: copy_rotary_interleaved (csrc/flash_attn/src/rotary.h:20-79: pairs (2i, 2i+1),
+    real = x0*cos - x1*sin, imag = x0*sin + x1*cos) and copy_rotary_contiguous (:83-150: feature j
+    pairs with j +- rotary_dim/2, out = x[j]*cos + other*(-sin for the left half, +sin for the
+    right)), both in fp32 with one rounding to the storage type; features at or past rotary_dim are
+    copied.  x: (rows, d) array of values exactly representable in the storage type, cos / sin:
+    (rows, rotary_dim / 2).  Returns float32 (rows, d) BEFORE the final rounding."""
+    import numpy as np
+    x = np.asarray(x, dtype=np.float32)
+    cos = np.asarray(cos, dtype=np.float32)
+    sin = np.asarray(sin, dtype=np.float32)
+    rows, d = x.shape
+    half = cos.shape[1]
+    rotary_dim = 2 * half
+    out = x.copy()
+    for r in range(rows):
+        if interleaved:
+            for i in range(half):
+                x0, x1 = x[r, 2 * i], x[r, 2 * i + 1]
+                out[r, 2 * i] = np.float32(x0 * cos[r, i]) - np.float32(x1 * sin[r, i])
+                out[r, 2 * i + 1] = np.float32(x0 * sin[r, i]) + np.float32(x1 * cos[r, i])
+        else:
+            for j in range(rotary_dim):
+                is_left = j < half
+                other = x[r, j + half] if is_left else x[r, j - half]
+                i = j if is_left else j - half
+                out[r, j] = np.float32(x[r, j] * cos[r, i]) + np.float32(other * (-sin[r, i] if is_left else sin[r, i]))
+    return out

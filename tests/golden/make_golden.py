@@ -205,6 +205,18 @@ def gen_stage2(mods, out):
     print(f"decode: oracle vs naive_attention max|diff| = {err:.2e}")
     cases.update(dec_shape=np.array([bsz, hq, hk, d, cache], dtype=np.int64),
                  dec_out=ref.numpy(), out_row_step=np.int64(OUT_ROW_STEP))
+    # rotary helper: the vectorised oracle against the element-by-element restatement of the
+    # reference's device loops (csrc/flash_attn/src/rotary.h:20-150), both layouts, rotary_dim < d
+    for name, rows_, rd, inter in (("a", 6, 128, True), ("b", 5, 64, True), ("c", 6, 128, False), ("d", 5, 32, False)):
+        x = torch.from_numpy(det_array((rows_, 128), 900 + ord(name))).to(torch.bfloat16)
+        ang = torch.from_numpy(det_array((rows_, rd // 2), 950 + ord(name), 3.0))
+        c, s_ = torch.cos(ang).to(torch.bfloat16), torch.sin(ang).to(torch.bfloat16)
+        lit = oracle.apply_rotary_literal(x.float().numpy(), c.float().numpy(), s_.float().numpy(), inter)
+        got = oracle.apply_rotary(x, c, s_, inter)
+        want = torch.from_numpy(lit).to(torch.bfloat16)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"rotary {name}"
+        cases[f"rotary_{name}_cfg"] = np.array([rows_, rd, int(inter), 900 + ord(name), 950 + ord(name)], dtype=np.int64)
+        cases[f"rotary_{name}_out"] = want.float().numpy()
     np.savez_compressed(os.path.join(out, "stage2.npz"), **cases)
 
 

@@ -175,3 +175,21 @@ def test_compress_golden(golden_dir):
         got, cu_c = oracle.compress_keys(k, cu, kernel, stride)
         assert cu_c == [int(x) for x in g[base + "_cu_c"]], key
         assert np.array_equal(got.float().numpy(), g[base + "_out"]), key
+
+
+def test_rotary_golden(golden_dir):
+    """The rotary helper against fixtures made from the element-by-element restatement of the
+    reference's device loops (csrc/flash_attn/src/rotary.h:20-150); the restatement is re-run."""
+    from inputs import det_array
+    g = _load(golden_dir, "stage2.npz")
+    names = sorted(k[len("rotary_"):-4] for k in g.files if k.startswith("rotary_") and k.endswith("_cfg"))
+    assert len(names) == 4
+    for name in names:
+        rows, rd, inter, sx, sa = (int(v) for v in g[f"rotary_{name}_cfg"])
+        x = torch.from_numpy(det_array((rows, 128), sx)).to(torch.bfloat16)
+        ang = torch.from_numpy(det_array((rows, rd // 2), sa, 3.0))
+        c, s_ = torch.cos(ang).to(torch.bfloat16), torch.sin(ang).to(torch.bfloat16)
+        got = oracle.apply_rotary(x, c, s_, bool(inter)).float().numpy()
+        assert np.array_equal(got, g[f"rotary_{name}_out"]), name
+        lit = oracle.apply_rotary_literal(x.float().numpy(), c.float().numpy(), s_.float().numpy(), bool(inter))
+        assert np.array_equal(torch.from_numpy(lit).to(torch.bfloat16).float().numpy(), g[f"rotary_{name}_out"]), name
