@@ -3,19 +3,19 @@
 // With a single token the query tile is 16 rows, far too small for a tcgen05 tile, and the work
 // is HBM-bound: every selected 64-key block is read once (K and V, 32 KB) and used by 16 rows.
 // So this kernel is built around bandwidth: the selected blocks of one (sequence, KV head) are
-// split over several CTAs, each warp streams its blocks as 32-key units into swizzled shared
-// memory with cp.async (K and V of the next unit are prefetched as soon as the current product
-// has consumed its tile; 64 KB per CTA, two CTAs per SM), the 16 x 32 products run on mma.sync
-// m16n8k16 (exactly one M tile), and
-// the per-split (max, sum, O) partials are merged by a small second kernel.
+// split over several CTAs (as many as fill the SMs in ONE wave, three CTAs per SM), each warp
+// streams its blocks as 32-key units into swizzled shared memory (K and V of the next unit are
+// fetched as soon as the current product has consumed its tile), the 16 x 32 products run on
+// mma.sync m16n8k16 (exactly one M tile), and the per-split (max, sum, O) partials are merged by
+// a small second kernel.
 //
 // Launches: [append new K/V in place] -> split kernel -> combine kernel.
 //
 // Tile loads: when the cache rows can be described by one tensor map (16-byte aligned base, batch
 // stride a whole number of rows) a warp's K and V tiles arrive as two TMA boxes each ({64 d, 1 head,
-// 32 keys}, 128-byte swizzle) on a per-warp mbarrier, issued by one lane: the 512 sixteen-byte
-// cp.async requests per tile of the plain path kept the load/store unit at one request per 1.3
-// clocks per SM, which is what held the kernel at half the HBM bandwidth.  Other layouts use cp.async.
+// 32 keys}, 128-byte swizzle) on a per-warp mbarrier, issued by one lane, instead of 512 sixteen-byte
+// cp.async requests per tile; other layouts use cp.async.  Both forms run at the same speed: what
+// held the step at half the HBM bandwidth was a launch of 1.15 waves, see the split count below.
 #include <string.h>
 #include "mma_sync.cuh"
 #include "tc05.cuh"
@@ -573,10 +573,14 @@ static int decode_impl(const void* q, void* k_cache, void* v_cache, const void* 
   p.cache_batch_idx = cache_batch_idx;
   p.leftpad = cache_leftpad;
   p.scale_log2 = softmax_scale * kLog2e;
-  // about four waves of two CTAs per SM over the whole launch
-  // (a power of two, so that top-k lists of 32 / 64 blocks divide evenly over CTAs and warps)
-  int splits = 1;
-  while (splits < kMaxSplits && (int64_t)2 * splits * batch * heads_k <= 8 * kNumSMs) splits *= 2;
+  // One wave: as many CTAs per (sequence, KV head) as still fit the SMs all at once.  A launch
+  // that spills into a second, mostly empty wave takes twice as long (measured at batch 64 x 2 KV
+  // heads, top-64: 3 splits = 384 CTAs on 444 slots 62 us, 4 splits = 512 CTAs 78 us, 8 splits 79 us).
+  const int64_t slots = (int64_t)kNumSMs * IFV2_DECODE_CTAS_PER_SM;
+  const int64_t pairs = (int64_t)batch * heads_k;
+  int splits = (int)(slots / pairs);
+  if (splits < 1) splits = 1;
+  if (splits > kMaxSplits) splits = kMaxSplits;
   p.splits = splits;
   p.partial = static_cast<float*>(workspace);
   p.out = static_cast<__nv_bfloat16*>(out);
