@@ -182,11 +182,15 @@ int ifv2_topk_select_mask(const void* score, int32_t* out_idx, int64_t* row_mask
  * identical to ifv2_max_pooling_1d_varlen -> ifv2_topk_select -> ifv2_topk_to_uint64 on the same
  * row (csrc/max_pooling_1d.cuh:11-103, the tie rule of csrc/topk.cuh:6-42,
  * csrc/topk_to_uint64.cuh:10-76); the reference runs these (and a torch.topk) as separate
- * launches. */
+ * launches.  dense_len (0 = off): a sequence whose query sits at a position below dense_len gets
+ * every block up to its own instead of a selection (short sequences attend densely; decided per
+ * sequence on the device, so a captured step and an eager one agree); its topk_idx row then names
+ * the first k of those blocks. */
 int ifv2_decode_select(const void* score, int is_bf16, int64_t row_stride, const int32_t* seqused_c,
                        const int32_t* positions, int64_t* mask, int32_t* topk_idx, int batch,
                        int heads, int max_seqlen_c, int n_blocks, int mask_words, int k,
-                       int local_blocks, int init_blocks, int block_size, int stride, void* stream);
+                       int local_blocks, int init_blocks, int block_size, int stride, int dense_len,
+                       void* stream);
 
 /* ---------------------------------------------------------------- stage 1 ------------------ */
 
@@ -233,15 +237,16 @@ int ifv2_stage1_decode_scores(const void* q, const void* kc, void* out, const in
  * shared memory and runs ifv2_decode_select's pool / top-k / mask pack on it -- the score row
  * never reaches HBM.  Arguments as in those two entries (positions, mask, topk_idx, n_blocks,
  * mask_words, k, local_blocks, init_blocks, block_size, stride as in ifv2_decode_select; the rest
- * as in ifv2_stage1_decode_scores, same workspace size); max_seqlen_k <= 32768.  Results are
- * identical to ifv2_stage1_decode_scores followed by ifv2_decode_select. */
+ * as in ifv2_stage1_decode_scores, same workspace size; dense_len as in ifv2_decode_select);
+ * max_seqlen_k <= 32768.  Results are identical to ifv2_stage1_decode_scores followed by
+ * ifv2_decode_select. */
 int ifv2_stage1_decode_select(const void* q, const void* kc, const int32_t* cu_seqlens_k,
                               const int32_t* seqused_k, const int32_t* positions, int64_t* mask,
                               int32_t* topk_idx, int batch, int64_t total_c, int heads_q,
                               int heads_k, int head_dim, int max_seqlen_k, int n_blocks,
                               int mask_words, int k, int local_blocks, int init_blocks,
-                              int block_size, int stride, float softmax_scale, int causal,
-                              void* workspace, int64_t workspace_bytes, void* stream);
+                              int block_size, int stride, int dense_len, float softmax_scale,
+                              int causal, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Stage-1 scorer with the 64-token max-pool fused in: writes block scores
  * (heads_k, total_q, n_blocks) bf16 that are bit-identical to ifv2_max_pooling_1d[_varlen]

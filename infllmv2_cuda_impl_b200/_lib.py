@@ -45,8 +45,8 @@ SIGNATURES = {
     "ifv2_stage1_decode_scores": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int,
                                   c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p, c_int64, c_void_p],
     "ifv2_decode_select": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "ifv2_stage1_decode_select": [c_void_p] * 7 + [c_int, c_int64] + [c_int] * 11 + [c_float, c_int, c_void_p,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ifv2_stage1_decode_select": [c_void_p] * 7 + [c_int, c_int64] + [c_int] * 12 + [c_float, c_int, c_void_p,
                                                                                c_int64, c_void_p],
     "ifv2_cache_fill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int,
                         c_void_p],

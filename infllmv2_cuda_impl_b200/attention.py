@@ -223,7 +223,7 @@ def _stage1_paged(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_
 
 def infllmv2_stage1_decode_select(q, k, cu_seqlens_k, positions, max_seqlen_k, cache_capacity, topk,
                                   local_blocks, init_blocks, seqused_k=None, softmax_scale=None,
-                                  causal=False, block_size=64, stride=16, return_topk=False):
+                                  causal=False, block_size=64, stride=16, return_topk=False, dense_len=0):
     """Block selection of a decode step straight from the compressed keys (an addition to the
     reference API): stage-1 scores of ONE query token per sequence (q: (B, Hq, 128)), 64-token
     max-pool, top-k and the packed block mask, in two launches and without the score rows ever
@@ -231,7 +231,8 @@ def infllmv2_stage1_decode_select(q, k, cu_seqlens_k, positions, max_seqlen_k, c
     infllmv2_attn_stage1; positions (B,) int32: position of each query token in its sequence;
     cache_capacity: key capacity of the KV cache the mask is for.  Returns the int64 mask
     (B, Hk, 1, words) that infllmv2_attn_with_kvcache takes as `block_mask` [, topk_idx
-    (B, Hk, 1, topk) int32]; both equal infllmv2_attn_stage1 -> ops.decode_select."""
+    (B, Hk, 1, topk) int32]; both equal infllmv2_attn_stage1 -> ops.decode_select.  dense_len: as in
+    ops.decode_select."""
     _check_common(q, k, 0.0, (-1, -1), 0.0, None, None, "infllmv2_stage1_decode_select")
     q, k = _dense(maybe_contiguous(q)), _dense(maybe_contiguous(k))
     if q.dim() != 3:
@@ -257,7 +258,8 @@ def infllmv2_stage1_decode_select(q, k, cu_seqlens_k, positions, max_seqlen_k, c
                   seqused_k.data_ptr() if seqused_k is not None else None, positions.contiguous().data_ptr(),
                   mask.data_ptr(), idx.data_ptr() if idx is not None else None, batch, k.shape[0], nheads,
                   nheads_k, d, max_seqlen_k, n_blocks, words, topk, local_blocks, init_blocks, block_size,
-                  stride, float(softmax_scale), int(bool(causal)), ws.data_ptr(), ws_bytes, _stream(q.device))
+                  stride, int(dense_len), float(softmax_scale), int(bool(causal)), ws.data_ptr(), ws_bytes,
+                  _stream(q.device))
     return (mask, idx) if return_topk else mask
 
 

@@ -49,7 +49,8 @@ __global__ void __launch_bounds__(kThreads) decode_select_kernel(const SelectPar
   }
   select_row<T>(xs, p.staged_elems > 0, k_len, bq, p.a, sm,
                 p.mask + ((int64_t)b * p.heads + h) * p.a.words,
-                p.topk_idx ? p.topk_idx + ((int64_t)b * p.heads + h) * p.a.k : nullptr);
+                p.topk_idx ? p.topk_idx + ((int64_t)b * p.heads + h) * p.a.k : nullptr,
+                p.positions[b] < p.a.dense_len);
 }
 
 }  // namespace
@@ -60,7 +61,8 @@ extern "C" int ifv2_decode_select(const void* score, int is_bf16, int64_t row_st
                                   const int32_t* seqused_c, const int32_t* positions, int64_t* mask,
                                   int32_t* topk_idx, int batch, int heads, int max_seqlen_c,
                                   int n_blocks, int mask_words, int k, int local_blocks,
-                                  int init_blocks, int block_size, int stride, void* stream) {
+                                  int init_blocks, int block_size, int stride, int dense_len,
+                                  void* stream) {
   IFV2_REQUIRE(batch >= 0 && heads >= 0 && max_seqlen_c >= 0 && n_blocks >= 0 && k >= 0 &&
                    mask_words >= 0 && local_blocks >= 0 && init_blocks >= 0,
                IFV2_ERR_INVALID_ARG, "decode_select: negative size");
@@ -81,7 +83,8 @@ extern "C" int ifv2_decode_select(const void* score, int is_bf16, int64_t row_st
                      padded <= row_stride && padded * 2 <= 64 * 1024;
   SelectParams p{score, seqused_c, positions, reinterpret_cast<unsigned long long*>(mask), topk_idx,
                  row_stride, batch, heads, max_seqlen_c, block_size, stage ? padded : 0,
-                 Args{n_blocks, mask_words, k, local_blocks, init_blocks, block_size / stride}};
+                 Args{n_blocks, mask_words, k, local_blocks, init_blocks, block_size / stride,
+                      dense_len > 0 ? dense_len : 0}};
   const size_t smem = stage ? (size_t)padded * 2 : 0;
   const dim3 grid(heads, batch);
   cudaError_t e = cudaSuccess;

@@ -27,6 +27,7 @@ struct Smem {
 
 struct Args {
   int n_blocks, words, k, local_blocks, init_blocks, pool_stride;
+  int dense_len;     // a query at a position below this attends every block it can see (0 = never)
 };
 
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -51,8 +52,20 @@ __device__ __forceinline__ uint32_t ordered_key(uint16_t bits) {
 // null.  Called by all kThreads threads of the CTA; sm.words need not be initialised.
 template <typename T>
 __device__ __forceinline__ void select_row(const T* xs, bool in_smem, int k_len, int bq, const Args& a,
-                                           Smem& sm, unsigned long long* mrow, int32_t* out_idx) {
+                                           Smem& sm, unsigned long long* mrow, int32_t* out_idx,
+                                           bool dense = false) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (dense) {
+    // a short sequence: every block up to the query's own (the list, where asked for, can only
+    // name the first k of them)
+    for (int w = tid; w < a.words; w += kThreads) {
+      const int first = w * 64;
+      mrow[w] = (bq < first) ? 0ull : ((bq - first >= 63) ? ~0ull : ((2ull << (bq - first)) - 1ull));
+    }
+    if (out_idx != nullptr)
+      for (int i = tid; i < a.k; i += kThreads) out_idx[i] = (i <= bq && i < a.n_blocks) ? i : -1;
+    return;
+  }
   const int n = a.n_blocks;
   const int per = (n + kThreads - 1) / kThreads;
   const int i0 = min(tid * per, n), i1 = min(i0 + per, n);

@@ -346,7 +346,8 @@ stage1_decode_select_kernel(const DecodeSelectParams q) {
   __syncthreads();
   dsel::select_row<__nv_bfloat16>(row, true, lc, q.positions[b] / q.block_size, q.a, sm,
                                   q.mask + pair * q.a.words,
-                                  q.topk_idx ? q.topk_idx + pair * q.a.k : nullptr);
+                                  q.topk_idx ? q.topk_idx + pair * q.a.k : nullptr,
+                                  q.positions[b] < q.a.dense_len);
 }
 
 }  // namespace
@@ -440,7 +441,7 @@ extern "C" int ifv2_stage1_decode_select(const void* q, const void* kc, const in
                                          int64_t* mask, int32_t* topk_idx, int batch, int64_t total_c,
                                          int heads_q, int heads_k, int head_dim, int max_seqlen_k,
                                          int n_blocks, int mask_words, int k, int local_blocks,
-                                         int init_blocks, int block_size, int stride,
+                                         int init_blocks, int block_size, int stride, int dense_len,
                                          float softmax_scale, int causal, void* workspace,
                                          int64_t workspace_bytes, void* stream) {
   IFV2_REQUIRE(batch >= 0 && max_seqlen_k >= 0 && n_blocks >= 0 && mask_words >= 0 && k >= 0 &&
@@ -466,7 +467,8 @@ extern "C" int ifv2_stage1_decode_select(const void* q, const void* kc, const in
   sp.mask = reinterpret_cast<unsigned long long*>(mask);
   sp.topk_idx = topk_idx;
   sp.block_size = block_size;
-  sp.a = dsel::Args{n_blocks, mask_words, k, local_blocks, init_blocks, block_size / stride};
+  sp.a = dsel::Args{n_blocks, mask_words, k, local_blocks, init_blocks, block_size / stride,
+                    dense_len > 0 ? dense_len : 0};
   cudaStream_t st = (cudaStream_t)stream;
   rc = launch_decode_scores(sp.s1, st);
   if (rc) return rc;

@@ -390,14 +390,15 @@ def decode_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tenso
 
 def decode_select(score: torch.Tensor, positions: torch.Tensor, k: int, max_seqlen_k: int,
                   local_blocks: int, init_blocks: int, seqused_c: Optional[torch.Tensor] = None,
-                  block_size: int = 64, stride: int = 16, return_topk: bool = False):
+                  block_size: int = 64, stride: int = 16, return_topk: bool = False, dense_len: int = 0):
     """Block selection of a decode step in one launch: max-pool of the stage-1 scores of ONE query
     token per sequence (score: (Hk, B, n_comp) bf16/fp16, e.g. from infllmv2_attn_stage1), top-k
     and the uint64 block mask (B, Hk, 1, ceil(ceil(max_seqlen_k / block_size) / 64)) int64 that
     infllmv2_attn_with_kvcache takes as `block_mask`.  positions (B,) int32: position of the query
     token in its sequence; seqused_c (B,) int32: compressed keys per sequence (default: all
     columns).  Equal to max_pooling_1d_varlen -> infllmv2_topk -> topk_to_uint64.  With
-    return_topk also returns topk_idx (B, Hk, 1, k) int32."""
+    return_topk also returns topk_idx (B, Hk, 1, k) int32.  dense_len: sequences whose query position
+    is below it get every block up to their own (dense attention for short sequences)."""
     assert score.dtype == torch.float16 or score.dtype == torch.bfloat16
     _require_cuda(score, "score")
     if score.dim() != 3:
@@ -416,5 +417,5 @@ def decode_select(score: torch.Tensor, positions: torch.Tensor, k: int, max_seql
         _lib.call("ifv2_decode_select", score.data_ptr(), int(score.dtype == torch.bfloat16), row_stride,
                   seqused_c.data_ptr() if seqused_c is not None else None, positions.contiguous().data_ptr(),
                   mask.data_ptr(), idx.data_ptr() if idx is not None else None, b, hk, n_c, n_blocks, words,
-                  k, local_blocks, init_blocks, block_size, stride, _stream(score.device))
+                  k, local_blocks, init_blocks, block_size, stride, int(dense_len), _stream(score.device))
     return (mask, idx) if return_topk else mask

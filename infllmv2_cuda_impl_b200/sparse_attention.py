@@ -159,6 +159,9 @@ class SparseAttention:
         bound = cache.capacity if static_shapes else cache.max_len       # >= every sequence length
         max_c = c.windows(bound)
         mask = None
+        # Dense or sparse is decided per sequence on the device (a sequence of at most dense_len
+        # tokens gets every block), so a captured step, which is sized for the capacity, and an
+        # eager one agree; the eager step merely skips the selection when no sequence can need it.
         if bound > c.dense_len and max_c > 0:
             kc_flat = cache.kc.view(-1, hk, HEAD_DIM)
             if cache.kc2 is not None:
@@ -167,12 +170,12 @@ class SparseAttention:
                                              seqused_v=cache.n_comp2)
                 # pool + top-k + packed mask of the few decode rows in one launch
                 mask = ops.decode_select(score, cache.positions, c.topk, cache.capacity, c.local_blocks,
-                                         c.init_blocks, seqused_c=cache.n_comp)
+                                         c.init_blocks, seqused_c=cache.n_comp, dense_len=c.dense_len)
             else:
                 # scores, pool, top-k and mask in two launches; the score rows stay on chip
                 mask = infllmv2_stage1_decode_select(q3, kc_flat, cache.cu_c, cache.positions, max_c,
                                                      cache.capacity, c.topk, c.local_blocks, c.init_blocks,
-                                                     seqused_k=cache.n_comp)
+                                                     seqused_k=cache.n_comp, dense_len=c.dense_len)
         return infllmv2_attn_with_kvcache(q3.view(b, 1, hk * GROUP, HEAD_DIM), cache.k, cache.v,
                                           cache_seqlens=cache.seqlens, softmax_scale=softmax_scale,
                                           block_mask=mask)

@@ -212,6 +212,38 @@ def test_decode_graph_replay_equals_eager_steps():
     assert torch.equal(caches[0].kc, caches[1].kc) and torch.equal(caches[0].k, caches[1].k)
 
 
+@pytest.mark.parametrize("coarse", [False, True])
+def test_decode_graph_equals_eager_with_a_dense_length(coarse):
+    """dense_len > 0 with sequences on both sides of it: the captured step (sized for the capacity)
+    and eager steps give the same outputs, and a sequence of at most dense_len tokens attends every
+    block (its output equals dense attention over its cache)."""
+    lens, cap, steps = [700, 90, 300], 768, 6
+    cfg = _config(topk=3, dense_len=384, coarse_lse=coarse)
+    layer = infllm_v2.SparseAttention(cfg)
+    g = torch.Generator().manual_seed(5)
+    qs = [(torch.randn(l + steps, HQ, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    ks = [(torch.randn(l + steps, HK, D, generator=g) * 0.5).to(torch.bfloat16) for l in lens]
+    vs = [torch.randn(l + steps, HK, D, generator=g).to(torch.bfloat16) for l in lens]
+    pack = lambda ts: torch.cat([t[:l] for t, l in zip(ts, lens)]).to(DEV)
+    caches = [infllm_v2.DecodeCache(len(lens), cap, HK, cfg, DEV) for _ in range(2)]
+    for c in caches:
+        layer.prefill(pack(qs), pack(ks), pack(vs), cu(lens, DEV), max(lens), seqlens=lens, cache=c)
+    step = layer.capture_decode(caches[1])
+    for s in range(steps):
+        qn = torch.stack([q[l + s] for q, l in zip(qs, lens)]).to(DEV)
+        kn = torch.stack([k[l + s] for k, l in zip(ks, lens)]).to(DEV)
+        vn = torch.stack([v[l + s] for v, l in zip(vs, lens)]).to(DEV)
+        eager = layer.decode(qn, kn, vn, caches[0])
+        replayed = step(qn, kn, vn)
+        assert torch.equal(eager, replayed), s
+        # sequences 1 and 2 (91.. and 301.. tokens) are below dense_len: dense attention
+        dense = infllm_v2.infllmv2_attn_with_kvcache(qn.view(len(lens), 1, HQ, D), caches[0].k, caches[0].v,
+                                                     cache_seqlens=caches[0].seqlens)
+        assert torch.equal(eager[1:], dense[1:]), s
+        assert not torch.equal(eager[0], dense[0]), s       # 700+ tokens, 3 of 11+ blocks: sparse
+    infllm_v2.check_device_status()
+
+
 @pytest.mark.parametrize("cap,topk", [(2048, 8), (40000, 64)])
 def test_stage1_decode_select_equals_scores_then_select(cap, topk):
     """The two-launch decode selection (scores stay on chip) against scorer -> decode_select, bit
