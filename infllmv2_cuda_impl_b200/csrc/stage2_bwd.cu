@@ -21,6 +21,7 @@ namespace {
 using namespace tc;
 
 constexpr int kTokPerTile = 8;
+constexpr int kDkvThreads = 384;    // dK / dV kernel: warp 0 TMA, warps 1 and 2 MMA issuers, warp 3 TMEM, warps 4-11 softmax
 constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9: two softmax groups, each takes
                                     // 32 of a block's 64 key columns for all 128 rows (no row reductions
                                     // are needed in the backward, so the halves are independent)
@@ -394,56 +395,105 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
 struct DkvSmem {
   uint8_t k[2][kKVHalfBytes];          // resident K block, [d half]
   uint8_t v[2][kKVHalfBytes];
-  uint8_t q[2][2][kTileHalfBytes];     // [stage][d half]
-  uint8_t dout[2][2][kTileHalfBytes];
-  uint8_t pmat[2][kTileHalfBytes];     // P  (128 rows x 64 keys bf16, 128-byte swizzle), double-buffered:
-  uint8_t dsmat[2][kTileHalfBytes];    // dS  the softmax warps write step i+1 while the products of step i read
-  // dvdk_done[s]: the dV / dK products of a step in ring slot s are complete -> the Q / dO tiles
-  // of the slot may be refilled, the P / dS tiles of the slot may be rewritten, and after the last
-  // step the accumulators are final (one commit per product group)
-  uint64_t kv_full, qdo_full[2], dvdk_done[2], sdp_full[2], sdp_empty[2], pds_ready[2];
+  uint8_t q[3][2][kTileHalfBytes];     // [ring slot][d half]: three Q tiles in flight,
+  uint8_t dout[2][2][kTileHalfBytes];  // two dO tiles
+  uint8_t pmat[kTileHalfBytes];        // P  (128 rows x 64 keys bf16, 128-byte swizzle)
+  uint8_t dsmat[kTileHalfBytes];       // dS
+  // q_full[s]: the Q tile of a step and its record (step_m, step_bits) are in slot s, or, once
+  //   total_steps is set, there is no such step;  do_full[s]: the dO tile;
+  // s_full / dp_full[b]: S (dP) of TMEM buffer b is complete;  sdp_empty[b]: both were read;
+  // p_ready / ds_ready: the softmax warps wrote P (dS);
+  // do_free[s] (two arrivals: after dP and after dV of a step): dO slot s may be refilled and P
+  //   rewritten;  dk_done[s]: the dK product is complete -> dS may be rewritten, Q slot s refilled,
+  //   and after the last step the accumulators are final
+  uint64_t kv_full, q_full[3], do_full[2], s_full[2], dp_full[2], sdp_empty[2], p_ready, ds_ready,
+      do_free[2], dk_done[3];
+  int step_m[3];                       // octet index of the step in Q slot s
+  uint32_t step_bits[3];               // which of its 8 tokens selected the block
+  int total_steps;                     // INT_MAX until the copy warp has reached the end of its walk
   uint32_t tmem_base;
   int abort_flag;
 };
 
 // Walk over the token octets [8m, 8m+8) of a sequence in which at least one token selected the
 // key block (bits of the transposed mask row, indexed by GLOBAL token), lowest octet first.
+// A whole warp walks together: lane l caches words wbase + l and wbase + 32 + l of the row, so a
+// step costs shuffles instead of a round trip to global memory, runs of empty words are skipped
+// with one ballot, and the next 32 words are fetched while the cached ones are in use.
+// Every lane must call next() (the calls are warp-collective) and every lane gets the same answer.
 struct OctetWalk {
   const unsigned long long* row;   // null = dense
-  int64_t words;
-  int q0, lq, m, m_end;
-  __device__ OctetWalk(const unsigned long long* r, int64_t w, int q0_, int lq_, int m_lo)
-      : row(r), words(w), q0(q0_), lq(lq_), m(m_lo), m_end((lq_ + 7) / 8) {}
-  __device__ uint32_t bits_at(int mm) const {      // selection bits of the octet's 8 tokens
-    const int ntok = min(8, lq - 8 * mm);
-    const uint32_t vmask = (1u << ntok) - 1u;
-    if (row == nullptr) return vmask;
-    const int64_t t = (int64_t)q0 + 8 * mm;
-    const int64_t w = t >> 6;
-    const int sh = (int)(t & 63);
-    unsigned long long lo = __ldg(row + w) >> sh;
-    if (sh > 56 && w + 1 < words) lo |= __ldg(row + w + 1) << (64 - sh);
-    return (uint32_t)lo & vmask;
+  int64_t words, wbase;
+  unsigned long long cur, nxt;
+  int q0, lq, m, m_end, lane;
+  __device__ unsigned long long fetch(int64_t w) const {
+    return (row != nullptr && w < words) ? __ldg(row + w) : 0ull;
   }
-  // returns the octet index and its bits, or -1 when exhausted
+  __device__ OctetWalk(const unsigned long long* r, int64_t w, int q0_, int lq_, int m_lo, int lane_)
+      : row(r), words(w), q0(q0_), lq(lq_), m(m_lo), m_end((lq_ + 7) / 8), lane(lane_) {
+    wbase = ((int64_t)q0 + 8 * (int64_t)m_lo) >> 6;
+    cur = fetch(wbase + lane);
+    nxt = fetch(wbase + 32 + lane);
+  }
+  __device__ unsigned long long word(int64_t w) const {   // wbase <= w < wbase + 64
+    const int off = (int)(w - wbase);
+    const unsigned long long a = __shfl_sync(0xFFFFFFFFu, cur, off & 31);
+    const unsigned long long b = __shfl_sync(0xFFFFFFFFu, nxt, off & 31);
+    return off < 32 ? a : b;
+  }
+  // returns the octet index and the selection bits of its 8 tokens, or -1 when exhausted
   __device__ int next(uint32_t& bits) {
     while (m < m_end) {
-      if (row != nullptr) {
-        const int64_t t = (int64_t)q0 + 8 * m;
-        if ((t & 63) == 0 && m + 8 <= m_end && __ldg(row + (t >> 6)) == 0ull) {   // empty word
-          m += 8;
-          continue;
-        }
+      const int ntok = min(8, lq - 8 * m);
+      const uint32_t vmask = (1u << ntok) - 1u;
+      if (row == nullptr) {
+        bits = vmask;
+        return m++;
       }
-      bits = bits_at(m);
-      const int cur = m++;
-      if (bits) return cur;
+      const int64_t t = (int64_t)q0 + 8 * (int64_t)m;
+      const int64_t w = t >> 6;
+      const int sh = (int)(t & 63);
+      while (w >= wbase + 32) {
+        cur = nxt;
+        wbase += 32;
+        nxt = fetch(wbase + 32 + lane);
+      }
+      const unsigned long long here = word(w) >> sh;
+      unsigned long long lo = here;
+      if (sh > 56) lo |= word(w + 1) << (64 - sh);
+      bits = (uint32_t)lo & vmask;
+      if (bits) return m++;
+      if (here != 0ull) {          // later tokens of this word selected the block
+        ++m;
+        continue;
+      }
+      // nothing left in word w: go to the first cached word after it that has a bit
+      const int off = (int)(w - wbase);
+      const uint32_t ne_cur = __ballot_sync(0xFFFFFFFFu, cur != 0ull);
+      const uint32_t ne_nxt = __ballot_sync(0xFFFFFFFFu, nxt != 0ull);
+      const uint32_t later = off < 31 ? (ne_cur & (0xFFFFFFFFu << (off + 1))) : 0u;
+      int64_t wn;
+      if (later) wn = wbase + __ffs(later) - 1;
+      else if (ne_nxt) wn = wbase + 32 + __ffs(ne_nxt) - 1;
+      else wn = wbase + 64;
+      // the first octet with a token in word wn (it may begin in the word before, which is empty)
+      const int64_t mn = (wn * 64 - (int64_t)q0) >> 3;
+      m = (int)max((int64_t)m + 1, min(mn, (int64_t)m_end));
     }
     return -1;
   }
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+// One step = one token octet that selected the block: S = Q K^T and dP = dO V^T into TMEM, the
+// softmax warps turn S into P = exp2(S * scale - lse) and dP into dS = P * (dP - D), both stored
+// to shared memory as bf16, then dV^T += dO^T P and dK^T += Q^T dS.
+// Roles: the copy warp is the only one that walks the mask row; it leaves each step's octet index
+// and selection bits beside the Q tile (and the step count at the end of the walk), so the other
+// warps learn them from the tile's barrier.  Two warps issue the products, one S and dP, the other
+// dV and dK: each waits, issues and commits on its own, so neither one's barrier round trips hold
+// up the other's instructions, and the S / dP warp runs up to two steps ahead (two TMEM buffers).
+// Q has three ring slots and dO two.
+__global__ void __launch_bounds__(kDkvThreads, 1)
 sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
                            const __grid_constant__ CUtensorMap map_do,
                            const __grid_constant__ CUtensorMap map_k,
@@ -452,7 +502,8 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
   DkvSmem& sm = *reinterpret_cast<DkvSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                             ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x, b = blockIdx.y, h = blockIdx.z;   // block 0 (selected by all) first
+  // block index slowest: the blocks every token selects (block 0 of each sequence) start first
+  const int b = blockIdx.x, h = blockIdx.y, n = blockIdx.z;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
   if (n * kBlockN >= lk) return;
@@ -468,18 +519,24 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    sm.total_steps = never_selected ? 0 : INT_MAX;
     mbar_init(&sm.kv_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&sm.q_full[s], 1);
+      mbar_init(&sm.dk_done[s], 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&sm.qdo_full[s], 1);
-      mbar_init(&sm.dvdk_done[s], 1);
-      mbar_init(&sm.sdp_full[s], 1);
+      mbar_init(&sm.do_full[s], 1);
+      mbar_init(&sm.do_free[s], 2);
+      mbar_init(&sm.s_full[s], 1);
+      mbar_init(&sm.dp_full[s], 1);
       mbar_init(&sm.sdp_empty[s], 8);
     }
-    mbar_init(&sm.pds_ready[0], 8);
-    mbar_init(&sm.pds_ready[1], 8);
+    mbar_init(&sm.p_ready, 8);
+    mbar_init(&sm.ds_ready, 8);
     fence_barrier_init();
   }
-  if (warp == 1) {
+  if (warp == 3) {
     tmem_alloc(&sm.tmem_base, 512);
     tmem_relinquish();
   }
@@ -489,134 +546,165 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
   const uint32_t tmem = __shfl_sync(0xFFFFFFFFu, sm.tmem_base, 0);   // warp-uniform for the compiler
   const uint32_t tmem_dv = tmem + 256, tmem_dk = tmem + 320;   // [128 d lanes x 64 key columns]
   volatile int* abort_flag = &sm.abort_flag;
+  volatile int* total_steps = &sm.total_steps;
 
-  // every role walks the same octet list; the count is not known up front, so the walk itself
-  // tells each role when to stop
+  // Step i uses Q slot i % 3, dO slot i & 1, TMEM buffer i & 1.
   if (warp == 0) {
-    if (lane == 0 && !never_selected) {
-      mbar_expect_tx(&sm.kv_full, 4 * kKVHalfBytes);
-      tma_load_3d(sm.k[0], &map_k, &sm.kv_full, 0, h, k0 + n * kBlockN);
-      tma_load_3d(sm.k[1], &map_k, &sm.kv_full, 64, h, k0 + n * kBlockN);
-      tma_load_3d(sm.v[0], &map_v, &sm.kv_full, 0, h, k0 + n * kBlockN);
-      tma_load_3d(sm.v[1], &map_v, &sm.kv_full, 64, h, k0 + n * kBlockN);
-      OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
+    // the whole warp walks the octet list; lane 0 waits for ring slots and issues the copies
+    if (!never_selected) {
+      if (lane == 0) {
+        mbar_expect_tx(&sm.kv_full, 4 * kKVHalfBytes);
+        tma_load_3d(sm.k[0], &map_k, &sm.kv_full, 0, h, k0 + n * kBlockN);
+        tma_load_3d(sm.k[1], &map_k, &sm.kv_full, 64, h, k0 + n * kBlockN);
+        tma_load_3d(sm.v[0], &map_v, &sm.kv_full, 0, h, k0 + n * kBlockN);
+        tma_load_3d(sm.v[1], &map_v, &sm.kv_full, 64, h, k0 + n * kBlockN);
+      }
+      OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo, lane);
       uint32_t bits;
-      int issued = 0;
+      int issued_q = 0, issued_do = 0;
+      int qs = 0, qround = 0;                      // i % 3, i / 3
       for (int i = 0;; ++i) {
         const int m = walk.next(bits);
-        if (m < 0) break;
-        const int s = i & 1;
-        if (i >= 2 && !mbar_wait(&sm.dvdk_done[s], (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag,
-                                 p.status, 81))
-          break;
-        mbar_expect_tx(&sm.qdo_full[s], 4 * kTileHalfBytes);
+        const int ds = i & 1;
         const int tok = q0 + m * kTokPerTile;
-        tma_load_3d(sm.q[s][0], &map_q, &sm.qdo_full[s], 0, h * kGroup, tok);
-        tma_load_3d(sm.q[s][1], &map_q, &sm.qdo_full[s], 64, h * kGroup, tok);
-        tma_load_3d(sm.dout[s][0], &map_do, &sm.qdo_full[s], 0, h * kGroup, tok);
-        tma_load_3d(sm.dout[s][1], &map_do, &sm.qdo_full[s], 64, h * kGroup, tok);
-        issued = i + 1;
+        bool ok = true;
+        if (lane == 0) {
+          if (i >= 3) ok = mbar_wait(&sm.dk_done[qs], (uint32_t)((qround & 1) ^ 1), abort_flag, p.status, 81);
+          if (ok && m < 0) {
+            // end of the walk: the slot's barrier completes without a tile and the count says why
+            *total_steps = i;
+            mbar_arrive(&sm.q_full[qs]);
+          } else if (ok) {
+            sm.step_m[qs] = m;
+            sm.step_bits[qs] = bits;
+            mbar_expect_tx(&sm.q_full[qs], 2 * kTileHalfBytes);
+            tma_load_3d(sm.q[qs][0], &map_q, &sm.q_full[qs], 0, h * kGroup, tok);
+            tma_load_3d(sm.q[qs][1], &map_q, &sm.q_full[qs], 64, h * kGroup, tok);
+            issued_q = i + 1;
+            if (i >= 2) ok = mbar_wait(&sm.do_free[ds], (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag, p.status, 89);
+            if (ok) {
+              mbar_expect_tx(&sm.do_full[ds], 2 * kTileHalfBytes);
+              tma_load_3d(sm.dout[ds][0], &map_do, &sm.do_full[ds], 0, h * kGroup, tok);
+              tma_load_3d(sm.dout[ds][1], &map_do, &sm.do_full[ds], 64, h * kGroup, tok);
+              issued_do = i + 1;
+            }
+          }
+        }
+        if (m < 0 || !__shfl_sync(0xFFFFFFFFu, ok, 0)) break;
+        if (++qs == 3) { qs = 0; ++qround; }
       }
-      if (*abort_flag) {
+      if (lane == 0 && *abort_flag) {
         mbar_wait_drain(&sm.kv_full, 0);
-        for (int j = max(0, issued - 2); j < issued; ++j)
-          mbar_wait_drain(&sm.qdo_full[j & 1], (uint32_t)((j >> 1) & 1));
+        for (int j = max(0, issued_q - 3); j < issued_q; ++j)
+          mbar_wait_drain(&sm.q_full[j % 3], (uint32_t)((j / 3) & 1));
+        for (int j = max(0, issued_do - 2); j < issued_do; ++j)
+          mbar_wait_drain(&sm.do_full[j & 1], (uint32_t)((j >> 1) & 1));
       }
     }
   } else if (warp == 1) {
-    // All 32 lanes run the same issue code (descriptors stay in uniform registers); `leader`
-    // enables the MMA / commit instructions in one lane only.
+    // S and dP.  All 32 lanes run the same issue code (descriptors stay in uniform registers);
+    // `leader` enables the MMA / commit instructions in one lane only.
     if (!never_selected) {
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);             // K-major x K-major
-      constexpr uint32_t idesc_t = umma_idesc_bf16(128, 64, true, true);        // MN-major x MN-major
       const uint64_t k_desc = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024);
       const uint64_t v_desc = umma_desc_sw128(smem_u32(sm.v[0]), 16, 1024);
-      const uint64_t p_desc0 = umma_desc_sw128(smem_u32(sm.pmat[0]), 16, 1024);
-      const uint64_t ds_desc0 = umma_desc_sw128(smem_u32(sm.dsmat[0]), 16, 1024);
-      constexpr uint32_t kPds = kTileHalfBytes >> 4;            // descriptor address units per P / dS buffer
-      // ring stage s = stage 0 + s * kRing (plain arithmetic keeps the descriptors in registers)
+      // ring slot s = slot 0 + s * kRing (plain arithmetic keeps the descriptors in registers)
       const uint64_t q_desc0 = umma_desc_sw128(smem_u32(sm.q[0][0]), 16, 1024);
       const uint64_t do_desc0 = umma_desc_sw128(smem_u32(sm.dout[0][0]), 16, 1024);
+      constexpr uint32_t kRing = (2 * kTileHalfBytes) >> 4;
+      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 82));
+      int qs = 0, qround = 0;
+      for (int j = 0; ok; ++j) {
+        const int bf = j & 1;
+        const uint32_t par = (uint32_t)((j >> 1) & 1);
+        bool w = mbar_wait(&sm.q_full[qs], (uint32_t)(qround & 1), abort_flag, p.status, 83);
+        if (!__all_sync(0xFFFFFFFFu, w)) break;
+        if (j >= *total_steps) break;
+        if (j >= 2) w = mbar_wait(&sm.sdp_empty[bf], par ^ 1u, abort_flag, p.status, 84);
+        if (!__all_sync(0xFFFFFFFFu, w)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
+          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
+          umma_ss_pred(tmem + bf * 128, q_desc0 + qs * kRing + aoff, k_desc + boff, idesc_s, kk > 0, leader);
+        }
+        umma_commit_pred(&sm.s_full[bf], leader);
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.do_full[bf], par, abort_flag, p.status, 90))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
+          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
+          umma_ss_pred(tmem + bf * 128 + 64, do_desc0 + bf * kRing + aoff, v_desc + boff, idesc_s, kk > 0, leader);
+        }
+        umma_commit_pred(&sm.dp_full[bf], leader);
+        umma_commit_pred(&sm.do_free[bf], leader);       // first of the two arrivals that release the dO slot
+        if (++qs == 3) { qs = 0; ++qround; }
+      }
+    }
+  } else if (warp == 2) {
+    // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
+    if (!never_selected) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      constexpr uint32_t idesc_t = umma_idesc_bf16(128, 64, true, true);        // MN-major x MN-major
+      const uint64_t p_desc = umma_desc_sw128(smem_u32(sm.pmat), 16, 1024);
+      const uint64_t ds_desc = umma_desc_sw128(smem_u32(sm.dsmat), 16, 1024);
       const uint64_t q_mn0 = umma_desc_sw128(smem_u32(sm.q[0][0]), kTileHalfBytes, 1024);
       const uint64_t do_mn0 = umma_desc_sw128(smem_u32(sm.dout[0][0]), kTileHalfBytes, 1024);
       constexpr uint32_t kRing = (2 * kTileHalfBytes) >> 4;
-      OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
-      uint32_t bits;
-      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 82));
-      int have = __shfl_sync(0xFFFFFFFFu, ok ? walk.next(bits) : -1, 0);      // octet of step 0
-      auto issue_sdp = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t par = (uint32_t)((j >> 1) & 1);
-        bool w = mbar_wait(&sm.qdo_full[s], par, abort_flag, p.status, 83);
-        if (w && j >= 2) w = mbar_wait(&sm.sdp_empty[s], par ^ 1u, abort_flag, p.status, 84);
-        if (!__all_sync(0xFFFFFFFFu, w)) return false;
+      int qs = 0, qround = 0;
+      for (int i = 0;; ++i) {
+        const int ds = i & 1;
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full[qs], (uint32_t)(qround & 1), abort_flag, p.status, 94)))
+          break;
+        if (i >= *total_steps) break;
+        // P of step i follows S of step i, which followed the dO tile's arrival only in program
+        // order of the other warp: wait for the tile here too
+        bool w = mbar_wait(&sm.do_full[ds], (uint32_t)((i >> 1) & 1), abort_flag, p.status, 95);
+        if (w) w = mbar_wait(&sm.p_ready, (uint32_t)(i & 1), abort_flag, p.status, 85);
+        if (!__all_sync(0xFFFFFFFFu, w)) break;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
-          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
-          umma_ss_pred(tmem + s * 128, q_desc0 + s * kRing + aoff, k_desc + boff, idesc_s, kk > 0, leader);
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = ((kk >> 2) * kTileHalfBytes + (kk & 3) * 32) >> 4;
-          const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
-          umma_ss_pred(tmem + s * 128 + 64, do_desc0 + s * kRing + aoff, v_desc + boff, idesc_s, kk > 0, leader);
-        }
-        umma_commit_pred(&sm.sdp_full[s], leader);
-        return true;
-      };
-      // dV^T (128 d x 64 keys) += dO^T . P ; dK^T += Q^T . dS ; K extent = the 128 tile rows
-      auto issue_dvdk = [&](int i) -> bool {
-        const int s = i & 1;
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.pds_ready[s], (uint32_t)((i >> 1) & 1), abort_flag, p.status, 85)))
-          return false;
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss_pred(tmem_dv, do_mn0 + ds * kRing + ((kk * 2048) >> 4), p_desc + ((kk * 2048) >> 4), idesc_t,
+                       (i > 0) || (kk > 0), leader);
+        umma_commit_pred(&sm.do_free[ds], leader);       // second arrival: dO slot and P are free
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.ds_ready, (uint32_t)(i & 1), abort_flag, p.status, 91))) break;
         tc_fence_after();
-        const uint64_t p_desc = p_desc0 + (uint32_t)s * kPds, ds_desc = ds_desc0 + (uint32_t)s * kPds;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss_pred(tmem_dv, do_mn0 + s * kRing + ((kk * 2048) >> 4), p_desc + ((kk * 2048) >> 4), idesc_t,
+          umma_ss_pred(tmem_dk, q_mn0 + qs * kRing + ((kk * 2048) >> 4), ds_desc + ((kk * 2048) >> 4), idesc_t,
                        (i > 0) || (kk > 0), leader);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss_pred(tmem_dk, q_mn0 + s * kRing + ((kk * 2048) >> 4), ds_desc + ((kk * 2048) >> 4), idesc_t,
-                       (i > 0) || (kk > 0), leader);
-        umma_commit_pred(&sm.dvdk_done[s], leader);
-        return true;
-      };
-      // dV / dK of a step go first, then S / dP of the next one: the Q / dO slot is released one
-      // product group earlier, which gives the copy of the tile two steps ahead most of a step to
-      // land.  What bounds the kernel is that copy: 64 KB of Q / dO per step and SM through L2 with
-      // two slots (shared memory has no room for a third), about 4.3 TB/s over the 148 SMs;
-      // issuing S / dP first, or double-buffering P / dS so that the softmax warps never wait for
-      // the products, changes the step time by less than 3 %.
-      int i = 0;
-      if (have >= 0) ok = issue_sdp(0);
-      while (ok && have >= 0) {
-        const int next = __shfl_sync(0xFFFFFFFFu, walk.next(bits), 0);   // (uniform for the compiler)
-        ok = issue_dvdk(i);
-        if (ok && next >= 0) ok = issue_sdp(i + 1);
-        have = next;
-        ++i;
+        umma_commit_pred(&sm.dk_done[qs], leader);
+        if (++qs == 3) { qs = 0; ++qround; }
       }
     }
-  } else {
+  } else if (warp >= 4) {
     const int quad = warp & 3;
-    const int grp = (warp - 2) >> 2;                 // softmax warp group: which 32 key columns
+    const int grp = (warp - 4) >> 2;                 // which 32 key columns
     const int r = quad * 32 + lane;
     const int tl = r >> 4, g = r & 15;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    OctetWalk walk(mask_row, p.bwd_words, q0, lq, m_lo);
-    uint32_t bits;
     bool ok = true;
     int steps = 0;
+    int qs = 0, qround = 0;                          // i % 3, i / 3
+    int pqs = 0, pround = 0;                         // (i - 1) % 3, (i - 1) / 3 (valid for i >= 1)
+    // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk (c ^ (r & 7))
+    uint8_t* prow = sm.pmat + r * 128;
+    uint8_t* drow = sm.dsmat + r * 128;
     if (!never_selected) {
       for (int i = 0;; ++i) {
-        const int m = walk.next(bits);
-        if (m < 0) break;
+        // the step's record arrives with its Q tile, well before its S
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full[qs], (uint32_t)(qround & 1), abort_flag, p.status, 96));
+        if (!ok) break;
+        if (i >= *total_steps) break;
         steps = i + 1;
-        const int s = i & 1;
+        const int m = sm.step_m[qs];
+        const uint32_t bits = sm.step_bits[qs];
+        const int bf = i & 1;
+        const uint32_t par = (uint32_t)((i >> 1) & 1);
         const int tok = m * kTokPerTile + tl;                     // local token of this row
         const bool selected = (bits >> tl) & 1u;
         const int64_t stat_idx = (int64_t)h * p.total_q * kGroup + (int64_t)(q0 + tok) * kGroup + g;
@@ -624,55 +712,76 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         const float dsum = selected ? __ldg(p.dvec + stat_idx) : 0.f;
         // keys of this block the row may see
         const int row_limit = selected ? min(lk, p.causal ? tok + shift + 1 : lk) : 0;
-        const int lim = min(max(row_limit - n * kBlockN, 0), kBlockN);
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.sdp_full[s], (uint32_t)((i >> 1) & 1),
-                                               abort_flag, p.status, 86));
+        const int lim = min(max(row_limit - n * kBlockN, 0), kBlockN) - grp * 32;   // within this group's columns
+        // ---- P = exp2(S * scale - lse), needs S only
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[bf], par, abort_flag, p.status, 86));
         if (!ok) break;
         tc_fence_after();
-        uint32_t pp[16], dd[16];
+        uint32_t x[32];                               // P of this thread's 32 columns, fp32 bits
         {
-          const int half = grp;                        // this warp group's 32 key columns
-          uint32_t sv[32], dpv[32];
-          tmem_ld32x2_wait(tmem + lane_off + s * 128 + half * 32, sv, tmem + lane_off + s * 128 + 64 + half * 32, dpv);
+          uint32_t pp[16];
+          tmem_ld32(tmem + lane_off + bf * 128 + grp * 32, x);
+          tmem_wait_ld_dep(x);
           const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_lse, neg_lse);
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float y0, y1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(x[c], x[c + 1]), c2, n2), y0, y1);
+            const float x0 = c < lim ? exp2f(y0) : 0.f, x1 = c + 1 < lim ? exp2f(y1) : 0.f;
+            x[c] = __float_as_uint(x0);
+            x[c + 1] = __float_as_uint(x1);
+            pp[c >> 1] = pack_bf16(x0, x1);
+          }
+          // the dV product of the step before must have read P before it is rewritten
+          if (i >= 1) {
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.do_free[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1),
+                                                   abort_flag, p.status, 87));
+            if (!ok) break;
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)                  // this group's four 16-byte chunks of the row
+            *reinterpret_cast<uint4*>(prow + (((grp * 4 + c) ^ (r & 7)) << 4)) =
+                make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+          fence_proxy_async_smem();
+          mbar_arrive_warp(&sm.p_ready);
+        }
+        // ---- dS = P * (dP - D)
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dp_full[bf], par, abort_flag, p.status, 92));
+        if (!ok) break;
+        tc_fence_after();
+        {
+          uint32_t dpv[32], dd[16];
+          tmem_ld32(tmem + lane_off + bf * 128 + 64 + grp * 32, dpv);
+          tmem_wait_ld_dep(dpv);
+          tc_fence_before();
+          mbar_arrive_warp(&sm.sdp_empty[bf]);               // S / dP of this buffer may be overwritten
           const uint64_t md2 = pack_f32x2(-dsum, -dsum);
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
-            float y0, y1, d0, d1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(sv[c], sv[c + 1]), c2, n2), y0, y1);
-            const float x0 = exp2f(y0), x1 = exp2f(y1);
-            unpack_f32x2(mul_f32x2(pack_f32x2(x0, x1), add_f32x2(pack_f32x2(dpv[c], dpv[c + 1]), md2)), d0, d1);
-            const bool v0 = half * 32 + c < lim, v1 = half * 32 + c + 1 < lim;
-            pp[c >> 1] = pack_bf16(v0 ? x0 : 0.f, v1 ? x1 : 0.f);
-            dd[c >> 1] = pack_bf16(v0 ? d0 : 0.f, v1 ? d1 : 0.f);
+            float d0, d1;
+            unpack_f32x2(mul_f32x2(pack_f32x2(x[c], x[c + 1]), add_f32x2(pack_f32x2(dpv[c], dpv[c + 1]), md2)), d0, d1);
+            dd[c >> 1] = pack_bf16(d0, d1);
           }
-        }
-        tc_fence_before();
-        mbar_arrive_warp(&sm.sdp_empty[s]);                  // S / dP of this buffer may be overwritten
-        // the products of step i - 2 must have consumed this slot's P and dS before they are rewritten
-        if (i >= 2) {
-          ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dvdk_done[s], (uint32_t)(((i >> 1) & 1) ^ 1),
-                                                 abort_flag, p.status, 87));
-          if (!ok) break;
-        }
-        // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk (c ^ (r & 7))
-        uint8_t* prow = sm.pmat[s] + r * 128;
-        uint8_t* drow = sm.dsmat[s] + r * 128;
+          // the dK product of the step before must have read dS before it is rewritten
+          if (i >= 1) {
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dk_done[pqs], (uint32_t)(pround & 1), abort_flag, p.status, 93));
+            if (!ok) break;
+          }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {                  // this group's four 16-byte chunks of the row
-          const int pc = ((grp * 4 + c) ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(prow + pc) =
-              make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
-          *reinterpret_cast<uint4*>(drow + pc) =
-              make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(drow + (((grp * 4 + c) ^ (r & 7)) << 4)) =
+                make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+          fence_proxy_async_smem();
+          mbar_arrive_warp(&sm.ds_ready);
         }
-        fence_proxy_async_smem();
-        mbar_arrive_warp(&sm.pds_ready[s]);
+        pqs = qs;
+        pround = qround;
+        if (++qs == 3) { qs = 0; ++qround; }
       }
     }
     if (ok && steps > 0) {
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dvdk_done[(steps - 1) & 1],
-                                             (uint32_t)(((steps - 1) >> 1) & 1), abort_flag, p.status, 88));
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dk_done[(steps - 1) % 3],
+                                             (uint32_t)(((steps - 1) / 3) & 1), abort_flag, p.status, 88));
       tc_fence_after();
     }
     if (ok) {
@@ -685,9 +794,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         const int c0 = grp * 32;
         uint32_t a[32], bb[32];
         if (steps > 0) {
-          tmem_ld32(tmem_dv + lane_off + c0, a);
-          tmem_ld32(tmem_dk + lane_off + c0, bb);
-          tmem_wait_ld();
+          tmem_ld32x2_wait(tmem_dv + lane_off + c0, a, tmem_dk + lane_off + c0, bb);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) { a[j] = 0u; bb[j] = 0u; }
@@ -705,7 +812,7 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
+  if (warp == 3) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace
@@ -827,8 +934,8 @@ extern "C" int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void*
     cudaError_t e = cudaFuncSetAttribute(sparse_attn_bwd_dkv_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error((int)e, "sparse_attn_bwd: %s", cudaGetErrorString(e));
-    dim3 grid(k_blocks, batch, heads_k);
-    sparse_attn_bwd_dkv_kernel<<<grid, kThreads, smem, st>>>(map_q, map_do, map_k, map_v, p);
+    dim3 grid(batch, heads_k, k_blocks);
+    sparse_attn_bwd_dkv_kernel<<<grid, kDkvThreads, smem, st>>>(map_q, map_do, map_k, map_v, p);
     rc = check_launch("sparse_attn_bwd_dkv");
     if (rc) return rc;
   }
