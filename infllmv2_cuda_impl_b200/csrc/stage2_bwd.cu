@@ -21,7 +21,9 @@ namespace {
 using namespace tc;
 
 constexpr int kTokPerTile = 8;
-constexpr int kDkvThreads = 384;    // dK / dV kernel: warp 0 TMA, warps 1 and 2 MMA issuers, warp 3 TMEM, warps 4-11 softmax
+constexpr int kDkvThreads = 640;    // dK / dV kernel: warp 0 TMA, warps 1 and 2 MMA issuers, warp 3 TMEM,
+                                    // warps 4-11 softmax of the even steps, 12-19 of the odd ones
+constexpr int kDqThreads = 640;     // dQ kernel: same roles as the dK / dV kernel
 constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9: two softmax groups, each takes
                                     // 32 of a block's 64 key columns for all 128 rows (no row reductions
                                     // are needed in the backward, so the halves are independent)
@@ -107,17 +109,21 @@ struct DqSmem {
   uint8_t k[3][2][kKVHalfBytes];      // [stage][d half]; K lives until dS.K of its block is done,
   uint8_t v[2][2][kKVHalfBytes];      // so it needs one more stage than V to be prefetched in time
   unsigned long long umask[kMaxMaskWords];
-  // One commit per product group (a tcgen05.commit costs the issuing warp about as much as two
-  // MMAs): sdp_full[s] also releases the V tile of slot s, dq_done[k] releases the K tile of ring
-  // slot k and, for the last block, tells the epilogue that dQ is complete.
-  uint64_t qdo_full, k_full[3], dq_done[3], v_full[2], sdp_full[2], ds_ready[2];
+  // s_full[s] / dp_full[s]: S (dP) of TMEM buffer s is complete; dp_full also releases the V tile of
+  // slot s; dq_done[k] releases the K tile of ring slot k and the TMEM buffer of that step and,
+  // for the last block, tells the epilogue that dQ is complete.
+  uint64_t qdo_full, k_full[3], dq_done[3], v_full[2], s_full[2], dp_full[2], ds_ready[2];
   uint64_t qdo_tmem;   // 8 arrivals: Q and dO have been copied from shared memory into TMEM
   uint32_t tmem_base;
   int n_blocks;
   int abort_flag;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+// Roles: warp 0 copies, warp 1 issues S = Q K^T and dP = dO V^T (A operands from TMEM), warp 2 issues
+// dQ += dS K, warp 3 owns the TMEM allocation, warps 4-11 do the softmax work of the even steps and
+// 12-19 of the odd ones (each turn has the TMEM buffer of its parity).  A step's P is computed as
+// soon as its S is there, while its dP product runs.
+__global__ void __launch_bounds__(kDqThreads, 1)
 sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
                           const __grid_constant__ CUtensorMap map_do,
                           const __grid_constant__ CUtensorMap map_k,
@@ -141,7 +147,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
     int last_blk = nblk_k - 1;
     if (p.causal) last_blk = min(last_blk, (tok0 + ntok - 1 + shift) >= 0
                                                ? (tok0 + ntok - 1 + shift) / kBlockN : -1);
-    for (int w = threadIdx.x; w < words; w += kThreads) {
+    for (int w = threadIdx.x; w < words; w += kDqThreads) {
       unsigned long long u = 0ull;
       if (p.fwd_mask != nullptr) {
         const unsigned long long* row =
@@ -165,13 +171,14 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.v_full[s], 1);
-      mbar_init(&sm.sdp_full[s], 1);
-      mbar_init(&sm.ds_ready[s], 8);         // one arrival per softmax warp
+      mbar_init(&sm.s_full[s], 1);
+      mbar_init(&sm.dp_full[s], 1);
+      mbar_init(&sm.ds_ready[s], 8);         // one arrival per softmax warp of the buffer's turn
     }
     mbar_init(&sm.qdo_tmem, 8);
     fence_barrier_init();
   }
-  if (warp == 1) {
+  if (warp == 3) {
     tmem_alloc(&sm.tmem_base, 512);
     tmem_relinquish();
   }
@@ -210,7 +217,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
         mbar_expect_tx(&sm.k_full[sk], 2 * kKVHalfBytes);
         tma_load_3d(sm.k[sk][0], &map_k, &sm.k_full[sk], 0, h, key);
         tma_load_3d(sm.k[sk][1], &map_k, &sm.k_full[sk], 64, h, key);
-        if (i >= 2 && !mbar_wait(&sm.sdp_full[s], par ^ 1u, abort_flag, p.status, 72)) {
+        if (i >= 2 && !mbar_wait(&sm.dp_full[s], par ^ 1u, abort_flag, p.status, 72)) {
           issued = i + 1;
           break;
         }
@@ -228,27 +235,27 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else if (warp == 1) {
-    // All 32 lanes run the same issue code (descriptors stay in uniform registers); `leader`
-    // enables the MMA / commit instructions in one lane only.
+    // S and dP.  All 32 lanes run the same issue code (descriptors stay in uniform registers);
+    // `leader` enables the MMA / commit instructions in one lane only.
     if (n_blocks > 0) {
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);
-      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, true);
       const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024);
-      const uint64_t k_desc0_mn = umma_desc_sw128(smem_u32(sm.k[0][0]), kKVHalfBytes, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sm.v[0][0]), 16, 1024);
       constexpr uint32_t kStage = (2 * kKVHalfBytes) >> 4;     // descriptor address units per ring stage
       // Q and dO are A operands read from TMEM: the Q.K^T and dO.V^T products then fetch only
       // their 2 KB key tiles from shared memory per step instead of 6 KB
       bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_tmem, 0, abort_flag, p.status, 73));
       tc_fence_after();
-      auto issue_sdp = [&](int j) -> bool {
-        const int s = j & 1, sk = j % 3;
+      int sk = 0, kround = 0;                       // j % 3, j / 3
+      int sk2 = 1, kround2 = -1;                    // (j - 2) % 3, (j - 2) / 3 (used from j = 2 on)
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int s = j & 1;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
-        if (!__all_sync(0xFFFFFFFFu,
-                        mbar_wait(&sm.k_full[sk], (uint32_t)((j / 3) & 1), abort_flag, p.status, 74) &&
-                            mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75)))
-          return false;
+        bool w = mbar_wait(&sm.k_full[sk], (uint32_t)(kround & 1), abort_flag, p.status, 74);
+        // the buffer's last user: dQ of step j - 2 read dS from it
+        if (w && j >= 2) w = mbar_wait(&sm.dq_done[sk2], (uint32_t)(kround2 & 1), abort_flag, p.status, 80);
+        if (!__all_sync(0xFFFFFFFFu, w)) break;
         tc_fence_after();
         const uint64_t k_desc = k_desc0 + (uint32_t)sk * kStage, v_desc = v_desc0 + (uint32_t)s * kStage;
 #pragma unroll
@@ -256,34 +263,46 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
           const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
           umma_ts_pred(tmem + s * 128, tmem_q + kk * 8, k_desc + boff, idesc_s, kk > 0, leader);
         }
+        umma_commit_pred(&sm.s_full[s], leader);
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75))) break;
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
           umma_ts_pred(tmem + s * 128 + 64, tmem_do + kk * 8, v_desc + boff, idesc_s, kk > 0, leader);
         }
-        umma_commit_pred(&sm.sdp_full[s], leader);
-        return true;
-      };
-      if (ok) ok = issue_sdp(0);
-      for (int i = 0; i < n_blocks && ok; ++i) {
-        const int s = i & 1;
-        if (i + 1 < n_blocks) ok = issue_sdp(i + 1);
-        if (!ok) break;
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.ds_ready[s], (uint32_t)((i >> 1) & 1), abort_flag,
-                                               p.status, 76));
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t k_mn = k_desc0_mn + (uint32_t)(i % 3) * kStage;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ts_pred(tmem_dq, tmem + s * 128 + kk * 8, k_mn + ((kk * 2048) >> 4), idesc_dq,
-                       (i > 0) || (kk > 0), leader);
-        umma_commit_pred(&sm.dq_done[i % 3], leader);
+        umma_commit_pred(&sm.dp_full[s], leader);
+        if (++sk == 3) { sk = 0; ++kround; }
+        if (++sk2 == 3) { sk2 = 0; ++kround2; }
       }
     }
-  } else {
+  } else if (warp == 2) {
+    // dQ += dS K (dS as bf16 pairs in the step's TMEM buffer, K read along the keys)
+    if (n_blocks > 0) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, true);
+      const uint64_t k_desc0_mn = umma_desc_sw128(smem_u32(sm.k[0][0]), kKVHalfBytes, 1024);
+      constexpr uint32_t kStage = (2 * kKVHalfBytes) >> 4;
+      int sk = 0, kround = 0;
+      for (int i = 0; i < n_blocks; ++i) {
+        const int s = i & 1;
+        bool w = mbar_wait(&sm.k_full[sk], (uint32_t)(kround & 1), abort_flag, p.status, 70);
+        if (w) w = mbar_wait(&sm.ds_ready[s], (uint32_t)((i >> 1) & 1), abort_flag, p.status, 76);
+        if (!__all_sync(0xFFFFFFFFu, w)) break;
+        tc_fence_after();
+        const uint64_t k_mn = k_desc0_mn + (uint32_t)sk * kStage;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)      // dS of keys 0-31 sits at columns [0, 16), of keys 32-63 at [32, 48)
+          umma_ts_pred(tmem_dq, tmem + s * 128 + (kk >> 1) * 32 + (kk & 1) * 8, k_mn + ((kk * 2048) >> 4), idesc_dq,
+                       (i > 0) || (kk > 0), leader);
+        umma_commit_pred(&sm.dq_done[sk], leader);
+        if (++sk == 3) { sk = 0; ++kround; }
+      }
+    }
+  } else if (warp >= 4) {
     const int quad = warp & 3;
-    const int grp = (warp - 2) >> 2;                 // softmax warp group: which 32 key columns
+    const int turn = (warp - 4) >> 3;                // this warp takes the steps with i & 1 == turn
+    const int grp = ((warp - 4) & 7) >> 2;           // which 32 key columns
     const int r = quad * 32 + lane;
     const int tl = r >> 4, g = r & 15;
     const int tok = tok0 + tl;
@@ -297,8 +316,9 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
     const float neg_lse = valid ? -p.lse[stat_idx] * kLog2e : -INFINITY;   // +inf lse -> P = 0
     const float dsum = valid ? p.dvec[stat_idx] : 0.f;
     bool ok = true;
-    if (n_blocks > 0) {
-      // group 0 moves this thread's Q row, group 1 its dO row, from the swizzled tiles into TMEM
+    if (n_blocks > 0 && turn == 0) {
+      // the warps of the first turn move Q and dO into TMEM: column group 0 this thread's Q row,
+      // group 1 its dO row, from the swizzled tiles
       // (row r of a d half: 16-byte chunk c sits at chunk c ^ (r & 7); TMEM column j = d 2j, 2j+1)
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 79));
       if (ok) {
@@ -321,37 +341,58 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
     BlockWalk walk(sm.umask, words);
-    for (int i = 0; i < n_blocks && ok; ++i) {
+    if (turn == 1 && n_blocks > 0) walk.next();
+    for (int i = turn; i < n_blocks && ok; i += 2) {
       const int blk = walk.next();
+      walk.next();                                   // the other turn's block
       const int s = i & 1;
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.sdp_full[s], (uint32_t)((i >> 1) & 1),
-                                             abort_flag, p.status, 77));
-      if (!ok) break;
-      tc_fence_after();
+      const uint32_t par = (uint32_t)((i >> 1) & 1);
       bool selected = valid;
       if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
-      const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
+      const int lim = (selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0) - grp * 32;
+      // ---- P = exp2(S * scale - lse): needs S only, runs while the dP product does
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[s], par, abort_flag, p.status, 77));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t x[32];
+      tmem_ld32(tmem + lane_off + s * 128 + grp * 32, x);
+      tmem_wait_ld_dep(x);
+      {
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_lse, neg_lse);
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float y0, y1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(x[c], x[c + 1]), c2, n2), y0, y1);
+          x[c] = __float_as_uint(c < lim ? exp2f(y0) : 0.f);
+          x[c + 1] = __float_as_uint(c + 1 < lim ? exp2f(y1) : 0.f);
+        }
+      }
+      // ---- dS = P * (dP - D), written over the first half of this thread's S columns as bf16 pairs
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dp_full[s], par, abort_flag, p.status, 69));
+      if (!ok) break;
+      tc_fence_after();
       uint32_t packed[16];
       {
-        const int half = grp;                          // this warp group's 32 key columns
-        uint32_t sv[32], dpv[32];
-        tmem_ld32x2_wait(tmem + lane_off + s * 128 + half * 32, sv, tmem + lane_off + s * 128 + 64 + half * 32, dpv);
-        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_lse, neg_lse);
+        uint32_t dpv[32];
+        tmem_ld32(tmem + lane_off + s * 128 + 64 + grp * 32, dpv);
+        tmem_wait_ld_dep(dpv);
         const uint64_t md2 = pack_f32x2(-dsum, -dsum);
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float y0, y1, d0, d1;
-          unpack_f32x2(fma_f32x2(pack_f32x2(sv[c], sv[c + 1]), c2, n2), y0, y1);
-          unpack_f32x2(mul_f32x2(pack_f32x2(exp2f(y0), exp2f(y1)),
-                                 add_f32x2(pack_f32x2(dpv[c], dpv[c + 1]), md2)), d0, d1);
-          packed[c >> 1] = pack_bf16((half * 32 + c < lim) ? d0 : 0.f, (half * 32 + c + 1 < lim) ? d1 : 0.f);
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(pack_f32x2(x[c], x[c + 1]), add_f32x2(pack_f32x2(dpv[c], dpv[c + 1]), md2)), d0, d1);
+          packed[c >> 1] = pack_bf16(d0, d1);
         }
       }
-      tmem_st16(tmem + lane_off + s * 128 + grp * 16, packed);
+      // (each column group writes inside the S columns it read itself: no warp's dS can land on
+      //  scores that another warp has yet to load)
+      tmem_st16(tmem + lane_off + s * 128 + grp * 32, packed);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&sm.ds_ready[s]);
     }
+    // the warps of the first turn write the tile's dQ
+    if (turn != 0) ok = false;
     if (ok && n_blocks > 0) {
       // the last block's product: S / dP of that block is complete, hence every dQ product up to
       // block n-3 is too, so this barrier is at most one phase behind and the parity is unambiguous
@@ -388,7 +429,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
+  if (warp == 3) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------ 3. dK / dV kernel --------
@@ -571,9 +612,13 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
         if (lane == 0) {
           if (i >= 3) ok = mbar_wait(&sm.dk_done[qs], (uint32_t)((qround & 1) ^ 1), abort_flag, p.status, 81);
           if (ok && m < 0) {
-            // end of the walk: the slot's barrier completes without a tile and the count says why
+            // end of the walk: the barriers of the next two steps (one for each softmax turn)
+            // complete without a tile, and the count says why
             *total_steps = i;
             mbar_arrive(&sm.q_full[qs]);
+            const int qs1 = (i + 1) % 3;
+            if (i + 1 >= 3) ok = mbar_wait(&sm.dk_done[qs1], (uint32_t)((((i + 1) / 3) & 1) ^ 1), abort_flag, p.status, 97);
+            if (ok) mbar_arrive(&sm.q_full[qs1]);
           } else if (ok) {
             sm.step_m[qs] = m;
             sm.step_bits[qs] = bits;
@@ -614,6 +659,8 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint64_t do_desc0 = umma_desc_sw128(smem_u32(sm.dout[0][0]), 16, 1024);
       constexpr uint32_t kRing = (2 * kTileHalfBytes) >> 4;
       bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 82));
+      // (issuing S(j + 1) ahead of dP(j), so that the exponentials of a step would not wait for its
+      // dO tile, measured 12 % slower: dS, dK and with them the Q slots then come later)
       int qs = 0, qround = 0;
       for (int j = 0; ok; ++j) {
         const int bf = j & 1;
@@ -682,25 +729,29 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else if (warp >= 4) {
+    // One step of softmax work (two TMEM loads, 32 exponentials per thread, two rounds of shared-
+    // memory stores + proxy fence + barrier, the row statistics from global memory) takes longer
+    // than the four products of a step, so two groups of eight warps take the steps in turn.
     const int quad = warp & 3;
-    const int grp = (warp - 4) >> 2;                 // which 32 key columns
+    const int turn = (warp - 4) >> 3;                // this warp takes the steps with i & 1 == turn
+    const int grp = ((warp - 4) & 7) >> 2;           // which 32 key columns
     const int r = quad * 32 + lane;
     const int tl = r >> 4, g = r & 15;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     bool ok = true;
     int steps = 0;
-    int qs = 0, qround = 0;                          // i % 3, i / 3
-    int pqs = 0, pround = 0;                         // (i - 1) % 3, (i - 1) / 3 (valid for i >= 1)
     // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk (c ^ (r & 7))
     uint8_t* prow = sm.pmat + r * 128;
     uint8_t* drow = sm.dsmat + r * 128;
     if (!never_selected) {
-      for (int i = 0;; ++i) {
+      for (int i = turn;; i += 2) {
+        const int qs = i % 3, qround = i / 3;
+        const int pqs = (i + 2) % 3, pround = (i - 1) / 3;         // of step i - 1 (used for i >= 1)
         // the step's record arrives with its Q tile, well before its S
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.q_full[qs], (uint32_t)(qround & 1), abort_flag, p.status, 96));
         if (!ok) break;
-        if (i >= *total_steps) break;
-        steps = i + 1;
+        steps = *total_steps;
+        if (i >= steps) break;
         const int m = sm.step_m[qs];
         const uint32_t bits = sm.step_bits[qs];
         const int bf = i & 1;
@@ -774,11 +825,10 @@ sparse_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q,
           fence_proxy_async_smem();
           mbar_arrive_warp(&sm.ds_ready);
         }
-        pqs = qs;
-        pround = qround;
-        if (++qs == 3) { qs = 0; ++qround; }
       }
     }
+    // the warps of the first turn write the block's gradients
+    if (turn != 0) ok = false;
     if (ok && steps > 0) {
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dk_done[(steps - 1) % 3],
                                              (uint32_t)(((steps - 1) / 3) & 1), abort_flag, p.status, 88));
@@ -925,7 +975,7 @@ extern "C" int ifv2_sparse_attn_bwd(const void* dout, const void* q, const void*
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error((int)e, "sparse_attn_bwd: %s", cudaGetErrorString(e));
     dim3 grid((max_seqlen_q + kTokPerTile - 1) / kTokPerTile, batch, heads_k);
-    sparse_attn_bwd_dq_kernel<<<grid, kThreads, smem, st>>>(map_q, map_do, map_k, map_v, p);
+    sparse_attn_bwd_dq_kernel<<<grid, kDqThreads, smem, st>>>(map_q, map_do, map_k, map_v, p);
     rc = check_launch("sparse_attn_bwd_dq");
     if (rc) return rc;
   }
