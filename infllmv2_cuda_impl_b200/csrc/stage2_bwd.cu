@@ -85,6 +85,26 @@ dot_do_o_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __r
   }
 }
 
+// One thread's mask row, read in the order the tile's blocks are walked (highest first): the word
+// of the current 64 blocks stays in a register and the word below it is fetched ahead, so that a
+// step does not start with a round trip to global memory.
+struct MaskRowReader {
+  const unsigned long long* row;   // null: every block counts as selected
+  int wi;                          // index of the word in `cur`, -1 before the first read
+  unsigned long long cur, below;
+  __device__ explicit MaskRowReader(const unsigned long long* r) : row(r), wi(-1), cur(0ull), below(0ull) {}
+  __device__ bool selected(int blk) {
+    if (row == nullptr) return true;
+    const int j = blk >> 6;
+    if (j != wi) {
+      cur = (wi >= 0 && j == wi - 1) ? below : __ldg(row + j);
+      wi = j;
+      below = j > 0 ? __ldg(row + j - 1) : 0ull;
+    }
+    return (cur >> (blk & 63)) & 1ull;
+  }
+};
+
 // Highest-to-lowest walk over the set bits of a tile's union mask.
 struct BlockWalk {
   const unsigned long long* words;
@@ -112,7 +132,9 @@ struct DqSmem {
   // s_full[s] / dp_full[s]: S (dP) of TMEM buffer s is complete; dp_full also releases the V tile of
   // slot s; dq_done[k] releases the K tile of ring slot k and the TMEM buffer of that step and,
   // for the last block, tells the epilogue that dQ is complete.
-  uint64_t qdo_full, k_full[3], dq_done[3], v_full[2], s_full[2], dp_full[2], ds_ready[2];
+  // s_empty[s]: the softmax warps have read S of buffer s (dS goes over the dP columns, so the next S
+  // for the buffer need not wait for the dQ product that reads dS).
+  uint64_t qdo_full, k_full[3], dq_done[3], v_full[2], s_full[2], dp_full[2], ds_ready[2], s_empty[2];
   uint64_t qdo_tmem;   // 8 arrivals: Q and dO have been copied from shared memory into TMEM
   uint32_t tmem_base;
   int n_blocks;
@@ -174,6 +196,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&sm.s_full[s], 1);
       mbar_init(&sm.dp_full[s], 1);
       mbar_init(&sm.ds_ready[s], 8);         // one arrival per softmax warp of the buffer's turn
+      mbar_init(&sm.s_empty[s], 8);
     }
     mbar_init(&sm.qdo_tmem, 8);
     fence_barrier_init();
@@ -253,8 +276,8 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
         const int s = j & 1;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
         bool w = mbar_wait(&sm.k_full[sk], (uint32_t)(kround & 1), abort_flag, p.status, 74);
-        // the buffer's last user: dQ of step j - 2 read dS from it
-        if (w && j >= 2) w = mbar_wait(&sm.dq_done[sk2], (uint32_t)(kround2 & 1), abort_flag, p.status, 80);
+        // the S columns were last read by the softmax warps of step j - 2
+        if (w && j >= 2) w = mbar_wait(&sm.s_empty[s], par ^ 1u, abort_flag, p.status, 80);
         if (!__all_sync(0xFFFFFFFFu, w)) break;
         tc_fence_after();
         const uint64_t k_desc = k_desc0 + (uint32_t)sk * kStage, v_desc = v_desc0 + (uint32_t)s * kStage;
@@ -264,7 +287,10 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
           umma_ts_pred(tmem + s * 128, tmem_q + kk * 8, k_desc + boff, idesc_s, kk > 0, leader);
         }
         umma_commit_pred(&sm.s_full[s], leader);
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75))) break;
+        // the dP columns hold dS of step j - 2 until its dQ product is complete
+        w = mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75);
+        if (w && j >= 2) w = mbar_wait(&sm.dq_done[sk2], (uint32_t)(kround2 & 1), abort_flag, p.status, 68);
+        if (!__all_sync(0xFFFFFFFFu, w)) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -292,8 +318,8 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         const uint64_t k_mn = k_desc0_mn + (uint32_t)sk * kStage;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)      // dS of keys 0-31 sits at columns [0, 16), of keys 32-63 at [32, 48)
-          umma_ts_pred(tmem_dq, tmem + s * 128 + (kk >> 1) * 32 + (kk & 1) * 8, k_mn + ((kk * 2048) >> 4), idesc_dq,
+        for (int kk = 0; kk < 4; ++kk)      // dS of keys 0-31 sits at columns [64, 80), of keys 32-63 at [96, 112)
+          umma_ts_pred(tmem_dq, tmem + s * 128 + 64 + (kk >> 1) * 32 + (kk & 1) * 8, k_mn + ((kk * 2048) >> 4), idesc_dq,
                        (i > 0) || (kk > 0), leader);
         umma_commit_pred(&sm.dq_done[sk], leader);
         if (++sk == 3) { sk = 0; ++kround; }
@@ -341,14 +367,14 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
     BlockWalk walk(sm.umask, words);
+    MaskRowReader mask_reader(mrow);
     if (turn == 1 && n_blocks > 0) walk.next();
     for (int i = turn; i < n_blocks && ok; i += 2) {
       const int blk = walk.next();
       walk.next();                                   // the other turn's block
       const int s = i & 1;
       const uint32_t par = (uint32_t)((i >> 1) & 1);
-      bool selected = valid;
-      if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
+      const bool selected = valid && mask_reader.selected(blk);
       const int lim = (selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0) - grp * 32;
       // ---- P = exp2(S * scale - lse): needs S only, runs while the dP product does
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.s_full[s], par, abort_flag, p.status, 77));
@@ -357,6 +383,8 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       uint32_t x[32];
       tmem_ld32(tmem + lane_off + s * 128 + grp * 32, x);
       tmem_wait_ld_dep(x);
+      tc_fence_before();
+      mbar_arrive_warp(&sm.s_empty[s]);
       {
         const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_lse, neg_lse);
 #pragma unroll
@@ -367,7 +395,7 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
           x[c + 1] = __float_as_uint(c + 1 < lim ? exp2f(y1) : 0.f);
         }
       }
-      // ---- dS = P * (dP - D), written over the first half of this thread's S columns as bf16 pairs
+      // ---- dS = P * (dP - D), written over the first half of this thread's dP columns as bf16 pairs
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.dp_full[s], par, abort_flag, p.status, 69));
       if (!ok) break;
       tc_fence_after();
@@ -384,9 +412,9 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
           packed[c >> 1] = pack_bf16(d0, d1);
         }
       }
-      // (each column group writes inside the S columns it read itself: no warp's dS can land on
-      //  scores that another warp has yet to load)
-      tmem_st16(tmem + lane_off + s * 128 + grp * 32, packed);
+      // (each column group writes inside the dP columns it read itself: no warp's dS can land on
+      //  values that another warp has yet to load)
+      tmem_st16(tmem + lane_off + s * 128 + 64 + grp * 32, packed);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&sm.ds_ready[s]);

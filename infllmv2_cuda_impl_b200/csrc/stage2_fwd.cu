@@ -69,6 +69,26 @@ struct Smem {
   int abort_flag;
 };
 
+// One thread's mask row, read in the order the tile's blocks are walked (highest first): the word
+// of the current 64 blocks stays in a register and the word below it is fetched ahead, so that a
+// step does not start with a round trip to global memory.
+struct MaskRowReader {
+  const unsigned long long* row;   // null: every block counts as selected
+  int wi;                          // index of the word in `cur`, -1 before the first read
+  unsigned long long cur, below;
+  __device__ explicit MaskRowReader(const unsigned long long* r) : row(r), wi(-1), cur(0ull), below(0ull) {}
+  __device__ bool selected(int blk) {
+    if (row == nullptr) return true;
+    const int j = blk >> 6;
+    if (j != wi) {
+      cur = (wi >= 0 && j == wi - 1) ? below : __ldg(row + j);
+      wi = j;
+      below = j > 0 ? __ldg(row + j - 1) : 0ull;
+    }
+    return (cur >> (blk & 63)) & 1ull;
+  }
+};
+
 // Highest-to-lowest walk over the set bits of the tile's union mask.
 struct BlockWalk {
   const unsigned long long* words;
@@ -272,12 +292,12 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     BlockWalk walk(sm.umask, words);
+    MaskRowReader mask_reader(mrow);
     for (int i = 0; i < n_blocks; ++i) {
       const int blk = walk.next();
       const int s = i & 1;
       const uint32_t par = (uint32_t)((i >> 1) & 1);
-      bool selected = valid;
-      if (mrow != nullptr) selected = (__ldg(mrow + (blk >> 6)) >> (blk & 63)) & 1ull;
+      const bool selected = valid && mask_reader.selected(blk);
       const int lim = selected ? min(max(row_limit - blk * kBlockN, 0), kBlockN) : 0;
       // only the diagonal / ragged block needs per-element masking; a row that did not select
       // the block is handled by the row-level terms below
