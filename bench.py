@@ -1100,7 +1100,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="with --only: a reduced size")
     ap.add_argument("--e2e-order", default="middle-out", choices=["middle-out", "ascending"],
                     help="order in which the host-to-host pipeline processes the query chunks")
-    ap.add_argument("--e2e-chunk", type=int, default=8192,
+    ap.add_argument("--e2e-chunk", type=int, default=4096,
                     help="query tokens per chunk of the host-to-host (e2e) pipeline")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the secondary configs (selection micro-benchmark, varlen fwd+bwd, decode)")
