@@ -52,15 +52,50 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    """SM clock and throttle-reason samples while the timed region runs: NVML from a thread every
+    5 ms (read-only queries), so that even a region of a few tens of milliseconds gets samples;
+    `nvidia-smi -lms` as the fallback when the NVML binding is missing."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event-reason bits (nvml.h)
+    BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+            "hw_thermal_slowdown": 0x40}
 
     def __init__(self, gpu_index):
         self.idx, self.proc, self.path = gpu_index, None, None
+        self.thread, self.stop, self.sm, self.smax, self.reasons = None, False, [], None, set()
+
+    def _nvml_loop(self, nv, handle):
+        reason_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                r = int(reason_fn(handle))
+                for n, bit in self.BITS.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def __enter__(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.idx).uuid)
+                handle = nv.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.idx)
+            self.smax = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -72,6 +107,9 @@ class ClockSampler:
         return self
 
     def __exit__(self, *exc):
+        if self.thread is not None:
+            self.stop = True
+            self.thread.join(timeout=2)
         if self.proc is not None:
             time.sleep(0.15)
             self.proc.terminate()
@@ -82,6 +120,12 @@ class ClockSampler:
 
     def summary(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.thread is not None:
+            if self.sm:
+                sm = sorted(self.sm)
+                out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=self.smax, reasons=sorted(self.reasons),
+                           samples=len(sm))
+            return out
         if not self.path or not os.path.exists(self.path):
             return out
         sm, smax, reasons = [], [], set()
