@@ -21,12 +21,12 @@ namespace {
 using namespace tc;
 
 constexpr int kTokPerTile = 8;
-constexpr int kDkvThreads = 640;    // dK / dV kernel: warp 0 TMA, warps 1 and 2 MMA issuers, warp 3 TMEM,
-                                    // warps 4-11 softmax of the even steps, 12-19 of the odd ones
-constexpr int kDqThreads = 640;     // dQ kernel: same roles as the dK / dV kernel
-constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9: two softmax groups, each takes
-                                    // 32 of a block's 64 key columns for all 128 rows (no row reductions
-                                    // are needed in the backward, so the halves are independent)
+// Both gradient kernels: warp 0 TMA, warps 1 and 2 MMA issuers, warp 3 owns the TMEM allocation,
+// warps 4-11 do the softmax work of the even steps and 12-19 of the odd ones.  Within a turn a warp
+// takes 32 of a block's 64 key columns for the 32 rows of its TMEM lane quadrant (no row reductions
+// are needed in the backward, so the column halves are independent).
+constexpr int kDkvThreads = 640;
+constexpr int kDqThreads = 640;
 constexpr int kMaxMaskWords = 128;
 constexpr uint32_t kTileHalfBytes = 128 * 128;   // 128 rows x 64 bf16
 constexpr uint32_t kKVHalfBytes = 64 * 128;      // 64 keys x 64 bf16
