@@ -19,7 +19,9 @@
 // CTA is the latency of the chain S ready -> P ready -> P.V -> next Q.K^T on each S buffer
 // while the co-resident CTA competes for the tensor pipe and the exponential unit.  Splitting a
 // row over two threads (8 softmax warps, half-row maxima exchanged through shared memory) or
-// giving each S buffer its own warp group did not shorten that chain and ran 8-12 % slower.
+// giving each S buffer its own warp group did not shorten that chain and ran 8-12 % slower;
+// evaluating every 2nd, 3rd or 4th pair of exponentials on the FMA pipe (degree-3 polynomial)
+// ran 8, 4 and 3 % slower: the exponential unit is not what the softmax warps wait for.
 #include "tc05.cuh"
 
 namespace ifv2 {
