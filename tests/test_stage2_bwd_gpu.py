@@ -71,3 +71,38 @@ def test_bwd_unselected_blocks_get_zero_grad_and_rerun_is_deterministic():
     b = _grads(q, k, v, do, cu([256]), cu([256]), idx, True)
     assert all(torch.equal(x, y) for x, y in zip(a, b))      # no atomics anywhere
     assert a[2][64:].abs().max() == 0 and a[3][64:].abs().max() == 0
+
+
+def test_bwd_column_masks_with_long_empty_stretches():
+    """Key blocks whose selecting tokens lie thousands of tokens apart: the dK / dV kernel's walk
+    over the column-mask row has to skip runs of more than 32 empty 64-bit words and refill its
+    cached words, with the second sequence starting in the middle of a word (q0 = 4200)."""
+    hk, d = 1, 128
+    hq = hk * 16
+    lens = [4200, 600]
+    rows = []
+    for lq in lens:
+        for t in range(lq):
+            blocks = {0, t // 64}
+            if lq == 4200 and (t == 200 or 4100 <= t < 4104):
+                blocks.add(1)                  # block 1: its own tokens, token 200, tokens 4100-4103
+            if lq == 4200 and t == 4199:
+                blocks.add(30)                 # block 30: its own tokens and the very last one
+            if lq == 600 and t in (70, 599):
+                blocks.add(1)
+            row = sorted(blocks) + [-1] * (4 - len(blocks))
+            rows.append(row)
+    idx = torch.tensor(rows, dtype=torch.int32).view(1, sum(lens), 4).repeat(hk, 1, 1)
+    q = det_tensor((sum(lens), hq, d), 21, 0.25)
+    k = det_tensor((sum(lens), hk, d), 22, 0.25)
+    v = det_tensor((sum(lens), hk, d), 23)
+    do = det_tensor((sum(lens), hq, d), 24, 0.5)
+    out, dq, dk, dv = _grads(q, k, v, do, cu(lens), cu(lens), idx, True)
+    _, _, rdq, rdk, rdv = oracle.sparse_attention_fwd_bwd(q, k, v, do, cu(lens), cu(lens), idx, causal=True)
+    for name, got, ref in (("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        assert not torch.isnan(got.float()).any(), name
+        mx, mr = err_stats(got, ref)
+        scale = max(1.0, ref.abs().max().item())
+        assert mx <= MAX_ABS * scale and mr <= MEAN_REL, (name, mx, mr, scale)
+    # the rows of block 1 of the first sequence get exactly the contributions of those 73 tokens
+    assert dk[64:128].abs().max() > 0 and dv[64:128].abs().max() > 0
