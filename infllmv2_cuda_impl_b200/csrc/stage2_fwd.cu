@@ -318,55 +318,76 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int c = 0; c < 64; ++c)
           if (c >= lim) raw[c] = 0xFF800000u;                              // -inf
       }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 64; c += 2)           // two scores per step: a three-input maximum each
-        mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(raw[c]), __uint_as_float(raw[c + 1])));
-      const float mx = (lim > 0) ? fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) : -INFINITY;
-      // raise the reference max only when it moves by more than the threshold
-      float f = 1.f;
-      if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > kRescaleThreshold)) {
-        if (m_ref != -INFINITY) f = exp2f((m_ref - mx) * p.scale_log2);
-        m_ref = mx;
-        l *= f;
-      }
-      if (i > 0 && __any_sync(0xFFFFFFFFu, f != 1.f)) {
-        // the previous block's product (slot (i-1)&1, its ((i-1)>>1)-th use).  S of this block is
-        // complete, so every product up to block i-2 is too: the barrier is at most one phase
-        // behind and the parity wait is unambiguous
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.pv_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1),
-                                               abort_flag, p.status, 32));
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < 128; c += 32) {
-          uint32_t o[32];
-          tmem_ld32(tmem_o + lane_off + c, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
-          tmem_st32(tmem_o + lane_off + c, o);
-        }
-        tmem_wait_st();
-      }
-      // rows that take nothing from this block get an exponent of -inf (P = 0) for every column
-      const float neg_m = (lim == 0) ? -INFINITY : -m_ref * p.scale_log2;
       uint32_t packed[32];
-      const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg_m, neg_m);
-      uint64_t sum2[4];
+      float sum = 0.f;
+      // P = exp2(S * c + neg) for the row's 64 scores, packed to bf16, and their sum
+      auto compute_p = [&](float neg) {
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), n2 = pack_f32x2(neg, neg);
+        uint64_t sum2[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) sum2[i] = pack_f32x2(0.f, 0.f);
+        for (int i = 0; i < 4; ++i) sum2[i] = pack_f32x2(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        float y0, y1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(raw[c], raw[c + 1]), c2, n2), y0, y1);
-        const float p0 = exp2f(y0), p1 = exp2f(y1);
-        sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
-        packed[c >> 1] = pack_bf16(p0, p1);
+        for (int c = 0; c < 64; c += 2) {
+          float y0, y1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(raw[c], raw[c + 1]), c2, n2), y0, y1);
+          const float p0 = exp2f(y0), p1 = exp2f(y1);
+          sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
+          packed[c >> 1] = pack_bf16(p0, p1);
+        }
+        float s_lo, s_hi;
+        unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), s_lo, s_hi);
+        sum = s_lo + s_hi;
+      };
+      auto row_max = [&]() -> float {
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 64; c += 2)           // two scores per step: a three-input maximum each
+          mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(raw[c]), __uint_as_float(raw[c + 1])));
+        return (lim > 0) ? fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) : -INFINITY;
+      };
+      // The reference maximum moves only when the row maximum exceeds it by more than the
+      // threshold, which after a row's first block almost never happens.  So once every row of the
+      // warp that takes part has a reference, the exponentials are started against the current one
+      // and the row maximum is computed beside them (it is off the chain S -> P); a block that does
+      // move some row's reference is redone below, with the result the in-order form would give.
+      bool done = false;
+      if (!__any_sync(0xFFFFFFFFu, lim > 0 && m_ref == -INFINITY)) {
+        compute_p((lim == 0) ? -INFINITY : -m_ref * p.scale_log2);
+        const float mx = row_max();
+        const bool moves = mx > m_ref && (mx - m_ref) * p.scale_log2 > kRescaleThreshold;
+        done = !__any_sync(0xFFFFFFFFu, moves);
       }
-      float s_lo, s_hi;
-      unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), s_lo, s_hi);
-      const float sum = s_lo + s_hi;
+      if (!done) {
+        const float mx = row_max();
+        // raise the reference max only when it moves by more than the threshold
+        float f = 1.f;
+        if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > kRescaleThreshold)) {
+          if (m_ref != -INFINITY) f = exp2f((m_ref - mx) * p.scale_log2);
+          m_ref = mx;
+          l *= f;
+        }
+        if (i > 0 && __any_sync(0xFFFFFFFFu, f != 1.f)) {
+          // the previous block's product (slot (i-1)&1, its ((i-1)>>1)-th use).  S of this block is
+          // complete, so every product up to block i-2 is too: the barrier is at most one phase
+          // behind and the parity wait is unambiguous
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.pv_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1),
+                                                 abort_flag, p.status, 32));
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 128; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(tmem_o + lane_off + c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
+            tmem_st32(tmem_o + lane_off + c, o);
+          }
+          tmem_wait_st();
+        }
+        // rows that take nothing from this block get an exponent of -inf (P = 0) for every column
+        compute_p((lim == 0) ? -INFINITY : -m_ref * p.scale_log2);
+      }
       // The V rows past the last key of a ragged block have P = 0, but 0 x inf or 0 x NaN is not 0,
       // so those rows are cleared before the product reads them.
       if (nk < kBlockN) {
