@@ -258,20 +258,18 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else if (warp == 1) {
-    // S and dP.  All 32 lanes run the same issue code (descriptors stay in uniform registers);
+    // S = Q K^T.  All 32 lanes run the same issue code (descriptors stay in uniform registers);
     // `leader` enables the MMA / commit instructions in one lane only.
     if (n_blocks > 0) {
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);
       const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024);
-      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sm.v[0][0]), 16, 1024);
       constexpr uint32_t kStage = (2 * kKVHalfBytes) >> 4;     // descriptor address units per ring stage
       // Q and dO are A operands read from TMEM: the Q.K^T and dO.V^T products then fetch only
       // their 2 KB key tiles from shared memory per step instead of 6 KB
       bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_tmem, 0, abort_flag, p.status, 73));
       tc_fence_after();
       int sk = 0, kround = 0;                       // j % 3, j / 3
-      int sk2 = 1, kround2 = -1;                    // (j - 2) % 3, (j - 2) / 3 (used from j = 2 on)
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int s = j & 1;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
@@ -280,25 +278,41 @@ sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
         if (w && j >= 2) w = mbar_wait(&sm.s_empty[s], par ^ 1u, abort_flag, p.status, 80);
         if (!__all_sync(0xFFFFFFFFu, w)) break;
         tc_fence_after();
-        const uint64_t k_desc = k_desc0 + (uint32_t)sk * kStage, v_desc = v_desc0 + (uint32_t)s * kStage;
+        const uint64_t k_desc = k_desc0 + (uint32_t)sk * kStage;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
           umma_ts_pred(tmem + s * 128, tmem_q + kk * 8, k_desc + boff, idesc_s, kk > 0, leader);
         }
         umma_commit_pred(&sm.s_full[s], leader);
+        if (++sk == 3) { sk = 0; ++kround; }
+      }
+    }
+  } else if (warp == 3) {
+    // dP = dO V^T, on a warp of its own: one warp issuing S and dP was busy four fifths of a step
+    if (n_blocks > 0) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false);
+      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sm.v[0][0]), 16, 1024);
+      constexpr uint32_t kStage = (2 * kKVHalfBytes) >> 4;
+      bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&sm.qdo_tmem, 0, abort_flag, p.status, 67));
+      tc_fence_after();
+      int sk2 = 1, kround2 = -1;                    // (j - 2) % 3, (j - 2) / 3 (used from j = 2 on)
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t par = (uint32_t)((j >> 1) & 1);
         // the dP columns hold dS of step j - 2 until its dQ product is complete
-        w = mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75);
+        bool w = mbar_wait(&sm.v_full[s], par, abort_flag, p.status, 75);
         if (w && j >= 2) w = mbar_wait(&sm.dq_done[sk2], (uint32_t)(kround2 & 1), abort_flag, p.status, 68);
         if (!__all_sync(0xFFFFFFFFu, w)) break;
         tc_fence_after();
+        const uint64_t v_desc = v_desc0 + (uint32_t)s * kStage;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t boff = ((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4;
           umma_ts_pred(tmem + s * 128 + 64, tmem_do + kk * 8, v_desc + boff, idesc_s, kk > 0, leader);
         }
         umma_commit_pred(&sm.dp_full[s], leader);
-        if (++sk == 3) { sk = 0; ++kround; }
         if (++sk2 == 3) { sk2 = 0; ++kround2; }
       }
     }
