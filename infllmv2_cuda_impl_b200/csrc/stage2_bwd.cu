@@ -21,8 +21,9 @@ namespace {
 using namespace tc;
 
 constexpr int kTokPerTile = 8;
-// Both gradient kernels: warp 0 TMA, warps 1 and 2 MMA issuers, warp 3 owns the TMEM allocation,
-// warps 4-11 do the softmax work of the even steps and 12-19 of the odd ones.  Within a turn a warp
+// Both gradient kernels: warp 0 TMA, warps 1 and 2 MMA issuers, warp 3 owns the TMEM allocation (and
+// in the dQ kernel issues a product of its own), warps 4-11 do the softmax work of the even steps
+// and 12-19 of the odd ones.  Within a turn a warp
 // takes 32 of a block's 64 key columns for the 32 rows of its TMEM lane quadrant (no row reductions
 // are needed in the backward, so the column halves are independent).
 constexpr int kDkvThreads = 640;
@@ -141,9 +142,11 @@ struct DqSmem {
   int abort_flag;
 };
 
-// Roles: warp 0 copies, warp 1 issues S = Q K^T and dP = dO V^T (A operands from TMEM), warp 2 issues
-// dQ += dS K, warp 3 owns the TMEM allocation, warps 4-11 do the softmax work of the even steps and
-// 12-19 of the odd ones (each turn has the TMEM buffer of its parity).  A step's P is computed as
+// Roles: warp 0 copies; warp 1 issues S = Q K^T, warp 3 (which also owns the TMEM allocation)
+// dP = dO V^T, both with the A operand in TMEM, warp 2 dQ += dS K: one issuing warp per product,
+// because a warp that shares its scheduler with four softmax warps needs 600-700 clocks to issue
+// eight MMAs; warps 4-11 do the softmax work of the even steps and 12-19 of the odd ones (each
+// turn has the TMEM buffer of its parity).  A step's P is computed as
 // soon as its S is there, while its dP product runs.
 __global__ void __launch_bounds__(kDqThreads, 1)
 sparse_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q,
