@@ -733,9 +733,10 @@ def config5_decode(device, pk, small=False):
     n_c_dev = torch.tensor(n_c, dtype=torch.int32, device=device)
 
     def full_step():
-        score = infllm_v2.infllmv2_attn_stage1(q2, kc, kc, cu_q, cu_c, cu_c, 1, max_c, causal=False)
-        mask = infllm_v2.decode_select(score, cache_lens, TOPK, cap, LOCAL_BLOCKS, INIT_BLOCKS,
-                                       seqused_c=n_c_dev)
+        # scores, pool, top-k and mask in two launches (the score rows stay on chip), as
+        # SparseAttention.decode does; equal to infllmv2_attn_stage1 -> decode_select
+        mask = infllm_v2.infllmv2_stage1_decode_select(q2, kc, cu_c, cache_lens, max_c, cap, TOPK,
+                                                       LOCAL_BLOCKS, INIT_BLOCKS, seqused_k=n_c_dev)
         return infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d, block_mask=mask)
 
     full_step()
@@ -761,7 +762,7 @@ def config5_decode(device, pk, small=False):
         "gbs": round(bytes_full / best_full / 1e6, 1),
         "frac": round(bytes_full / best_full / 1e6 / pk["hbm_gbs"], 4),
         "tokens_per_s": round(B / (best_full * 1e-3), 1),
-        "note": "stage 1 (one token per sequence) + one-launch pool/top-k/mask + sparse decode; algorithmic bytes = "
+        "note": "stage 1 (one token per sequence) with pool/top-k/mask in its second launch + sparse decode; algorithmic bytes = "
                 "compressed keys once (%d MB) + selected K/V" % (kc.numel() * 2 // 1000000)}
 
     # ---- the same step through the caller-side layer: the new token's key / value are appended
@@ -970,8 +971,8 @@ def sharded_decode_bench(device, rank, world, pk):
     max_c, q2 = max(n_c), q.view(nb, hk * 16, D)
 
     def full_step():
-        score = infllm_v2.infllmv2_attn_stage1(q2, kc, kc, cu_q, cu_c, cu_c, 1, max_c, causal=False)
-        mask = infllm_v2.decode_select(score, positions, TOPK, cap, LOCAL_BLOCKS, INIT_BLOCKS, seqused_c=n_c_dev)
+        mask = infllm_v2.infllmv2_stage1_decode_select(q2, kc, cu_c, positions, max_c, cap, TOPK,
+                                                       LOCAL_BLOCKS, INIT_BLOCKS, seqused_k=n_c_dev)
         return infllm_v2.infllmv2_attn_with_kvcache(q, kcache, vcache, cache_seqlens=lens_d, block_mask=mask)
 
     full_step()
