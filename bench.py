@@ -1013,7 +1013,7 @@ def multi_gpu_configs(device, rank, world, pk):
 
 def _reference_functions():
     """The reference's own pure-PyTorch functions (its test oracles), when a checkout is reachable
-    through INFLLMV2_REFERENCE or at /root/reference: torch_naive_softmax (stage 1) and
+    through INFLLMV2_REFERENCE (or at the default location below): torch_naive_softmax (stage 1) and
     convert_topk_to_base_blockmask / prepare_mixed_mask / attention_blocksparse_ref (stage 2).
     Returns None where there is no checkout (the GPU box): the CPU port in oracle/ is timed then."""
     import importlib
