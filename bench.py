@@ -420,7 +420,8 @@ def run_e2e(args, step, q, k, v, kc, seqlen, world, device):
 
     def one():
         runner(host[0], host[1], host[2], host[3], out_host, TOPK, INIT_BLOCKS, LOCAL_BLOCKS,
-               order=(list(range(seqlen // chunk)) if args.e2e_order == "ascending" else None))
+               order=(list(range(seqlen // chunk)) if args.e2e_order == "ascending" else None),
+               split_ends=args.e2e_split)
 
     one()
     if world > 1:
@@ -1147,6 +1148,8 @@ def main():
                     help="order in which the host-to-host pipeline processes the query chunks")
     ap.add_argument("--e2e-chunk", type=int, default=4096,
                     help="query tokens per chunk of the host-to-host (e2e) pipeline")
+    ap.add_argument("--e2e-split", type=int, default=4,
+                    help="pieces into which the first and the last chunk of the e2e pipeline are cut")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the secondary configs (selection micro-benchmark, varlen fwd+bwd, decode)")
     args = ap.parse_args()

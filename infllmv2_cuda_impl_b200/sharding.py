@@ -299,27 +299,41 @@ class StreamedPrefill:
                 lo -= 1
         return order
 
+    def pieces(self, order: Sequence[int], split_ends: int) -> List[Tuple[int, int]]:
+        """Token ranges in processing order.  The first and the last chunk of `order` are cut into
+        `split_ends` equal pieces: the kernels can start after a quarter of a chunk has been copied
+        in, and only a quarter of a chunk is left to copy out when the last kernel has finished."""
+        out = []
+        for pos, c in enumerate(order):
+            start = c * self.chunk
+            parts = split_ends if pos in (0, len(order) - 1) else 1
+            if parts < 1 or self.chunk % (parts * 64) != 0:
+                parts = 1
+            step = self.chunk // parts
+            out += [(start + j * step, start + (j + 1) * step) for j in range(parts)]
+        return out
+
     def __call__(self, q_host, k_host, v_host, kc_host, out_host, topk: int, init_blocks: int,
                  local_blocks: int, ops: Optional[PrefillOps] = None, kernel: int = 32,
-                 stride: int = 16, order: Optional[Sequence[int]] = None):
+                 stride: int = 16, order: Optional[Sequence[int]] = None, split_ends: int = 4):
         """Enqueue one full prefill; returns when everything is ENQUEUED (synchronise the device, or
         the returned event, before reading out_host).  `order`: the sequence in which the query
         chunks are processed (default `middle_out`); chunks are independent given the keys before
-        their end, which are copied on demand."""
+        their end, which are copied on demand.  `split_ends`: see `pieces`."""
         main = torch.cuda.current_stream(self.device)
         n = self.seqlen // self.chunk
         order = list(order) if order is not None else self.middle_out(n)
         if sorted(order) != list(range(n)):
             raise ValueError("order must be a permutation of the chunk indices")
+        pieces = self.pieces(order, split_ends)
         self.s_in.wait_stream(main)
         self.s_out.wait_stream(main)
         ev_in = {}
         with torch.cuda.stream(self.s_in):
             kv_done, kc_done = 0, 0                 # tokens / compressed keys already on the device
-            for c in order:
-                # chunk c needs the keys before its own end: K / V / compressed K travel piecewise
+            for start, lk in pieces:
+                # a piece needs the keys before its own end: K / V / compressed K travel piecewise
                 # too, so the first kernels start after a fraction of the input has landed
-                lk = (c + 1) * self.chunk
                 if lk > kv_done:
                     self.k[kv_done:lk].copy_(k_host[kv_done:lk], non_blocking=True)
                     self.v[kv_done:lk].copy_(v_host[kv_done:lk], non_blocking=True)
@@ -328,15 +342,15 @@ class StreamedPrefill:
                 if n_c > kc_done:
                     self.kc[kc_done:n_c].copy_(kc_host[kc_done:n_c], non_blocking=True)
                     kc_done = n_c
-                sl = slice(c * self.chunk, (c + 1) * self.chunk)
+                sl = slice(start, lk)
                 self.q[sl].copy_(q_host[sl], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.s_in)
-                ev_in[c] = ev
+                ev_in[start] = ev
         keep = []
-        for c in order:
-            ch = Chunk(c, c * self.chunk, (c + 1) * self.chunk)
-            main.wait_event(ev_in[c])
+        for start, end in pieces:
+            ch = Chunk(start // self.chunk, start, end)
+            main.wait_event(ev_in[start])
             out, _ = prefill_chunk(self.q[ch.start:ch.end], self.kc, self.k, self.v, ch, topk,
                                    init_blocks, local_blocks, ops)
             ev = torch.cuda.Event()
